@@ -1,0 +1,6 @@
+"""B200-native (sm_100a) Forgetting Attention: a drop-in for
+``forgetting_transformer.forgetting_attention`` and the FoX-Pro fused
+RMSNorm + output gate, backed by hand-written CUDA kernels behind a C ABI."""
+from .ops import ForgettingAttention, forgetting_attention  # noqa: F401
+
+__all__ = ["forgetting_attention", "ForgettingAttention"]

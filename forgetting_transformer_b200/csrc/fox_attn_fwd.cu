@@ -1,0 +1,403 @@
+// Forgetting Attention forward for sm_100a: TMA-staged Q/K/V tiles, tcgen05 MMAs
+// with TMEM accumulators, decay bias from the log-gate prefix, causal /
+// seq_start / tail masking, online softmax with lazy rescaling, block pruning.
+//
+// Stands in for upstream's Triton `_fwd_kernel`
+// (src/forgetting_transformer/ops/forgetting_attention.py:505-693).
+//
+// One CTA = one (batch, head, 128-row query tile); two CTAs share an SM so that
+// one CTA's softmax overlaps the other's matrix products.
+//   warps 0-3 : softmax / correction / epilogue, thread t owns query row t and
+//               TMEM lane t (no cross-thread reductions)
+//   warp 4    : TMA producer (one elected lane)
+//   warp 5    : tcgen05.mma issuer (one elected lane)
+// TMEM (256 columns): S = Q K^T fp32 in columns [0,128); the probabilities are
+// written back over S as packed 16-bit pairs (columns [0,64)) and consumed as the
+// TMEM A operand of P V; O accumulates in columns [128, 128+D).
+//
+// KV tiles are visited from the diagonal leftwards: with forget gates the
+// largest logits sit next to the diagonal, so the running row maximum is found
+// on the first tile and the O accumulator hardly ever needs rescaling.
+#include "fox_common.cuh"
+#include "fox_host.h"
+
+namespace fox {
+
+constexpr int kFwdBM = FOX_FWD_BLOCK_M;
+constexpr int kFwdBN = FOX_FWD_BLOCK_N;
+constexpr int kFwdThreads = 192;
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+// the reference maximum is only moved when it is off by more than 2^kLazyShift
+constexpr float kLazyShift = 8.0f;
+
+struct FwdParams {
+  const float* lam;            // (B,H,N) inclusive prefix of the log gates
+  const int64_t* seq_start;    // (B,) or nullptr
+  const int64_t* start_index;  // (B,H,ceil(M/128)) or nullptr
+  void* o;
+  int64_t o_sb, o_sh, o_st;
+  float* L;                    // (B,H,M)
+  int* status;
+  int H, M, N;
+  float qk_scale;              // sm_scale * log2(e)
+};
+
+enum FwdWaitSite {
+  kSiteQFull = 11, kSiteKFull = 12, kSiteVFull = 13, kSiteKEmpty = 14, kSiteVEmpty = 15,
+  kSiteSFull = 16, kSitePFull = 17, kSiteODone = 18, kSiteDrain = 19, kSiteNegB = 20
+};
+
+template <int D, bool kBf16, int STAGES>
+__global__ void __launch_bounds__(kFwdThreads, 2)
+fox_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                    const __grid_constant__ CUtensorMap tmV, const FwdParams p) {
+  constexpr int kTileBytes = 128 * D * 2;  // one [128][D] 16-bit tile (D/64 swizzled sub-tiles)
+  constexpr int kSub = D / 64;
+  constexpr uint32_t kFmt = kBf16 ? 1u : 0u;
+  constexpr uint32_t kTmemCols = 256;
+  constexpr uint32_t kColO = 128;
+
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ uint64_t bar_q_full, bar_s_full, bar_p_full, bar_o_done;
+  __shared__ uint64_t bar_k_full[STAGES], bar_k_empty[STAGES], bar_v_full[STAGES], bar_v_empty[STAGES];
+  __shared__ uint64_t bar_negb[2];
+  __shared__ float s_negb[2][kFwdBN];
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag;
+
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sK = sQ + kTileBytes;
+  uint8_t* sV = sK + STAGES * kTileBytes;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int mb = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);  // heavy tiles first
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int M = p.M, N = p.N, P = N - M;
+
+  // ---- KV range of this query tile (upstream lines 591-613) ----
+  const int hi = min(N, P + (mb + 1) * kFwdBM);
+  const int seq0 = p.seq_start ? static_cast<int>(p.seq_start[b]) : 0;
+  int lo = min(seq0, hi);
+  if (p.start_index) {
+    const int64_t si = p.start_index[(static_cast<int64_t>(b) * p.H + h) * gridDim.x + mb];
+    lo = max(lo, static_cast<int>(si < static_cast<int64_t>(hi) ? si : static_cast<int64_t>(hi)));
+  }
+  lo = (lo / kFwdBN) * kFwdBN;
+  const int nb_lo = lo / kFwdBN;
+  const int nb_hi = (hi + kFwdBN - 1) / kFwdBN;  // exclusive
+  const int n_tiles = max(nb_hi - nb_lo, 0);
+
+  if (tid == 0) {
+    abort_flag = 0;
+    mbar_init(&bar_q_full, 1);
+    mbar_init(&bar_s_full, 1);
+    mbar_init(&bar_p_full, 128);
+    mbar_init(&bar_o_done, 1);
+    mbar_init(&bar_negb[0], 128);
+    mbar_init(&bar_negb[1], 128);
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&bar_k_full[s], 1);
+      mbar_init(&bar_k_empty[s], 1);
+      mbar_init(&bar_v_full[s], 1);
+      mbar_init(&bar_v_empty[s], 1);
+    }
+    mbar_fence_init();
+  }
+  if (warp == 4) {
+    tmem_alloc(&tmem_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tbase = tmem_slot;
+  volatile int* abortp = &abort_flag;
+
+  if (warp == 4) {
+    // ===================== TMA producer =====================
+    if (lane == 0 && n_tiles > 0) {
+      tma_prefetch_desc(&tmQ);
+      tma_prefetch_desc(&tmK);
+      tma_prefetch_desc(&tmV);
+      mbar_expect_tx(&bar_q_full, kTileBytes);
+#pragma unroll
+      for (int s = 0; s < kSub; ++s) tma_load_4d(sQ + s * 16384, &tmQ, &bar_q_full, s * 64, mb * kFwdBM, h, b);
+      bool ok = true;
+      int issued = 0;
+      for (int it = 0; it < n_tiles && ok; ++it) {
+        const int nb = nb_hi - 1 - it;
+        const int st = it % STAGES;
+        const uint32_t ph = (it / STAGES) & 1;
+        ok = mbar_wait(&bar_k_empty[st], ph ^ 1, abortp, p.status, kSiteKEmpty, it);
+        if (!ok) break;
+        mbar_expect_tx(&bar_k_full[st], kTileBytes);
+#pragma unroll
+        for (int s = 0; s < kSub; ++s)
+          tma_load_4d(sK + st * kTileBytes + s * 16384, &tmK, &bar_k_full[st], s * 64, nb * kFwdBN, h, b);
+        ok = mbar_wait(&bar_v_empty[st], ph ^ 1, abortp, p.status, kSiteVEmpty, it);
+        if (!ok) { issued = it * 2 + 1; break; }
+        mbar_expect_tx(&bar_v_full[st], kTileBytes);
+#pragma unroll
+        for (int s = 0; s < kSub; ++s)
+          tma_load_4d(sV + st * kTileBytes + s * 16384, &tmV, &bar_v_full[st], s * 64, nb * kFwdBN, h, b);
+        issued = it * 2 + 2;
+      }
+      if (*abortp) {
+        // error path only: let the copies already in flight land before the CTA retires
+        mbar_wait(&bar_q_full, 0, abortp, p.status, kSiteDrain);
+        const long long t0 = clock64();
+        for (int c = max(issued - 2 * STAGES, 0); c < issued; ++c) {
+          const int it = c >> 1, st = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          uint64_t* bar = (c & 1) ? &bar_v_full[st] : &bar_k_full[st];
+          while (!mbar_try_wait(bar, ph) && clock64() - t0 < 200000000LL) {
+          }
+        }
+      }
+    }
+  } else if (warp == 5) {
+    // ===================== MMA issuer =====================
+    if (lane == 0 && n_tiles > 0) {
+      constexpr uint32_t idQK = umma_idesc(kFmt, 128, 128, 0, 0);
+      constexpr uint32_t idPV = umma_idesc(kFmt, 128, D, 0, 1);
+      const uint32_t q0 = smem_u32(sQ);
+      bool ok = mbar_wait(&bar_q_full, 0, abortp, p.status, kSiteQFull);
+      for (int it = 0; it < n_tiles && ok; ++it) {
+        const int st = it % STAGES;
+        const uint32_t ph = (it / STAGES) & 1;
+        ok = mbar_wait(&bar_k_full[st], ph, abortp, p.status, kSiteKFull, it);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t k0 = smem_u32(sK + st * kTileBytes);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
+          mma_ss(tbase, umma_desc_kmajor(q0 + off), umma_desc_kmajor(k0 + off), idQK, kk > 0);
+        }
+        tc_commit(&bar_s_full);
+        tc_commit(&bar_k_empty[st]);
+        ok = mbar_wait(&bar_p_full, it & 1, abortp, p.status, kSitePFull, it);
+        if (!ok) break;
+        ok = mbar_wait(&bar_v_full[st], ph, abortp, p.status, kSiteVFull, it);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t v0 = smem_u32(sV + st * kTileBytes);
+#pragma unroll
+        for (int kk = 0; kk < kFwdBN / 16; ++kk)
+          mma_ts(tbase + kColO, tbase + kk * 8, umma_desc_mnmajor(v0 + kk * 2048, 16384), idPV,
+                 (it > 0 || kk > 0) ? 1u : 0u);
+        tc_commit(&bar_v_empty[st]);
+      }
+      if (ok) tc_commit(&bar_o_done);
+    }
+  } else {
+    // ===================== softmax / correction / epilogue =====================
+    const int row = mb * kFwdBM + tid;  // query row inside (b,h)
+    const bool row_ok = row < M;
+    const int64_t bh = static_cast<int64_t>(b) * p.H + h;
+    const float* lam = p.lam + bh * N;
+    const float a_i = row_ok ? lam[P + row] * kLog2e : 0.f;
+    const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+    const uint32_t tS = tbase + lane_base;
+    const uint32_t tO = tbase + lane_base + kColO;
+
+    float m_ref = -INFINITY, l_sum = 0.f;
+    bool ok = true;
+    float negb_next = 0.f;
+    if (n_tiles > 0) {
+      const int col = (nb_hi - 1) * kFwdBN + tid;
+      negb_next = col < N ? -lam[col] * kLog2e : 0.f;
+    }
+    for (int it = 0; it < n_tiles; ++it) {
+      const int nb = nb_hi - 1 - it;
+      const int col0 = nb * kFwdBN;
+      s_negb[it & 1][tid] = negb_next;
+      mbar_arrive(&bar_negb[it & 1]);
+      ok = mbar_wait(&bar_negb[it & 1], (it >> 1) & 1, abortp, p.status, kSiteNegB, it);
+      ok = mbar_wait(&bar_s_full, it & 1, abortp, p.status, kSiteSFull, it) && ok;
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      uint32_t sreg[128];
+      tmem_ld32(tS, sreg);
+      tmem_ld32(tS + 32, sreg + 32);
+      tmem_ld32(tS + 64, sreg + 64);
+      tmem_ld32(tS + 96, sreg + 96);
+      tmem_ld_wait();
+      if (it + 1 < n_tiles) {
+        const int col = (nb - 1) * kFwdBN + tid;
+        negb_next = -lam[col] * kLog2e;  // nb-1 >= nb_lo >= 0 and this tile lies left of the tail
+      }
+      // ---- pass 1: u = s*scale - b_j, row maximum ----
+      const float4* nb4 = reinterpret_cast<const float4*>(s_negb[it & 1]);
+      const bool need_mask = (col0 + kFwdBN - 1 > P + mb * kFwdBM) || (col0 < seq0) || (col0 + kFwdBN > N);
+      float umax = -INFINITY;
+      if (!need_mask) {
+#pragma unroll
+        for (int c4 = 0; c4 < 32; ++c4) {
+          const float4 nbv = nb4[c4];
+          float u0 = fmaf(__uint_as_float(sreg[4 * c4 + 0]), p.qk_scale, nbv.x);
+          float u1 = fmaf(__uint_as_float(sreg[4 * c4 + 1]), p.qk_scale, nbv.y);
+          float u2 = fmaf(__uint_as_float(sreg[4 * c4 + 2]), p.qk_scale, nbv.z);
+          float u3 = fmaf(__uint_as_float(sreg[4 * c4 + 3]), p.qk_scale, nbv.w);
+          sreg[4 * c4 + 0] = __float_as_uint(u0);
+          sreg[4 * c4 + 1] = __float_as_uint(u1);
+          sreg[4 * c4 + 2] = __float_as_uint(u2);
+          sreg[4 * c4 + 3] = __float_as_uint(u3);
+          umax = fmaxf(umax, fmaxf(fmaxf(u0, u1), fmaxf(u2, u3)));
+        }
+      } else {
+        // valid columns of this row inside the tile: [c_lo, c_hi]
+        const int c_lo = max(seq0 - col0, 0);
+        const int c_hi = row_ok ? min(min(P + row, N - 1) - col0, kFwdBN - 1) : -1;
+#pragma unroll
+        for (int c4 = 0; c4 < 32; ++c4) {
+          const float4 nbv = nb4[c4];
+          const float nbs[4] = {nbv.x, nbv.y, nbv.z, nbv.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int c = 4 * c4 + e;
+            float u = fmaf(__uint_as_float(sreg[c]), p.qk_scale, nbs[e]);
+            u = (c >= c_lo && c <= c_hi) ? u : -INFINITY;
+            sreg[c] = __float_as_uint(u);
+            umax = fmaxf(umax, u);
+          }
+        }
+      }
+      // ---- running maximum with lazy rescaling ----
+      const float m_new = fmaxf(m_ref, a_i + umax);
+      const bool need = (m_new - m_ref) > kLazyShift;  // false when both are -inf (NaN compare)
+      if (__any_sync(0xffffffffu, need)) {
+        const float alpha = (m_new == -INFINITY) ? 1.f : fast_exp2(m_ref - m_new);
+        l_sum *= alpha;
+        if (it > 0) {
+#pragma unroll
+          for (int c = 0; c < D; c += 32) {
+            uint32_t o[32];
+            tmem_ld32(tO + c, o);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * alpha);
+            tmem_st32(tO + c, o);
+          }
+        }
+        m_ref = m_new;
+      }
+      const float off = a_i - ((m_ref == -INFINITY) ? 0.f : m_ref);
+      // ---- pass 2: p = 2^(u + off), row sum, pack, write back over S ----
+      float psum = 0.f;
+#pragma unroll
+      for (int ch = 0; ch < 4; ++ch) {
+        uint32_t pk[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const float p0 = fast_exp2(__uint_as_float(sreg[32 * ch + 2 * j]) + off);
+          const float p1 = fast_exp2(__uint_as_float(sreg[32 * ch + 2 * j + 1]) + off);
+          psum += p0 + p1;
+          pk[j] = pack2<kBf16>(p0, p1);
+        }
+        tmem_st16(tS + ch * 16, pk);
+      }
+      l_sum += psum;
+      tmem_st_wait();
+      tc_fence_before();
+      mbar_arrive(&bar_p_full);
+    }
+
+    // ---- epilogue: O / l -> 16-bit -> global, L = m ln2 + ln l ----
+    if (n_tiles > 0 && ok) {
+      ok = mbar_wait(&bar_o_done, 0, abortp, p.status, kSiteODone);
+      ok = __all_sync(0xffffffffu, ok);
+    }
+    if (ok) {
+      tc_fence_after();
+      const bool empty = (n_tiles == 0) || (P + row < seq0) || !(l_sum > 0.f);
+      const float inv_l = empty ? 0.f : 1.f / l_sum;
+      uint16_t* orow = reinterpret_cast<uint16_t*>(p.o) + b * p.o_sb + h * p.o_sh + static_cast<int64_t>(row) * p.o_st;
+#pragma unroll
+      for (int c = 0; c < D; c += 32) {
+        uint32_t o[32];
+        if (n_tiles > 0) {
+          tmem_ld32(tO + c, o);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) o[j] = 0u;
+        }
+        if (row_ok) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 8) {
+            uint4 w;
+            w.x = pack2<kBf16>(empty ? 0.f : __uint_as_float(o[j + 0]) * inv_l, empty ? 0.f : __uint_as_float(o[j + 1]) * inv_l);
+            w.y = pack2<kBf16>(empty ? 0.f : __uint_as_float(o[j + 2]) * inv_l, empty ? 0.f : __uint_as_float(o[j + 3]) * inv_l);
+            w.z = pack2<kBf16>(empty ? 0.f : __uint_as_float(o[j + 4]) * inv_l, empty ? 0.f : __uint_as_float(o[j + 5]) * inv_l);
+            w.w = pack2<kBf16>(empty ? 0.f : __uint_as_float(o[j + 6]) * inv_l, empty ? 0.f : __uint_as_float(o[j + 7]) * inv_l);
+            *reinterpret_cast<uint4*>(orow + c + j) = w;
+          }
+        }
+      }
+      if (row_ok) p.L[bh * M + row] = empty ? -INFINITY : m_ref * kLn2 + __logf(l_sum);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 4) tmem_dealloc(tbase, kTmemCols);
+}
+
+template <int D, bool kBf16, int STAGES>
+static int launch_fwd(int device, cudaStream_t stream, int64_t B, int64_t H, int64_t M, int64_t N, const fox_tensor4* q,
+                      const fox_tensor4* k, const fox_tensor4* v, const FwdParams& prm) {
+  CUtensorMap tmQ, tmK, tmV;
+  Tensor4 tq{q->ptr, B, H, M, D, q->sb, q->sh, q->st};
+  Tensor4 tk{k->ptr, B, H, N, D, k->sb, k->sh, k->st};
+  Tensor4 tv{v->ptr, B, H, N, D, v->sb, v->sh, v->st};
+  if (!tma_compatible(tq, 2) || !tma_compatible(tk, 2) || !tma_compatible(tv, 2)) return FOX_ERR_ALIGNMENT;
+  int rc;
+  if ((rc = cached_tmap_4d(&tmQ, tq, 2, false, kBf16, 64, 128, true))) return rc;
+  if ((rc = cached_tmap_4d(&tmK, tk, 2, false, kBf16, 64, 128, true))) return rc;
+  if ((rc = cached_tmap_4d(&tmV, tv, 2, false, kBf16, 64, 128, true))) return rc;
+  constexpr int smem = (1 + 2 * STAGES) * 128 * D * 2 + 1024;
+  auto kern = fox_attn_fwd_kernel<D, kBf16, STAGES>;
+  static bool configured[64] = {};  // per template instance and device
+  if (device < 0 || device >= 64) return FOX_ERR_DEVICE;
+  if (!configured[device]) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return FOX_ERR_LAUNCH;
+    configured[device] = true;
+  }
+  dim3 grid((unsigned)((M + kFwdBM - 1) / kFwdBM), (unsigned)H, (unsigned)B);
+  kern<<<grid, kFwdThreads, smem, stream>>>(tmQ, tmK, tmV, prm);
+  return cudaGetLastError() == cudaSuccess ? FOX_OK : FOX_ERR_LAUNCH;
+}
+
+}  // namespace fox
+
+extern "C" int fox_attn_fwd(int device, void* stream, int dtype, int64_t B, int64_t H, int64_t M, int64_t N,
+                            int64_t D, const fox_tensor4* q, const fox_tensor4* k, const fox_tensor4* v,
+                            const float* log_lambda, const int64_t* seq_start, const int64_t* start_index,
+                            float sm_scale, const fox_tensor4* o, float* L, int32_t* status) {
+  using namespace fox;
+  if (!q || !k || !v || !o || !q->ptr || !k->ptr || !v->ptr || !o->ptr || !log_lambda || !L || !status)
+    return FOX_ERR_BAD_ARG;
+  if (B <= 0 || H <= 0 || M <= 0 || N <= 0 || M > N || H > 65535 || B > 65535) return FOX_ERR_BAD_ARG;
+  if (D != 64 && D != 128) return FOX_ERR_HEAD_DIM;
+  if (dtype != FOX_DTYPE_BF16 && dtype != FOX_DTYPE_FP16) return FOX_ERR_BAD_ARG;
+  if (reinterpret_cast<uintptr_t>(o->ptr) % 16 || (o->sb * 2) % 16 || (o->sh * 2) % 16 || (o->st * 2) % 16)
+    return FOX_ERR_ALIGNMENT;
+  if (cudaSetDevice(device) != cudaSuccess) return FOX_ERR_DEVICE;
+  FwdParams prm;
+  prm.lam = log_lambda;
+  prm.seq_start = seq_start;
+  prm.start_index = start_index;
+  prm.o = o->ptr; prm.o_sb = o->sb; prm.o_sh = o->sh; prm.o_st = o->st;
+  prm.L = L;
+  prm.status = status;
+  prm.H = (int)H; prm.M = (int)M; prm.N = (int)N;
+  prm.qk_scale = sm_scale * 1.4426950408889634f;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const bool bf = dtype == FOX_DTYPE_BF16;
+  if (D == 64) return bf ? launch_fwd<64, true, 2>(device, st, B, H, M, N, q, k, v, prm) : launch_fwd<64, false, 2>(device, st, B, H, M, N, q, k, v, prm);
+  return bf ? launch_fwd<128, true, 1>(device, st, B, H, M, N, q, k, v, prm) : launch_fwd<128, false, 1>(device, st, B, H, M, N, q, k, v, prm);
+}

@@ -1,0 +1,249 @@
+"""Forgetting Attention operator backed by the sm_100a kernels.
+
+Host-side mirror of upstream's ``ForgettingAttention`` autograd function and
+``forgetting_attention`` wrapper
+(src/forgetting_transformer/ops/forgetting_attention.py:44-455): same argument
+order, defaults, assertions and returned gradients, so it can be dropped in for
+the Triton operator.  All device work goes through the C ABI of
+``libfox_b200.so``; there is no Triton, no eager fallback and no CPU path.
+"""
+from __future__ import annotations
+
+import math
+import os
+from typing import Literal, Optional, Union
+
+import torch
+
+from . import _lib
+
+__all__ = ["forgetting_attention", "ForgettingAttention", "FWD_BLOCK", "BWD_BLOCK"]
+
+# (BLOCK_M, BLOCK_N) of the kernels; pruning indices are defined on this grid.
+FWD_BLOCK = (128, 128)
+BWD_BLOCK = (128, 128)
+
+_DEBUG_SYNC = os.environ.get("FOX_B200_DEBUG_SYNC", "0") == "1"
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _tma_view(x: torch.Tensor) -> torch.Tensor:
+    """Return ``x`` when TMA can address it, else a contiguous copy (upstream only
+    insists on a unit inner stride, lines 35-38)."""
+    return x if _lib.tma_ready(x) else x.contiguous()
+
+
+def max_row_norm(x: torch.Tensor) -> torch.Tensor:
+    """max_t ||x[b,h,t,:]||_2 in x's dtype, i.e.
+    ``torch.linalg.vector_norm(x, dim=-1).max(dim=-1).values`` (upstream lines 95-96)."""
+    lib = _lib.load()
+    B, H, T, D = x.shape
+    x = _tma_view(x)
+    out = torch.zeros((B, H), dtype=torch.float32, device=x.device)
+    _lib.check(lib.fox_max_row_norm(x.device.index, _stream(), _lib.dtype_code(x.dtype), B, H, T, D,
+                                    _lib.t4(x), out.data_ptr()), "fox_max_row_norm")
+    return out.to(x.dtype)
+
+
+def log_lambda_cumsum(log_fgate: torch.Tensor, seq_start: Optional[torch.Tensor],
+                      carry_in: Optional[torch.Tensor] = None, return_total: bool = False):
+    """fp32 inclusive prefix sum over the last axis of a (B,H,N) tensor of any
+    strides with the gates left of ``seq_start`` treated as zero (upstream lines
+    117-127).  ``carry_in`` (B,H) is added to every prefix (context-parallel
+    chunks); ``return_total`` also returns the last prefix per (b,h)."""
+    lib = _lib.load()
+    B, H, N = log_fgate.shape
+    out = torch.empty((B, H, N), dtype=torch.float32, device=log_fgate.device)
+    total = torch.empty((B, H), dtype=torch.float32, device=log_fgate.device) if return_total else None
+    _lib.check(lib.fox_cumsum_fwd(log_fgate.device.index, _stream(), B, H, N, log_fgate.data_ptr(),
+                                  log_fgate.stride(0), log_fgate.stride(1), log_fgate.stride(2),
+                                  _lib.ptr(seq_start), _lib.ptr(carry_in), out.data_ptr(), _lib.ptr(total)),
+               "fox_cumsum_fwd")
+    return (out, total) if return_total else out
+
+
+def find_index(log_lambda: torch.Tensor, threshold: torch.Tensor, M: int, block_m: int, block_n: int,
+               want_start: bool = True, want_end: bool = False):
+    """Block-pruning index arrays (upstream lines 695-795) on a (block_m, block_n) grid."""
+    lib = _lib.load()
+    B, H, N = log_lambda.shape
+    dev = log_lambda.device
+    start = torch.empty((B, H, -(-M // block_m)), dtype=torch.long, device=dev) if want_start else None
+    end = torch.empty((B, H, -(-N // block_n)), dtype=torch.long, device=dev) if want_end else None
+    _lib.check(lib.fox_find_index(dev.index, _stream(), B, H, M, N, block_m, block_n, log_lambda.data_ptr(),
+                                  threshold.data_ptr(), threshold.stride(0), threshold.stride(1),
+                                  _lib.ptr(start), _lib.ptr(end)), "fox_find_index")
+    return start, end
+
+
+class ForgettingAttention(torch.autograd.Function):
+    """Same positional signature as upstream's autograd function (line 73); the three
+    trailing timing arguments are accepted and ignored."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, log_fgate, seq_start, causal, sm_scale, adaptive_threshold,
+                return_log_normalizer=False, return_start_index=False, record_time_key=None,
+                record_attention_time=False, record_find_index_time=False):
+        assert causal, "Only causal attention is supported"
+        Dq, Dk, Dv = q.shape[-1], k.shape[-1], v.shape[-1]
+        assert Dq == Dk == Dv, "feature size of q, k, v should be equal"
+        assert Dk in {16, 32, 64, 128}, "We only support head dims in {16, 32, 64, 128}"
+
+        B, H, M, D = q.shape
+        N = k.shape[2]
+        assert log_fgate.shape == (B, H, N)
+        assert log_fgate.dtype == torch.float32, "log_fgate must be in torch.float32. It is best to do this cast before logsigmoid, e.g., torch.nn.functional.logsigmoid(fgate_logit.float())."
+        if sm_scale is None:
+            sm_scale = 1. / math.sqrt(D)
+        if not q.is_cuda:
+            raise _lib.FoxError("forgetting_attention needs CUDA tensors on an sm_100 device; there is no CPU path")
+        if D not in (64, 128):
+            raise _lib.FoxError(f"head dim {D} has no sm_100a kernel yet (64 and 128 are built)")
+
+        Hk, Hv = k.shape[1], v.shape[1]
+        assert Hk == Hv, "num of heads in k and v should be equal"
+        assert H == Hk, "groupped query attention has not been tested. You can uncomment this if you know what you are doing."
+        assert not (M > N), "The key/value tensors must be longer than the query tensor"
+
+        lib = _lib.load()
+        with torch.cuda.device(q.device):
+            dev = q.device
+            q, k, v = _tma_view(q), _tma_view(k), _tma_view(v)
+
+            if adaptive_threshold is not None:
+                if isinstance(adaptive_threshold, str):
+                    assert adaptive_threshold == "auto", f'adaptive_threshold must be either the string "auto", a float, or a Tensor, but got {adaptive_threshold}.'
+                    max_q_norm = max_row_norm(q)
+                    max_k_norm = max_row_norm(k)
+                    logit_upper_bound = max_q_norm * max_k_norm * sm_scale
+                    tolerance = -10
+                    adaptive_threshold = -(2 * logit_upper_bound + math.log(N)) + tolerance
+                adaptive_threshold = torch.as_tensor(adaptive_threshold, dtype=torch.float, device=dev)
+                try:
+                    adaptive_threshold = torch.broadcast_to(adaptive_threshold, (B, H))
+                except RuntimeError:
+                    raise RuntimeError(f'adaptive_threshold must be either the string "auto" or broadcastable to (batch_size, num_heads) = ({B}, {H}), but got {adaptive_threshold.size()}.')
+                assert adaptive_threshold.size() == (B, H)
+
+            if seq_start is not None:
+                has_seq_start = True
+                assert seq_start.shape == (B,)
+                seq_start = seq_start.to(device=dev, dtype=torch.long).contiguous()
+            else:
+                has_seq_start = False
+
+            log_lambda = log_lambda_cumsum(log_fgate, seq_start)
+
+            start_index = None
+            if adaptive_threshold is not None:
+                start_index, _ = find_index(log_lambda, adaptive_threshold, M, *FWD_BLOCK)
+
+            o = torch.empty_like(q)
+            if not _lib.tma_ready(o):
+                o = torch.empty(q.shape, dtype=q.dtype, device=dev)
+            L = torch.empty((B, H, M), device=dev, dtype=torch.float32)
+            status = _lib.status_buffer(dev)
+            _lib.check(lib.fox_attn_fwd(dev.index, _stream(), _lib.dtype_code(q.dtype), B, H, M, N, D,
+                                        _lib.t4(q), _lib.t4(k), _lib.t4(v), log_lambda.data_ptr(),
+                                        _lib.ptr(seq_start), _lib.ptr(start_index), float(sm_scale),
+                                        _lib.t4(o), L.data_ptr(), status.data_ptr()), "fox_attn_fwd")
+            if _DEBUG_SYNC:
+                _lib.check_status(dev)
+
+        ctx.save_for_backward(q, k, v, o, L, log_lambda, seq_start, adaptive_threshold)
+        ctx.sm_scale = sm_scale
+        ctx.has_seq_start = has_seq_start
+        if return_log_normalizer or return_start_index:
+            ctx.mark_non_differentiable(*[t for t in (L, start_index) if t is not None])
+            return (o, L if return_log_normalizer else None, start_index if return_start_index else None)
+        return o
+
+    @staticmethod
+    def backward(ctx, do, *ignored):
+        q, k, v, o, L, log_lambda, seq_start, adaptive_threshold = ctx.saved_tensors
+        sm_scale = ctx.sm_scale
+        B, H, M, D = q.shape
+        N = k.shape[2]
+        lib = _lib.load()
+        # the autograd engine runs this on its own thread: select the device explicitly
+        with torch.cuda.device(q.device):
+            dev = q.device
+            do = _tma_view(do)
+            code = _lib.dtype_code(q.dtype)
+            delta = torch.empty_like(L)
+            _lib.check(lib.fox_bwd_delta(dev.index, _stream(), code, B, H, M, D, _lib.t4(o), _lib.t4(do),
+                                         delta.data_ptr()), "fox_bwd_delta")
+            end_index = None
+            if adaptive_threshold is not None:
+                _, end_index = find_index(log_lambda, adaptive_threshold, M, *BWD_BLOCK, want_start=False,
+                                          want_end=True)
+            dk = torch.empty_like(k)
+            dv = torch.empty_like(v)
+            dq = torch.empty_like(q)
+            if not _lib.tma_ready(dk):
+                dk = torch.empty(k.shape, dtype=k.dtype, device=dev)
+            if not _lib.tma_ready(dv):
+                dv = torch.empty(v.shape, dtype=v.dtype, device=dev)
+            if not _lib.tma_ready(dq):
+                dq = torch.empty(q.shape, dtype=q.dtype, device=dev)
+            # scratch: fp32 dQ accumulator and the query-side log-gate gradient (both reduced into)
+            scratch = torch.zeros(B * H * M * (D + 1), dtype=torch.float32, device=dev)
+            dq_accum = scratch[: B * H * M * D]
+            dlam_row = scratch[B * H * M * D:]
+            dlam_col = torch.empty((B, H, N), dtype=torch.float32, device=dev)
+            status = _lib.status_buffer(dev)
+            _lib.check(lib.fox_attn_bwd(dev.index, _stream(), code, B, H, M, N, D, _lib.t4(q), _lib.t4(k),
+                                        _lib.t4(v), _lib.t4(do), log_lambda.data_ptr(), L.data_ptr(),
+                                        delta.data_ptr(), _lib.ptr(seq_start), _lib.ptr(end_index),
+                                        float(sm_scale), dq_accum.data_ptr(), dlam_row.data_ptr(),
+                                        dlam_col.data_ptr(), _lib.t4(dk), _lib.t4(dv), status.data_ptr()),
+                       "fox_attn_bwd")
+            _lib.check(lib.fox_dq_convert(dev.index, _stream(), code, B, H, M, D, dq_accum.data_ptr(),
+                                          float(sm_scale), _lib.t4(dq)), "fox_dq_convert")
+            dlog_fgate = torch.empty((B, H, N), dtype=torch.float32, device=dev)
+            _lib.check(lib.fox_revcumsum(dev.index, _stream(), B, H, M, N, dlam_col.data_ptr(),
+                                         dlam_row.data_ptr(), None, dlog_fgate.data_ptr(), None),
+                       "fox_revcumsum")
+            if _DEBUG_SYNC:
+                _lib.check_status(dev)
+        return dq, dk, dv, dlog_fgate, None, None, None, None, None, None, None, None, None
+
+
+def forgetting_attention(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    log_fgate: torch.Tensor,
+    *,
+    head_first: bool = False,
+    seq_start: Optional[torch.Tensor] = None,
+    sm_scale: Optional[float] = None,
+    adaptive_threshold: Optional[Union[Literal["auto"], float, torch.Tensor]] = None,
+):
+    """Forgetting Attention (causal softmax attention with the decay bias
+    ``cumsum(log_fgate)_i - cumsum(log_fgate)_j``), same contract as upstream's
+    ``forgetting_transformer.forgetting_attention`` (lines 403-455):
+
+    - q (B, Tq, H, D), k/v (B, Tk, H, D) in fp16/bf16 and log_fgate (B, Tk, H) in
+      fp32, or with the H and T axes swapped when ``head_first=True``;
+    - Tq <= Tk, causal, D in {16, 32, 64, 128} (sm_100a kernels exist for 64, 128);
+    - ``seq_start`` (B,) long: no attention to positions left of it (left padding);
+    - ``sm_scale`` defaults to 1/sqrt(D);
+    - ``adaptive_threshold``: "auto", a float or a tensor broadcastable to (B, H);
+      whole KV blocks whose decay-bounded logits fall below it are skipped.
+
+    Returns the output in q's layout; differentiable w.r.t. q, k, v and log_fgate.
+    """
+    for name, entry in dict(q=q, k=k, v=v).items():
+        assert entry.dtype in [torch.float16, torch.bfloat16], f"Only torch.float16 or torch.bfloat16 are supported for q/k/v, but got {entry.dtype} for {name}."
+    if not head_first:
+        q, k, v = [item.permute(0, 2, 1, 3) for item in (q, k, v)]
+        log_fgate = log_fgate.permute(0, 2, 1)
+    out = ForgettingAttention.apply(q, k, v, log_fgate, seq_start, True, sm_scale, adaptive_threshold,
+                                    False, False, None, False, False)
+    if not head_first:
+        out = out.permute(0, 2, 1, 3)
+    return out

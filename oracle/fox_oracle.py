@@ -1,0 +1,312 @@
+"""CPU oracle for the Forgetting Attention hot path.  TEST INFRASTRUCTURE ONLY.
+
+This module restates, in plain PyTorch/NumPy on the CPU, the arithmetic of the
+upstream project's operator so that the CUDA kernels can be checked against it.
+Nothing in the shipped package imports it: only the test-suite, the smoke entry
+point and the benchmark's CPU-baseline leg do.
+
+Parity pinning: the functions below are checked (tests/test_oracle.py) against
+fixtures under tests/golden/ that were produced by importing the upstream
+package itself and running its Triton kernels in Triton's CPU interpreter and
+its in-file dense PyTorch formulation (tests/golden/make_golden.py).
+
+Upstream citations use paths inside the upstream repository:
+  OPS = src/forgetting_transformer/ops/forgetting_attention.py
+  FNG = src/forgetting_transformer/model/forgetting_transformer/fuse_norm_gate.py
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional, Tuple
+
+import numpy as np
+import torch
+
+LOG2E = 1.4426950408889634
+
+
+# --------------------------------------------------------------------------
+# log-gate prefix (OPS:111-127)
+# --------------------------------------------------------------------------
+def masked_log_fgate(log_fgate: torch.Tensor, seq_start: Optional[torch.Tensor]) -> torch.Tensor:
+    """Zero the log gates left of ``seq_start`` (OPS:117-125).  (B, H, N) fp32."""
+    lf = log_fgate.float()
+    if seq_start is None:
+        return lf
+    N = lf.shape[-1]
+    mask = torch.arange(N, device=lf.device)[None, None, :] < seq_start[:, None, None]
+    return lf.masked_fill(mask, 0.0)
+
+
+def log_lambda(log_fgate: torch.Tensor, seq_start: Optional[torch.Tensor]) -> torch.Tensor:
+    """Inclusive prefix sum of the (masked) log gates, fp32 (OPS:127)."""
+    return torch.cumsum(masked_log_fgate(log_fgate, seq_start), dim=-1, dtype=torch.float32)
+
+
+def reverse_cumsum(dlog_lambda: torch.Tensor) -> torch.Tensor:
+    """dlog_fgate_t = sum_{u >= t} dlog_lambda_u, written as upstream does (OPS:390-392)."""
+    cs = torch.cumsum(dlog_lambda, dim=-1, dtype=dlog_lambda.dtype)
+    return (dlog_lambda + cs[..., -1:] - cs).float()
+
+
+# --------------------------------------------------------------------------
+# dense formulation (upstream's in-file known-answer math, OPS:1380-1404)
+# --------------------------------------------------------------------------
+def dense_forgetting_attention(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    log_fgate: torch.Tensor,
+    seq_start: Optional[torch.Tensor] = None,
+    sm_scale: Optional[float] = None,
+    mask_gates: bool = False,
+) -> torch.Tensor:
+    """Head-first dense forgetting attention, differentiable through autograd.
+
+    q (B,H,M,D); k, v (B,H,N,D); log_fgate (B,H,N) fp32.  Follows OPS:1380-1399
+    line by line: logits in the input dtype, bias and softmax in fp32, the
+    probabilities cast back to the input dtype before ``p @ v``, NaN rows
+    (rows with nothing to attend to) set to zero.
+
+    ``mask_gates=True`` additionally zeroes the gates left of ``seq_start``
+    before the prefix sum, which is what the operator itself does (OPS:117-125);
+    the upstream test leaves them in (the bias is a difference, so the result
+    is the same up to rounding).
+    """
+    B, H, M, D = q.shape
+    N = k.shape[2]
+    if sm_scale is None:
+        sm_scale = 1.0 / math.sqrt(D)
+    P_SEQ = N - M
+    dev = q.device
+    mask = torch.tril(torch.ones((M, N), device=dev), diagonal=P_SEQ)
+    p = torch.matmul(q, k.transpose(2, 3)) * sm_scale
+    p = p.float()
+    lf = masked_log_fgate(log_fgate, seq_start) if mask_gates else log_fgate
+    lam = torch.cumsum(lf, dim=-1)
+    decay_bias = lam[..., -M:, None] - lam[..., None, :]
+    p = p + decay_bias
+    p = p.masked_fill((mask == 0)[None, None], float("-inf"))
+    if seq_start is not None:
+        attention_mask = torch.arange(N, device=dev) < seq_start[:, None, None, None]
+        p = torch.where(attention_mask, float("-inf"), p)
+    p = torch.softmax(p.float(), dim=-1).to(q.dtype)
+    p = torch.nan_to_num(p, nan=0.0) if False else torch.where(torch.isnan(p), torch.zeros_like(p), p)
+    return torch.matmul(p, v)
+
+
+def dense_fwd_bwd(q, k, v, log_fgate, dout, seq_start=None, sm_scale=None, mask_gates=False):
+    """Forward + autograd backward of the dense formulation.  Returns
+    (out, dq, dk, dv, dlog_fgate)."""
+    q, k, v, log_fgate = [t.detach().clone().requires_grad_() for t in (q, k, v, log_fgate)]
+    out = dense_forgetting_attention(q, k, v, log_fgate, seq_start, sm_scale, mask_gates)
+    out.backward(dout)
+    return out.detach(), q.grad, k.grad, v.grad, log_fgate.grad
+
+
+# --------------------------------------------------------------------------
+# Adaptive Computation Pruning: threshold and block index scans
+# --------------------------------------------------------------------------
+def auto_threshold(q: torch.Tensor, k: torch.Tensor, sm_scale: float) -> torch.Tensor:
+    """``adaptive_threshold="auto"`` (OPS:95-104).  The norms are evaluated in the
+    input dtype (torch.linalg.vector_norm of a bf16 tensor returns bf16), then the
+    result is cast to fp32.  q (B,H,M,D), k (B,H,N,D) -> (B,H) fp32."""
+    N = k.shape[2]
+    max_q_norm = torch.linalg.vector_norm(q, dim=-1).max(dim=-1).values
+    max_k_norm = torch.linalg.vector_norm(k, dim=-1).max(dim=-1).values
+    logit_upper_bound = max_q_norm * max_k_norm * sm_scale
+    thr = -(2 * logit_upper_bound + math.log(N)) + (-10)
+    return torch.as_tensor(thr, dtype=torch.float32)
+
+
+def find_start_index(lam: np.ndarray, thr: np.ndarray, M: int, N: int, BM: int, BN: int) -> np.ndarray:
+    """First KV column (a multiple of BN) each query block has to visit (OPS:695-745).
+
+    lam (B,H,N) fp32, thr (B,H) fp32 -> int64 (B,H,ceil(M/BM)).  The scan position
+    is carried from one query block to the next, exactly as upstream does.
+    Thresholds must be <= 0 (otherwise upstream's loop does not terminate)."""
+    lam = np.asarray(lam, dtype=np.float32)
+    thr = np.asarray(thr, dtype=np.float32)
+    B, H, _ = lam.shape
+    P = N - M
+    nmb = -(-M // BM)
+    out = np.zeros((B, H, nmb), dtype=np.int64)
+    for b in range(B):
+        for h in range(H):
+            row = lam[b, h]
+            t = thr[b, h]
+            s = 0
+            for mb in range(nmb):
+                lo = row[P + mb * BM]
+                while np.float32(lo - row[min(N - 1, s + BN - 1)]) < t:
+                    s += BN
+                out[b, h, mb] = s
+    return out
+
+
+def find_end_index(lam: np.ndarray, thr: np.ndarray, M: int, N: int, BM: int, BN: int) -> np.ndarray:
+    """First query row (block aligned, clipped to M) past which a KV block is pruned
+    (OPS:747-795).  Note the row index carries no N-M offset upstream (OPS:783).
+    -> int64 (B,H,ceil(N/BN))."""
+    lam = np.asarray(lam, dtype=np.float32)
+    thr = np.asarray(thr, dtype=np.float32)
+    B, H, _ = lam.shape
+    nnb = -(-N // BN)
+    out = np.zeros((B, H, nnb), dtype=np.int64)
+    for b in range(B):
+        for h in range(H):
+            row = lam[b, h]
+            t = thr[b, h]
+            e = 0
+            for nb in range(nnb):
+                li = row[min(N - 1, nb * BN + BN - 1)]
+                while np.float32(row[min(e, M - 1)] - li) >= t and e < M:
+                    e = min(e + BM, M)
+                out[b, h, nb] = e
+    return out
+
+
+# --------------------------------------------------------------------------
+# block-level restatement of the kernels (used when pruning is on)
+# --------------------------------------------------------------------------
+def _tile_masks(B, H, M, N, BM, BN, seq_start, start_index, end_index, bwd_kv_bm=None, bwd_kv_bn=None):
+    """Element masks (B,H,M,N) of the tiles each kernel visits.
+
+    forward / dQ pass (OPS:591-613, 1239-1261): columns >= floor(max(start_index,
+    min(seq_start, hi))/BN)*BN and < hi.   dK/dV pass (OPS:1003-1049): rows
+    < min(end_index, M), and nothing for KV blocks entirely left of seq_start-1.
+    Causal/seq_start element masks are applied separately."""
+    P = N - M
+    rows = torch.arange(M)
+    cols = torch.arange(N)
+    fwd = torch.ones(B, H, M, N, dtype=torch.bool)
+    if start_index is not None:
+        si = torch.as_tensor(start_index)  # (B,H,nmb)
+        lo = si.clone()
+        if seq_start is not None:
+            hi = torch.minimum(torch.tensor(N), P + (torch.arange(si.shape[-1]) + 1) * BM)
+            lo = torch.maximum(lo, torch.minimum(seq_start[:, None, None], hi[None, None, :]))
+        lo = (lo // BN) * BN
+        lo_rows = lo[..., rows // BM]  # (B,H,M)
+        fwd = cols[None, None, None, :] >= lo_rows[..., None]
+    kv = torch.ones(B, H, M, N, dtype=torch.bool)
+    if end_index is not None:
+        bm = bwd_kv_bm or BM
+        bn = bwd_kv_bn or BN
+        ei = torch.clamp(torch.as_tensor(end_index), max=M)  # (B,H,nnb)
+        hi_cols = ei[..., cols // bn]  # (B,H,N)
+        if seq_start is not None:
+            nb = cols // bn
+            keep = (nb * bn + bn)[None, :] >= (seq_start[:, None] - 1)  # (B,N)
+            hi_cols = torch.where(keep[:, None, :], hi_cols, torch.zeros_like(hi_cols))
+        # rows are visited in blocks of bm starting at the causal lower bound; a row is
+        # visited iff its block start < hi
+        row_block_start = (rows // bm) * bm
+        kv = row_block_start[None, None, :, None] < hi_cols[:, :, None, :]
+    return fwd, kv
+
+
+def blockwise_fwd_bwd(
+    q, k, v, log_fgate, dout, seq_start=None, sm_scale=None,
+    start_index=None, end_index=None, start_index_bwd=None,
+    BM=128, BN=128, bwd_kv_bm=None, bwd_kv_bn=None, bwd_q_bm=None, bwd_q_bn=None,
+    low_precision_matmul=True,
+):
+    """Restatement of the kernels' arithmetic with block pruning (OPS:505-693,
+    956-1344): the same formulas as the dense path, but tiles excluded by the
+    index arrays contribute nothing, exactly as a skipped loop iteration.
+
+    Returns dict(out, L, delta, dq, dk, dv, dlog_lambda, dlog_fgate).  All math in
+    fp32 on the CPU; when ``low_precision_matmul`` the probabilities and dS are
+    rounded to the input dtype before their matmuls as the kernels do
+    (OPS:666, 1101, 1121, 1325)."""
+    B, H, M, D = q.shape
+    N = k.shape[2]
+    P = N - M
+    if sm_scale is None:
+        sm_scale = 1.0 / math.sqrt(D)
+    dt = q.dtype
+    qf, kf, vf, dof = q.float(), k.float(), v.float(), dout.float()
+    lam = log_lambda(log_fgate, seq_start)
+    s = torch.matmul(qf, kf.transpose(2, 3)) * sm_scale + (lam[..., P:, None] - lam[..., None, :])
+    rows = torch.arange(M)
+    cols = torch.arange(N)
+    elem = (P + rows)[:, None] >= cols[None, :]
+    elem = elem[None, None].expand(B, H, M, N)
+    if seq_start is not None:
+        elem = elem & (cols[None, None, None, :] >= seq_start[:, None, None, None])
+    fwd_mask, _ = _tile_masks(B, H, M, N, BM, BN, seq_start, start_index, None)
+    _, kv_mask = _tile_masks(B, H, M, N, bwd_kv_bm or BM, bwd_kv_bn or BN, seq_start, None, end_index,
+                             bwd_kv_bm, bwd_kv_bn)
+    q_mask, _ = _tile_masks(B, H, M, N, bwd_q_bm or BM, bwd_q_bn or BN, seq_start,
+                            start_index_bwd if start_index_bwd is not None else start_index, None)
+    neg = torch.tensor(float("-inf"))
+    s_f = torch.where(elem & fwd_mask, s, neg)
+    L = torch.logsumexp(s_f, dim=-1)  # -inf on empty rows
+    p_f = torch.exp(s_f - torch.where(torch.isinf(L), torch.zeros_like(L), L)[..., None])
+    p_f = torch.where(elem & fwd_mask, p_f, torch.zeros_like(p_f))
+
+    def lp(x):
+        return x.to(dt).float() if low_precision_matmul else x
+
+    out = torch.matmul(lp(p_f), vf)
+    out_lp = out.to(dt)
+    delta = (out_lp.float() * dof).sum(-1)
+    # backward: probabilities recomputed from the saved normaliser, no fwd tile mask
+    Lz = torch.where(torch.isinf(L), torch.zeros_like(L), L)
+    p = torch.exp(s - Lz[..., None])
+    p = torch.where(elem & ~torch.isinf(L)[..., None], p, torch.zeros_like(p))
+    dp = torch.matmul(dof, vf.transpose(2, 3))
+    ds = p * (dp - delta[..., None])
+    p_kv = torch.where(kv_mask, p, torch.zeros_like(p))
+    ds_kv = torch.where(kv_mask, ds, torch.zeros_like(ds))
+    ds_q = torch.where(q_mask, ds, torch.zeros_like(ds))
+    dv = torch.matmul(lp(p_kv).transpose(2, 3), dof)
+    dk = torch.matmul(lp(ds_kv).transpose(2, 3), qf) * sm_scale
+    dq = torch.matmul(lp(ds_q), kf) * sm_scale
+    dlam = -ds_kv.sum(dim=2)
+    dlam[..., P:] += ds_q.sum(dim=3)
+    if seq_start is not None:
+        colmask = cols[None, None, :] >= seq_start[:, None, None]
+        dk = dk * colmask[..., None]
+        dv = dv * colmask[..., None]
+    return dict(out=out_lp, L=L, delta=delta, dq=dq.to(dt), dk=dk.to(dt), dv=dv.to(dt), dlog_lambda=dlam,
+                dlog_fgate=reverse_cumsum(dlam), log_lambda=lam)
+
+
+def pruned_tile_fraction(start_index: np.ndarray, M: int, N: int, BM: int, BN: int,
+                         seq_start: Optional[np.ndarray] = None) -> float:
+    """Fraction of causal (q-block, kv-block) tiles the forward skips because of the
+    index array: sum(min(start_index, hi)//BN) / sum(ceil(hi/BN))."""
+    P = N - M
+    nmb = start_index.shape[-1]
+    hi = np.minimum(N, P + (np.arange(nmb) + 1) * BM)
+    total = np.ceil(hi / BN).sum() * start_index.shape[0] * start_index.shape[1]
+    skipped = (np.minimum(start_index, hi[None, None, :]) // BN).sum()
+    return float(skipped) / float(total)
+
+
+# --------------------------------------------------------------------------
+# fused RMSNorm + sigmoid output gate (FNG:18-53 with is_rms_norm, no bias/residual)
+# --------------------------------------------------------------------------
+def group_rmsnorm_gated(x: torch.Tensor, g: torch.Tensor, weight: torch.Tensor, num_groups: int,
+                        eps: float = 1e-6, upcast: bool = True) -> torch.Tensor:
+    """y = rmsnorm_per_group(x) * weight * sigmoid(g), cast back to x.dtype.
+    x, g (..., G*D); weight (G*D,)."""
+    dtype = x.dtype
+    if upcast:
+        x, g, weight = x.float(), g.float(), weight.float()
+    shp = x.shape
+    xg = x.reshape(*shp[:-1], num_groups, shp[-1] // num_groups)
+    wg = weight.reshape(num_groups, -1)
+    rstd = 1 / torch.sqrt(xg.square().mean(dim=-1, keepdim=True) + eps)
+    out = (xg * rstd * wg).reshape(shp)
+    out = out * torch.sigmoid(g)
+    return out.to(dtype)
+
+
+def group_rmsnorm_gated_fwd_bwd(x, g, weight, dy, num_groups, eps=1e-6):
+    x, g, weight = [t.detach().clone().requires_grad_() for t in (x, g, weight)]
+    y = group_rmsnorm_gated(x, g, weight, num_groups, eps)
+    y.backward(dy)
+    return y.detach(), x.grad, g.grad, weight.grad
