@@ -1,0 +1,361 @@
+#!/usr/bin/env python
+"""Benchmark of the Forgetting Attention hot path (fwd + bwd) on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload cfg3] [--impl ours|reference]
+
+One "step" is one forward + backward pass of the operator over one synthetic batch of
+the named workload.  With N > 1 (launched by torch.distributed.run, one rank per GPU)
+every rank runs its own batch of the same shape -- the (batch, head) units are
+independent, there is no collective on the data path -- so the job is N times larger
+("scaling": "weak") and `value` is the whole-job rate: FLOPs of all ranks / max-over-ranks
+device time.  FLOPs are the algorithmic count 14 * D * H * sum_b n_b (n_b + 1) / 2 with
+n_b = T - seq_start_b (4 forward + 10 backward per query/key pair and head-dim element).
+
+Prints ONE JSON line (rank 0).  `--impl reference` times the upstream project's own CPU
+formulation of the operator (the dense PyTorch math, restated in oracle/) on the host
+cores, on a bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "fwd+bwd Forgetting Attention TFLOP/s"
+UNIT = "TFLOP/s"
+
+# name: (B, T, H, D, gate-logit mean, gate-logit std, has seq_start, adaptive_threshold, per-head input scale)
+WORKLOADS = {
+    "cfg2": dict(B=4, T=512, H=12, D=64, mu=0.0, sigma=1.0, seq=False, thr=None, head_scale=False, seed=1002),
+    "cfg3": dict(B=2, T=16384, H=24, D=64, mu=4.0, sigma=1.0, seq=True, thr=None, head_scale=False, seed=1003),
+    "cfg4": dict(B=4, T=16384, H=16, D=128, mu=-1.0, sigma=1.5, seq=False, thr=None, head_scale=True, seed=1004),
+    "cfg4_acp": dict(B=4, T=16384, H=16, D=128, mu=-1.0, sigma=1.5, seq=False, thr="auto", head_scale=True, seed=1004),
+}
+DESCR = {
+    "cfg2": "kernel-level op B4 T512 H12 D64 bf16",
+    "cfg3": "long-context FoX-760M layer shape B2 T16384 H24 D64 bf16, gate logits N(4,1), seq_start U[0,2048)",
+    "cfg4": "ACP stress shape B4 T16384 H16 D128 bf16, gate logits N(-1,1.5), pruning off",
+    "cfg4_acp": "ACP stress shape B4 T16384 H16 D128 bf16, gate logits N(-1,1.5), adaptive_threshold=auto",
+}
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return dict(hbm_gbs=p["hbm_gbs"], bf16=p["bf16_tflops"], bf16_sustained=p["bf16_tflops_sustained"],
+                    source="measured")
+    return dict(hbm_gbs=6650.0, bf16=1590.0, bf16_sustained=1400.0, source="fallback")
+
+
+def make_inputs(w, rank, pin=False):
+    """Seeded synthetic inputs on the CPU generator (device independent bits): q, k, v,
+    gate logits, dout, then config-specific extras, in that order."""
+    g = torch.Generator().manual_seed(w["seed"] + 7919 * rank)
+    B, T, H, D = w["B"], w["T"], w["H"], w["D"]
+    q = torch.randn(B, H, T, D, generator=g)
+    k = torch.randn(B, H, T, D, generator=g)
+    v = torch.randn(B, H, T, D, generator=g)
+    logit = torch.randn(B, H, T, generator=g) * w["sigma"] + w["mu"]
+    dout = torch.randn(B, H, T, D, generator=g)
+    seq = torch.randint(0, 2048, (B,), generator=g) if w["seq"] else None
+    if w["head_scale"]:
+        s = (torch.rand(H, generator=g) * 1.5 + 0.5).view(1, H, 1, 1)
+        q, k, v = q * s, k * s, v * s
+    q, k, v, dout = [t.to(torch.bfloat16) for t in (q, k, v, dout)]
+    log_fgate = torch.nn.functional.logsigmoid(logit.float())
+    ts = dict(q=q, k=k, v=v, log_fgate=log_fgate, dout=dout)
+    if pin:
+        ts = {n: t.pin_memory() for n, t in ts.items()}
+    ts["seq_start"] = seq
+    return ts
+
+
+def flops_of(w, seq):
+    n = torch.full((w["B"],), float(w["T"]), dtype=torch.float64)
+    if seq is not None:
+        n = n - seq.double()
+    pairs = float((n * (n + 1) / 2).sum()) * w["H"]
+    return 14.0 * w["D"] * pairs, pairs
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index = index
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.index)], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except Exception:
+            self.proc.kill()
+            out = ""
+        clocks, mx, reasons = [], None, set()
+        for line in out.splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                clocks.append(float(f[1]))
+                mx = float(f[2])
+            except ValueError:
+                continue
+            for name, val in zip(["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"], f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        if not clocks:
+            return {"sm_mhz": None, "sm_max_mhz": mx, "reasons": ["no samples"]}
+        top = max(clocks)
+        loaded = [c for c in clocks if c >= 0.5 * top] or clocks
+        return {"sm_mhz": statistics.median(loaded), "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(clocks)}
+
+
+# --------------------------------------------------------------------------- CPU arm
+def cpu_sample(w, threads, rows=None):
+    """The upstream dense formulation (oracle) on the host: ONE (batch, head) unit of the
+    workload at full key length, fwd + autograd bwd, evaluated over query-row chunks so the
+    T x T matrices stay bounded.  rows=None: every query row; rows=r: only the last r query
+    rows (a smaller sample of the same unit).  Returns (seconds, flops, description)."""
+    from oracle import fox_oracle as orc
+    torch.set_num_threads(threads)
+    T, D = w["T"], w["D"]
+    g = torch.Generator().manual_seed(w["seed"])
+    q, k, v, dout = [torch.randn(1, 1, T, D, generator=g) for _ in range(4)]
+    lf = torch.nn.functional.logsigmoid(torch.randn(1, 1, T, generator=g) * w["sigma"] + w["mu"])
+    chunk = min(T, 2048)
+    first = 0 if rows is None else max(T - rows, 0)
+    t0 = time.perf_counter()
+    kk, vv, ll = [t.clone().requires_grad_() for t in (k, v, lf)]
+    for r0 in range(first, T, chunk):
+        r1 = min(T, r0 + chunk)
+        qq = q[:, :, r0:r1].clone().requires_grad_()
+        out = orc.dense_forgetting_attention(qq, kk[:, :, :r1], vv[:, :, :r1], ll[:, :, :r1], None, None)
+        out.backward(dout[:, :, r0:r1])
+    dt = time.perf_counter() - t0
+    pairs = T * (T + 1) / 2 - first * (first + 1) / 2
+    flops = 14.0 * D * pairs
+    what = "every query row" if rows is None else f"the last {T - first} query rows"
+    return dt, flops, (f"1 of {w['B'] * w['H']} (batch, head) units, {what} against keys [0, T={T}), fp32 dense "
+                       f"PyTorch fwd+autograd bwd in {chunk}-row chunks")
+
+
+def run_reference(args, w, wname):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    rows = min(w["T"], 2048)
+    for _ in range(args.warmup):
+        cpu_sample(w, threads, rows)
+    times = []
+    flops = 0.0
+    desc = ""
+    for _ in range(args.steps):
+        dt, flops, desc = cpu_sample(w, threads, rows)
+        times.append(dt)
+    mean = sum(times) / len(times)
+    val = flops / mean / 1e12
+    line = {
+        "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": mean * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": wname, "description": DESCR[wname], "step": "bounded CPU sample: " + desc},
+        "cpu_baseline": {"value": val, "unit": UNIT, "cores": threads, "kind": "port", "sample": desc},
+        "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# --------------------------------------------------------------------------- GPU arm
+def run_ours(args, w, wname):
+    import torch.distributed as dist
+    import forgetting_transformer_b200 as fox
+    from forgetting_transformer_b200 import _lib, ops
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (sm_100a); the product has no CPU path")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    _lib.load()
+
+    host = make_inputs(w, rank, pin=True)
+    seq = host["seq_start"]
+    flops, pairs = flops_of(w, seq)
+    seq_d = None if seq is None else seq.to(dev)
+    d = {n: host[n].to(dev, non_blocking=True) for n in ("q", "k", "v", "log_fgate", "dout")}
+    q, k, v, lf = [d[n].requires_grad_() for n in ("q", "k", "v", "log_fgate")]
+    dout = d["dout"]
+    thr = w["thr"]
+
+    def step():
+        q.grad = k.grad = v.grad = lf.grad = None
+        out = fox.forgetting_attention(q, k, v, lf, head_first=True, seq_start=seq_d, adaptive_threshold=thr)
+        out.backward(dout)
+        return out
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    _lib.check_status()
+
+    # ---- timed region: K steps, device-timed, inputs resident in HBM ----
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ops.KernelTimer() as timer:
+        barrier()
+        e0.record()
+        for _ in range(args.steps):
+            step()
+        e1.record()
+        barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    _lib.check_status()
+    ms = e0.elapsed_time(e1)
+    kern = timer.summary()
+    launches = sum(n for n, _ in kern.values())
+    t = torch.tensor([ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_max = float(t.item())
+    ms_per_step = ms_max / args.steps
+    value = world * flops / (ms_per_step * 1e-3) / 1e12
+
+    # ---- end to end through the public API with host buffers ----
+    outs_host = None
+
+    def e2e_step():
+        nonlocal outs_host
+        dd = {n: host[n].to(dev, non_blocking=True) for n in ("q", "k", "v", "log_fgate", "dout")}
+        qq, kk, vv, ll = [dd[n].requires_grad_() for n in ("q", "k", "v", "log_fgate")]
+        out = fox.forgetting_attention(qq, kk, vv, ll, head_first=True, seq_start=seq_d, adaptive_threshold=thr)
+        out.backward(dd["dout"])
+        res = [out.detach(), qq.grad, kk.grad, vv.grad, ll.grad]
+        if outs_host is None:
+            outs_host = [torch.empty(r.shape, dtype=r.dtype).pin_memory() for r in res]
+        for hbuf, r in zip(outs_host, res):
+            hbuf.copy_(r, non_blocking=True)
+
+    h2d = sum(host[n].numel() * host[n].element_size() for n in ("q", "k", "v", "log_fgate", "dout"))
+    e2e_step()
+    barrier()
+    d2h = sum(hb.numel() * hb.element_size() for hb in outs_host)
+    n_e2e = max(3, min(args.steps, 10))
+    barrier()
+    e0.record()
+    for _ in range(n_e2e):
+        e2e_step()
+    e1.record()
+    barrier()
+    t2 = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t2, op=dist.ReduceOp.MAX)
+    e2e_val = world * flops / (float(t2.item()) / n_e2e * 1e-3) / 1e12
+
+    if rank == 0:
+        peaks = load_peaks()
+        bwd_n, bwd_ms = kern.get("fox_attn_bwd", (0, float("nan")))
+        fwd_n, fwd_ms = kern.get("fox_attn_fwd", (0, float("nan")))
+        # executed FLOPs of the dominant kernel (backward: 10 of the 14 per pair)
+        bwd_tf = (10.0 / 14.0) * flops / (bwd_ms * 1e-3) / 1e12
+        fwd_tf = (4.0 / 14.0) * flops / (fwd_ms * 1e-3) / 1e12
+        roof = {
+            "kernel": "fox_attn_bwd_kernel", "bound": "tensor", "achieved": bwd_tf,
+            "peak": peaks["bf16_sustained"], "unit": "TFLOP/s", "frac": bwd_tf / peaks["bf16_sustained"],
+            "peak_kind": f"bf16_tflops_sustained of {peaks['source']} (kernel timed inside the stepping loop)",
+            "frac_of_burst_peak": bwd_tf / peaks["bf16"], "traffic": TRAFFIC_BYTES_PER_LAUNCH.get(wname),
+            "ms_per_launch": bwd_ms, "launches": bwd_n,
+            "fwd_kernel": {"achieved": fwd_tf, "frac": fwd_tf / peaks["bf16_sustained"], "ms_per_launch": fwd_ms},
+            "all_kernels_ms": {k_: round(v_[1], 4) for k_, v_ in kern.items()},
+        }
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": wname, "description": DESCR[wname], "per_gpu_batch": w["B"],
+                       "global_batch": w["B"] * world, "seq_len": w["T"], "heads": w["H"], "head_dim": w["D"],
+                       "sharding": "independent (batch, head) units per rank, no collective",
+                       "l2": "inputs (>=400 MB per step) larger than the 126 MB L2; no explicit flush",
+                       "algorithmic_flops_per_step_per_gpu": flops,
+                       "frac_of_bf16_peak": value / world / peaks["bf16"],
+                       "frac_of_nominal_2250": value / world / 2250.0},
+            "roofline": roof,
+            "e2e": {"value": e2e_val, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "steps": n_e2e},
+            "gpu_launches": launches,
+            "clocks": clocks,
+        }
+        if world == 1 and not args.no_cpu:
+            dt, fl, desc = cpu_sample(w, os.cpu_count() or 1)
+            line["cpu_baseline"] = {"value": fl / dt / 1e12, "unit": UNIT, "cores": os.cpu_count() or 1,
+                                    "kind": "port", "sample": desc, "seconds": dt}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+# DRAM bytes (read + write) of one backward-kernel launch from an ncu capture, per workload;
+# filled from profiles/ (None = not captured).
+TRAFFIC_BYTES_PER_LAUNCH = {"cfg3": None}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--workload", default="cfg3", choices=sorted(WORKLOADS))
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    w = WORKLOADS[args.workload]
+    if args.impl == "reference":
+        run_reference(args, w, args.workload)
+    else:
+        run_ours(args, w, args.workload)
+
+
+if __name__ == "__main__":
+    main()

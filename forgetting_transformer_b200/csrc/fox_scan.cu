@@ -191,8 +191,11 @@ fox_max_row_norm_kernel(const uint16_t* __restrict__ x, int64_t sb, int64_t sh, 
   const int r_in = threadIdx.x / lanes_per_row;
   const uint16_t* base = x + b * sb + h * sh;
   float best = 0.f;
-  for (int t = blockIdx.x * rows_per_block + r_in; t < T; t += gridDim.x * rows_per_block) {
-    const uint4 v = *reinterpret_cast<const uint4*>(base + static_cast<int64_t>(t) * st + sub * 8);
+  // every lane runs the same number of iterations (the shuffles below need the full warp)
+  for (int t0 = blockIdx.x * rows_per_block; t0 < T; t0 += gridDim.x * rows_per_block) {
+    const int t = t0 + r_in;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (t < T) v = *reinterpret_cast<const uint4*>(base + static_cast<int64_t>(t) * st + sub * 8);
     const uint32_t w[4] = {v.x, v.y, v.z, v.w};
     float acc = 0.f;
 #pragma unroll

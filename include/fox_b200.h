@@ -63,6 +63,85 @@ typedef struct fox_tensor4 {
 /* Library / build information: returns a static string. */
 const char* fox_version(void);
 
+/* log_lambda[b,h,t] = carry_in[b,h] + sum_{seq_start[b] <= u <= t} log_fgate[b,h,u], fp32.
+ * Replaces the masked clone + torch.cumsum of forgetting_attention.py:117-127 (one pass,
+ * the seq_start masking is a predicate on the load).  log_fgate may have any element
+ * strides (sb, sh, sn) -- e.g. the (B,H,N) view of a (B,N,H) tensor; log_lambda is a
+ * contiguous (B,H,N) array.  seq_start (B,) int64 or NULL.  carry_in (B,H) or NULL is a
+ * prefix carried in from the tokens to the left (context-parallel shards); total_out
+ * (B,H) or NULL receives the last prefix. */
+int fox_cumsum_fwd(int device, void* stream, int64_t B, int64_t H, int64_t N, const float* log_fgate,
+                   int64_t sb, int64_t sh, int64_t sn, const int64_t* seq_start, const float* carry_in,
+                   float* log_lambda, float* total_out);
+
+/* dlog_fgate[b,h,t] = carry_in[b,h] + sum_{u >= t} (dlam_col[b,h,u] + dlam_row[b,h,u-(N-M)]),
+ * the reverse prefix sum of forgetting_attention.py:390-392 fused with the addition of the
+ * key-side and query-side halves of dlog_lambda (lines 1122, 1326-1344).  dlam_row may be NULL. */
+int fox_revcumsum(int device, void* stream, int64_t B, int64_t H, int64_t M, int64_t N, const float* dlam_col,
+                  const float* dlam_row, const float* carry_in, float* dlog_fgate, float* total_out);
+
+/* Block-pruning index scans, bit-identical decisions to _find_start_index_kernel and
+ * _find_end_index_kernel (forgetting_attention.py:695-745, 747-795) on a
+ * (block_m, block_n) grid.  threshold is a (B,H) fp32 view with element strides
+ * (thr_sb, thr_sh) (0 for broadcast axes) and must be <= 0.  start_index
+ * (B,H,ceil(M/block_m)) and/or end_index (B,H,ceil(N/block_n)), int64; either may be NULL. */
+int fox_find_index(int device, void* stream, int64_t B, int64_t H, int64_t M, int64_t N, int64_t block_m,
+                   int64_t block_n, const float* log_lambda, const float* threshold, int64_t thr_sb,
+                   int64_t thr_sh, int64_t* start_index, int64_t* end_index);
+
+/* out[b,h] = max_t ||x[b,h,t,:]||_2 in fp32: the reduction behind adaptive_threshold="auto"
+ * (torch.linalg.vector_norm(...).max(...), forgetting_attention.py:95-96).  out (B,H) fp32 must
+ * be zero on entry.  D in {16,32,64,128}. */
+int fox_max_row_norm(int device, void* stream, int dtype, int64_t B, int64_t H, int64_t T, int64_t D,
+                     const fox_tensor4* x, float* out_zeroed);
+
+/* Forward attention: replaces the _fwd_kernel launch (forgetting_attention.py:186-204, kernel
+ * 505-693).  q (B,H,M,D); k, v (B,H,N,D); M <= N; D in {64,128}.  log_lambda from
+ * fox_cumsum_fwd.  seq_start (B,) int64 or NULL.  start_index from fox_find_index with
+ * FOX_FWD_BLOCK_M/N, or NULL for no pruning.  Writes o (same dtype, caller's strides) and the
+ * log-normaliser L (B,H,M) fp32 (natural log; -inf for rows left of seq_start, whose output is
+ * 0).  status: int32[4], zero on entry; [0] != 0 after the kernel means a bounded wait ran out. */
+int fox_attn_fwd(int device, void* stream, int dtype, int64_t B, int64_t H, int64_t M, int64_t N, int64_t D,
+                 const fox_tensor4* q, const fox_tensor4* k, const fox_tensor4* v, const float* log_lambda,
+                 const int64_t* seq_start, const int64_t* start_index, float sm_scale, const fox_tensor4* o,
+                 float* L, int32_t* status);
+
+/* delta[b,h,m] = sum_d o[b,h,m,d] * d_o[b,h,m,d] in fp32: replaces _bwd_preprocess
+ * (forgetting_attention.py:267-277, kernel 902-943). */
+int fox_bwd_delta(int device, void* stream, int dtype, int64_t B, int64_t H, int64_t M, int64_t D,
+                  const fox_tensor4* o, const fox_tensor4* d_o, float* delta);
+
+/* Backward attention in one pass: replaces the _bwd_kv_kernel and _bwd_q_kernel launches
+ * (forgetting_attention.py:313-334, 366-386; kernels 956-1143, 1156-1344).  end_index from
+ * fox_find_index with FOX_BWD_BLOCK_M/N, or NULL.  Outputs: dk, dv (input dtype, caller's
+ * strides, zero left of seq_start); dlam_col (B,H,N) fp32 = -sum_i dS_ij, fully written;
+ * and two caller-provided scratch arrays that must be zero on entry and are reduced into:
+ * dq_accum (B,H,M,D) fp32 = sum_j dS_ij k_j (unscaled) and dlam_row (B,H,M) fp32 = sum_j dS_ij. */
+int fox_attn_bwd(int device, void* stream, int dtype, int64_t B, int64_t H, int64_t M, int64_t N, int64_t D,
+                 const fox_tensor4* q, const fox_tensor4* k, const fox_tensor4* v, const fox_tensor4* d_o,
+                 const float* log_lambda, const float* L, const float* delta, const int64_t* seq_start,
+                 const int64_t* end_index, float sm_scale, float* dq_accum_zeroed, float* dlam_row_zeroed,
+                 float* dlam_col, const fox_tensor4* dk, const fox_tensor4* dv, int32_t* status);
+
+/* dq = dq_accum * scale, fp32 -> input dtype with the caller's strides (the `dq *= sm_scale`
+ * and store of forgetting_attention.py:1333-1343). */
+int fox_dq_convert(int device, void* stream, int dtype, int64_t B, int64_t H, int64_t M, int64_t D,
+                   const float* dq_accum, float scale, const fox_tensor4* dq);
+
+/* Fused per-head RMSNorm + sigmoid gate, forward: y = x * rstd * w_h * sigmoid(g) with
+ * rstd = (mean_d x^2 + eps)^-1/2 per (token, head).  Replaces layer_norm_gated_fwd
+ * (fuse_norm_gate.py:539-617, kernel 132-206) for is_rms_norm, activation "sigmoid", no
+ * bias/residual.  x, g, y: contiguous (tokens, G*D) 16-bit; w: (G*D) fp32; rstd: (tokens*G) fp32. */
+int fox_normgate_fwd(int device, void* stream, int dtype, int64_t tokens, int64_t G, int64_t D, const void* x,
+                     const void* g, const float* w, float eps, void* y, float* rstd);
+
+/* Backward of the above: dx, dg (16-bit) and per-CTA partial weight gradients dw_partial
+ * (n_partials, G*D) fp32, fully written, to be summed over axis 0 by the caller.  Replaces
+ * layer_norm_gated_bwd (fuse_norm_gate.py:620-723, kernel 309-421). */
+int fox_normgate_bwd(int device, void* stream, int dtype, int64_t tokens, int64_t G, int64_t D, const void* x,
+                     const void* g, const float* w, const float* rstd, const void* dy, void* dx, void* dg,
+                     float* dw_partial, int64_t n_partials);
+
 #ifdef __cplusplus
 }
 #endif

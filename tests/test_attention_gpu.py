@@ -1,0 +1,312 @@
+"""GPU parity tests (B200): the CUDA path, called through the C ABI, against the CPU
+oracle on the same seeded inputs, against the golden fixtures produced by upstream's
+own kernels, and through size-independent properties at the benchmark's full sizes."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import forgetting_transformer_b200 as fox
+from forgetting_transformer_b200 import _lib, ops
+from oracle import fox_oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+# tolerances: upstream's own known-answer bar is atol 1e-2 (fp16); for bf16 the bar is
+# 2e-2 max-abs or 1e-2 relative; fp32-computed by-products (prefix sum, log-normaliser)
+# must agree with the fp32 formulation to 1e-4 relative.
+ATOL_FP16 = 1e-2
+ATOL_BF16, RTOL_BF16 = 2e-2, 1e-2
+RTOL_FP32 = 1e-4
+
+
+def _close(a, b, atol, rtol=0.0):
+    """Pass when max|a-b| <= atol, or (rtol > 0) when max|a-b| <= rtol * max|b|: the bf16 bar
+    "2e-2 max-abs / 1e-2 relative" read as either an absolute bound or a bound relative to
+    the tensor's magnitude (gradients of N(0,1) inputs reach 5-10, where one bf16 ulp is
+    already 3e-2)."""
+    a, b = a.float().cpu(), b.float().cpu()
+    assert a.shape == b.shape
+    assert not torch.isnan(a).any()
+    if a.numel() == 0:
+        return
+    err = (a - b).abs().max().item()
+    ok = err <= atol or (rtol > 0 and err <= rtol * b.abs().max().item())
+    assert ok, f"max abs err {err:.3e} vs atol {atol} / rtol {rtol} * max|ref| {b.abs().max().item():.3e}"
+
+
+def _run(q, k, v, lf, do, seq=None, sm_scale=None, thr=None, head_first=True):
+    dev = "cuda"
+    qq, kk, vv, ll = [t.to(dev).detach().requires_grad_() for t in (q, k, v, lf)]
+    ss = None if seq is None else seq.to(dev)
+    th = thr.to(dev) if isinstance(thr, torch.Tensor) else thr
+    out = fox.forgetting_attention(qq, kk, vv, ll, head_first=head_first, seq_start=ss, sm_scale=sm_scale,
+                                   adaptive_threshold=th)
+    out.backward(do.to(dev))
+    torch.cuda.synchronize()
+    _lib.check_status()
+    return out.detach().cpu(), qq.grad.cpu(), kk.grad.cpu(), vv.grad.cpu(), ll.grad.cpu()
+
+
+def _inputs(seed, B, H, M, N, D, dtype, mu=0.0, sigma=1.0, std=1.0):
+    g = torch.Generator().manual_seed(seed)
+    q = (torch.randn(B, H, M, D, generator=g) * std).to(dtype)
+    k = (torch.randn(B, H, N, D, generator=g) * std).to(dtype)
+    v = (torch.randn(B, H, N, D, generator=g) * std).to(dtype)
+    lf = torch.nn.functional.logsigmoid(torch.randn(B, H, N, generator=g) * sigma + mu)
+    do = torch.randn(B, H, M, D, generator=g).to(dtype)
+    return q, k, v, lf, do
+
+
+# ------------------------------------------------------------------ golden fixtures
+def test_against_upstream_kernel_outputs(golden):
+    """Same inputs as upstream's Triton kernels were run on (fp16): outputs, log-normaliser
+    and all four gradients within upstream's own tolerance; pruning indices identical."""
+    g = golden
+    dev = "cuda"
+    B, H, M, D = g["q"].shape
+    N = g["k"].shape[2]
+    qq, kk, vv, ll = [g[n].to(dev).requires_grad_() for n in ("q", "k", "v", "log_fgate")]
+    ss = None if g["seq_start"] is None else g["seq_start"].to(dev)
+    thr = None if g["threshold"] is None else g["threshold"].to(dev)
+    out, L, si = ops.ForgettingAttention.apply(qq, kk, vv, ll, ss, True, g["sm_scale"], thr, True,
+                                               thr is not None, None, False, False)
+    out.backward(g["dout"].to(dev))
+    torch.cuda.synchronize()
+    _lib.check_status()
+    _close(out, g["out"], 2e-3)
+    fin = torch.isfinite(g["L"])
+    assert torch.equal(torch.isfinite(L.cpu()), fin)
+    _close(L.cpu()[fin], g["L"][fin], 1e-3, RTOL_FP32)
+    _close(qq.grad, g["dq"], 4e-3)
+    _close(kk.grad, g["dk"], 4e-3)
+    _close(vv.grad, g["dv"], 4e-3)
+    _close(ll.grad, g["dlog_fgate"], ATOL_FP16)
+    if thr is not None:
+        assert torch.equal(si.cpu(), g["start_index"])
+
+
+# --------------------------------------------------- upstream's own known-answer grid
+@pytest.mark.parametrize("Z,H,M,N,D", [(4, 2, 1020, 2098, 64), (4, 2, 1024, 2048, 128)])
+@pytest.mark.parametrize("fgate_logit_range", [(0, 5), (5, 10)])
+@pytest.mark.parametrize("has_seq_start", [True, False])
+@pytest.mark.parametrize("adaptive_threshold", [-10.0, None, "per_head"])
+def test_upstream_known_answer_grid(Z, H, M, N, D, fgate_logit_range, has_seq_start, adaptive_threshold):
+    """The parametrisation of upstream's in-file test_op (forgetting_attention.py:1360-1425):
+    fp16, q/k/v ~ N(0, 0.5^2), sm_scale 0.5, atol 1e-2, against the dense formulation."""
+    g = torch.Generator().manual_seed(24)
+    dtype = torch.float16
+    q = torch.empty(Z, H, M, D).normal_(0.0, 0.5, generator=g).to(dtype)
+    k = torch.empty(Z, H, N, D).normal_(0.0, 0.5, generator=g).to(dtype)
+    v = torch.empty(Z, H, N, D).normal_(0.0, 0.5, generator=g).to(dtype)
+    lf = torch.nn.functional.logsigmoid(torch.empty(Z, H, N).uniform_(*fgate_logit_range, generator=g))
+    seq = torch.randint(0, N, (Z,), generator=g) if has_seq_start else None
+    do = torch.randn(Z, H, M, D, generator=g).to(dtype)
+    thr = torch.tensor([-1000.0, -100.0]) if adaptive_threshold == "per_head" else adaptive_threshold
+    out, dq, dk, dv, dlf = _run(q, k, v, lf, do, seq, 0.5, thr)
+    ro, rdq, rdk, rdv, rdl = orc.dense_fwd_bwd(q.float(), k.float(), v.float(), lf, do.float(), seq, 0.5)
+    _close(out, ro, ATOL_FP16)
+    _close(dv, rdv, ATOL_FP16)
+    _close(dk, rdk, ATOL_FP16)
+    _close(dq, rdq, ATOL_FP16)
+    _close(dlf, rdl, ATOL_FP16)
+
+
+# ------------------------------------------------------------- benchmark configs 1, 2
+def test_config1_fp32_reference_case():
+    """B=2, T=256, H=4, D=64, seq_start=[0, 37], sm_scale=1/8: the CPU fp32 formulation
+    against the bf16 and fp16 kernels."""
+    for dtype, atol, rtol in [(torch.bfloat16, ATOL_BF16, RTOL_BF16), (torch.float16, 4e-3, 0.0)]:
+        q, k, v, lf, do = _inputs(1001, 2, 4, 256, 256, 64, dtype)
+        seq = torch.tensor([0, 37])
+        out, dq, dk, dv, dlf = _run(q, k, v, lf, do, seq, 1 / 8)
+        ro, rdq, rdk, rdv, rdl = orc.dense_fwd_bwd(q.float(), k.float(), v.float(), lf, do.float(), seq, 1 / 8, True)
+        for a, b in [(out, ro), (dq, rdq), (dk, rdk), (dv, rdv)]:
+            _close(a, b, atol, rtol)
+        _close(dlf, rdl, atol * 2, rtol)
+        assert torch.all(out[1, :, :37] == 0)
+
+
+def test_config2_bf16_kernel_case():
+    """B=4, T=512, H=12, D=64 bf16, no seq_start, no pruning, against the fp32 formulation
+    of the same bf16 inputs (2e-2 abs / 1e-2 rel)."""
+    q, k, v, lf, do = _inputs(1002, 4, 12, 512, 512, 64, torch.bfloat16)
+    out, dq, dk, dv, dlf = _run(q, k, v, lf, do)
+    r = orc.blockwise_fwd_bwd(q, k, v, lf, do, low_precision_matmul=False)
+    _close(out, r["out"], ATOL_BF16, RTOL_BF16)
+    _close(dq, r["dq"], ATOL_BF16, RTOL_BF16)
+    _close(dk, r["dk"], ATOL_BF16, RTOL_BF16)
+    _close(dv, r["dv"], ATOL_BF16, RTOL_BF16)
+    _close(dlf, r["dlog_fgate"], 2 * ATOL_BF16, RTOL_BF16)
+
+
+def test_fp32_byproducts_match_fp32_path():
+    """Prefix sum and log-normaliser are fp32 quantities: 1e-4 relative to the fp32 path."""
+    q, k, v, lf, do = _inputs(5, 2, 3, 700, 700, 64, torch.bfloat16, mu=2.0)
+    seq = torch.tensor([0, 300])
+    lam = ops.log_lambda_cumsum(lf.cuda(), seq.cuda()).cpu()
+    ref = orc.log_lambda(lf, seq)
+    _close(lam, ref, 1e-5, RTOL_FP32)
+    out, L, _ = ops.ForgettingAttention.apply(q.cuda(), k.cuda(), v.cuda(), lf.cuda(), seq.cuda(), True, None,
+                                              None, True, False, None, False, False)
+    r = orc.blockwise_fwd_bwd(q, k, v, lf, do, seq, low_precision_matmul=False)
+    fin = torch.isfinite(r["L"])
+    assert torch.equal(torch.isfinite(L.cpu()), fin)
+    _close(L.cpu()[fin], r["L"][fin], 1e-4, RTOL_FP32)
+
+
+# ---------------------------------------------------------------------- edge cases
+@pytest.mark.parametrize("T", [1, 7, 127, 128, 129, 300])
+@pytest.mark.parametrize("D", [64, 128])
+def test_small_and_ragged_lengths(T, D):
+    q, k, v, lf, do = _inputs(T + D, 2, 2, T, T, D, torch.bfloat16)
+    out, dq, dk, dv, dlf = _run(q, k, v, lf, do)
+    r = orc.blockwise_fwd_bwd(q, k, v, lf, do, low_precision_matmul=False)
+    for a, b in [(out, r["out"]), (dq, r["dq"]), (dk, r["dk"]), (dv, r["dv"])]:
+        _close(a, b, ATOL_BF16, RTOL_BF16)
+    _close(dlf, r["dlog_fgate"], 2 * ATOL_BF16, RTOL_BF16)
+
+
+def test_seq_start_extremes():
+    """seq_start = 0, in the middle of a block, on a block boundary and at the last token."""
+    B, H, T, D = 4, 2, 384, 64
+    q, k, v, lf, do = _inputs(11, B, H, T, T, D, torch.bfloat16)
+    seq = torch.tensor([0, 200, 256, T - 1])
+    out, dq, dk, dv, dlf = _run(q, k, v, lf, do, seq)
+    r = orc.blockwise_fwd_bwd(q, k, v, lf, do, seq, low_precision_matmul=False)
+    for a, b in [(out, r["out"]), (dq, r["dq"]), (dk, r["dk"]), (dv, r["dv"])]:
+        _close(a, b, ATOL_BF16, RTOL_BF16)
+    _close(dlf, r["dlog_fgate"], 2 * ATOL_BF16, RTOL_BF16)
+    for b in range(B):
+        s = int(seq[b])
+        assert torch.all(out[b, :, :s] == 0) and torch.all(dk[b, :, :s] == 0) and torch.all(dv[b, :, :s] == 0)
+    # the last row of batch 3 attends to itself only
+    _close(out[3, :, T - 1], v[3, :, T - 1], 1e-2)
+
+
+def test_seq_len_q_shorter_than_kv():
+    q, k, v, lf, do = _inputs(12, 2, 2, 130, 517, 64, torch.bfloat16, mu=1.0)
+    seq = torch.tensor([3, 400])
+    out, dq, dk, dv, dlf = _run(q, k, v, lf, do, seq)
+    r = orc.blockwise_fwd_bwd(q, k, v, lf, do, seq, low_precision_matmul=False)
+    for a, b in [(out, r["out"]), (dq, r["dq"]), (dk, r["dk"]), (dv, r["dv"])]:
+        _close(a, b, ATOL_BF16, RTOL_BF16)
+    _close(dlf, r["dlog_fgate"], 2 * ATOL_BF16, RTOL_BF16)
+
+
+def test_layout_b_t_h_d_views_and_output_strides():
+    """head_first=False hands the kernels permuted views; the output keeps q's layout."""
+    B, T, H, D = 2, 320, 3, 64
+    g = torch.Generator().manual_seed(13)
+    q, k, v, do = [torch.randn(B, T, H, D, generator=g).bfloat16() for _ in range(4)]
+    lf = torch.nn.functional.logsigmoid(torch.randn(B, T, H, generator=g) + 1)
+    qq, kk, vv, ll = [t.cuda().requires_grad_() for t in (q, k, v, lf)]
+    out = fox.forgetting_attention(qq, kk, vv, ll)
+    assert out.shape == (B, T, H, D) and out.is_contiguous()
+    out.backward(do.cuda())
+    _lib.check_status()
+    r = orc.blockwise_fwd_bwd(*[t.transpose(1, 2) for t in (q, k, v)], lf.transpose(1, 2), do.transpose(1, 2),
+                              low_precision_matmul=False)
+    _close(out.transpose(1, 2), r["out"], ATOL_BF16, RTOL_BF16)
+    _close(qq.grad.transpose(1, 2), r["dq"], ATOL_BF16, RTOL_BF16)
+    _close(kk.grad.transpose(1, 2), r["dk"], ATOL_BF16, RTOL_BF16)
+    _close(vv.grad.transpose(1, 2), r["dv"], ATOL_BF16, RTOL_BF16)
+    _close(ll.grad.transpose(1, 2), r["dlog_fgate"], 2 * ATOL_BF16, RTOL_BF16)
+    assert ll.grad.shape == lf.shape
+
+
+def test_threshold_validation():
+    q, k, v, lf, do = [t.cuda() for t in _inputs(14, 2, 2, 128, 128, 64, torch.bfloat16)]
+    with pytest.raises(AssertionError, match="adaptive_threshold must be either"):
+        fox.forgetting_attention(q, k, v, lf, head_first=True, adaptive_threshold="automatic")
+    with pytest.raises(RuntimeError, match="broadcastable"):
+        fox.forgetting_attention(q, k, v, lf, head_first=True, adaptive_threshold=torch.zeros(3, device="cuda"))
+
+
+def test_runs_under_autocast_and_checkpoint():
+    from torch.utils.checkpoint import checkpoint
+    q, k, v, lf, do = [t.cuda() for t in _inputs(15, 1, 2, 256, 256, 64, torch.bfloat16)]
+    q.requires_grad_(); lf.requires_grad_()
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        out = checkpoint(lambda *a: fox.forgetting_attention(*a, head_first=True), q, k, v, lf, use_reentrant=False)
+    out.backward(do)
+    _lib.check_status()
+    r = orc.blockwise_fwd_bwd(q.detach().cpu(), k.cpu(), v.cpu(), lf.detach().cpu(), do.cpu(),
+                              low_precision_matmul=False)
+    _close(out, r["out"], ATOL_BF16, RTOL_BF16)
+    _close(q.grad, r["dq"], ATOL_BF16, RTOL_BF16)
+
+
+# ------------------------------------------------------------------------- pruning
+@pytest.mark.parametrize("M,N", [(512, 512), (1020, 2098), (1000, 1000), (128, 128)])
+def test_pruning_indices_bit_exact(M, N):
+    rng = np.random.default_rng(M + N)
+    B, H = 2, 3
+    lf = -np.abs(rng.normal(0.05, 0.08, size=(B, H, N))).astype(np.float32)
+    lam = np.cumsum(lf, axis=-1, dtype=np.float32)
+    thr = np.array([[-1.0, -5.0, -20.0], [0.0, -3.0, -1000.0]], dtype=np.float32)
+    for bm, bn in [(128, 128), (128, 64), (64, 64)]:
+        si, ei = ops.find_index(torch.from_numpy(lam).cuda(), torch.from_numpy(thr).cuda(), M, bm, bn, True, True)
+        assert np.array_equal(si.cpu().numpy(), orc.find_start_index(lam, thr, M, N, bm, bn))
+        assert np.array_equal(ei.cpu().numpy(), orc.find_end_index(lam, thr, M, N, bm, bn))
+
+
+def test_auto_threshold_identical_to_upstream_expression():
+    g = torch.Generator().manual_seed(16)
+    for dtype in (torch.bfloat16, torch.float16):
+        q = (torch.randn(2, 3, 333, 64, generator=g) * torch.rand(1, 3, 1, 1, generator=g) * 2).to(dtype)
+        k = torch.randn(2, 3, 333, 64, generator=g).to(dtype)
+        got_q = ops.max_row_norm(q.cuda()).cpu()
+        assert torch.equal(got_q, torch.linalg.vector_norm(q, dim=-1).max(dim=-1).values)
+        got_k = ops.max_row_norm(k.cuda()).cpu()
+        thr = (-(2 * (got_q * got_k * 0.125) + math.log(333)) + (-10)).float()
+        assert torch.equal(thr, orc.auto_threshold(q, k, 0.125))
+
+
+def test_pruned_attention_matches_block_oracle():
+    """Strong decay + "auto": most KV blocks are pruned; outputs and gradients match the
+    oracle that skips exactly the blocks named by the index arrays."""
+    B, H, T, D = 2, 2, 1024, 128
+    q, k, v, lf, do = _inputs(17, B, H, T, T, D, torch.bfloat16, mu=-1.0, sigma=1.5)
+    out, dq, dk, dv, dlf = _run(q, k, v, lf, do, thr="auto")
+    thr = orc.auto_threshold(q, k, D ** -0.5).numpy()
+    lam = orc.log_lambda(lf, None).numpy()
+    si = orc.find_start_index(lam, thr, T, T, 128, 128)
+    ei = orc.find_end_index(lam, thr, T, T, 128, 128)
+    assert orc.pruned_tile_fraction(si, T, T, 128, 128) > 0.3
+    r = orc.blockwise_fwd_bwd(q, k, v, lf, do, start_index=si, end_index=ei, low_precision_matmul=False)
+    for a, b in [(out, r["out"]), (dq, r["dq"]), (dk, r["dk"]), (dv, r["dv"])]:
+        _close(a, b, ATOL_BF16, RTOL_BF16)
+    _close(dlf, r["dlog_fgate"], 2 * ATOL_BF16, RTOL_BF16)
+
+
+# ----------------------------------------------- properties at the benchmark's full sizes
+def test_full_size_properties_config3():
+    """B=2, T=16384, H=24, D=64 (too big for the dense oracle): with v = 1 every non-empty
+    row outputs exactly 1; with dout = 1 the column sums of dv count the non-empty rows;
+    the gradient w.r.t. the first log gate vanishes; outputs are linear in v."""
+    B, H, T, D = 2, 24, 16384, 64
+    g = torch.Generator().manual_seed(1003)
+    dev = "cuda"
+    q = torch.randn(B, H, T, D, generator=g).bfloat16().to(dev)
+    k = torch.randn(B, H, T, D, generator=g).bfloat16().to(dev)
+    v1 = torch.randn(B, H, T, D, generator=g).bfloat16().to(dev)
+    lf = torch.nn.functional.logsigmoid(torch.randn(B, H, T, generator=g) + 4).to(dev).requires_grad_()
+    seq = torch.randint(0, 2048, (B,), generator=g).to(dev)
+    ones = torch.ones_like(v1).requires_grad_()
+    out = fox.forgetting_attention(q, k, ones, lf, head_first=True, seq_start=seq)
+    out.backward(torch.ones_like(out))
+    torch.cuda.synchronize()
+    _lib.check_status()
+    for b in range(B):
+        s = int(seq[b])
+        assert torch.all(out[b, :, :s] == 0)
+        assert torch.all((out[b, :, s:].float() - 1).abs() < 1e-2)
+        colsum = ones.grad[b].float().sum(dim=1)  # (H, D): sum_j dv_j = number of non-empty rows
+        assert torch.all((colsum - (T - s)).abs() < 1e-3 * T)
+    assert lf.grad[..., 0].abs().max().item() < 5e-2
+    v2 = torch.randn(B, H, T, D, generator=g).bfloat16().to(dev)
+    f = lambda vv: fox.forgetting_attention(q, k, vv, lf.detach(), head_first=True, seq_start=seq).float()
+    lin = (f(v1) + f(v2) - f((v1.float() + v2.float()).bfloat16())).abs().max().item()
+    assert lin < 8e-2

@@ -1,0 +1,151 @@
+"""CPU tests: the oracle (oracle/fox_oracle.py) against the golden fixtures that were
+produced by upstream's own Triton kernels (interpreter mode), plus its internal
+consistency.  No GPU needed."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import fox_oracle as orc
+
+# upstream's own known-answer tolerance (forgetting_attention.py:1416-1425): atol 1e-2, rtol 0, fp16
+ATOL = 1e-2
+
+
+def _err(a, b):
+    return (a.float() - b.float()).abs().max().item()
+
+
+def test_golden_fixtures_present():
+    from conftest import golden_names
+    assert len(golden_names()) >= 6
+
+
+def test_dense_oracle_matches_upstream_kernels(golden):
+    g = golden
+    out, dq, dk, dv, dlf = orc.dense_fwd_bwd(g["q"].float(), g["k"].float(), g["v"].float(), g["log_fgate"],
+                                             g["dout"].float(), g["seq_start"], g["sm_scale"], mask_gates=True)
+    # pruning (where on) removes at most exp(threshold) of the mass: same tolerance
+    assert _err(out, g["out"]) < ATOL
+    assert _err(dq, g["dq"]) < ATOL
+    assert _err(dk, g["dk"]) < ATOL
+    assert _err(dv, g["dv"]) < ATOL
+    assert _err(dlf, g["dlog_fgate"]) < ATOL
+
+
+def test_blockwise_oracle_matches_upstream_kernels(golden):
+    """The block-level restatement with pruning index arrays reproduces upstream's
+    outputs, log-normaliser and gradients (tighter than the dense one when pruning is on)."""
+    g = golden
+    B, H, M, D = g["q"].shape
+    N = g["k"].shape[2]
+    si = ei = None
+    if g["threshold"] is not None:
+        lam = orc.log_lambda(g["log_fgate"], g["seq_start"]).numpy()
+        si = orc.find_start_index(lam, g["threshold"].numpy(), M, N, 128, 128)
+        ei = orc.find_end_index(lam, g["threshold"].numpy(), M, N, 128, 128)
+    r = orc.blockwise_fwd_bwd(g["q"], g["k"], g["v"], g["log_fgate"], g["dout"], g["seq_start"], g["sm_scale"],
+                              start_index=si, end_index=ei)
+    assert _err(r["out"], g["out"]) < 2e-3
+    Lg = g["L"]
+    finite = torch.isfinite(Lg)
+    assert torch.equal(finite, torch.isfinite(r["L"]))
+    assert _err(r["L"][finite], Lg[finite]) < 2e-3
+    assert _err(r["dq"], g["dq"]) < 4e-3
+    assert _err(r["dk"], g["dk"]) < 4e-3
+    assert _err(r["dv"], g["dv"]) < 4e-3
+    assert _err(r["dlog_fgate"], g["dlog_fgate"]) < ATOL  # a sum over up to N terms of magnitude ~1
+
+
+def test_find_start_index_bit_exact(golden):
+    g = golden
+    if g["threshold"] is None:
+        pytest.skip("no pruning in this fixture")
+    B, H, M, D = g["q"].shape
+    N = g["k"].shape[2]
+    # upstream computes log_lambda with torch.cumsum on the masked gates: same call here
+    lam = orc.log_lambda(g["log_fgate"], g["seq_start"]).numpy()
+    si = orc.find_start_index(lam, g["threshold"].numpy(), M, N, 128, 128)
+    assert np.array_equal(si, g["start_index"].numpy())
+
+
+def test_some_fixture_actually_prunes():
+    from conftest import load_golden
+    assert int(load_golden("acp_thr_m10")["start_index"].max()) >= 128
+
+
+def test_index_scans_monotone_equivalence():
+    """With a non-increasing prefix the carried scans equal the per-tile predicate
+    keep(mb, nb) = lam[P + mb*BM] - lam[last col of nb] >= thr."""
+    rng = np.random.default_rng(0)
+    for (M, N, BM, BN) in [(512, 512, 128, 128), (1020, 2098, 128, 64), (1024, 2048, 64, 64), (500, 500, 32, 128)]:
+        lf = -np.abs(rng.normal(0.05, 0.05, size=(2, 3, N))).astype(np.float32)
+        lam = np.cumsum(lf, axis=-1, dtype=np.float32)
+        thr = np.array([[-1.0, -5.0, -20.0], [-0.5, -3.0, -1000.0]], dtype=np.float32)
+        si = orc.find_start_index(lam, thr, M, N, BM, BN)
+        ei = orc.find_end_index(lam, thr, M, N, BM, BN)
+        P = N - M
+        for b in range(2):
+            for h in range(3):
+                for mb in range(si.shape[-1]):
+                    row = lam[b, h, P + mb * BM]
+                    exp = 0
+                    while np.float32(row - lam[b, h, min(N - 1, exp + BN - 1)]) < thr[b, h]:
+                        exp += BN
+                    assert si[b, h, mb] == exp
+                assert np.all(np.diff(si[b, h]) >= 0) and np.all(np.diff(ei[b, h]) >= 0)
+                assert ei[b, h].max() <= M
+
+
+def test_auto_threshold_dtype_path():
+    """The automatic threshold is evaluated in the input dtype (bf16) and only then cast
+    to fp32 (upstream lines 95-104)."""
+    g = torch.Generator().manual_seed(0)
+    q = torch.randn(2, 3, 64, 64, generator=g).bfloat16()
+    k = torch.randn(2, 3, 64, 64, generator=g).bfloat16()
+    thr = orc.auto_threshold(q, k, 0.125)
+    assert thr.dtype == torch.float32 and thr.shape == (2, 3)
+    # every value is exactly representable in bf16
+    assert torch.equal(thr, thr.bfloat16().float())
+    ub = (q.float().norm(dim=-1).amax(-1) * k.float().norm(dim=-1).amax(-1) * 0.125)
+    assert torch.allclose(thr, -(2 * ub + math.log(64)) - 10, rtol=2e-2)
+
+
+def test_reverse_cumsum():
+    x = torch.randn(2, 3, 100)
+    ref = torch.flip(torch.cumsum(torch.flip(x, [-1]), -1), [-1])
+    assert torch.allclose(orc.reverse_cumsum(x), ref, atol=1e-5)
+
+
+def test_masked_prefix_ignores_gates_left_of_seq_start():
+    lf = -torch.rand(2, 2, 50)
+    ss = torch.tensor([0, 17])
+    lam = orc.log_lambda(lf, ss)
+    assert torch.all(lam[1, :, :17] == 0)
+    assert torch.allclose(lam[0], torch.cumsum(lf[0], -1))
+    lf2 = lf.clone()
+    lf2[1, :, :17] = -100.0
+    assert torch.equal(orc.log_lambda(lf2, ss), lam)
+
+
+def test_rowsum_of_ds_vanishes_in_exact_arithmetic():
+    """Softmax is shift invariant, so the query-side part of the log-gate gradient is
+    pure rounding residue; the blockwise oracle in fp32 shows it is tiny."""
+    g = torch.Generator().manual_seed(1)
+    q, k, v, do = [torch.randn(1, 1, 96, 64, generator=g) for _ in range(4)]
+    lf = torch.nn.functional.logsigmoid(torch.randn(1, 1, 96, generator=g))
+    r = orc.blockwise_fwd_bwd(q, k, v, lf, do, low_precision_matmul=False)
+    _, _, _, _, dlf = orc.dense_fwd_bwd(q, k, v, lf, do)
+    assert _err(r["dlog_fgate"], dlf) < 1e-4
+
+
+def test_norm_gate_reference_math():
+    g = torch.Generator().manual_seed(2)
+    x = torch.randn(2, 5, 4 * 64, generator=g)
+    gate = torch.randn(2, 5, 4 * 64, generator=g)
+    w = torch.rand(4 * 64, generator=g) + 0.5
+    y = orc.group_rmsnorm_gated(x, gate, w, 4, eps=1e-6)
+    xg = x.view(2, 5, 4, 64)
+    ref = (xg / xg.pow(2).mean(-1, keepdim=True).add(1e-6).sqrt()).reshape(2, 5, -1) * w * torch.sigmoid(gate)
+    assert torch.allclose(y, ref, atol=1e-5)
