@@ -48,6 +48,9 @@ _SIGNATURES = {
                              _F, _F, _F, c_float, _T4P, _F, _F]),
     "fox_attn_bwd": (c_int, [c_int, c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, c_int64, _T4P, _T4P, _T4P,
                              _T4P, _F, _F, _F, _F, _F, c_float, _F, _F, _F, _T4P, _T4P, _F]),
+    "fox_attn_bwd_noalloc": (c_int, [c_int, c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, c_int64, _T4P, _T4P,
+                                     _T4P, _T4P, _F, _F, _F, _F, _F, c_float, _T4P, _T4P, _T4P, _F, _F, _F]),
+    "fox_noalloc_scratch_floats": (c_int64, []),
     "fox_normgate_fwd": (c_int, [c_int, c_void_p, c_int, c_int64, c_int64, c_int64, _F, _F, _F, c_float, _F, _F]),
     "fox_normgate_bwd": (c_int, [c_int, c_void_p, c_int, c_int64, c_int64, c_int64, _F, _F, _F, _F, _F, _F, _F, _F, c_int64]),
 }

@@ -142,6 +142,24 @@ int fox_normgate_bwd(int device, void* stream, int dtype, int64_t tokens, int64_
                      const void* g, const float* w, const float* rstd, const void* dy, void* dx, void* dg,
                      float* dw_partial, int64_t n_partials);
 
+/* Backward attention that allocates nothing (no counterpart upstream, where torch allocates
+ * every buffer).  For hosts that cannot obtain device memory at call time -- the GPU was
+ * handed to their own arena at start-up, or their thread may not make a call that serialises
+ * the device as cudaMalloc/cudaFree do.  Same inputs as fox_attn_bwd; the fp32 dQ / query-side
+ * gate-gradient scratch lives in a fixed 64 MiB array inside the library (held by every GPU
+ * that loads it), so B*H*M*(D+1) must be <= fox_noalloc_scratch_floats() (2^24), else
+ * FOX_ERR_TOO_LARGE.  Also finishes the job: writes dq (input dtype), dk, dv, dlam_col (B,H,N)
+ * and dlog_fgate (B,H,N) fp32.  The scratch is shared by all calls on a device and is cleared
+ * on `stream` at the start of each call: calls that overlap on the GPU race.  The first call on
+ * a device resolves the array's address; make it before any stream capture. */
+int fox_attn_bwd_noalloc(int device, void* stream, int dtype, int64_t B, int64_t H, int64_t M, int64_t N,
+                         int64_t D, const fox_tensor4* q, const fox_tensor4* k, const fox_tensor4* v,
+                         const fox_tensor4* d_o, const float* log_lambda, const float* L, const float* delta,
+                         const int64_t* seq_start, const int64_t* end_index, float sm_scale,
+                         const fox_tensor4* dq, const fox_tensor4* dk, const fox_tensor4* dv, float* dlam_col,
+                         float* dlog_fgate, int32_t* status);
+int64_t fox_noalloc_scratch_floats(void);
+
 #ifdef __cplusplus
 }
 #endif
