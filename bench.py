@@ -40,12 +40,17 @@ WORKLOADS = {
     "cfg3": dict(B=2, T=16384, H=24, D=64, mu=4.0, sigma=1.0, seq=True, thr=None, head_scale=False, seed=1003),
     "cfg4": dict(B=4, T=16384, H=16, D=128, mu=-1.0, sigma=1.5, seq=False, thr=None, head_scale=True, seed=1004),
     "cfg4_acp": dict(B=4, T=16384, H=16, D=128, mu=-1.0, sigma=1.5, seq=False, thr="auto", head_scale=True, seed=1004),
+    # small cases for profiler captures: inputs (4 x 34 / 67 MB) exceed the 126 MB L2, kernels last a few ms
+    "prof_d64": dict(B=2, T=8192, H=16, D=64, mu=4.0, sigma=1.0, seq=True, thr=None, head_scale=False, seed=1005),
+    "prof_d128": dict(B=2, T=8192, H=16, D=128, mu=-1.0, sigma=1.5, seq=False, thr=None, head_scale=True, seed=1006),
 }
 DESCR = {
     "cfg2": "kernel-level op B4 T512 H12 D64 bf16",
     "cfg3": "long-context FoX-760M layer shape B2 T16384 H24 D64 bf16, gate logits N(4,1), seq_start U[0,2048)",
     "cfg4": "ACP stress shape B4 T16384 H16 D128 bf16, gate logits N(-1,1.5), pruning off",
     "cfg4_acp": "ACP stress shape B4 T16384 H16 D128 bf16, gate logits N(-1,1.5), adaptive_threshold=auto",
+    "prof_d64": "profiler-sized case B2 T8192 H16 D64 bf16 (cfg3 distributions)",
+    "prof_d128": "profiler-sized case B2 T8192 H16 D128 bf16 (cfg4 distributions, pruning off)",
 }
 
 
@@ -103,7 +108,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-lms", "100", "-i", str(self.index)], stdout=subprocess.PIPE,
+                                          "-lms", "50", "-i", str(self.index)], stdout=subprocess.PIPE,
                                          stderr=subprocess.DEVNULL, text=True)
         except Exception:
             self.proc = None
@@ -233,7 +238,7 @@ def run_ours(args, w, wname):
             dist.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(max(args.warmup, 3)):
+    for _ in range(args.warmup if args.no_e2e else max(args.warmup, 3)):
         step()
     barrier()
     _lib.check_status()
@@ -278,20 +283,22 @@ def run_ours(args, w, wname):
             hbuf.copy_(r, non_blocking=True)
 
     h2d = sum(host[n].numel() * host[n].element_size() for n in ("q", "k", "v", "log_fgate", "dout"))
-    e2e_step()
-    barrier()
-    d2h = sum(hb.numel() * hb.element_size() for hb in outs_host)
-    n_e2e = max(3, min(args.steps, 10))
-    barrier()
-    e0.record()
-    for _ in range(n_e2e):
+    e2e_val, d2h, n_e2e = None, 0, 0
+    if not args.no_e2e:
         e2e_step()
-    e1.record()
-    barrier()
-    t2 = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(t2, op=dist.ReduceOp.MAX)
-    e2e_val = world * flops / (float(t2.item()) / n_e2e * 1e-3) / 1e12
+        barrier()
+        d2h = sum(hb.numel() * hb.element_size() for hb in outs_host)
+        n_e2e = max(3, min(args.steps, 10))
+        barrier()
+        e0.record()
+        for _ in range(n_e2e):
+            e2e_step()
+        e1.record()
+        barrier()
+        t2 = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(t2, op=dist.ReduceOp.MAX)
+        e2e_val = world * flops / (float(t2.item()) / n_e2e * 1e-3) / 1e12
 
     if rank == 0:
         peaks = load_peaks()
@@ -349,6 +356,7 @@ def main():
     ap.add_argument("--workload", default="cfg3", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg (profiler runs)")
     args = ap.parse_args()
     w = WORKLOADS[args.workload]
     if args.impl == "reference":
