@@ -6,20 +6,25 @@
 // which recompute S and dP twice (seven products per pair).
 //
 // One CTA = one (batch, head, 128-row KV tile); it keeps K and V resident and
-// streams the query tiles from the causal diagonal downwards.
-//   warps 0-3 : thread t owns KV row t (TMEM lane t of S^T, dP^T, dK, dV) and,
-//               when draining dQ, query row t of the current tile
-//   warp 4    : TMA producer,  warp 5 : tcgen05.mma issuer
-// Per pair:  S^T = K Q^T,  dP^T = V dO^T            (smem x smem -> TMEM)
-//            P^T = 2^(S^T scale + bias - L)          (registers, written over S^T as 16-bit)
-//            dS^T = P^T (dP^T - delta)               (registers -> swizzled smem, 16-bit)
-//            dV += P^T dO   (TMEM x smem),  dK += dS^T Q   (smem x smem)
-//            dQ_tile = dS K | dS 1                   (smem x smem, fresh accumulator)
-// dQ tiles are added into an fp32 workspace with vector reductions; the extra 16
-// "ones" columns appended to K make the same product deliver rowsum(dS), i.e. the
-// query-side part of the log-gate gradient, built from exactly the rounded dS
-// values whose column sums form the key-side part (so the two cancel the way
-// they do upstream when the reverse prefix sum is taken).
+// streams the query tiles from the causal diagonal downwards.  448 threads:
+//   warps 0-7  : compute.  Thread (g = warp/4, r = tid%128) owns KV row r (TMEM lane r
+//                of S^T / dP^T) and the 64 query columns [64g, 64g+64) of the tile.
+//   warp  8    : TMA producer          warp 9 : tcgen05.mma issuer
+//   warps 10-13: dQ drain.  Thread owns one query row of the dQ tile accumulator,
+//                adds it into the fp32 workspace and stages the per-row vectors.
+// Per pair i (all products 128-wide, fp32 accumulation in TMEM):
+//   S^T = K Q^T ; dP^T = V dO^T                         (smem x smem)
+//   phase A: P^T = 2^(S^T c + (L_i-corrected bias))      -> 16-bit, written over S^T
+//   phase B: dS^T = P^T (dP^T - delta)                   -> 16-bit, over dP^T and to smem
+//   dV += P^T dO ; dK += dS^T Q                          (TMEM x smem)
+//   dQ_i = dS [K | 1]                                    (smem x smem, fresh accumulator)
+// The tensor pipe and the compute warps overlap: while phase B(i) runs the pipe does
+// dV(i) and S(i+1); while phase A(i+1) runs it does dK(i), dQ(i), dP(i+1).
+// A 16-column "ones" tile appended (through the descriptor's leading offset) to K makes
+// the dQ product also deliver rowsum(dS), the query-side log-gate gradient; at D=64 the
+// same tile appended to Q makes the dK product deliver colsum(dS), the key-side one.
+// Both sums are thus formed from the same rounded dS values and cancel in the reverse
+// prefix sum the way upstream's fp32 sums do.
 #include "fox_common.cuh"
 #include "fox_host.h"
 
@@ -27,7 +32,7 @@ namespace fox {
 
 constexpr int kBwdBM = FOX_BWD_BLOCK_M;
 constexpr int kBwdBN = FOX_BWD_BLOCK_N;
-constexpr int kBwdThreads = 192;
+constexpr int kBwdThreads = 448;
 constexpr float kLog2eB = 1.4426950408889634f;
 
 struct BwdParams {
@@ -42,13 +47,16 @@ struct BwdParams {
   void* dk; int64_t dk_sb, dk_sh, dk_st;
   void* dv; int64_t dv_sb, dv_sh, dv_st;
   int* status;
+  long long* trace;          // optional (debug builds of the kernel only): clock64 stamps of CTA (0,0,0)
   int H, M, N;
+  int ablate;                // timing experiments only: bit0 no dQ reductions, bit1 no exp/math, bit2 no dS smem stores
   float sm_scale, qk_scale;
 };
 
 enum BwdWaitSite {
-  kBSiteKV = 31, kBSiteQFull = 32, kBSiteQEmpty = 33, kBSiteSFull = 34, kBSitePds = 35, kBSiteDq = 36,
-  kBSiteVec = 37, kBSiteDone = 38, kBSiteDrained = 39, kBSiteDrain = 40
+  kBSiteKV = 31, kBSiteQFull = 32, kBSiteQEmpty = 33, kBSiteSFull = 34, kBSitePDone = 35, kBSiteDq = 36,
+  kBSiteVec = 37, kBSiteDone = 38, kBSiteDqFree = 39, kBSiteDOFull = 40, kBSiteDOEmpty = 41, kBSiteDpFull = 42,
+  kBSiteDsDone = 43, kBSiteDsmFree = 44, kBSiteColsum = 45, kBSiteStaged = 46, kBSiteStageFree = 47
 };
 
 __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
@@ -56,34 +64,49 @@ __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float 
                : "memory");
 }
 
-template <int D, bool kBf16, int STAGES>
+template <int D, bool kBf16, bool kTrace, int kPoly>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 fox_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                     const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
-                    const BwdParams p) {
+                    const __grid_constant__ CUtensorMap tmDQ, const BwdParams p) {
   constexpr int kTileBytes = 128 * D * 2;
   constexpr int kSub = D / 64;
   constexpr uint32_t kFmt = kBf16 ? 1u : 0u;
-  constexpr bool kAliasDQ = (D == 128);      // dQ accumulator shares columns with S^T / dP^T
+  constexpr bool kAliasDQ = (D == 128);     // dQ accumulator shares columns with S^T / dP^T
+  constexpr bool kColsumMMA = (D == 64);    // colsum(dS) from the dK product
+  constexpr int STQ = 2;
+  constexpr int STDO = (D == 64) ? 2 : 1;
+  constexpr int kDsBufs = (D == 64) ? 2 : 1;
+  constexpr int kStageSub = (D == 64) ? 2 : 1;  // 32-column fp32 sub-tiles of the dQ staging buffer
   constexpr uint32_t kTmemCols = 512;
-  constexpr uint32_t kColS = 0, kColDP = 128, kColDK = 256, kColDV = 256 + D;
-  constexpr uint32_t kColDQ = kAliasDQ ? 0 : 256 + 2 * D;
-  constexpr int kNdq = D + 16;               // dQ columns + rowsum columns
+  constexpr int kNdk = kColsumMMA ? D + 16 : D;
+  constexpr int kNdq = D + 16;
+  constexpr uint32_t kColS = 0, kColDP = 128, kColDK = 256, kColDV = 256 + kNdk;
+  constexpr uint32_t kColDQ = kAliasDQ ? 0 : kColDV + D;
+  static_assert(kAliasDQ || kColDQ + kNdq <= 512, "TMEM budget");
 
-  extern __shared__ uint8_t smem_raw[];
-  __shared__ uint64_t bar_kv, bar_s_full, bar_pds, bar_dq, bar_done, bar_drained;
-  __shared__ uint64_t bar_q_full[STAGES], bar_q_empty[STAGES], bar_vec[2];
-  __shared__ float s_e[2][kBwdBM], s_delta[2][kBwdBM];
+  // 1024-byte aligned by declaration: at D=128 the tiles use all but 3 KiB of the 227 KiB a CTA may
+  // have, so there is no room for a manual alignment slack.
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  __shared__ uint64_t bar_kv, bar_s_full, bar_dp_full, bar_p_done, bar_ds_done, bar_dq_full, bar_dq_free, bar_done,
+      bar_colsum;
+  __shared__ uint64_t bar_q_full[STQ], bar_q_empty[STQ], bar_do_full[STDO], bar_do_empty[STDO], bar_vec[2],
+      bar_dsm_free[2], bar_staged, bar_stage_free;
+  __shared__ __align__(16) float s_e[2][kBwdBM];      // read as float4
+  __shared__ __align__(16) float s_delta[2][kBwdBM];
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
 
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* sK = smem;                         // kSub sub-tiles, then the "ones" sub-tile
+  uint8_t* smem = smem_raw;
+  // The "ones" tile directly follows K (it is K's next 64-column block for the dQ product) and
+  // lies above the Q stages (whose descriptors reach it through their leading-dimension offset).
+  uint8_t* sQ = smem;
+  uint8_t* sDO = sQ + STQ * kTileBytes;
+  uint8_t* sK = sDO + STDO * kTileBytes;
   uint8_t* sOnes = sK + kTileBytes;
   uint8_t* sV = sOnes + 16384;
-  uint8_t* sdS = sV + kTileBytes;             // [128 kv][128 q] as two 64-wide sub-tiles
-  uint8_t* sQ = sdS + 32768;
-  uint8_t* sDO = sQ + STAGES * kTileBytes;
+  uint8_t* sdS = sV + kTileBytes;                 // kDsBufs x [128 kv][128 q] (two 64-wide sub-tiles each)
+  uint8_t* sStage = sdS + kDsBufs * 32768;        // kStageSub x [128 q][32 fp32], 128-byte swizzled, for the dQ reduction
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int nb = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
@@ -108,19 +131,21 @@ fox_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     abort_flag = 0;
     mbar_init(&bar_kv, 1);
     mbar_init(&bar_s_full, 1);
-    mbar_init(&bar_pds, 128);
-    mbar_init(&bar_dq, 1);
+    mbar_init(&bar_dp_full, 1);
+    mbar_init(&bar_p_done, 256);
+    mbar_init(&bar_ds_done, 256);
+    mbar_init(&bar_dq_full, 1);
+    mbar_init(&bar_dq_free, 128);
     mbar_init(&bar_done, 1);
-    mbar_init(&bar_drained, 128);
-    mbar_init(&bar_vec[0], 128);
-    mbar_init(&bar_vec[1], 128);
-    for (int s = 0; s < STAGES; ++s) {
-      mbar_init(&bar_q_full[s], 1);
-      mbar_init(&bar_q_empty[s], 1);
-    }
+    mbar_init(&bar_colsum, 128);
+    for (int s = 0; s < STQ; ++s) { mbar_init(&bar_q_full[s], 1); mbar_init(&bar_q_empty[s], 1); }
+    for (int s = 0; s < STDO; ++s) { mbar_init(&bar_do_full[s], 1); mbar_init(&bar_do_empty[s], 1); }
+    for (int s = 0; s < 2; ++s) { mbar_init(&bar_vec[s], 128); mbar_init(&bar_dsm_free[s], 1); }
+    mbar_init(&bar_staged, 128);
+    mbar_init(&bar_stage_free, 1);
     mbar_fence_init();
   }
-  if (warp == 4) {
+  if (warp == 8) {
     tmem_alloc(&tmem_slot, kTmemCols);
     tmem_relinquish();
   }
@@ -138,268 +163,450 @@ fox_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   tc_fence_after();
   const uint32_t tbase = tmem_slot;
   volatile int* abortp = &abort_flag;
+  // debug time stamps: trace[(role * 64 + event) * 16 + tile] for the first 16 tiles of CTA (0,0,0)
+  auto stamp = [&](int role, int event, int it) {
+    if (kTrace && p.trace && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0 && it < 16)
+      p.trace[(role * 8 + event) * 16 + it] = clock64();
+  };
 
-  if (warp == 4) {
-    // ===================== TMA producer =====================
-    if (lane == 0 && n_tiles > 0) {
-      tma_prefetch_desc(&tmQ);
-      tma_prefetch_desc(&tmK);
-      tma_prefetch_desc(&tmV);
-      tma_prefetch_desc(&tmDO);
-      mbar_expect_tx(&bar_kv, 2 * kTileBytes);
-#pragma unroll
-      for (int s = 0; s < kSub; ++s) {
-        tma_load_4d(sK + s * 16384, &tmK, &bar_kv, s * 64, nb * kBwdBN, h, b);
-        tma_load_4d(sV + s * 16384, &tmV, &bar_kv, s * 64, nb * kBwdBN, h, b);
-      }
-      int issued = 0;
-      for (int it = 0; it < n_tiles; ++it) {
-        const int mb = mb_lo + it;
-        const int st = it % STAGES;
-        const uint32_t ph = (it / STAGES) & 1;
-        if (!mbar_wait(&bar_q_empty[st], ph ^ 1, abortp, p.status, kBSiteQEmpty, it)) break;
-        mbar_expect_tx(&bar_q_full[st], 2 * kTileBytes);
+  if (warp == 8) {
+    // ===================== TMA producer (whole warp converged, one elected lane issues) =====================
+    if (n_tiles > 0) {
+      if (elect_one()) {
+        tma_prefetch_desc(&tmQ);
+        tma_prefetch_desc(&tmK);
+        tma_prefetch_desc(&tmV);
+        tma_prefetch_desc(&tmDO);
+        mbar_expect_tx(&bar_kv, 2 * kTileBytes);
 #pragma unroll
         for (int s = 0; s < kSub; ++s) {
-          tma_load_4d(sQ + st * kTileBytes + s * 16384, &tmQ, &bar_q_full[st], s * 64, mb * kBwdBM, h, b);
-          tma_load_4d(sDO + st * kTileBytes + s * 16384, &tmDO, &bar_q_full[st], s * 64, mb * kBwdBM, h, b);
+          tma_load_4d(sK + s * 16384, &tmK, &bar_kv, s * 64, nb * kBwdBN, h, b);
+          tma_load_4d(sV + s * 16384, &tmV, &bar_kv, s * 64, nb * kBwdBN, h, b);
         }
-        issued = it + 1;
       }
-      if (*abortp) {
+      __syncwarp();
+      int issued_q = 0, issued_do = 0;
+      for (int it = 0; it < n_tiles; ++it) {
+        const int mb = mb_lo + it;
+        {
+          const int st = it % STQ;
+          const uint32_t ph = (it / STQ) & 1;
+          if (!mbar_wait_warp(&bar_q_empty[st], ph ^ 1, abortp, p.status, kBSiteQEmpty, it)) break;
+          if (elect_one()) {
+            mbar_expect_tx(&bar_q_full[st], kTileBytes);
+#pragma unroll
+            for (int s = 0; s < kSub; ++s)
+              tma_load_4d(sQ + st * kTileBytes + s * 16384, &tmQ, &bar_q_full[st], s * 64, mb * kBwdBM, h, b);
+          }
+          __syncwarp();
+          issued_q = it + 1;
+        }
+        {
+          const int st = it % STDO;
+          const uint32_t ph = (it / STDO) & 1;
+          if (!mbar_wait_warp(&bar_do_empty[st], ph ^ 1, abortp, p.status, kBSiteDOEmpty, it)) break;
+          if (elect_one()) {
+            mbar_expect_tx(&bar_do_full[st], kTileBytes);
+#pragma unroll
+            for (int s = 0; s < kSub; ++s)
+              tma_load_4d(sDO + st * kTileBytes + s * 16384, &tmDO, &bar_do_full[st], s * 64, mb * kBwdBM, h, b);
+          }
+          __syncwarp();
+          issued_do = it + 1;
+        }
+      }
+      if (*abortp && lane == 0) {
         // error path only: let the copies already in flight land before the CTA retires
         const long long t0 = clock64();
         while (!mbar_try_wait(&bar_kv, 0) && clock64() - t0 < 200000000LL) {
         }
-        for (int it = max(issued - STAGES, 0); it < issued; ++it) {
-          const int st = it % STAGES;
-          const uint32_t ph = (it / STAGES) & 1;
-          while (!mbar_try_wait(&bar_q_full[st], ph) && clock64() - t0 < 200000000LL) {
+        for (int it = max(issued_q - STQ, 0); it < issued_q; ++it)
+          while (!mbar_try_wait(&bar_q_full[it % STQ], (it / STQ) & 1) && clock64() - t0 < 200000000LL) {
           }
-        }
+        for (int it = max(issued_do - STDO, 0); it < issued_do; ++it)
+          while (!mbar_try_wait(&bar_do_full[it % STDO], (it / STDO) & 1) && clock64() - t0 < 200000000LL) {
+          }
       }
     }
-  } else if (warp == 5) {
-    // ===================== MMA issuer =====================
-    if (lane == 0 && n_tiles > 0) {
+  } else if (warp == 9) {
+    // ===================== MMA issuer (whole warp converged, one elected lane issues) =====================
+    if (n_tiles > 0) {
       constexpr uint32_t idS = umma_idesc(kFmt, 128, 128, 0, 0);
-      constexpr uint32_t idKV = umma_idesc(kFmt, 128, D, 0, 1);
+      constexpr uint32_t idDV = umma_idesc(kFmt, 128, D, 0, 1);
+      constexpr uint32_t idDK = umma_idesc(kFmt, 128, kNdk, 0, 1);
       constexpr uint32_t idDQ = umma_idesc(kFmt, 128, kNdq, 1, 1);
-      const uint32_t k0 = smem_u32(sK), v0 = smem_u32(sV), ds0 = smem_u32(sdS);
-      bool ok = mbar_wait(&bar_kv, 0, abortp, p.status, kBSiteKV);
+      // Operand descriptors are built once; inside the loops only the start-address field moves
+      // (the issuing thread must stay far ahead of the tensor pipe, so its instruction count matters).
+      const uint32_t q_base = smem_u32(sQ), do_base = smem_u32(sDO), ones0 = smem_u32(sOnes);
+      const uint64_t dK_k = umma_desc_kmajor(smem_u32(sK));            // S^T : A = K
+      const uint64_t dV_k = umma_desc_kmajor(smem_u32(sV));            // dP^T: A = V
+      const uint64_t dK_mn = umma_desc_mnmajor(smem_u32(sK), 16384);   // dQ  : B = [K | 1]
+      const uint64_t dQ_k = umma_desc_kmajor(q_base);                  // S^T : B = Q (stage 0)
+      const uint64_t dDO_k = umma_desc_kmajor(do_base);                // dP^T: B = dO (stage 0)
+      const uint64_t dDO_mn = umma_desc_mnmajor(do_base, 16384);       // dV  : B = dO (stage 0)
+      const uint64_t dDS_mn = umma_desc_mnmajor(smem_u32(sdS), 16384); // dQ  : A = dS (buffer 0)
+      // dK: B = [Q | 1]; the ones tile is reached through the leading offset, which depends on the stage
+      uint64_t dQ_mn[STQ];
+#pragma unroll
+      for (int s_ = 0; s_ < STQ; ++s_)
+        dQ_mn[s_] = umma_desc_mnmajor(q_base + s_ * kTileBytes, kColsumMMA ? (ones0 - (q_base + s_ * kTileBytes)) : 16384u);
+      auto issue_S = [&](int it) -> bool {
+        const int st = it % STQ;
+        if (!mbar_wait_warp(&bar_q_full[st], (it / STQ) & 1, abortp, p.status, kBSiteQFull, it)) return false;
+        tc_fence_after();
+        const uint64_t bq = umma_desc_advance(dQ_k, st * kTileBytes);
+        if (elect_one()) {
+#pragma unroll
+          for (int kk = 0; kk < D / 16; ++kk) {
+            const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
+            mma_ss_raw(tbase + kColS, umma_desc_advance(dK_k, off), umma_desc_advance(bq, off), idS, kk > 0);
+          }
+          tc_commit_raw(&bar_s_full);
+        }
+        __syncwarp();
+        return true;
+      };
+      auto issue_dP = [&](int it) -> bool {
+        const int st = it % STDO;
+        if (!mbar_wait_warp(&bar_do_full[st], (it / STDO) & 1, abortp, p.status, kBSiteDOFull, it)) return false;
+        tc_fence_after();
+        const uint64_t bdo = umma_desc_advance(dDO_k, st * kTileBytes);
+        if (elect_one()) {
+#pragma unroll
+          for (int kk = 0; kk < D / 16; ++kk) {
+            const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
+            mma_ss_raw(tbase + kColDP, umma_desc_advance(dV_k, off), umma_desc_advance(bdo, off), idS, kk > 0);
+          }
+          tc_commit_raw(&bar_dp_full);
+        }
+        __syncwarp();
+        return true;
+      };
+      bool ok = mbar_wait_warp(&bar_kv, 0, abortp, p.status, kBSiteKV);
+      ok = ok && issue_S(0) && issue_dP(0);
       for (int it = 0; it < n_tiles && ok; ++it) {
-        const int st = it % STAGES;
-        const uint32_t ph = (it / STAGES) & 1;
-        ok = mbar_wait(&bar_q_full[st], ph, abortp, p.status, kBSiteQFull, it);
-        if (!ok) break;
-        if (kAliasDQ && it > 0) {
-          ok = mbar_wait(&bar_drained, (it - 1) & 1, abortp, p.status, kBSiteDrained, it);
-          if (!ok) break;
-        }
-        tc_fence_after();
-        const uint32_t q0 = smem_u32(sQ + st * kTileBytes), do0 = smem_u32(sDO + st * kTileBytes);
-#pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
-          mma_ss(tbase + kColS, umma_desc_kmajor(k0 + off), umma_desc_kmajor(q0 + off), idS, kk > 0);
-        }
-#pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
-          mma_ss(tbase + kColDP, umma_desc_kmajor(v0 + off), umma_desc_kmajor(do0 + off), idS, kk > 0);
-        }
-        tc_commit(&bar_s_full);
-        ok = mbar_wait(&bar_pds, it & 1, abortp, p.status, kBSitePds, it);
-        if (!ok) break;
-        tc_fence_after();
         const uint32_t acc = it > 0 ? 1u : 0u;
+        const uint64_t bdo_mn = umma_desc_advance(dDO_mn, (it % STDO) * kTileBytes);
+        const uint64_t bq_mn = dQ_mn[it % STQ];
+        const uint64_t ads_mn = umma_desc_advance(dDS_mn, (it % kDsBufs) * 32768);
+        // ---- dV += P^T dO (P^T in TMEM: query columns [0,64) at S columns 0.., [64,128) at 64..) ----
+        stamp(0, 0, it);
+        ok = mbar_wait_warp(&bar_p_done, it & 1, abortp, p.status, kBSitePDone, it);
+        if (!ok) break;
+        stamp(0, 1, it);
+        tc_fence_after();
+        if (elect_one()) {
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk)   // dV += P^T dO
-          mma_ts(tbase + kColDV, tbase + kColS + kk * 8, umma_desc_mnmajor(do0 + kk * 2048, 16384), idKV,
-                 acc | (kk > 0));
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk) { // dK += dS^T Q
-          const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
-          mma_ss(tbase + kColDK, umma_desc_kmajor(ds0 + off), umma_desc_mnmajor(q0 + kk * 2048, 16384), idKV,
-                 acc | (kk > 0));
+          for (int kk = 0; kk < 8; ++kk)
+            mma_ts_raw(tbase + kColDV, tbase + kColS + (kk >> 2) * 64 + (kk & 3) * 8,
+                       umma_desc_advance(bdo_mn, kk * 2048), idDV, acc | (kk > 0));
+          tc_commit_raw(&bar_do_empty[it % STDO]);
         }
+        __syncwarp();
+        if (!kAliasDQ && it + 1 < n_tiles) {
+          ok = issue_S(it + 1);  // overwrites P^T(it): ordered behind dV(it) in the tensor pipe
+          if (!ok) break;
+          stamp(0, 7, it);
+        }
+        // ---- dK += dS^T [Q | 1] ----
+        stamp(0, 2, it);
+        ok = mbar_wait_warp(&bar_ds_done, it & 1, abortp, p.status, kBSiteDsDone, it);
+        if (!ok) break;
+        stamp(0, 3, it);
+        tc_fence_after();
+        if (elect_one()) {
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk)   // dQ_tile = dS [K | 1]
-          mma_ss(tbase + kColDQ, umma_desc_mnmajor(ds0 + kk * 2048, 16384),
-                 umma_desc_mnmajor(k0 + kk * 2048, 16384), idDQ, kk > 0);
-        tc_commit(&bar_dq);
-        tc_commit(&bar_q_empty[st]);
+          for (int kk = 0; kk < 8; ++kk)
+            mma_ts_raw(tbase + kColDK, tbase + kColDP + (kk >> 2) * 64 + (kk & 3) * 8,
+                       umma_desc_advance(bq_mn, kk * 2048), idDK, acc | (kk > 0));
+        }
+        __syncwarp();
+        // ---- dQ_tile = dS [K | 1] ----
+        if (it > 0) {
+          ok = mbar_wait_warp(&bar_dq_free, (it - 1) & 1, abortp, p.status, kBSiteDqFree, it);
+          if (!ok) break;
+          tc_fence_after();
+        }
+        if (elect_one()) {
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk)
+            mma_ss_raw(tbase + kColDQ, umma_desc_advance(ads_mn, kk * 2048), umma_desc_advance(dK_mn, kk * 2048),
+                       idDQ, kk > 0);
+          tc_commit_raw(&bar_dq_full);
+          tc_commit_raw(&bar_dsm_free[it % kDsBufs]);
+          tc_commit_raw(&bar_q_empty[it % STQ]);
+        }
+        __syncwarp();
+        stamp(0, 4, it);
+        if (it + 1 < n_tiles) {
+          if (kAliasDQ) {
+            // the dQ tile sits on the S^T / dP^T columns: wait until it has been drained
+            ok = mbar_wait_warp(&bar_dq_free, it & 1, abortp, p.status, kBSiteDqFree, it);
+            if (!ok) break;
+            tc_fence_after();
+            ok = issue_S(it + 1);
+            if (!ok) break;
+          }
+          stamp(0, 5, it);
+          ok = issue_dP(it + 1);  // overwrites dS^T(it): ordered behind dK(it)
+          if (!ok) break;
+          stamp(0, 6, it);
+        }
       }
       if (ok) tc_commit(&bar_done);
     }
+  } else if (warp >= 10) {
+    // ===================== dQ drain + per-row vectors =====================
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;  // query row inside the tile == TMEM lane
+    const uint32_t tDQ = tbase + (static_cast<uint32_t>(quarter * 32) << 16) + kColDQ;
+    const float* lam = p.lam + bh * N;
+    auto stage_vec = [&](int it) {
+      const int i = (mb_lo + it) * kBwdBM + r;
+      float e = -INFINITY, dl = 0.f;
+      if (i < M) {
+        const float Li = p.L[bh * M + i];
+        e = (Li == -INFINITY) ? -INFINITY : (lam[P + i] - Li) * kLog2eB;
+        dl = p.delta[bh * M + i];
+      }
+      s_e[it & 1][r] = e;
+      s_delta[it & 1][r] = dl;
+      mbar_arrive(&bar_vec[it & 1]);
+    };
+    if (n_tiles > 0) stage_vec(0);
+    bool ok = true;
+    for (int it = 0; it < n_tiles; ++it) {
+      // buffer (it+1)&1 was last read by phase B(it-1), which finished before dQ(it-1) was issued
+      if (it + 1 < n_tiles) stage_vec(it + 1);
+      if (warp == 10) stamp(1, 0, it);
+      ok = mbar_wait_warp(&bar_dq_full, it & 1, abortp, p.status, kBSiteDq, it);
+      if (!ok) break;
+      if (warp == 10) stamp(1, 1, it);
+      tc_fence_after();
+      const int i = (mb_lo + it) * kBwdBM + r;
+      // The dQ tile goes TMEM -> registers -> swizzled shared memory -> one TMA add-reduction per
+      // 32-column sub-tile into the fp32 workspace (the TMA unit issues the L2 reductions; rows past M
+      // are clipped by the tensor map).  The accumulator is released as soon as it has been read.
+      uint32_t rs[16];
+      tmem_ld16(tDQ + D, rs);  // rowsum(dS) sits in the column after the dQ columns
+#pragma unroll
+      for (int round = 0; round < D / (32 * kStageSub); ++round) {
+        const int n_round = it * (D / (32 * kStageSub)) + round;
+        if (n_round > 0) {
+          ok = mbar_wait_warp(&bar_stage_free, (n_round - 1) & 1, abortp, p.status, kBSiteStageFree, it);
+          if (!ok) break;
+        }
+#pragma unroll
+        for (int sub = 0; sub < kStageSub; ++sub) {
+          uint32_t v[32];
+          tmem_ld32(tDQ + (round * kStageSub + sub) * 32, v);
+          tmem_ld_wait();
+          uint8_t* srow = sStage + sub * 16384 + r * 128;
+#pragma unroll
+          for (int q4 = 0; q4 < 8; ++q4)
+            *reinterpret_cast<uint4*>(srow + ((q4 ^ (r & 7)) << 4)) =
+                make_uint4(v[q4 * 4], v[q4 * 4 + 1], v[q4 * 4 + 2], v[q4 * 4 + 3]);
+        }
+        if (round == D / (32 * kStageSub) - 1) {
+          tc_fence_before();
+          mbar_arrive(&bar_dq_free);
+        }
+        fence_proxy_async_smem();
+        mbar_arrive(&bar_staged);
+        if (warp == 10) {
+          ok = mbar_wait_warp(&bar_staged, n_round & 1, abortp, p.status, kBSiteStaged, it);
+          if (!ok) break;
+          if (elect_one()) {
+            if (!(p.ablate & 1)) {
+#pragma unroll
+              for (int sub = 0; sub < kStageSub; ++sub)
+                tma_reduce_add_4d(&tmDQ, sStage + sub * 16384, (round * kStageSub + sub) * 32,
+                                  (mb_lo + it) * kBwdBM, h, b);
+              tma_store_commit();
+              tma_store_wait_read<0>();
+            }
+            mbar_arrive(&bar_stage_free);
+          }
+          __syncwarp();
+        }
+      }
+      if (!ok) break;
+      if (warp == 10) stamp(1, 2, it);
+      if (i < M) atomicAdd(p.dlam_row + bh * M + i, __uint_as_float(rs[0]));
+    }
+    if (warp == 10) tma_store_wait_all<0>();
   } else {
     // ===================== compute warps =====================
-    const int j = nb * kBwdBN + tid;  // KV row owned by this thread
+    const int g = warp >> 2;              // column half of the query tile
+    const int r = tid & 127;              // KV row inside the tile == TMEM lane
+    const int j = nb * kBwdBN + r;
     const bool j_ok = (j < N) && (j >= seq0);
     const float* lam = p.lam + bh * N;
-    const float b_j = (j < N) ? lam[j] * kLog2eB : 0.f;
-    const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+    // an invalid KV row gets b_j = +inf, i.e. probability 0 everywhere
+    const float b_j = j_ok ? lam[j] * kLog2eB : INFINITY;
+    const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const uint32_t tS = tbase + lane_base + kColS, tDP = tbase + lane_base + kColDP;
-    const uint32_t tDQ = tbase + lane_base + kColDQ;
     float colsum = 0.f;
     bool ok = true;
 
-    float e_next = -INFINITY, delta_next = 0.f;
-    if (n_tiles > 0) {
-      const int i = mb_lo * kBwdBM + tid;
-      if (i < M) {
-        const float Li = p.L[bh * M + i];
-        e_next = (Li == -INFINITY) ? -INFINITY : (lam[P + i] - Li) * kLog2eB;
-        delta_next = p.delta[bh * M + i];
-      }
-    }
     for (int it = 0; it < n_tiles; ++it) {
       const int mb = mb_lo + it;
-      s_e[it & 1][tid] = e_next;
-      s_delta[it & 1][tid] = delta_next;
-      mbar_arrive(&bar_vec[it & 1]);
-      if (it + 1 < n_tiles) {
-        const int i = (mb + 1) * kBwdBM + tid;
-        e_next = -INFINITY;
-        delta_next = 0.f;
-        if (i < M) {
-          const float Li = p.L[bh * M + i];
-          e_next = (Li == -INFINITY) ? -INFINITY : (lam[P + i] - Li) * kLog2eB;
-          delta_next = p.delta[bh * M + i];
-        }
-      }
       ok = mbar_wait(&bar_vec[it & 1], (it >> 1) & 1, abortp, p.status, kBSiteVec, it);
       ok = mbar_wait(&bar_s_full, it & 1, abortp, p.status, kBSiteSFull, it) && ok;
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      // first query column of this tile this KV row may attend from (causal)
-      const int c_min = j_ok ? max(j - P - mb * kBwdBM, 0) : kBwdBM;
-      const float4* e4 = reinterpret_cast<const float4*>(s_e[it & 1]);
-      const float4* d4 = reinterpret_cast<const float4*>(s_delta[it & 1]);
+      stamp(6 + warp, 0, it);
+      // first query column of this tile this KV row may be attended from (causal)
+      const int c_min = j - P - mb * kBwdBM;
+      const bool diag = (nb * kBwdBN + kBwdBN - 1 - P - mb * kBwdBM) > 0;
+      float pf[64];
+      // ---------------- phase A: probabilities ----------------
 #pragma unroll
-      for (int ch = 0; ch < 4; ++ch) {
-        uint32_t sreg[32], dpreg[32], pk[16], dsk[16];
-        tmem_ld32(tS + ch * 32, sreg);
-        tmem_ld32(tDP + ch * 32, dpreg);
+      for (int ch = 0; ch < 2; ++ch) {
+        const int col0 = g * 64 + ch * 32;
+        uint32_t sreg[32], pk[16];
+        tmem_ld32(tS + col0, sreg);
         tmem_ld_wait();
+        const float4* e4 = reinterpret_cast<const float4*>(&s_e[it & 1][col0]);
 #pragma unroll
         for (int c4 = 0; c4 < 8; ++c4) {
-          const float4 ev = e4[ch * 8 + c4];
-          const float4 dv = d4[ch * 8 + c4];
+          const float4 ev = e4[c4];
           const float es[4] = {ev.x, ev.y, ev.z, ev.w};
-          const float dl[4] = {dv.x, dv.y, dv.z, dv.w};
-          float pv[4], dsv[4];
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
-            const int c = ch * 32 + c4 * 4 + e;
-            float x = fmaf(__uint_as_float(sreg[c4 * 4 + e]), p.qk_scale, es[e]) - b_j;
-            float pe = fast_exp2(x);
-            pe = (c >= c_min) ? pe : 0.f;
-            pv[e] = pe;
-            dsv[e] = pe * (__uint_as_float(dpreg[c4 * 4 + e]) - dl[e]);
+            const float x = fmaf(__uint_as_float(sreg[c4 * 4 + e]), p.qk_scale, es[e]) - b_j;
+            float pe = (p.ablate & 2) ? x : ((kPoly == 1 || (kPoly == 2 && (e & 1))) ? exp2_poly(x) : fast_exp2(x));
+            if (diag) pe = (col0 + c4 * 4 + e >= c_min) ? pe : 0.f;
+            pf[ch * 32 + c4 * 4 + e] = pe;
           }
-          pk[c4 * 2] = pack2<kBf16>(pv[0], pv[1]);
-          pk[c4 * 2 + 1] = pack2<kBf16>(pv[2], pv[3]);
+          pk[c4 * 2] = pack2<kBf16>(pf[ch * 32 + c4 * 4], pf[ch * 32 + c4 * 4 + 1]);
+          pk[c4 * 2 + 1] = pack2<kBf16>(pf[ch * 32 + c4 * 4 + 2], pf[ch * 32 + c4 * 4 + 3]);
+        }
+        tmem_st16(tS + g * 64 + ch * 16, pk);  // inside this warpgroup's own (already loaded) S columns
+      }
+      tmem_st_wait();
+      tc_fence_before();
+      mbar_arrive(&bar_p_done);
+      stamp(6 + warp, 1, it);
+
+      // ---------------- phase B: dS ----------------
+      ok = mbar_wait(&bar_dp_full, it & 1, abortp, p.status, kBSiteDpFull, it);
+      if (it >= kDsBufs)
+        ok = mbar_wait(&bar_dsm_free[it % kDsBufs], ((it / kDsBufs) - 1) & 1, abortp, p.status, kBSiteDsmFree, it) && ok;
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      stamp(6 + warp, 2, it);
+      uint8_t* drow = sdS + (it % kDsBufs) * 32768 + g * 16384 + r * 128;
+#pragma unroll
+      for (int ch = 0; ch < 2; ++ch) {
+        const int col0 = g * 64 + ch * 32;
+        uint32_t dpreg[32], dsk[16];
+        tmem_ld32(tDP + col0, dpreg);
+        tmem_ld_wait();
+        const float4* d4 = reinterpret_cast<const float4*>(&s_delta[it & 1][col0]);
+#pragma unroll
+        for (int c4 = 0; c4 < 8; ++c4) {
+          const float4 dv4 = d4[c4];
+          const float dl[4] = {dv4.x, dv4.y, dv4.z, dv4.w};
+          float dsv[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e)
+            dsv[e] = pf[ch * 32 + c4 * 4 + e] * (__uint_as_float(dpreg[c4 * 4 + e]) - dl[e]);
           const uint32_t d01 = pack2<kBf16>(dsv[0], dsv[1]), d23 = pack2<kBf16>(dsv[2], dsv[3]);
           dsk[c4 * 2] = d01;
           dsk[c4 * 2 + 1] = d23;
-          const float2 r01 = unpack2<kBf16>(d01), r23 = unpack2<kBf16>(d23);
-          colsum += (r01.x + r01.y) + (r23.x + r23.y);
+          if (!kColsumMMA) {
+            const float2 r01 = unpack2<kBf16>(d01), r23 = unpack2<kBf16>(d23);
+            colsum += (r01.x + r01.y) + (r23.x + r23.y);
+          }
         }
-        tmem_st16(tS + ch * 16, pk);  // columns [16 ch, 16 ch + 16) <- 32 probabilities; S chunk already in registers
-        // dS^T row `tid`, columns [32 ch, 32 ch + 32): four 16-byte chunks of sub-tile ch/2
-        uint8_t* drow = sdS + (ch >> 1) * 16384 + tid * 128;
+        tmem_st16(tDP + g * 64 + ch * 16, dsk);
+        if (!(p.ablate & 4))
 #pragma unroll
         for (int q4 = 0; q4 < 4; ++q4) {
-          const int cj = (ch & 1) * 4 + q4;
-          *reinterpret_cast<uint4*>(drow + ((cj ^ (tid & 7)) << 4)) =
+          const int cj = ch * 4 + q4;
+          *reinterpret_cast<uint4*>(drow + ((cj ^ (r & 7)) << 4)) =
               make_uint4(dsk[q4 * 4], dsk[q4 * 4 + 1], dsk[q4 * 4 + 2], dsk[q4 * 4 + 3]);
         }
       }
       tmem_st_wait();
       fence_proxy_async_smem();
       tc_fence_before();
-      mbar_arrive(&bar_pds);
-
-      // ---- drain dQ tile: thread t now owns query row mb*128 + t ----
-      ok = mbar_wait(&bar_dq, it & 1, abortp, p.status, kBSiteDq, it);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      tc_fence_after();
-      {
-        const int i = mb * kBwdBM + tid;
-        float* dst = p.dq_accum + (bh * M + i) * D;
-#pragma unroll
-        for (int c = 0; c < D; c += 32) {
-          uint32_t r[32];
-          tmem_ld32(tDQ + c, r);
-          tmem_ld_wait();
-          if (i < M) {
-#pragma unroll
-            for (int q4 = 0; q4 < 8; ++q4)
-              red_add_v4(dst + c + q4 * 4, __uint_as_float(r[q4 * 4]), __uint_as_float(r[q4 * 4 + 1]),
-                         __uint_as_float(r[q4 * 4 + 2]), __uint_as_float(r[q4 * 4 + 3]));
-          }
-        }
-        uint32_t rs[16];
-        tmem_ld16(tDQ + D, rs);
-        tmem_ld_wait();
-        if (i < M) atomicAdd(p.dlam_row + bh * M + i, __uint_as_float(rs[0]));
-      }
-      if (kAliasDQ) {
-        tc_fence_before();
-        mbar_arrive(&bar_drained);
-      }
+      mbar_arrive(&bar_ds_done);
+      stamp(6 + warp, 3, it);
     }
 
-    // ---- epilogue: dK, dV, key-side log-gate gradient ----
+    // ---- epilogue: warpgroup 0 writes dK (and the key-side gate gradient), warpgroup 1 writes dV ----
     if (n_tiles > 0 && ok) {
       ok = mbar_wait(&bar_done, 0, abortp, p.status, kBSiteDone);
       ok = __all_sync(0xffffffffu, ok);
     }
+    if (!kColsumMMA && ok) {
+      if (g == 1) {
+        s_e[0][r] = colsum;  // the per-row vectors are dead by now: reuse their buffer
+        mbar_arrive(&bar_colsum);
+      } else {
+        ok = mbar_wait(&bar_colsum, 0, abortp, p.status, kBSiteColsum);
+        ok = __all_sync(0xffffffffu, ok);
+        if (ok) colsum += s_e[0][r];
+      }
+    }
     if (ok) {
       tc_fence_after();
       const bool keep = j_ok && n_tiles > 0;
-      uint16_t* dkrow = reinterpret_cast<uint16_t*>(p.dk) + b * p.dk_sb + h * p.dk_sh + static_cast<int64_t>(j) * p.dk_st;
-      uint16_t* dvrow = reinterpret_cast<uint16_t*>(p.dv) + b * p.dv_sb + h * p.dv_sh + static_cast<int64_t>(j) * p.dv_st;
+      const uint32_t tcol = tbase + lane_base + (g == 0 ? kColDK : kColDV);
+      const float sc = g == 0 ? p.sm_scale : 1.f;
+      uint16_t* orow = g == 0
+          ? reinterpret_cast<uint16_t*>(p.dk) + b * p.dk_sb + h * p.dk_sh + static_cast<int64_t>(j) * p.dk_st
+          : reinterpret_cast<uint16_t*>(p.dv) + b * p.dv_sb + h * p.dv_sh + static_cast<int64_t>(j) * p.dv_st;
 #pragma unroll
-      for (int which = 0; which < 2; ++which) {
-        const uint32_t tcol = tbase + lane_base + (which == 0 ? kColDK : kColDV);
-        const float sc = which == 0 ? p.sm_scale : 1.f;
-        uint16_t* orow = which == 0 ? dkrow : dvrow;
+      for (int c = 0; c < D; c += 32) {
+        uint32_t v[32];
+        if (n_tiles > 0) {
+          tmem_ld32(tcol + c, v);
+          tmem_ld_wait();
+        }
+        if (j < N) {
 #pragma unroll
-        for (int c = 0; c < D; c += 32) {
-          uint32_t r[32];
-          if (n_tiles > 0) {
-            tmem_ld32(tcol + c, r);
-            tmem_ld_wait();
-          }
-          if (j < N) {
-#pragma unroll
-            for (int q8 = 0; q8 < 32; q8 += 8) {
-              uint4 w = make_uint4(0, 0, 0, 0);
-              if (keep) {
-                w.x = pack2<kBf16>(__uint_as_float(r[q8 + 0]) * sc, __uint_as_float(r[q8 + 1]) * sc);
-                w.y = pack2<kBf16>(__uint_as_float(r[q8 + 2]) * sc, __uint_as_float(r[q8 + 3]) * sc);
-                w.z = pack2<kBf16>(__uint_as_float(r[q8 + 4]) * sc, __uint_as_float(r[q8 + 5]) * sc);
-                w.w = pack2<kBf16>(__uint_as_float(r[q8 + 6]) * sc, __uint_as_float(r[q8 + 7]) * sc);
-              }
-              *reinterpret_cast<uint4*>(orow + c + q8) = w;
+          for (int q8 = 0; q8 < 32; q8 += 8) {
+            uint4 w = make_uint4(0, 0, 0, 0);
+            if (keep) {
+              w.x = pack2<kBf16>(__uint_as_float(v[q8 + 0]) * sc, __uint_as_float(v[q8 + 1]) * sc);
+              w.y = pack2<kBf16>(__uint_as_float(v[q8 + 2]) * sc, __uint_as_float(v[q8 + 3]) * sc);
+              w.z = pack2<kBf16>(__uint_as_float(v[q8 + 4]) * sc, __uint_as_float(v[q8 + 5]) * sc);
+              w.w = pack2<kBf16>(__uint_as_float(v[q8 + 6]) * sc, __uint_as_float(v[q8 + 7]) * sc);
             }
+            *reinterpret_cast<uint4*>(orow + c + q8) = w;
           }
         }
       }
-      if (j < N) p.dlam_col[bh * N + j] = keep ? -colsum : 0.f;
+      if (g == 0) {
+        if (kColsumMMA && n_tiles > 0) {
+          uint32_t cs[16];
+          tmem_ld16(tbase + lane_base + kColDK + D, cs);
+          tmem_ld_wait();
+          colsum = __uint_as_float(cs[0]);
+        }
+        if (j < N) p.dlam_col[bh * N + j] = keep ? -colsum : 0.f;
+      }
     }
   }
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 4) tmem_dealloc(tbase, kTmemCols);
+  if (warp == 8) tmem_dealloc(tbase, kTmemCols);
 }
 
-template <int D, bool kBf16, int STAGES>
+// Debug hook: when set, the next backward launches record clock64 stamps of CTA (0,0,0).
+static long long* g_bwd_trace = nullptr;
+// Tuning hook: MMA groups (of four) in flight; 1..7.
+static int g_bwd_mma_depth = 0;
+// Tuning hook: 0 = ex2 unit only, 1 = polynomial only, 2 = every other exponential on the FMA pipe.
+static int g_bwd_poly = 0;
+
+template <int D, bool kBf16>
 static int launch_bwd(int device, cudaStream_t stream, int64_t B, int64_t H, int64_t M, int64_t N,
                       const fox_tensor4* q, const fox_tensor4* k, const fox_tensor4* v, const fox_tensor4* d_o,
                       const BwdParams& prm) {
@@ -415,20 +622,37 @@ static int launch_bwd(int device, cudaStream_t stream, int64_t B, int64_t H, int
   if ((rc = cached_tmap_4d(&tmK, tk, 2, false, kBf16, 64, 128, true))) return rc;
   if ((rc = cached_tmap_4d(&tmV, tv, 2, false, kBf16, 64, 128, true))) return rc;
   if ((rc = cached_tmap_4d(&tmDO, tdo, 2, false, kBf16, 64, 128, true))) return rc;
-  constexpr int smem = (2 + 2 * STAGES) * 128 * D * 2 + 16384 + 32768 + 1024;
-  auto kern = fox_attn_bwd_kernel<D, kBf16, STAGES>;
-  static bool configured[64] = {};
+  CUtensorMap tmDQ;
+  Tensor4 tdq{prm.dq_accum, B, H, M, D, H * M * D, M * D, D};
+  if ((rc = cached_tmap_4d(&tmDQ, tdq, 4, true, false, 32, 128, true))) return rc;
+  constexpr int kStQ = 2, kStDO = (D == 64) ? 2 : 1, kDsBufs = (D == 64) ? 2 : 1;
+  constexpr int kStageSub = (D == 64) ? 2 : 1;
+  constexpr int smem = (2 + kStQ + kStDO) * 128 * D * 2 + kDsBufs * 32768 + 16384 + kStageSub * 16384;
+  static_assert(smem + 3072 <= 232448, "shared memory budget (tiles + static barriers/vectors rounded to 1 KiB)");
+  const bool tracing = prm.trace != nullptr;
+  const int poly = g_bwd_poly;
+  auto kern = tracing ? fox_attn_bwd_kernel<D, kBf16, true, 0>
+              : (poly == 1 ? fox_attn_bwd_kernel<D, kBf16, false, 1>
+                 : (poly == 2 ? fox_attn_bwd_kernel<D, kBf16, false, 2> : fox_attn_bwd_kernel<D, kBf16, false, 0>));
+  static bool configured[4][64] = {};
   if (device < 0 || device >= 64) return FOX_ERR_DEVICE;
-  if (!configured[device]) {
+  const int slot = tracing ? 3 : poly;
+  if (!configured[slot][device]) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return FOX_ERR_LAUNCH;
-    configured[device] = true;
+    configured[slot][device] = true;
   }
   dim3 grid((unsigned)((N + kBwdBN - 1) / kBwdBN), (unsigned)H, (unsigned)B);
-  kern<<<grid, kBwdThreads, smem, stream>>>(tmQ, tmK, tmV, tmDO, prm);
+  kern<<<grid, kBwdThreads, smem, stream>>>(tmQ, tmK, tmV, tmDO, tmDQ, prm);
   return cudaGetLastError() == cudaSuccess ? FOX_OK : FOX_ERR_LAUNCH;
 }
 
 }  // namespace fox
+
+extern "C" void fox_debug_set_bwd_poly(int mode) { fox::g_bwd_poly = mode < 0 ? 0 : (mode > 2 ? 2 : mode); }
+
+extern "C" void fox_debug_set_bwd_mma_depth(int depth) { fox::g_bwd_mma_depth = depth; }
+
+extern "C" void fox_debug_set_bwd_trace(void* device_buffer) { fox::g_bwd_trace = static_cast<long long*>(device_buffer); }
 
 extern "C" int fox_attn_bwd(int device, void* stream, int dtype, int64_t B, int64_t H, int64_t M, int64_t N,
                             int64_t D, const fox_tensor4* q, const fox_tensor4* k, const fox_tensor4* v,
@@ -457,14 +681,16 @@ extern "C" int fox_attn_bwd(int device, void* stream, int dtype, int64_t B, int6
   prm.dk = dk->ptr; prm.dk_sb = dk->sb; prm.dk_sh = dk->sh; prm.dk_st = dk->st;
   prm.dv = dv->ptr; prm.dv_sb = dv->sb; prm.dv_sh = dv->sh; prm.dv_st = dv->st;
   prm.status = status;
+  prm.trace = g_bwd_trace;
+  prm.ablate = g_bwd_mma_depth;
   prm.H = (int)H; prm.M = (int)M; prm.N = (int)N;
   prm.sm_scale = sm_scale;
   prm.qk_scale = sm_scale * 1.4426950408889634f;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const bool bf = dtype == FOX_DTYPE_BF16;
   if (D == 64)
-    return bf ? launch_bwd<64, true, 2>(device, st, B, H, M, N, q, k, v, d_o, prm)
-              : launch_bwd<64, false, 2>(device, st, B, H, M, N, q, k, v, d_o, prm);
-  return bf ? launch_bwd<128, true, 1>(device, st, B, H, M, N, q, k, v, d_o, prm)
-            : launch_bwd<128, false, 1>(device, st, B, H, M, N, q, k, v, d_o, prm);
+    return bf ? launch_bwd<64, true>(device, st, B, H, M, N, q, k, v, d_o, prm)
+              : launch_bwd<64, false>(device, st, B, H, M, N, q, k, v, d_o, prm);
+  return bf ? launch_bwd<128, true>(device, st, B, H, M, N, q, k, v, d_o, prm)
+            : launch_bwd<128, false>(device, st, B, H, M, N, q, k, v, d_o, prm);
 }

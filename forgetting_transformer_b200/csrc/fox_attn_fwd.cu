@@ -62,7 +62,7 @@ fox_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   __shared__ uint64_t bar_q_full, bar_s_full, bar_p_full, bar_o_done;
   __shared__ uint64_t bar_k_full[STAGES], bar_k_empty[STAGES], bar_v_full[STAGES], bar_v_empty[STAGES];
   __shared__ uint64_t bar_negb[2];
-  __shared__ float s_negb[2][kFwdBN];
+  __shared__ __align__(16) float s_negb[2][kFwdBN];  // read as float4
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
 
@@ -116,38 +116,46 @@ fox_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   volatile int* abortp = &abort_flag;
 
   if (warp == 4) {
-    // ===================== TMA producer =====================
-    if (lane == 0 && n_tiles > 0) {
-      tma_prefetch_desc(&tmQ);
-      tma_prefetch_desc(&tmK);
-      tma_prefetch_desc(&tmV);
-      mbar_expect_tx(&bar_q_full, kTileBytes);
+    // ===================== TMA producer (whole warp converged, one elected lane issues) =====================
+    if (n_tiles > 0) {
+      if (elect_one()) {
+        tma_prefetch_desc(&tmQ);
+        tma_prefetch_desc(&tmK);
+        tma_prefetch_desc(&tmV);
+        mbar_expect_tx(&bar_q_full, kTileBytes);
 #pragma unroll
-      for (int s = 0; s < kSub; ++s) tma_load_4d(sQ + s * 16384, &tmQ, &bar_q_full, s * 64, mb * kFwdBM, h, b);
-      bool ok = true;
+        for (int s = 0; s < kSub; ++s) tma_load_4d(sQ + s * 16384, &tmQ, &bar_q_full, s * 64, mb * kFwdBM, h, b);
+      }
+      __syncwarp();
       int issued = 0;
-      for (int it = 0; it < n_tiles && ok; ++it) {
+      for (int it = 0; it < n_tiles; ++it) {
         const int nb = nb_hi - 1 - it;
         const int st = it % STAGES;
         const uint32_t ph = (it / STAGES) & 1;
-        ok = mbar_wait(&bar_k_empty[st], ph ^ 1, abortp, p.status, kSiteKEmpty, it);
-        if (!ok) break;
-        mbar_expect_tx(&bar_k_full[st], kTileBytes);
+        if (!mbar_wait_warp(&bar_k_empty[st], ph ^ 1, abortp, p.status, kSiteKEmpty, it)) break;
+        if (elect_one()) {
+          mbar_expect_tx(&bar_k_full[st], kTileBytes);
 #pragma unroll
-        for (int s = 0; s < kSub; ++s)
-          tma_load_4d(sK + st * kTileBytes + s * 16384, &tmK, &bar_k_full[st], s * 64, nb * kFwdBN, h, b);
-        ok = mbar_wait(&bar_v_empty[st], ph ^ 1, abortp, p.status, kSiteVEmpty, it);
-        if (!ok) { issued = it * 2 + 1; break; }
-        mbar_expect_tx(&bar_v_full[st], kTileBytes);
+          for (int s = 0; s < kSub; ++s)
+            tma_load_4d(sK + st * kTileBytes + s * 16384, &tmK, &bar_k_full[st], s * 64, nb * kFwdBN, h, b);
+        }
+        __syncwarp();
+        issued = it * 2 + 1;
+        if (!mbar_wait_warp(&bar_v_empty[st], ph ^ 1, abortp, p.status, kSiteVEmpty, it)) break;
+        if (elect_one()) {
+          mbar_expect_tx(&bar_v_full[st], kTileBytes);
 #pragma unroll
-        for (int s = 0; s < kSub; ++s)
-          tma_load_4d(sV + st * kTileBytes + s * 16384, &tmV, &bar_v_full[st], s * 64, nb * kFwdBN, h, b);
+          for (int s = 0; s < kSub; ++s)
+            tma_load_4d(sV + st * kTileBytes + s * 16384, &tmV, &bar_v_full[st], s * 64, nb * kFwdBN, h, b);
+        }
+        __syncwarp();
         issued = it * 2 + 2;
       }
-      if (*abortp) {
+      if (*abortp && lane == 0) {
         // error path only: let the copies already in flight land before the CTA retires
-        mbar_wait(&bar_q_full, 0, abortp, p.status, kSiteDrain);
         const long long t0 = clock64();
+        while (!mbar_try_wait(&bar_q_full, 0) && clock64() - t0 < 200000000LL) {
+        }
         for (int c = max(issued - 2 * STAGES, 0); c < issued; ++c) {
           const int it = c >> 1, st = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
@@ -158,36 +166,38 @@ fox_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       }
     }
   } else if (warp == 5) {
-    // ===================== MMA issuer =====================
-    if (lane == 0 && n_tiles > 0) {
+    // ===================== MMA issuer (whole warp converged, one elected lane issues) =====================
+    if (n_tiles > 0) {
       constexpr uint32_t idQK = umma_idesc(kFmt, 128, 128, 0, 0);
       constexpr uint32_t idPV = umma_idesc(kFmt, 128, D, 0, 1);
-      const uint32_t q0 = smem_u32(sQ);
-      bool ok = mbar_wait(&bar_q_full, 0, abortp, p.status, kSiteQFull);
+      // descriptors are built once; the loops only move the start-address field
+      const uint64_t dQ = umma_desc_kmajor(smem_u32(sQ));
+      const uint64_t dK0 = umma_desc_kmajor(smem_u32(sK));
+      const uint64_t dV0 = umma_desc_mnmajor(smem_u32(sV), 16384);
+      bool ok = mbar_wait_warp(&bar_q_full, 0, abortp, p.status, kSiteQFull);
       for (int it = 0; it < n_tiles && ok; ++it) {
         const int st = it % STAGES;
         const uint32_t ph = (it / STAGES) & 1;
-        ok = mbar_wait(&bar_k_full[st], ph, abortp, p.status, kSiteKFull, it);
+        ok = mbar_wait_warp(&bar_k_full[st], ph, abortp, p.status, kSiteKFull, it);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t k0 = smem_u32(sK + st * kTileBytes);
+        const uint64_t dK = umma_desc_advance(dK0, st * kTileBytes);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
-          mma_ss(tbase, umma_desc_kmajor(q0 + off), umma_desc_kmajor(k0 + off), idQK, kk > 0);
+          mma_ss(tbase, umma_desc_advance(dQ, off), umma_desc_advance(dK, off), idQK, kk > 0);
         }
         tc_commit(&bar_s_full);
         tc_commit(&bar_k_empty[st]);
-        ok = mbar_wait(&bar_p_full, it & 1, abortp, p.status, kSitePFull, it);
+        ok = mbar_wait_warp(&bar_p_full, it & 1, abortp, p.status, kSitePFull, it);
         if (!ok) break;
-        ok = mbar_wait(&bar_v_full[st], ph, abortp, p.status, kSiteVFull, it);
+        ok = mbar_wait_warp(&bar_v_full[st], ph, abortp, p.status, kSiteVFull, it);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t v0 = smem_u32(sV + st * kTileBytes);
+        const uint64_t dV = umma_desc_advance(dV0, st * kTileBytes);
 #pragma unroll
         for (int kk = 0; kk < kFwdBN / 16; ++kk)
-          mma_ts(tbase + kColO, tbase + kk * 8, umma_desc_mnmajor(v0 + kk * 2048, 16384), idPV,
-                 (it > 0 || kk > 0) ? 1u : 0u);
+          mma_ts(tbase + kColO, tbase + kk * 8, umma_desc_advance(dV, kk * 2048), idPV, (it > 0 || kk > 0) ? 1u : 0u);
         tc_commit(&bar_v_empty[st]);
       }
       if (ok) tc_commit(&bar_o_done);

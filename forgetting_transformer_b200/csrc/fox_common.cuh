@@ -22,8 +22,6 @@ namespace fox {
 //   [2] thread index, [3] free-form detail (tile index).
 constexpr int kStatusWords = 4;
 
-// Wait budget in SM clock cycles (~1.5 s at 1.9 GHz).
-constexpr long long kWaitBudgetCycles = 3000000000LL;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -57,26 +55,67 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 }
 
 // Bounded wait.  `abort_flag` lives in shared memory; `status` in global.
+// The fast path is a two-instruction loop around mbarrier.try_wait with a suspend-time hint:
+// a waiting warp is parked by the hardware instead of burning issue slots that the compute
+// warps on the same scheduler need.  kWaitTries x kWaitHintNs (~2 s) bounds the wait.
+constexpr uint32_t kWaitHintNs = 500000u;
+constexpr uint32_t kWaitTries = 4000u;
+constexpr uint32_t kWaitTriesBackoff = 20000000u;  // x (>= 32 ns sleep + poll) ~ 2 s
+template <bool kBackoff = false>
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
                                           int* status, int site, int detail = 0) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const long long t0 = clock64();
-  int spins = 0;
-  while (true) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((++spins & 63) == 0) {
-      if (*abort_flag) return false;
-      if (clock64() - t0 > kWaitBudgetCycles) {
-        *abort_flag = 1;
-        if (atomicCAS(&status[0], 0, site) == 0) {
-          status[1] = static_cast<int>(blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z));
-          status[2] = static_cast<int>(threadIdx.x);
-          status[3] = detail;
-        }
-        return false;
-      }
+  uint32_t ok;
+  const uint32_t addr = smem_u32(bar);
+  if (kBackoff) {
+    // producer / issuer / drain warps: sleep between polls so that the poll loop does not take
+    // issue slots from the compute warps that share the scheduler
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t.reg .u32 n;\n\tmov.u32 n, 0;\n"
+        "FOX_WAITB_LOOP:\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "@p bra FOX_WAITB_DONE;\n\t"
+        "nanosleep.u32 20;\n\t"
+        "add.u32 n, n, 1;\n\t"
+        "setp.lt.u32 q, n, %3;\n\t"
+        "@q bra FOX_WAITB_LOOP;\n"
+        "FOX_WAITB_DONE:\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(addr), "r"(parity), "r"(*abort_flag ? 1u : kWaitTriesBackoff)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t.reg .u32 n;\n\tmov.u32 n, 0;\n"
+        "FOX_WAIT_LOOP:\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "@p bra FOX_WAIT_DONE;\n\t"
+        "add.u32 n, n, 1;\n\t"
+        "setp.lt.u32 q, n, %4;\n\t"
+        "@q bra FOX_WAIT_LOOP;\n"
+        "FOX_WAIT_DONE:\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(addr), "r"(parity), "r"(kWaitHintNs), "r"(*abort_flag ? 1u : kWaitTries)
+        : "memory");
+  }
+  if (ok) return true;
+  // ran out of budget (or another waiter already did): record the first failing site and give up
+  if (!*abort_flag) {
+    *abort_flag = 1;
+    if (atomicCAS(&status[0], 0, site) == 0) {
+      status[1] = static_cast<int>(blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z));
+      status[2] = static_cast<int>(threadIdx.x);
+      status[3] = detail;
     }
   }
+  return false;
+}
+
+// Warp-collective form: every lane waits, the verdict is made uniform so the warp stays converged.
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                               int* status, int site, int detail = 0) {
+  const bool ok = mbar_wait<false>(bar, parity, abort_flag, status, site, detail);
+  return __all_sync(0xffffffffu, ok);
 }
 
 // ----------------------------------------------------------------------- TMA
@@ -126,6 +165,15 @@ __device__ __forceinline__ void fence_proxy_async_smem() {
 }
 
 // ------------------------------------------------------------------- tcgen05
+// One lane of a fully converged warp.  tcgen05.mma / commit / TMA take their operands from
+// uniform registers: issued from a converged warp (every lane computes the same operands, one
+// elected lane executes) they issue back to back; issued from a diverged `lane == 0` branch
+// each instruction costs ~170 cycles (measured), several times the tensor pipe's own rate.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile("{\n\t.reg .pred px;\n\telect.sync _|px, 0xffffffff;\n\tselp.u32 %0, 1, 0, px;\n\t}" : "=r"(pred));
+  return pred != 0;
+}
 __device__ __forceinline__ void tmem_alloc(uint32_t* smem_result, uint32_t ncols) {
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_result)),
                "r"(ncols)
@@ -143,14 +191,14 @@ __device__ __forceinline__ void tc_fence_before() {
 __device__ __forceinline__ void tc_fence_after() {
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 }
-// arrive (count 1) on `bar` once every tcgen05.mma issued so far by this thread retired
-__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+// Raw forms: to be executed by ONE lane, inside an `if (elect_one())` block of a converged warp
+// whose operands were computed by all lanes (so they live in uniform registers).
+__device__ __forceinline__ void tc_commit_raw(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
                : "memory");
 }
-// D[tmem] (+)= A[smem desc] * B[smem desc]
-__device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                       uint32_t accumulate) {
+__device__ __forceinline__ void mma_ss_raw(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                           uint32_t accumulate) {
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
       "setp.ne.b32 p, %4, 0;\n\t"
@@ -158,15 +206,46 @@ __device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_
       "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
-// D[tmem] (+)= A[tmem] * B[smem desc]
-__device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
-                                       uint32_t accumulate) {
+__device__ __forceinline__ void mma_ts_raw(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                           uint32_t accumulate) {
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
       "setp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d_tmem),
       "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
+}
+// The three wrappers below must be called by ALL lanes of a converged warp; one lane executes.
+// arrive (count 1) on `bar` once every tcgen05.mma issued so far by this warp retired
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+  const uint32_t addr = smem_u32(bar);
+  if (elect_one())
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(addr) : "memory");
+  __syncwarp();
+}
+// D[tmem] (+)= A[smem desc] * B[smem desc]
+__device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                       uint32_t accumulate) {
+  if (elect_one())
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  __syncwarp();
+}
+// D[tmem] (+)= A[tmem] * B[smem desc]
+__device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                       uint32_t accumulate) {
+  if (elect_one())
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d_tmem),
+        "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  __syncwarp();
 }
 
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
@@ -253,6 +332,11 @@ __device__ __forceinline__ uint64_t umma_desc_mnmajor(uint32_t smem_addr, uint32
   d |= static_cast<uint64_t>(2) << 61;
   return d;
 }
+// Advance a descriptor's start address by `bytes` (a multiple of 16; the tile stays below the
+// 256 KiB the 14-bit field can address, so the add never carries into the next field).
+__device__ __forceinline__ uint64_t umma_desc_advance(uint64_t desc, uint32_t bytes) {
+  return desc + static_cast<uint64_t>(bytes >> 4);
+}
 // kind::f16 instruction descriptor, fp32 accumulate.  fmt: 0 = fp16, 1 = bf16.
 __host__ __device__ constexpr uint32_t umma_idesc(uint32_t fmt, uint32_t m, uint32_t n, uint32_t a_mn_major,
                                                   uint32_t b_mn_major) {
@@ -278,6 +362,22 @@ __device__ __forceinline__ float2 unpack2(uint32_t u) {
   } else {
     return __half22float2(*reinterpret_cast<__half2*>(&u));
   }
+}
+// 2^x on the FMA pipe (no MUFU): floor(x) by a round-down add of 1.5*2^23, a degree-3 polynomial
+// for 2^frac (max relative error 7.5e-5, fitted for this library) and the exponent put in with one
+// integer shift-add.  Valid for |x| <= 126; smaller inputs are clamped (result 2^-126).
+// The ex2 unit does 16 results per clock per SM against 128 FMA lanes, and its instructions share
+// the scheduler's memory-I/O queue with shared-memory, TMEM and MMA instructions, so moving part
+// of the exponentials here relieves both.
+__device__ __forceinline__ float exp2_poly(float x) {
+  x = fmaxf(x, -126.f);
+  float r;
+  asm("add.rm.ftz.f32 %0, %1, %2;" : "=f"(r) : "f"(x), "f"(12582912.f));
+  const float f = x - (r - 12582912.f);
+  float p = fmaf(f, 0.07802452f, 0.22606716f);
+  p = fmaf(p, f, 0.69583356f);
+  p = fmaf(p, f, 0.9999252f);
+  return __uint_as_float(__float_as_uint(p) + (__float_as_uint(r) << 23));
 }
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;

@@ -1,0 +1,90 @@
+"""CPU tests (gloo, world_size 2) of the multi-GPU host logic: batch x head unit slicing and
+the zig-zag context-parallel wrapper, with the oracle standing in for the CUDA operator."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from forgetting_transformer_b200 import sharding
+from oracle import fox_oracle as orc
+
+
+def test_unit_slices_cover_everything_once():
+    for n, w in [(48, 1), (48, 2), (48, 8), (7, 4), (3, 8)]:
+        got = []
+        for r in range(w):
+            a, b = sharding.unit_slice(n, w, r)
+            got += list(range(a, b))
+        assert got == list(range(n))
+
+
+def test_shard_batch_heads_views_and_metadata():
+    B, H, T, D = 2, 3, 8, 4
+    q = torch.arange(B * H * T * D, dtype=torch.float32).reshape(B, H, T, D)
+    lf = torch.zeros(B, H, T)
+    seq = torch.tensor([1, 5])
+    thr = torch.tensor([-1.0, -2.0, -3.0])
+    pieces = []
+    for r in range(4):
+        qs, ks, vs, ls, ss, th = sharding.shard_batch_heads(q, q, q, lf, seq, thr, world=4, rank=r)
+        assert qs.shape[1] == 1 and qs.shape[0] == ss.shape[0] == th.shape[0]
+        assert qs.data_ptr() >= q.data_ptr()  # views, not copies
+        pieces.append((qs, ss, th))
+    assert torch.equal(torch.cat([p[0] for p in pieces]).reshape(B, H, T, D), q)
+    assert torch.cat([p[1] for p in pieces]).tolist() == [1, 1, 1, 5, 5, 5]
+    assert torch.cat([p[2] for p in pieces]).flatten().tolist() == [-1, -2, -3, -1, -2, -3]
+
+
+def _oracle_attn(q, k, v, lf, head_first=True, sm_scale=None, adaptive_threshold=None):
+    return orc.dense_forgetting_attention(q, k, v, lf, None, sm_scale)
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _cp_worker(rank, world, port, ret):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        torch.manual_seed(0)
+        B, H, D = 1, 2, 16
+        tc = 8
+        T = 2 * world * tc
+        q, k, v, do = [torch.randn(B, H, T, D, dtype=torch.float64) for _ in range(4)]
+        lf = torch.nn.functional.logsigmoid(torch.randn(B, H, T, dtype=torch.float64))
+        # unsharded reference
+        ro, rdq, rdk, rdv, rdl = orc.dense_fwd_bwd(q, k, v, lf, do)
+        a, b = sharding.zigzag_chunks(world, rank)
+        idx = torch.cat([torch.arange(a * tc, (a + 1) * tc), torch.arange(b * tc, (b + 1) * tc)])
+        ql, kl, vl, ll = [t.index_select(2, idx).clone().requires_grad_() for t in (q, k, v, lf)]
+        out = sharding.context_parallel_attention(ql, kl, vl, ll, attn_fn=_oracle_attn)
+        out.backward(do.index_select(2, idx))
+        errs = [
+            (out - ro.index_select(2, idx)).abs().max().item(),
+            (ql.grad - rdq.index_select(2, idx)).abs().max().item(),
+            (kl.grad - rdk.index_select(2, idx)).abs().max().item(),
+            (vl.grad - rdv.index_select(2, idx)).abs().max().item(),
+            (ll.grad - rdl.index_select(2, idx)).abs().max().item(),
+        ]
+        ret[rank] = max(errs)
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.timeout(120)
+def test_context_parallel_matches_unsharded_world2():
+    world = 2
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_cp_worker, args=(world, _free_port(), ret), nprocs=world, join=True)
+    assert len(ret) == world
+    assert max(ret.values()) < 1e-5  # the dense formulation does its softmax in fp32
