@@ -90,10 +90,10 @@ fox_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   __shared__ uint64_t bar_kv, bar_s_full, bar_dp_full, bar_p_done, bar_ds_done, bar_dq_full, bar_dq_free, bar_done,
       bar_colsum;
-  __shared__ uint64_t bar_q_full[STQ], bar_q_empty[STQ], bar_do_full[STDO], bar_do_empty[STDO], bar_vec[2],
-      bar_dsm_free[2], bar_staged, bar_stage_free;
-  __shared__ __align__(16) float s_e[2][kBwdBM];      // read as float4
-  __shared__ __align__(16) float s_delta[2][kBwdBM];
+  __shared__ uint64_t bar_q_full[STQ], bar_q_empty[STQ], bar_do_full[STDO], bar_do_empty[STDO],
+      bar_staged, bar_stage_free;
+  __shared__ __align__(16) float s_e[STQ][kBwdBM];      // per Q stage; read as float4
+  __shared__ __align__(16) float s_delta[STQ][kBwdBM];
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
 
@@ -138,9 +138,9 @@ fox_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     mbar_init(&bar_dq_free, 128);
     mbar_init(&bar_done, 1);
     mbar_init(&bar_colsum, 128);
-    for (int s = 0; s < STQ; ++s) { mbar_init(&bar_q_full[s], 1); mbar_init(&bar_q_empty[s], 1); }
+    // q_full: the TMA transaction plus one arrival of the producer warp for the per-row vectors
+    for (int s = 0; s < STQ; ++s) { mbar_init(&bar_q_full[s], 2); mbar_init(&bar_q_empty[s], 1); }
     for (int s = 0; s < STDO; ++s) { mbar_init(&bar_do_full[s], 1); mbar_init(&bar_do_empty[s], 1); }
-    for (int s = 0; s < 2; ++s) { mbar_init(&bar_vec[s], 128); mbar_init(&bar_dsm_free[s], 1); }
     mbar_init(&bar_staged, 128);
     mbar_init(&bar_stage_free, 1);
     mbar_fence_init();
@@ -185,6 +185,22 @@ fox_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         }
       }
       __syncwarp();
+      float vec_e[kBwdBM / 32], vec_d[kBwdBM / 32];
+      auto load_vec = [&](int mb_) {
+#pragma unroll
+        for (int rr = 0; rr < kBwdBM / 32; ++rr) {
+          const int i = mb_ * kBwdBM + rr * 32 + lane;
+          float e = -INFINITY, dl = 0.f;
+          if (i < M) {
+            const float Li = p.L[bh * M + i];
+            e = (Li == -INFINITY) ? -INFINITY : (p.lam[bh * N + P + i] - Li) * kLog2eB;
+            dl = p.delta[bh * M + i];
+          }
+          vec_e[rr] = e;
+          vec_d[rr] = dl;
+        }
+      };
+      load_vec(mb_lo);
       int issued_q = 0, issued_do = 0;
       for (int it = 0; it < n_tiles; ++it) {
         const int mb = mb_lo + it;
@@ -200,6 +216,18 @@ fox_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           }
           __syncwarp();
           issued_q = it + 1;
+          // per-row vectors of this query tile, same stage as Q (fetched one tile ahead into registers):
+          // e_i = (Lambda_i - L_i) log2 e (-inf for an empty or out-of-range row) and delta_i.  Consumers
+          // reach them through s_full, which the MMA warp commits only after it has seen q_full.
+#pragma unroll
+          for (int rr = 0; rr < kBwdBM / 32; ++rr) {
+            s_e[st][rr * 32 + lane] = vec_e[rr];
+            s_delta[st][rr * 32 + lane] = vec_d[rr];
+          }
+          __syncwarp();
+          if (elect_one()) mbar_arrive(&bar_q_full[st]);
+          __syncwarp();
+          if (it + 1 < n_tiles) load_vec(mb + 1);
         }
         {
           const int st = it % STDO;
@@ -333,7 +361,6 @@ fox_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             mma_ss_raw(tbase + kColDQ, umma_desc_advance(ads_mn, kk * 2048), umma_desc_advance(dK_mn, kk * 2048),
                        idDQ, kk > 0);
           tc_commit_raw(&bar_dq_full);
-          tc_commit_raw(&bar_dsm_free[it % kDsBufs]);
           tc_commit_raw(&bar_q_empty[it % STQ]);
         }
         __syncwarp();
@@ -360,24 +387,8 @@ fox_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     const int quarter = warp & 3;
     const int r = quarter * 32 + lane;  // query row inside the tile == TMEM lane
     const uint32_t tDQ = tbase + (static_cast<uint32_t>(quarter * 32) << 16) + kColDQ;
-    const float* lam = p.lam + bh * N;
-    auto stage_vec = [&](int it) {
-      const int i = (mb_lo + it) * kBwdBM + r;
-      float e = -INFINITY, dl = 0.f;
-      if (i < M) {
-        const float Li = p.L[bh * M + i];
-        e = (Li == -INFINITY) ? -INFINITY : (lam[P + i] - Li) * kLog2eB;
-        dl = p.delta[bh * M + i];
-      }
-      s_e[it & 1][r] = e;
-      s_delta[it & 1][r] = dl;
-      mbar_arrive(&bar_vec[it & 1]);
-    };
-    if (n_tiles > 0) stage_vec(0);
     bool ok = true;
     for (int it = 0; it < n_tiles; ++it) {
-      // buffer (it+1)&1 was last read by phase B(it-1), which finished before dQ(it-1) was issued
-      if (it + 1 < n_tiles) stage_vec(it + 1);
       if (warp == 10) stamp(1, 0, it);
       ok = mbar_wait_warp(&bar_dq_full, it & 1, abortp, p.status, kBSiteDq, it);
       if (!ok) break;
@@ -451,8 +462,9 @@ fox_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 
     for (int it = 0; it < n_tiles; ++it) {
       const int mb = mb_lo + it;
-      ok = mbar_wait(&bar_vec[it & 1], (it >> 1) & 1, abortp, p.status, kBSiteVec, it);
-      ok = mbar_wait(&bar_s_full, it & 1, abortp, p.status, kBSiteSFull, it) && ok;
+      stamp(6 + warp, 4, it);
+      ok = mbar_wait(&bar_s_full, it & 1, abortp, p.status, kBSiteSFull, it);
+      stamp(6 + warp, 6, it);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
@@ -468,7 +480,7 @@ fox_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         uint32_t sreg[32], pk[16];
         tmem_ld32(tS + col0, sreg);
         tmem_ld_wait();
-        const float4* e4 = reinterpret_cast<const float4*>(&s_e[it & 1][col0]);
+        const float4* e4 = reinterpret_cast<const float4*>(&s_e[it % STQ][col0]);
 #pragma unroll
         for (int c4 = 0; c4 < 8; ++c4) {
           const float4 ev = e4[c4];
@@ -491,9 +503,10 @@ fox_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       stamp(6 + warp, 1, it);
 
       // ---------------- phase B: dS ----------------
+      stamp(6 + warp, 7, it);
       ok = mbar_wait(&bar_dp_full, it & 1, abortp, p.status, kBSiteDpFull, it);
-      if (it >= kDsBufs)
-        ok = mbar_wait(&bar_dsm_free[it % kDsBufs], ((it / kDsBufs) - 1) & 1, abortp, p.status, kBSiteDsmFree, it) && ok;
+      // dP(it) was issued behind dQ(it - kDsBufs) and a commit covers everything issued before it, so the
+      // dS buffer about to be overwritten is no longer being read.
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
@@ -505,7 +518,7 @@ fox_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         uint32_t dpreg[32], dsk[16];
         tmem_ld32(tDP + col0, dpreg);
         tmem_ld_wait();
-        const float4* d4 = reinterpret_cast<const float4*>(&s_delta[it & 1][col0]);
+        const float4* d4 = reinterpret_cast<const float4*>(&s_delta[it % STQ][col0]);
 #pragma unroll
         for (int c4 = 0; c4 < 8; ++c4) {
           const float4 dv4 = d4[c4];

@@ -25,7 +25,6 @@ namespace fox {
 
 constexpr int kFwdBM = FOX_FWD_BLOCK_M;
 constexpr int kFwdBN = FOX_FWD_BLOCK_N;
-constexpr int kFwdThreads = 192;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 // the reference maximum is only moved when it is off by more than 2^kLazyShift
@@ -45,30 +44,42 @@ struct FwdParams {
 
 enum FwdWaitSite {
   kSiteQFull = 11, kSiteKFull = 12, kSiteVFull = 13, kSiteKEmpty = 14, kSiteVEmpty = 15,
-  kSiteSFull = 16, kSitePFull = 17, kSiteODone = 18, kSiteDrain = 19, kSiteNegB = 20
+  kSiteSFull = 16, kSitePFull = 17, kSiteODone = 18, kSiteDrain = 19, kSiteNegB = 20, kSiteMerge = 21
 };
 
-template <int D, bool kBf16, int STAGES>
-__global__ void __launch_bounds__(kFwdThreads, 2)
+template <int D, bool kBf16, int BN, int STAGES, int CTAS, bool SPLIT>
+__global__ void __launch_bounds__(SPLIT ? 320 : 192, CTAS)
 fox_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                     const __grid_constant__ CUtensorMap tmV, const FwdParams p) {
-  constexpr int kTileBytes = 128 * D * 2;  // one [128][D] 16-bit tile (D/64 swizzled sub-tiles)
+  // KV tiles of BN rows (64 or 128; the pruning grid stays 128 wide, BN = 64 just walks it in halves).
+  // SPLIT: two softmax warpgroups per CTA, each owning half of the tile's columns with its own running
+  // maximum, row sum and O accumulator (two independent online-softmax streams, merged in the epilogue),
+  // so that four softmax warps per scheduler hide each other's ex2 / TMEM latency without any exchange
+  // between the warpgroups inside the loop.
+  constexpr int kWG = SPLIT ? 2 : 1;
+  constexpr int CW = BN / kWG;              // columns per softmax thread
+  constexpr int kQBytes = 128 * D * 2;      // Q tile: D/64 swizzled [128][64] sub-tiles
+  constexpr int kTileBytes = BN * D * 2;    // K / V tile: D/64 swizzled [BN][64] sub-tiles
+  constexpr int kSubBytes = BN * 128;       // one K / V sub-tile
   constexpr int kSub = D / 64;
   constexpr uint32_t kFmt = kBf16 ? 1u : 0u;
-  constexpr uint32_t kTmemCols = 256;
-  constexpr uint32_t kColO = 128;
+  constexpr uint32_t kColO = BN;            // S (fp32) in columns [0, BN), O_g in [BN + g D, BN + (g+1) D)
+  constexpr uint32_t kTmemCols = (BN + kWG * D <= 128) ? 128 : ((BN + kWG * D <= 256) ? 256 : 512);
+  constexpr int kTmaWarp = 4 * kWG, kMmaWarp = 4 * kWG + 1;
 
   extern __shared__ uint8_t smem_raw[];
-  __shared__ uint64_t bar_q_full, bar_s_full, bar_p_full, bar_o_done;
+  __shared__ uint64_t bar_q_full, bar_s_full, bar_o_done, bar_merge;
+  __shared__ uint64_t bar_p_full[2];
   __shared__ uint64_t bar_k_full[STAGES], bar_k_empty[STAGES], bar_v_full[STAGES], bar_v_empty[STAGES];
   __shared__ uint64_t bar_negb[2];
-  __shared__ __align__(16) float s_negb[2][kFwdBN];  // read as float4
+  __shared__ __align__(16) float s_negb[2][BN];  // read as float4
+  __shared__ float s_m1[128], s_l1[128];
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
 
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sQ = smem;
-  uint8_t* sK = sQ + kTileBytes;
+  uint8_t* sK = sQ + kQBytes;
   uint8_t* sV = sK + STAGES * kTileBytes;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -85,16 +96,18 @@ fox_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     lo = max(lo, static_cast<int>(si < static_cast<int64_t>(hi) ? si : static_cast<int64_t>(hi)));
   }
   lo = (lo / kFwdBN) * kFwdBN;
-  const int nb_lo = lo / kFwdBN;
-  const int nb_hi = (hi + kFwdBN - 1) / kFwdBN;  // exclusive
+  const int nb_lo = lo / BN;
+  const int nb_hi = (hi + BN - 1) / BN;  // exclusive
   const int n_tiles = max(nb_hi - nb_lo, 0);
 
   if (tid == 0) {
     abort_flag = 0;
     mbar_init(&bar_q_full, 1);
     mbar_init(&bar_s_full, 1);
-    mbar_init(&bar_p_full, 128);
+    mbar_init(&bar_p_full[0], 128);
+    mbar_init(&bar_p_full[1], 128);
     mbar_init(&bar_o_done, 1);
+    mbar_init(&bar_merge, 128);
     mbar_init(&bar_negb[0], 128);
     mbar_init(&bar_negb[1], 128);
     for (int s = 0; s < STAGES; ++s) {
@@ -105,7 +118,7 @@ fox_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     }
     mbar_fence_init();
   }
-  if (warp == 4) {
+  if (warp == kTmaWarp) {
     tmem_alloc(&tmem_slot, kTmemCols);
     tmem_relinquish();
   }
@@ -115,14 +128,14 @@ fox_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   const uint32_t tbase = tmem_slot;
   volatile int* abortp = &abort_flag;
 
-  if (warp == 4) {
+  if (warp == kTmaWarp) {
     // ===================== TMA producer (whole warp converged, one elected lane issues) =====================
     if (n_tiles > 0) {
       if (elect_one()) {
         tma_prefetch_desc(&tmQ);
         tma_prefetch_desc(&tmK);
         tma_prefetch_desc(&tmV);
-        mbar_expect_tx(&bar_q_full, kTileBytes);
+        mbar_expect_tx(&bar_q_full, kQBytes);
 #pragma unroll
         for (int s = 0; s < kSub; ++s) tma_load_4d(sQ + s * 16384, &tmQ, &bar_q_full, s * 64, mb * kFwdBM, h, b);
       }
@@ -137,7 +150,7 @@ fox_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           mbar_expect_tx(&bar_k_full[st], kTileBytes);
 #pragma unroll
           for (int s = 0; s < kSub; ++s)
-            tma_load_4d(sK + st * kTileBytes + s * 16384, &tmK, &bar_k_full[st], s * 64, nb * kFwdBN, h, b);
+            tma_load_4d(sK + st * kTileBytes + s * kSubBytes, &tmK, &bar_k_full[st], s * 64, nb * BN, h, b);
         }
         __syncwarp();
         issued = it * 2 + 1;
@@ -146,7 +159,7 @@ fox_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           mbar_expect_tx(&bar_v_full[st], kTileBytes);
 #pragma unroll
           for (int s = 0; s < kSub; ++s)
-            tma_load_4d(sV + st * kTileBytes + s * 16384, &tmV, &bar_v_full[st], s * 64, nb * kFwdBN, h, b);
+            tma_load_4d(sV + st * kTileBytes + s * kSubBytes, &tmV, &bar_v_full[st], s * 64, nb * BN, h, b);
         }
         __syncwarp();
         issued = it * 2 + 2;
@@ -165,15 +178,15 @@ fox_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         }
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == kMmaWarp) {
     // ===================== MMA issuer (whole warp converged, one elected lane issues) =====================
     if (n_tiles > 0) {
-      constexpr uint32_t idQK = umma_idesc(kFmt, 128, 128, 0, 0);
+      constexpr uint32_t idQK = umma_idesc(kFmt, 128, BN, 0, 0);
       constexpr uint32_t idPV = umma_idesc(kFmt, 128, D, 0, 1);
       // descriptors are built once; the loops only move the start-address field
       const uint64_t dQ = umma_desc_kmajor(smem_u32(sQ));
       const uint64_t dK0 = umma_desc_kmajor(smem_u32(sK));
-      const uint64_t dV0 = umma_desc_mnmajor(smem_u32(sV), 16384);
+      const uint64_t dV0 = umma_desc_mnmajor(smem_u32(sV), kSubBytes);
       bool ok = mbar_wait_warp(&bar_q_full, 0, abortp, p.status, kSiteQFull);
       for (int it = 0; it < n_tiles && ok; ++it) {
         const int st = it % STAGES;
@@ -182,71 +195,85 @@ fox_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         if (!ok) break;
         tc_fence_after();
         const uint64_t dK = umma_desc_advance(dK0, st * kTileBytes);
+        if (elect_one()) {
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
-          mma_ss(tbase, umma_desc_advance(dQ, off), umma_desc_advance(dK, off), idQK, kk > 0);
+          for (int kk = 0; kk < D / 16; ++kk)
+            mma_ss_raw(tbase, umma_desc_advance(dQ, (kk >> 2) * 16384 + (kk & 3) * 32),
+                       umma_desc_advance(dK, (kk >> 2) * kSubBytes + (kk & 3) * 32), idQK, kk > 0);
+          tc_commit_raw(&bar_s_full);
+          tc_commit_raw(&bar_k_empty[st]);
         }
-        tc_commit(&bar_s_full);
-        tc_commit(&bar_k_empty[st]);
-        ok = mbar_wait_warp(&bar_p_full, it & 1, abortp, p.status, kSitePFull, it);
-        if (!ok) break;
+        __syncwarp();
         ok = mbar_wait_warp(&bar_v_full[st], ph, abortp, p.status, kSiteVFull, it);
         if (!ok) break;
-        tc_fence_after();
         const uint64_t dV = umma_desc_advance(dV0, st * kTileBytes);
 #pragma unroll
-        for (int kk = 0; kk < kFwdBN / 16; ++kk)
-          mma_ts(tbase + kColO, tbase + kk * 8, umma_desc_advance(dV, kk * 2048), idPV, (it > 0 || kk > 0) ? 1u : 0u);
-        tc_commit(&bar_v_empty[st]);
+        for (int g = 0; g < kWG; ++g) {
+          ok = mbar_wait_warp(&bar_p_full[g], it & 1, abortp, p.status, kSitePFull, it);
+          if (!ok) break;
+          tc_fence_after();
+          if (elect_one()) {
+            // O_g += P[:, g CW : (g+1) CW] V[g CW : (g+1) CW, :]; the 16-bit P sits at S columns g CW ...
+#pragma unroll
+            for (int kk = 0; kk < CW / 16; ++kk)
+              mma_ts_raw(tbase + kColO + g * D, tbase + g * CW + kk * 8,
+                         umma_desc_advance(dV, (g * (CW / 16) + kk) * 2048), idPV, (it > 0 || kk > 0) ? 1u : 0u);
+            if (g == kWG - 1) tc_commit_raw(&bar_v_empty[st]);
+          }
+          __syncwarp();
+        }
+        if (!ok) break;
       }
       if (ok) tc_commit(&bar_o_done);
     }
   } else {
     // ===================== softmax / correction / epilogue =====================
-    const int row = mb * kFwdBM + tid;  // query row inside (b,h)
+    const int g = SPLIT ? (warp >> 2) : 0;    // column half owned by this warpgroup
+    const int r = tid & 127;                  // query row inside the tile == TMEM lane
+    const int row = mb * kFwdBM + r;
     const bool row_ok = row < M;
     const int64_t bh = static_cast<int64_t>(b) * p.H + h;
     const float* lam = p.lam + bh * N;
     const float a_i = row_ok ? lam[P + row] * kLog2e : 0.f;
-    const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
-    const uint32_t tS = tbase + lane_base;
-    const uint32_t tO = tbase + lane_base + kColO;
+    const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const uint32_t tS = tbase + lane_base + g * CW;
+    const uint32_t tO = tbase + lane_base + kColO + g * D;
 
     float m_ref = -INFINITY, l_sum = 0.f;
     bool ok = true;
     float negb_next = 0.f;
-    if (n_tiles > 0) {
-      const int col = (nb_hi - 1) * kFwdBN + tid;
+    const bool stager = (g == 0) && (r < BN);  // these threads stage one -b_j each per tile
+    if (n_tiles > 0 && stager) {
+      const int col = (nb_hi - 1) * BN + r;
       negb_next = col < N ? -lam[col] * kLog2e : 0.f;
     }
     for (int it = 0; it < n_tiles; ++it) {
       const int nb = nb_hi - 1 - it;
-      const int col0 = nb * kFwdBN;
-      s_negb[it & 1][tid] = negb_next;
-      mbar_arrive(&bar_negb[it & 1]);
+      const int col0 = nb * BN + g * CW;  // first column of this thread's slice
+      if (g == 0) {
+        if (stager) s_negb[it & 1][r] = negb_next;
+        mbar_arrive(&bar_negb[it & 1]);
+      }
       ok = mbar_wait(&bar_negb[it & 1], (it >> 1) & 1, abortp, p.status, kSiteNegB, it);
       ok = mbar_wait(&bar_s_full, it & 1, abortp, p.status, kSiteSFull, it) && ok;
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      uint32_t sreg[128];
-      tmem_ld32(tS, sreg);
-      tmem_ld32(tS + 32, sreg + 32);
-      tmem_ld32(tS + 64, sreg + 64);
-      tmem_ld32(tS + 96, sreg + 96);
+      uint32_t sreg[CW];
+#pragma unroll
+      for (int c = 0; c < CW; c += 32) tmem_ld32(tS + c, sreg + c);
       tmem_ld_wait();
-      if (it + 1 < n_tiles) {
-        const int col = (nb - 1) * kFwdBN + tid;
+      if (it + 1 < n_tiles && stager) {
+        const int col = (nb - 1) * BN + r;
         negb_next = -lam[col] * kLog2e;  // nb-1 >= nb_lo >= 0 and this tile lies left of the tail
       }
       // ---- pass 1: u = s*scale - b_j, row maximum ----
-      const float4* nb4 = reinterpret_cast<const float4*>(s_negb[it & 1]);
-      const bool need_mask = (col0 + kFwdBN - 1 > P + mb * kFwdBM) || (col0 < seq0) || (col0 + kFwdBN > N);
+      const float4* nb4 = reinterpret_cast<const float4*>(&s_negb[it & 1][g * CW]);
+      const bool need_mask = (col0 + CW - 1 > P + mb * kFwdBM) || (col0 < seq0) || (col0 + CW > N);
       float umax = -INFINITY;
       if (!need_mask) {
 #pragma unroll
-        for (int c4 = 0; c4 < 32; ++c4) {
+        for (int c4 = 0; c4 < CW / 4; ++c4) {
           const float4 nbv = nb4[c4];
           float u0 = fmaf(__uint_as_float(sreg[4 * c4 + 0]), p.qk_scale, nbv.x);
           float u1 = fmaf(__uint_as_float(sreg[4 * c4 + 1]), p.qk_scale, nbv.y);
@@ -259,11 +286,11 @@ fox_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           umax = fmaxf(umax, fmaxf(fmaxf(u0, u1), fmaxf(u2, u3)));
         }
       } else {
-        // valid columns of this row inside the tile: [c_lo, c_hi]
+        // valid columns of this row inside the slice: [c_lo, c_hi]
         const int c_lo = max(seq0 - col0, 0);
-        const int c_hi = row_ok ? min(min(P + row, N - 1) - col0, kFwdBN - 1) : -1;
+        const int c_hi = row_ok ? min(min(P + row, N - 1) - col0, CW - 1) : -1;
 #pragma unroll
-        for (int c4 = 0; c4 < 32; ++c4) {
+        for (int c4 = 0; c4 < CW / 4; ++c4) {
           const float4 nbv = nb4[c4];
           const float nbs[4] = {nbv.x, nbv.y, nbv.z, nbv.w};
 #pragma unroll
@@ -296,10 +323,10 @@ fox_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         m_ref = m_new;
       }
       const float off = a_i - ((m_ref == -INFINITY) ? 0.f : m_ref);
-      // ---- pass 2: p = 2^(u + off), row sum, pack, write back over S ----
+      // ---- pass 2: p = 2^(u + off), row sum, pack, write back over this slice of S ----
       float psum = 0.f;
 #pragma unroll
-      for (int ch = 0; ch < 4; ++ch) {
+      for (int ch = 0; ch < CW / 32; ++ch) {
         uint32_t pk[16];
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
@@ -313,37 +340,66 @@ fox_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       l_sum += psum;
       tmem_st_wait();
       tc_fence_before();
-      mbar_arrive(&bar_p_full);
+      mbar_arrive(&bar_p_full[g]);
     }
 
-    // ---- epilogue: O / l -> 16-bit -> global, L = m ln2 + ln l ----
+    // ---- epilogue: merge the streams, O / l -> 16-bit -> global, L = m ln2 + ln l ----
+    if (SPLIT && g == 1) {
+      s_m1[r] = m_ref;
+      s_l1[r] = l_sum;
+      mbar_arrive(&bar_merge);
+    }
     if (n_tiles > 0 && ok) {
       ok = mbar_wait(&bar_o_done, 0, abortp, p.status, kSiteODone);
       ok = __all_sync(0xffffffffu, ok);
     }
-    if (ok) {
+    if (SPLIT && g == 0 && ok) {
+      ok = mbar_wait(&bar_merge, 0, abortp, p.status, kSiteMerge);
+      ok = __all_sync(0xffffffffu, ok);
+    }
+    if (ok && g == 0) {
       tc_fence_after();
+      float w0 = 1.f, w1 = 0.f;
+      if (SPLIT) {
+        const float m1 = s_m1[r], l1 = s_l1[r];
+        const float m = fmaxf(m_ref, m1);
+        w0 = (m_ref == -INFINITY) ? 0.f : fast_exp2(m_ref - m);
+        w1 = (m1 == -INFINITY) ? 0.f : fast_exp2(m1 - m);
+        l_sum = l_sum * w0 + l1 * w1;
+        m_ref = m;
+      }
       const bool empty = (n_tiles == 0) || (P + row < seq0) || !(l_sum > 0.f);
       const float inv_l = empty ? 0.f : 1.f / l_sum;
+      w0 *= inv_l;
+      w1 *= inv_l;
       uint16_t* orow = reinterpret_cast<uint16_t*>(p.o) + b * p.o_sb + h * p.o_sh + static_cast<int64_t>(row) * p.o_st;
 #pragma unroll
       for (int c = 0; c < D; c += 32) {
-        uint32_t o[32];
+        float o[32];
         if (n_tiles > 0) {
-          tmem_ld32(tO + c, o);
+          uint32_t t0[32];
+          tmem_ld32(tO + c, t0);
           tmem_ld_wait();
-        } else {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) o[j] = 0u;
+          for (int j = 0; j < 32; ++j) o[j] = __uint_as_float(t0[j]) * w0;
+          if (SPLIT) {
+            uint32_t t1[32];
+            tmem_ld32(tO + D + c, t1);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) o[j] = fmaf(__uint_as_float(t1[j]), w1, o[j]);
+          }
         }
         if (row_ok) {
 #pragma unroll
           for (int j = 0; j < 32; j += 8) {
-            uint4 w;
-            w.x = pack2<kBf16>(empty ? 0.f : __uint_as_float(o[j + 0]) * inv_l, empty ? 0.f : __uint_as_float(o[j + 1]) * inv_l);
-            w.y = pack2<kBf16>(empty ? 0.f : __uint_as_float(o[j + 2]) * inv_l, empty ? 0.f : __uint_as_float(o[j + 3]) * inv_l);
-            w.z = pack2<kBf16>(empty ? 0.f : __uint_as_float(o[j + 4]) * inv_l, empty ? 0.f : __uint_as_float(o[j + 5]) * inv_l);
-            w.w = pack2<kBf16>(empty ? 0.f : __uint_as_float(o[j + 6]) * inv_l, empty ? 0.f : __uint_as_float(o[j + 7]) * inv_l);
+            uint4 w = make_uint4(0, 0, 0, 0);
+            if (!empty) {
+              w.x = pack2<kBf16>(o[j + 0], o[j + 1]);
+              w.y = pack2<kBf16>(o[j + 2], o[j + 3]);
+              w.z = pack2<kBf16>(o[j + 4], o[j + 5]);
+              w.w = pack2<kBf16>(o[j + 6], o[j + 7]);
+            }
             *reinterpret_cast<uint4*>(orow + c + j) = w;
           }
         }
@@ -354,10 +410,14 @@ fox_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 4) tmem_dealloc(tbase, kTmemCols);
+  if (warp == kTmaWarp) tmem_dealloc(tbase, kTmemCols);
 }
 
-template <int D, bool kBf16, int STAGES>
+// Tuning hook: 0 = default shapes (D=64: one softmax warpgroup, 128-row KV tiles; D=128: 64-row KV tiles,
+// two stages), 1 = D=128 with 128-row KV tiles, 2 = D=64 with two softmax warpgroups (split columns).
+static int g_fwd_variant = 0;
+
+template <int D, bool kBf16, int BN, int STAGES, int CTAS, bool SPLIT>
 static int launch_fwd(int device, cudaStream_t stream, int64_t B, int64_t H, int64_t M, int64_t N, const fox_tensor4* q,
                       const fox_tensor4* k, const fox_tensor4* v, const FwdParams& prm) {
   CUtensorMap tmQ, tmK, tmV;
@@ -367,10 +427,10 @@ static int launch_fwd(int device, cudaStream_t stream, int64_t B, int64_t H, int
   if (!tma_compatible(tq, 2) || !tma_compatible(tk, 2) || !tma_compatible(tv, 2)) return FOX_ERR_ALIGNMENT;
   int rc;
   if ((rc = cached_tmap_4d(&tmQ, tq, 2, false, kBf16, 64, 128, true))) return rc;
-  if ((rc = cached_tmap_4d(&tmK, tk, 2, false, kBf16, 64, 128, true))) return rc;
-  if ((rc = cached_tmap_4d(&tmV, tv, 2, false, kBf16, 64, 128, true))) return rc;
-  constexpr int smem = (1 + 2 * STAGES) * 128 * D * 2 + 1024;
-  auto kern = fox_attn_fwd_kernel<D, kBf16, STAGES>;
+  if ((rc = cached_tmap_4d(&tmK, tk, 2, false, kBf16, 64, BN, true))) return rc;
+  if ((rc = cached_tmap_4d(&tmV, tv, 2, false, kBf16, 64, BN, true))) return rc;
+  constexpr int smem = 128 * D * 2 + 2 * STAGES * BN * D * 2 + 1024;
+  auto kern = fox_attn_fwd_kernel<D, kBf16, BN, STAGES, CTAS, SPLIT>;
   static bool configured[64] = {};  // per template instance and device
   if (device < 0 || device >= 64) return FOX_ERR_DEVICE;
   if (!configured[device]) {
@@ -378,11 +438,13 @@ static int launch_fwd(int device, cudaStream_t stream, int64_t B, int64_t H, int
     configured[device] = true;
   }
   dim3 grid((unsigned)((M + kFwdBM - 1) / kFwdBM), (unsigned)H, (unsigned)B);
-  kern<<<grid, kFwdThreads, smem, stream>>>(tmQ, tmK, tmV, prm);
+  kern<<<grid, SPLIT ? 320 : 192, smem, stream>>>(tmQ, tmK, tmV, prm);
   return cudaGetLastError() == cudaSuccess ? FOX_OK : FOX_ERR_LAUNCH;
 }
 
 }  // namespace fox
+
+extern "C" void fox_debug_set_fwd_variant(int v) { fox::g_fwd_variant = v; }
 
 extern "C" int fox_attn_fwd(int device, void* stream, int dtype, int64_t B, int64_t H, int64_t M, int64_t N,
                             int64_t D, const fox_tensor4* q, const fox_tensor4* k, const fox_tensor4* v,
@@ -408,6 +470,17 @@ extern "C" int fox_attn_fwd(int device, void* stream, int dtype, int64_t B, int6
   prm.qk_scale = sm_scale * 1.4426950408889634f;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const bool bf = dtype == FOX_DTYPE_BF16;
-  if (D == 64) return bf ? launch_fwd<64, true, 2>(device, st, B, H, M, N, q, k, v, prm) : launch_fwd<64, false, 2>(device, st, B, H, M, N, q, k, v, prm);
-  return bf ? launch_fwd<128, true, 1>(device, st, B, H, M, N, q, k, v, prm) : launch_fwd<128, false, 1>(device, st, B, H, M, N, q, k, v, prm);
+  const int variant = g_fwd_variant;
+  if (D == 64) {
+    if (variant == 2)
+      return bf ? launch_fwd<64, true, 128, 2, 2, true>(device, st, B, H, M, N, q, k, v, prm)
+                : launch_fwd<64, false, 128, 2, 2, true>(device, st, B, H, M, N, q, k, v, prm);
+    return bf ? launch_fwd<64, true, 128, 2, 2, false>(device, st, B, H, M, N, q, k, v, prm)
+              : launch_fwd<64, false, 128, 2, 2, false>(device, st, B, H, M, N, q, k, v, prm);
+  }
+  if (variant == 1)
+    return bf ? launch_fwd<128, true, 128, 1, 2, false>(device, st, B, H, M, N, q, k, v, prm)
+              : launch_fwd<128, false, 128, 1, 2, false>(device, st, B, H, M, N, q, k, v, prm);
+  return bf ? launch_fwd<128, true, 64, 2, 2, false>(device, st, B, H, M, N, q, k, v, prm)
+            : launch_fwd<128, false, 64, 2, 2, false>(device, st, B, H, M, N, q, k, v, prm);
 }

@@ -64,11 +64,11 @@ constexpr uint32_t kWaitTriesBackoff = 20000000u;  // x (>= 32 ns sleep + poll) 
 template <bool kBackoff = false>
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
                                           int* status, int site, int detail = 0) {
+  // fast path: the phase has usually completed already; one plain try_wait costs ~15 cycles
+  if (mbar_try_wait(bar, parity)) return true;
   uint32_t ok;
   const uint32_t addr = smem_u32(bar);
   if (kBackoff) {
-    // producer / issuer / drain warps: sleep between polls so that the poll loop does not take
-    // issue slots from the compute warps that share the scheduler
     asm volatile(
         "{\n\t.reg .pred p, q;\n\t.reg .u32 n;\n\tmov.u32 n, 0;\n"
         "FOX_WAITB_LOOP:\n\t"
