@@ -32,7 +32,6 @@ namespace fox {
 
 constexpr int kBwdBM = FOX_BWD_BLOCK_M;
 constexpr int kBwdBN = FOX_BWD_BLOCK_N;
-constexpr int kBwdThreads = 448;
 constexpr float kLog2eB = 1.4426950408889634f;
 
 struct BwdParams {
@@ -64,8 +63,8 @@ __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float 
                : "memory");
 }
 
-template <int D, bool kBf16, bool kTrace, int kPoly>
-__global__ void __launch_bounds__(kBwdThreads, 1)
+template <int D, bool kBf16, bool kTrace, int kPoly, int kCWG>
+__global__ void __launch_bounds__((4 * kCWG + 6) * 32, 1)
 fox_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                     const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
                     const __grid_constant__ CUtensorMap tmDQ, const BwdParams p) {
@@ -78,6 +77,9 @@ fox_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   constexpr int STDO = (D == 64) ? 2 : 1;
   constexpr int kDsBufs = (D == 64) ? 2 : 1;
   constexpr int kStageSub = (D == 64) ? 2 : 1;  // 32-column fp32 sub-tiles of the dQ staging buffer
+  // warp roles: kCWG compute warpgroups (each owns CW query columns of the tile), producer, issuer, 4 drain warps
+  constexpr int CW = 128 / kCWG;
+  constexpr int kTmaWarp = 4 * kCWG, kMmaWarp = 4 * kCWG + 1, kDrainWarp0 = 4 * kCWG + 2;
   constexpr uint32_t kTmemCols = 512;
   constexpr int kNdk = kColsumMMA ? D + 16 : D;
   constexpr int kNdq = D + 16;
@@ -132,12 +134,12 @@ fox_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     mbar_init(&bar_kv, 1);
     mbar_init(&bar_s_full, 1);
     mbar_init(&bar_dp_full, 1);
-    mbar_init(&bar_p_done, 256);
-    mbar_init(&bar_ds_done, 256);
+    mbar_init(&bar_p_done, 128 * kCWG);
+    mbar_init(&bar_ds_done, 128 * kCWG);
     mbar_init(&bar_dq_full, 1);
     mbar_init(&bar_dq_free, 128);
     mbar_init(&bar_done, 1);
-    mbar_init(&bar_colsum, 128);
+    mbar_init(&bar_colsum, 128 * (kCWG - 1));
     // q_full: the TMA transaction plus one arrival of the producer warp for the per-row vectors
     for (int s = 0; s < STQ; ++s) { mbar_init(&bar_q_full[s], 2); mbar_init(&bar_q_empty[s], 1); }
     for (int s = 0; s < STDO; ++s) { mbar_init(&bar_do_full[s], 1); mbar_init(&bar_do_empty[s], 1); }
@@ -145,7 +147,7 @@ fox_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     mbar_init(&bar_stage_free, 1);
     mbar_fence_init();
   }
-  if (warp == 8) {
+  if (warp == kTmaWarp) {
     tmem_alloc(&tmem_slot, kTmemCols);
     tmem_relinquish();
   }
@@ -169,7 +171,7 @@ fox_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       p.trace[(role * 8 + event) * 16 + it] = clock64();
   };
 
-  if (warp == 8) {
+  if (warp == kTmaWarp) {
     // ===================== TMA producer (whole warp converged, one elected lane issues) =====================
     if (n_tiles > 0) {
       if (elect_one()) {
@@ -256,7 +258,7 @@ fox_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           }
       }
     }
-  } else if (warp == 9) {
+  } else if (warp == kMmaWarp) {
     // ===================== MMA issuer (whole warp converged, one elected lane issues) =====================
     if (n_tiles > 0) {
       constexpr uint32_t idS = umma_idesc(kFmt, 128, 128, 0, 0);
@@ -326,7 +328,7 @@ fox_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         if (elect_one()) {
 #pragma unroll
           for (int kk = 0; kk < 8; ++kk)
-            mma_ts_raw(tbase + kColDV, tbase + kColS + (kk >> 2) * 64 + (kk & 3) * 8,
+            mma_ts_raw(tbase + kColDV, tbase + kColS + ((kk * 16) / CW) * CW + ((kk * 16) % CW) / 2,
                        umma_desc_advance(bdo_mn, kk * 2048), idDV, acc | (kk > 0));
           tc_commit_raw(&bar_do_empty[it % STDO]);
         }
@@ -345,7 +347,7 @@ fox_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         if (elect_one()) {
 #pragma unroll
           for (int kk = 0; kk < 8; ++kk)
-            mma_ts_raw(tbase + kColDK, tbase + kColDP + (kk >> 2) * 64 + (kk & 3) * 8,
+            mma_ts_raw(tbase + kColDK, tbase + kColDP + ((kk * 16) / CW) * CW + ((kk * 16) % CW) / 2,
                        umma_desc_advance(bq_mn, kk * 2048), idDK, acc | (kk > 0));
         }
         __syncwarp();
@@ -382,17 +384,17 @@ fox_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       }
       if (ok) tc_commit(&bar_done);
     }
-  } else if (warp >= 10) {
+  } else if (warp >= kDrainWarp0) {
     // ===================== dQ drain + per-row vectors =====================
     const int quarter = warp & 3;
     const int r = quarter * 32 + lane;  // query row inside the tile == TMEM lane
     const uint32_t tDQ = tbase + (static_cast<uint32_t>(quarter * 32) << 16) + kColDQ;
     bool ok = true;
     for (int it = 0; it < n_tiles; ++it) {
-      if (warp == 10) stamp(1, 0, it);
+      if (warp == kDrainWarp0) stamp(1, 0, it);
       ok = mbar_wait_warp(&bar_dq_full, it & 1, abortp, p.status, kBSiteDq, it);
       if (!ok) break;
-      if (warp == 10) stamp(1, 1, it);
+      if (warp == kDrainWarp0) stamp(1, 1, it);
       tc_fence_after();
       const int i = (mb_lo + it) * kBwdBM + r;
       // The dQ tile goes TMEM -> registers -> swizzled shared memory -> one TMA add-reduction per
@@ -424,7 +426,7 @@ fox_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         }
         fence_proxy_async_smem();
         mbar_arrive(&bar_staged);
-        if (warp == 10) {
+        if (warp == kDrainWarp0) {
           ok = mbar_wait_warp(&bar_staged, n_round & 1, abortp, p.status, kBSiteStaged, it);
           if (!ok) break;
           if (elect_one()) {
@@ -442,13 +444,13 @@ fox_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         }
       }
       if (!ok) break;
-      if (warp == 10) stamp(1, 2, it);
+      if (warp == kDrainWarp0) stamp(1, 2, it);
       if (i < M) atomicAdd(p.dlam_row + bh * M + i, __uint_as_float(rs[0]));
     }
-    if (warp == 10) tma_store_wait_all<0>();
+    if (warp == kDrainWarp0) tma_store_wait_all<0>();
   } else {
     // ===================== compute warps =====================
-    const int g = warp >> 2;              // column half of the query tile
+    const int g = warp >> 2;              // which CW-column slice of the query tile
     const int r = tid & 127;              // KV row inside the tile == TMEM lane
     const int j = nb * kBwdBN + r;
     const bool j_ok = (j < N) && (j >= seq0);
@@ -462,21 +464,21 @@ fox_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 
     for (int it = 0; it < n_tiles; ++it) {
       const int mb = mb_lo + it;
-      stamp(6 + warp, 4, it);
+      if (warp < 8) stamp(6 + warp, 4, it);
       ok = mbar_wait(&bar_s_full, it & 1, abortp, p.status, kBSiteSFull, it);
-      stamp(6 + warp, 6, it);
+      if (warp < 8) stamp(6 + warp, 6, it);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      stamp(6 + warp, 0, it);
+      if (warp < 8) stamp(6 + warp, 0, it);
       // first query column of this tile this KV row may be attended from (causal)
       const int c_min = j - P - mb * kBwdBM;
       const bool diag = (nb * kBwdBN + kBwdBN - 1 - P - mb * kBwdBM) > 0;
-      float pf[64];
+      float pf[CW];
       // ---------------- phase A: probabilities ----------------
 #pragma unroll
-      for (int ch = 0; ch < 2; ++ch) {
-        const int col0 = g * 64 + ch * 32;
+      for (int ch = 0; ch < CW / 32; ++ch) {
+        const int col0 = g * CW + ch * 32;
         uint32_t sreg[32], pk[16];
         tmem_ld32(tS + col0, sreg);
         tmem_ld_wait();
@@ -495,26 +497,26 @@ fox_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           pk[c4 * 2] = pack2<kBf16>(pf[ch * 32 + c4 * 4], pf[ch * 32 + c4 * 4 + 1]);
           pk[c4 * 2 + 1] = pack2<kBf16>(pf[ch * 32 + c4 * 4 + 2], pf[ch * 32 + c4 * 4 + 3]);
         }
-        tmem_st16(tS + g * 64 + ch * 16, pk);  // inside this warpgroup's own (already loaded) S columns
+        tmem_st16(tS + g * CW + ch * 16, pk);  // inside this warpgroup's own (already loaded) S columns
       }
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(&bar_p_done);
-      stamp(6 + warp, 1, it);
+      if (warp < 8) stamp(6 + warp, 1, it);
 
       // ---------------- phase B: dS ----------------
-      stamp(6 + warp, 7, it);
+      if (warp < 8) stamp(6 + warp, 7, it);
       ok = mbar_wait(&bar_dp_full, it & 1, abortp, p.status, kBSiteDpFull, it);
       // dP(it) was issued behind dQ(it - kDsBufs) and a commit covers everything issued before it, so the
       // dS buffer about to be overwritten is no longer being read.
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      stamp(6 + warp, 2, it);
-      uint8_t* drow = sdS + (it % kDsBufs) * 32768 + g * 16384 + r * 128;
+      if (warp < 8) stamp(6 + warp, 2, it);
+      uint8_t* dbuf = sdS + (it % kDsBufs) * 32768 + r * 128;
 #pragma unroll
-      for (int ch = 0; ch < 2; ++ch) {
-        const int col0 = g * 64 + ch * 32;
+      for (int ch = 0; ch < CW / 32; ++ch) {
+        const int col0 = g * CW + ch * 32;
         uint32_t dpreg[32], dsk[16];
         tmem_ld32(tDP + col0, dpreg);
         tmem_ld_wait();
@@ -535,12 +537,12 @@ fox_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             colsum += (r01.x + r01.y) + (r23.x + r23.y);
           }
         }
-        tmem_st16(tDP + g * 64 + ch * 16, dsk);
+        tmem_st16(tDP + g * CW + ch * 16, dsk);
         if (!(p.ablate & 4))
 #pragma unroll
         for (int q4 = 0; q4 < 4; ++q4) {
-          const int cj = ch * 4 + q4;
-          *reinterpret_cast<uint4*>(drow + ((cj ^ (r & 7)) << 4)) =
+          const int cj = ((col0 & 63) >> 3) + q4;
+          *reinterpret_cast<uint4*>(dbuf + (col0 >> 6) * 16384 + ((cj ^ (r & 7)) << 4)) =
               make_uint4(dsk[q4 * 4], dsk[q4 * 4 + 1], dsk[q4 * 4 + 2], dsk[q4 * 4 + 3]);
         }
       }
@@ -548,7 +550,7 @@ fox_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       fence_proxy_async_smem();
       tc_fence_before();
       mbar_arrive(&bar_ds_done);
-      stamp(6 + warp, 3, it);
+      if (warp < 8) stamp(6 + warp, 3, it);
     }
 
     // ---- epilogue: warpgroup 0 writes dK (and the key-side gate gradient), warpgroup 1 writes dV ----
@@ -557,25 +559,34 @@ fox_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       ok = __all_sync(0xffffffffu, ok);
     }
     if (!kColsumMMA && ok) {
-      if (g == 1) {
-        s_e[0][r] = colsum;  // the per-row vectors are dead by now: reuse their buffer
+      // per-thread partial column sums of the kCWG slices -> slice 0 (the per-row vector buffers are dead by now)
+      float* part = (g - 1) < 2 ? &s_e[(g - 1) & 1][0] : &s_delta[0][0];
+      if (g > 0) {
+        part[r] = colsum;
         mbar_arrive(&bar_colsum);
       } else {
         ok = mbar_wait(&bar_colsum, 0, abortp, p.status, kBSiteColsum);
         ok = __all_sync(0xffffffffu, ok);
-        if (ok) colsum += s_e[0][r];
+        if (ok) {
+          colsum += s_e[0][r];
+          if (kCWG > 2) colsum += s_e[1][r] + s_delta[0][r];
+        }
       }
     }
     if (ok) {
+      // warpgroups [0, kCWG/2) write dK, the rest dV; each a D / (kCWG/2) wide column slice
       tc_fence_after();
+      constexpr int kPer = kCWG / 2;
+      constexpr int kCols = D / kPer;
+      const int which = g / kPer, part_c = (g % kPer) * kCols;
       const bool keep = j_ok && n_tiles > 0;
-      const uint32_t tcol = tbase + lane_base + (g == 0 ? kColDK : kColDV);
-      const float sc = g == 0 ? p.sm_scale : 1.f;
-      uint16_t* orow = g == 0
+      const uint32_t tcol = tbase + lane_base + (which == 0 ? kColDK : kColDV) + part_c;
+      const float sc = which == 0 ? p.sm_scale : 1.f;
+      uint16_t* orow = (which == 0
           ? reinterpret_cast<uint16_t*>(p.dk) + b * p.dk_sb + h * p.dk_sh + static_cast<int64_t>(j) * p.dk_st
-          : reinterpret_cast<uint16_t*>(p.dv) + b * p.dv_sb + h * p.dv_sh + static_cast<int64_t>(j) * p.dv_st;
+          : reinterpret_cast<uint16_t*>(p.dv) + b * p.dv_sb + h * p.dv_sh + static_cast<int64_t>(j) * p.dv_st) + part_c;
 #pragma unroll
-      for (int c = 0; c < D; c += 32) {
+      for (int c = 0; c < kCols; c += 32) {
         uint32_t v[32];
         if (n_tiles > 0) {
           tmem_ld32(tcol + c, v);
@@ -609,7 +620,7 @@ fox_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 8) tmem_dealloc(tbase, kTmemCols);
+  if (warp == kTmaWarp) tmem_dealloc(tbase, kTmemCols);
 }
 
 // Debug hook: when set, the next backward launches record clock64 stamps of CTA (0,0,0).
@@ -618,6 +629,8 @@ static long long* g_bwd_trace = nullptr;
 static int g_bwd_mma_depth = 0;
 // Tuning hook: 0 = ex2 unit only, 1 = polynomial only, 2 = every other exponential on the FMA pipe.
 static int g_bwd_poly = 0;
+// Tuning hook: compute warpgroups per CTA (2 or 4).
+static int g_bwd_cwg = 4;
 
 template <int D, bool kBf16>
 static int launch_bwd(int device, cudaStream_t stream, int64_t B, int64_t H, int64_t M, int64_t N,
@@ -644,22 +657,27 @@ static int launch_bwd(int device, cudaStream_t stream, int64_t B, int64_t H, int
   static_assert(smem + 3072 <= 232448, "shared memory budget (tiles + static barriers/vectors rounded to 1 KiB)");
   const bool tracing = prm.trace != nullptr;
   const int poly = g_bwd_poly;
-  auto kern = tracing ? fox_attn_bwd_kernel<D, kBf16, true, 0>
-              : (poly == 1 ? fox_attn_bwd_kernel<D, kBf16, false, 1>
-                 : (poly == 2 ? fox_attn_bwd_kernel<D, kBf16, false, 2> : fox_attn_bwd_kernel<D, kBf16, false, 0>));
-  static bool configured[4][64] = {};
+  const bool wide = g_bwd_cwg == 4;
+  auto kern = tracing ? (wide ? fox_attn_bwd_kernel<D, kBf16, true, 0, 4> : fox_attn_bwd_kernel<D, kBf16, true, 0, 2>)
+              : (poly == 1 ? fox_attn_bwd_kernel<D, kBf16, false, 1, 2>
+                 : (poly == 2 ? fox_attn_bwd_kernel<D, kBf16, false, 2, 2>
+                    : (wide ? fox_attn_bwd_kernel<D, kBf16, false, 0, 4> : fox_attn_bwd_kernel<D, kBf16, false, 0, 2>)));
+  const int threads = ((wide && (tracing || poly == 0)) ? 22 : 14) * 32;
+  static bool configured[8][64] = {};
   if (device < 0 || device >= 64) return FOX_ERR_DEVICE;
-  const int slot = tracing ? 3 : poly;
+  const int slot = (tracing ? 3 : poly) + (wide ? 4 : 0);
   if (!configured[slot][device]) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return FOX_ERR_LAUNCH;
     configured[slot][device] = true;
   }
   dim3 grid((unsigned)((N + kBwdBN - 1) / kBwdBN), (unsigned)H, (unsigned)B);
-  kern<<<grid, kBwdThreads, smem, stream>>>(tmQ, tmK, tmV, tmDO, tmDQ, prm);
+  kern<<<grid, threads, smem, stream>>>(tmQ, tmK, tmV, tmDO, tmDQ, prm);
   return cudaGetLastError() == cudaSuccess ? FOX_OK : FOX_ERR_LAUNCH;
 }
 
 }  // namespace fox
+
+extern "C" void fox_debug_set_bwd_cwg(int n) { fox::g_bwd_cwg = (n == 2) ? 2 : 4; }
 
 extern "C" void fox_debug_set_bwd_poly(int mode) { fox::g_bwd_poly = mode < 0 ? 0 : (mode > 2 ? 2 : mode); }
 

@@ -47,7 +47,7 @@ enum FwdWaitSite {
   kSiteSFull = 16, kSitePFull = 17, kSiteODone = 18, kSiteDrain = 19, kSiteNegB = 20, kSiteMerge = 21
 };
 
-template <int D, bool kBf16, int BN, int STAGES, int CTAS, bool SPLIT>
+template <int D, bool kBf16, int BN, int STAGES, int CTAS, bool SPLIT, bool TWOPASS>
 __global__ void __launch_bounds__(SPLIT ? 320 : 192, CTAS)
 fox_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                     const __grid_constant__ CUtensorMap tmV, const FwdParams p) {
@@ -259,49 +259,48 @@ fox_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      uint32_t sreg[CW];
-#pragma unroll
-      for (int c = 0; c < CW; c += 32) tmem_ld32(tS + c, sreg + c);
-      tmem_ld_wait();
       if (it + 1 < n_tiles && stager) {
         const int col = (nb - 1) * BN + r;
         negb_next = -lam[col] * kLog2e;  // nb-1 >= nb_lo >= 0 and this tile lies left of the tail
       }
-      // ---- pass 1: u = s*scale - b_j, row maximum ----
+      // Two passes over this thread's slice of S, 32 columns at a time.  TWOPASS reads S from TMEM in both
+      // (a TMEM load costs ~50 cycles; holding a 64/128-column slice in registers costs spills):
+      //   pass 1: u = s*scale - b_j (masked on boundary tiles), row maximum
+      //   pass 2: the same u again, p = 2^(u + a_i - m), row sum, pack, write back over S
       const float4* nb4 = reinterpret_cast<const float4*>(&s_negb[it & 1][g * CW]);
       const bool need_mask = (col0 + CW - 1 > P + mb * kFwdBM) || (col0 < seq0) || (col0 + CW > N);
-      float umax = -INFINITY;
-      if (!need_mask) {
+      // valid columns of this row inside the slice: [c_lo, c_hi]
+      const int c_lo = need_mask ? max(seq0 - col0, 0) : 0;
+      const int c_hi = need_mask ? (row_ok ? min(min(P + row, N - 1) - col0, CW - 1) : -1) : CW - 1;
+      auto load_u = [&](int ch, float* u) {
+        uint32_t sreg[32];
+        tmem_ld32(tS + ch * 32, sreg);
+        tmem_ld_wait();
 #pragma unroll
-        for (int c4 = 0; c4 < CW / 4; ++c4) {
-          const float4 nbv = nb4[c4];
-          float u0 = fmaf(__uint_as_float(sreg[4 * c4 + 0]), p.qk_scale, nbv.x);
-          float u1 = fmaf(__uint_as_float(sreg[4 * c4 + 1]), p.qk_scale, nbv.y);
-          float u2 = fmaf(__uint_as_float(sreg[4 * c4 + 2]), p.qk_scale, nbv.z);
-          float u3 = fmaf(__uint_as_float(sreg[4 * c4 + 3]), p.qk_scale, nbv.w);
-          sreg[4 * c4 + 0] = __float_as_uint(u0);
-          sreg[4 * c4 + 1] = __float_as_uint(u1);
-          sreg[4 * c4 + 2] = __float_as_uint(u2);
-          sreg[4 * c4 + 3] = __float_as_uint(u3);
-          umax = fmaxf(umax, fmaxf(fmaxf(u0, u1), fmaxf(u2, u3)));
+        for (int c4 = 0; c4 < 8; ++c4) {
+          const float4 nbv = nb4[ch * 8 + c4];
+          u[4 * c4 + 0] = fmaf(__uint_as_float(sreg[4 * c4 + 0]), p.qk_scale, nbv.x);
+          u[4 * c4 + 1] = fmaf(__uint_as_float(sreg[4 * c4 + 1]), p.qk_scale, nbv.y);
+          u[4 * c4 + 2] = fmaf(__uint_as_float(sreg[4 * c4 + 2]), p.qk_scale, nbv.z);
+          u[4 * c4 + 3] = fmaf(__uint_as_float(sreg[4 * c4 + 3]), p.qk_scale, nbv.w);
         }
-      } else {
-        // valid columns of this row inside the slice: [c_lo, c_hi]
-        const int c_lo = max(seq0 - col0, 0);
-        const int c_hi = row_ok ? min(min(P + row, N - 1) - col0, CW - 1) : -1;
+        if (need_mask) {
 #pragma unroll
-        for (int c4 = 0; c4 < CW / 4; ++c4) {
-          const float4 nbv = nb4[c4];
-          const float nbs[4] = {nbv.x, nbv.y, nbv.z, nbv.w};
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int c = 4 * c4 + e;
-            float u = fmaf(__uint_as_float(sreg[c]), p.qk_scale, nbs[e]);
-            u = (c >= c_lo && c <= c_hi) ? u : -INFINITY;
-            sreg[c] = __float_as_uint(u);
-            umax = fmaxf(umax, u);
+          for (int c = 0; c < 32; ++c) {
+            const int cc = ch * 32 + c;
+            u[c] = (cc >= c_lo && cc <= c_hi) ? u[c] : -INFINITY;
           }
         }
+      };
+      float umax = -INFINITY;
+      float ukeep[TWOPASS ? 1 : CW];  // one-pass form: u stays in registers between the passes
+#pragma unroll
+      for (int ch = 0; ch < CW / 32; ++ch) {
+        float utmp[32];
+        float* u = TWOPASS ? utmp : &ukeep[TWOPASS ? 0 : ch * 32];
+        load_u(ch, u);
+#pragma unroll
+        for (int c = 0; c < 32; c += 4) umax = fmaxf(umax, fmaxf(fmaxf(u[c], u[c + 1]), fmaxf(u[c + 2], u[c + 3])));
       }
       // ---- running maximum with lazy rescaling ----
       const float m_new = fmaxf(m_ref, a_i + umax);
@@ -323,19 +322,21 @@ fox_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         m_ref = m_new;
       }
       const float off = a_i - ((m_ref == -INFINITY) ? 0.f : m_ref);
-      // ---- pass 2: p = 2^(u + off), row sum, pack, write back over this slice of S ----
       float psum = 0.f;
 #pragma unroll
       for (int ch = 0; ch < CW / 32; ++ch) {
+        float utmp[32];
+        float* u = TWOPASS ? utmp : &ukeep[TWOPASS ? 0 : ch * 32];
+        if (TWOPASS) load_u(ch, u);
         uint32_t pk[16];
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
-          const float p0 = fast_exp2(__uint_as_float(sreg[32 * ch + 2 * j]) + off);
-          const float p1 = fast_exp2(__uint_as_float(sreg[32 * ch + 2 * j + 1]) + off);
+          const float p0 = fast_exp2(u[2 * j] + off);
+          const float p1 = fast_exp2(u[2 * j + 1] + off);
           psum += p0 + p1;
           pk[j] = pack2<kBf16>(p0, p1);
         }
-        tmem_st16(tS + ch * 16, pk);
+        tmem_st16(tS + ch * 16, pk);  // columns already consumed by this thread
       }
       l_sum += psum;
       tmem_st_wait();
@@ -413,11 +414,11 @@ fox_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   if (warp == kTmaWarp) tmem_dealloc(tbase, kTmemCols);
 }
 
-// Tuning hook: 0 = default shapes (D=64: one softmax warpgroup, 128-row KV tiles; D=128: 64-row KV tiles,
-// two stages), 1 = D=128 with 128-row KV tiles, 2 = D=64 with two softmax warpgroups (split columns).
+// Shapes: D=64 -> 128-row KV tiles, two softmax warpgroups with independent streams, S re-read from TMEM;
+// D=128 -> 64-row KV tiles, two stages, one softmax warpgroup.  Tuning hook: 1 = D=64 with one warpgroup.
 static int g_fwd_variant = 0;
 
-template <int D, bool kBf16, int BN, int STAGES, int CTAS, bool SPLIT>
+template <int D, bool kBf16, int BN, int STAGES, int CTAS, bool SPLIT, bool TWOPASS>
 static int launch_fwd(int device, cudaStream_t stream, int64_t B, int64_t H, int64_t M, int64_t N, const fox_tensor4* q,
                       const fox_tensor4* k, const fox_tensor4* v, const FwdParams& prm) {
   CUtensorMap tmQ, tmK, tmV;
@@ -430,7 +431,7 @@ static int launch_fwd(int device, cudaStream_t stream, int64_t B, int64_t H, int
   if ((rc = cached_tmap_4d(&tmK, tk, 2, false, kBf16, 64, BN, true))) return rc;
   if ((rc = cached_tmap_4d(&tmV, tv, 2, false, kBf16, 64, BN, true))) return rc;
   constexpr int smem = 128 * D * 2 + 2 * STAGES * BN * D * 2 + 1024;
-  auto kern = fox_attn_fwd_kernel<D, kBf16, BN, STAGES, CTAS, SPLIT>;
+  auto kern = fox_attn_fwd_kernel<D, kBf16, BN, STAGES, CTAS, SPLIT, TWOPASS>;
   static bool configured[64] = {};  // per template instance and device
   if (device < 0 || device >= 64) return FOX_ERR_DEVICE;
   if (!configured[device]) {
@@ -472,15 +473,12 @@ extern "C" int fox_attn_fwd(int device, void* stream, int dtype, int64_t B, int6
   const bool bf = dtype == FOX_DTYPE_BF16;
   const int variant = g_fwd_variant;
   if (D == 64) {
-    if (variant == 2)
-      return bf ? launch_fwd<64, true, 128, 2, 2, true>(device, st, B, H, M, N, q, k, v, prm)
-                : launch_fwd<64, false, 128, 2, 2, true>(device, st, B, H, M, N, q, k, v, prm);
-    return bf ? launch_fwd<64, true, 128, 2, 2, false>(device, st, B, H, M, N, q, k, v, prm)
-              : launch_fwd<64, false, 128, 2, 2, false>(device, st, B, H, M, N, q, k, v, prm);
+    if (variant == 1)
+      return bf ? launch_fwd<64, true, 128, 2, 2, false, true>(device, st, B, H, M, N, q, k, v, prm)
+                : launch_fwd<64, false, 128, 2, 2, false, true>(device, st, B, H, M, N, q, k, v, prm);
+    return bf ? launch_fwd<64, true, 128, 2, 2, true, true>(device, st, B, H, M, N, q, k, v, prm)
+              : launch_fwd<64, false, 128, 2, 2, true, true>(device, st, B, H, M, N, q, k, v, prm);
   }
-  if (variant == 1)
-    return bf ? launch_fwd<128, true, 128, 1, 2, false>(device, st, B, H, M, N, q, k, v, prm)
-              : launch_fwd<128, false, 128, 1, 2, false>(device, st, B, H, M, N, q, k, v, prm);
-  return bf ? launch_fwd<128, true, 64, 2, 2, false>(device, st, B, H, M, N, q, k, v, prm)
-            : launch_fwd<128, false, 64, 2, 2, false>(device, st, B, H, M, N, q, k, v, prm);
+  return bf ? launch_fwd<128, true, 64, 2, 2, false, false>(device, st, B, H, M, N, q, k, v, prm)
+            : launch_fwd<128, false, 64, 2, 2, false, false>(device, st, B, H, M, N, q, k, v, prm);
 }
