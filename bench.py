@@ -300,6 +300,57 @@ def run_ours(args, w, wname):
             dist.all_reduce(t2, op=dist.ReduceOp.MAX)
         e2e_val = world * flops / (float(t2.item()) / n_e2e * 1e-3) / 1e12
 
+    # ---- pruning statistics and dense comparison (ACP workloads) ----
+    acp = None
+    if thr is not None:
+        with torch.no_grad():
+            _, _, si = ops.ForgettingAttention.apply(q, k, v, lf, seq_d, True, None, thr, False, True, None, False, False)
+        T = w["T"]
+        nmb = si.shape[-1]
+        hi = torch.clamp((torch.arange(nmb, device=dev) + 1) * 128, max=T)
+        skipped = (torch.minimum(si, hi[None, None, :]) // 128).sum().item()
+        total = float(torch.ceil(hi / 128).sum().item()) * si.shape[0] * si.shape[1]
+        pfrac = skipped / total
+        n_off = max(3, min(args.steps, 5))
+
+        def step_off():
+            q.grad = k.grad = v.grad = lf.grad = None
+            out = fox.forgetting_attention(q, k, v, lf, head_first=True, seq_start=seq_d, adaptive_threshold=None)
+            out.backward(dout)
+
+        step_off()
+        barrier()
+        e0.record()
+        for _ in range(n_off):
+            step_off()
+        e1.record()
+        barrier()
+        ms_off = e0.elapsed_time(e1) / n_off
+        acp = {"pruned_tile_fraction": pfrac, "ms_per_step_pruning_off": ms_off, "speedup": ms_off / ms_per_step,
+               "speedup_predicted_by_pruned_fraction": 1.0 / max(1.0 - pfrac, 1e-9),
+               "executed_tflops": value * (1.0 - pfrac)}
+
+    # ---- HBM-bound kernels: fused per-head RMSNorm + gate at the FoX-Pro layer shape ----
+    normgate = None
+    if world == 1 and not args.no_e2e:
+        tokens, G, Dh = 65536, 24, 64
+        m = fox.FusedGroupNormGated(G, G * Dh, is_rms_norm=True, eps=1e-6, activation="sigmoid").to(dev)
+        x = torch.randn(1, tokens, G * Dh, device=dev, dtype=torch.bfloat16).requires_grad_()
+        gate = torch.randn(1, tokens, G * Dh, device=dev, dtype=torch.bfloat16).requires_grad_()
+        dy = torch.randn(1, tokens, G * Dh, device=dev, dtype=torch.bfloat16)
+        for _ in range(3):
+            m(x, gate).backward(dy)
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+        tf = tb = 0.0
+        for _ in range(10):
+            ev[0].record(); y = m(x, gate); ev[1].record(); y.backward(dy); ev[2].record()
+            torch.cuda.synchronize()
+            tf += ev[0].elapsed_time(ev[1]); tb += ev[1].elapsed_time(ev[2])
+        n_el = tokens * G * Dh
+        normgate = {"shape": "tokens 65536 x 24 heads x 64", "fwd_ms": tf / 10, "bwd_ms": tb / 10,
+                    "fwd_gbs": (6 * n_el + 4 * tokens * G) / (tf / 10 * 1e-3) / 1e9,
+                    "bwd_gbs_incl_host_dw_sum": (10 * n_el + 4 * tokens * G) / (tb / 10 * 1e-3) / 1e9}
+
     if rank == 0:
         peaks = load_peaks()
         bwd_n, bwd_ms = kern.get("fox_attn_bwd", (0, float("nan")))
@@ -333,6 +384,19 @@ def run_ours(args, w, wname):
             "gpu_launches": launches,
             "clocks": clocks,
         }
+        if acp is not None:
+            line["acp"] = acp
+        if normgate is not None:
+            normgate["frac_of_hbm_peak_fwd"] = normgate["fwd_gbs"] / peaks["hbm_gbs"]
+            line["normgate"] = normgate
+        n_vec = w["B"] * w["H"] * w["T"]
+        aux = {}
+        for name, bytes_ in (("fox_cumsum_fwd", 8 * n_vec), ("fox_revcumsum", 12 * n_vec),
+                             ("fox_bwd_delta", 2 * 2 * n_vec * w["D"] + 4 * n_vec),
+                             ("fox_dq_convert", 6 * n_vec * w["D"])):
+            if name in kern:
+                aux[name] = {"ms": kern[name][1], "gbs": bytes_ / (kern[name][1] * 1e-3) / 1e9}
+        line["hbm_kernels"] = aux
         if world == 1 and not args.no_cpu:
             dt, fl, desc = cpu_sample(w, os.cpu_count() or 1)
             line["cpu_baseline"] = {"value": fl / dt / 1e12, "unit": UNIT, "cores": os.cpu_count() or 1,

@@ -6,12 +6,13 @@
 // which recompute S and dP twice (seven products per pair).
 //
 // One CTA = one (batch, head, 128-row KV tile); it keeps K and V resident and
-// streams the query tiles from the causal diagonal downwards.  448 threads:
-//   warps 0-7  : compute.  Thread (g = warp/4, r = tid%128) owns KV row r (TMEM lane r
-//                of S^T / dP^T) and the 64 query columns [64g, 64g+64) of the tile.
-//   warp  8    : TMA producer          warp 9 : tcgen05.mma issuer
-//   warps 10-13: dQ drain.  Thread owns one query row of the dQ tile accumulator,
-//                adds it into the fp32 workspace and stages the per-row vectors.
+// streams the query tiles from the causal diagonal downwards.  704 threads:
+//   warps 0-15 : compute.  Thread (g = warp/4, r = tid%128) owns KV row r (TMEM lane r
+//                of S^T / dP^T) and the 32 query columns [32g, 32g+32) of the tile; four
+//                warps per scheduler are what it takes to keep the ex2 unit busy.
+//   warp  16   : TMA producer (also stages the per-row vectors)    warp 17 : tcgen05.mma issuer
+//   warps 18-21: dQ drain.  Thread owns one query row of the dQ tile accumulator: TMEM ->
+//                swizzled shared memory -> TMA add-reduction into the fp32 workspace.
 // Per pair i (all products 128-wide, fp32 accumulation in TMEM):
 //   S^T = K Q^T ; dP^T = V dO^T                         (smem x smem)
 //   phase A: P^T = 2^(S^T c + (L_i-corrected bias))      -> 16-bit, written over S^T
@@ -48,7 +49,6 @@ struct BwdParams {
   int* status;
   long long* trace;          // optional (debug builds of the kernel only): clock64 stamps of CTA (0,0,0)
   int H, M, N;
-  int ablate;                // timing experiments only: bit0 no dQ reductions, bit1 no exp/math, bit2 no dS smem stores
   float sm_scale, qk_scale;
 };
 
@@ -63,7 +63,7 @@ __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float 
                : "memory");
 }
 
-template <int D, bool kBf16, bool kTrace, int kPoly, int kCWG>
+template <int D, bool kBf16, bool kTrace, int kCWG>
 __global__ void __launch_bounds__((4 * kCWG + 6) * 32, 1)
 fox_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                     const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
@@ -430,14 +430,12 @@ fox_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           ok = mbar_wait_warp(&bar_staged, n_round & 1, abortp, p.status, kBSiteStaged, it);
           if (!ok) break;
           if (elect_one()) {
-            if (!(p.ablate & 1)) {
 #pragma unroll
-              for (int sub = 0; sub < kStageSub; ++sub)
-                tma_reduce_add_4d(&tmDQ, sStage + sub * 16384, (round * kStageSub + sub) * 32,
-                                  (mb_lo + it) * kBwdBM, h, b);
-              tma_store_commit();
-              tma_store_wait_read<0>();
-            }
+            for (int sub = 0; sub < kStageSub; ++sub)
+              tma_reduce_add_4d(&tmDQ, sStage + sub * 16384, (round * kStageSub + sub) * 32, (mb_lo + it) * kBwdBM,
+                                h, b);
+            tma_store_commit();
+            tma_store_wait_read<0>();
             mbar_arrive(&bar_stage_free);
           }
           __syncwarp();
@@ -490,7 +488,7 @@ fox_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
             const float x = fmaf(__uint_as_float(sreg[c4 * 4 + e]), p.qk_scale, es[e]) - b_j;
-            float pe = (p.ablate & 2) ? x : ((kPoly == 1 || (kPoly == 2 && (e & 1))) ? exp2_poly(x) : fast_exp2(x));
+            float pe = fast_exp2(x);
             if (diag) pe = (col0 + c4 * 4 + e >= c_min) ? pe : 0.f;
             pf[ch * 32 + c4 * 4 + e] = pe;
           }
@@ -538,7 +536,6 @@ fox_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           }
         }
         tmem_st16(tDP + g * CW + ch * 16, dsk);
-        if (!(p.ablate & 4))
 #pragma unroll
         for (int q4 = 0; q4 < 4; ++q4) {
           const int cj = ((col0 & 63) >> 3) + q4;
@@ -625,12 +622,6 @@ fox_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 
 // Debug hook: when set, the next backward launches record clock64 stamps of CTA (0,0,0).
 static long long* g_bwd_trace = nullptr;
-// Tuning hook: MMA groups (of four) in flight; 1..7.
-static int g_bwd_mma_depth = 0;
-// Tuning hook: 0 = ex2 unit only, 1 = polynomial only, 2 = every other exponential on the FMA pipe.
-static int g_bwd_poly = 0;
-// Tuning hook: compute warpgroups per CTA (2 or 4).
-static int g_bwd_cwg = 4;
 
 template <int D, bool kBf16>
 static int launch_bwd(int device, cudaStream_t stream, int64_t B, int64_t H, int64_t M, int64_t N,
@@ -656,16 +647,12 @@ static int launch_bwd(int device, cudaStream_t stream, int64_t B, int64_t H, int
   constexpr int smem = (2 + kStQ + kStDO) * 128 * D * 2 + kDsBufs * 32768 + 16384 + kStageSub * 16384;
   static_assert(smem + 3072 <= 232448, "shared memory budget (tiles + static barriers/vectors rounded to 1 KiB)");
   const bool tracing = prm.trace != nullptr;
-  const int poly = g_bwd_poly;
-  const bool wide = g_bwd_cwg == 4;
-  auto kern = tracing ? (wide ? fox_attn_bwd_kernel<D, kBf16, true, 0, 4> : fox_attn_bwd_kernel<D, kBf16, true, 0, 2>)
-              : (poly == 1 ? fox_attn_bwd_kernel<D, kBf16, false, 1, 2>
-                 : (poly == 2 ? fox_attn_bwd_kernel<D, kBf16, false, 2, 2>
-                    : (wide ? fox_attn_bwd_kernel<D, kBf16, false, 0, 4> : fox_attn_bwd_kernel<D, kBf16, false, 0, 2>)));
-  const int threads = ((wide && (tracing || poly == 0)) ? 22 : 14) * 32;
-  static bool configured[8][64] = {};
+  constexpr int kCWG = 4;  // compute warpgroups per CTA (2 was measured no faster at D=64 and slower at D=128)
+  auto kern = tracing ? fox_attn_bwd_kernel<D, kBf16, true, kCWG> : fox_attn_bwd_kernel<D, kBf16, false, kCWG>;
+  const int threads = (4 * kCWG + 6) * 32;
+  static bool configured[2][64] = {};
   if (device < 0 || device >= 64) return FOX_ERR_DEVICE;
-  const int slot = (tracing ? 3 : poly) + (wide ? 4 : 0);
+  const int slot = tracing ? 1 : 0;
   if (!configured[slot][device]) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return FOX_ERR_LAUNCH;
     configured[slot][device] = true;
@@ -676,12 +663,6 @@ static int launch_bwd(int device, cudaStream_t stream, int64_t B, int64_t H, int
 }
 
 }  // namespace fox
-
-extern "C" void fox_debug_set_bwd_cwg(int n) { fox::g_bwd_cwg = (n == 2) ? 2 : 4; }
-
-extern "C" void fox_debug_set_bwd_poly(int mode) { fox::g_bwd_poly = mode < 0 ? 0 : (mode > 2 ? 2 : mode); }
-
-extern "C" void fox_debug_set_bwd_mma_depth(int depth) { fox::g_bwd_mma_depth = depth; }
 
 extern "C" void fox_debug_set_bwd_trace(void* device_buffer) { fox::g_bwd_trace = static_cast<long long*>(device_buffer); }
 
@@ -713,7 +694,6 @@ extern "C" int fox_attn_bwd(int device, void* stream, int dtype, int64_t B, int6
   prm.dv = dv->ptr; prm.dv_sb = dv->sb; prm.dv_sh = dv->sh; prm.dv_st = dv->st;
   prm.status = status;
   prm.trace = g_bwd_trace;
-  prm.ablate = g_bwd_mma_depth;
   prm.H = (int)H; prm.M = (int)M; prm.N = (int)N;
   prm.sm_scale = sm_scale;
   prm.qk_scale = sm_scale * 1.4426950408889634f;

@@ -363,22 +363,6 @@ __device__ __forceinline__ float2 unpack2(uint32_t u) {
     return __half22float2(*reinterpret_cast<__half2*>(&u));
   }
 }
-// 2^x on the FMA pipe (no MUFU): floor(x) by a round-down add of 1.5*2^23, a degree-3 polynomial
-// for 2^frac (max relative error 7.5e-5, fitted for this library) and the exponent put in with one
-// integer shift-add.  Valid for |x| <= 126; smaller inputs are clamped (result 2^-126).
-// The ex2 unit does 16 results per clock per SM against 128 FMA lanes, and its instructions share
-// the scheduler's memory-I/O queue with shared-memory, TMEM and MMA instructions, so moving part
-// of the exponentials here relieves both.
-__device__ __forceinline__ float exp2_poly(float x) {
-  x = fmaxf(x, -126.f);
-  float r;
-  asm("add.rm.ftz.f32 %0, %1, %2;" : "=f"(r) : "f"(x), "f"(12582912.f));
-  const float f = x - (r - 12582912.f);
-  float p = fmaf(f, 0.07802452f, 0.22606716f);
-  p = fmaf(p, f, 0.69583356f);
-  p = fmaf(p, f, 0.9999252f);
-  return __uint_as_float(__float_as_uint(p) + (__float_as_uint(r) << 23));
-}
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
