@@ -201,7 +201,7 @@ def run_reference(args, w, wname):
         "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line), flush=True)
+    _emit(line)
 
 
 # --------------------------------------------------------------------------- GPU arm
@@ -218,6 +218,9 @@ def run_ours(args, w, wname):
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
+        # NCCL prints its version banner on stdout at NCCL_DEBUG=VERSION/INFO; stdout carries the JSON line only
+        if os.environ.get("NCCL_DEBUG", "").upper() in ("VERSION", "INFO", "TRACE"):
+            os.environ["NCCL_DEBUG"] = "WARN"
         dist.init_process_group("nccl", device_id=dev)
     _lib.load()
 
@@ -404,7 +407,7 @@ def run_ours(args, w, wname):
             dt, fl, desc = cpu_sample(w, os.cpu_count() or 1)
             line["cpu_baseline"] = {"value": fl / dt / 1e12, "unit": UNIT, "cores": os.cpu_count() or 1,
                                     "kind": "port", "sample": desc, "seconds": dt}
-        print(json.dumps(line), flush=True)
+        _emit(line)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
@@ -422,7 +425,21 @@ TRAFFIC_BYTES_PER_LAUNCH = {
 }
 
 
+def _emit(line: dict) -> None:
+    """Write the one JSON line to the real stdout (see main: fd 1 is pointed at stderr while the
+    benchmark runs so that library banners, e.g. NCCL's version line, cannot land next to it)."""
+    data = (json.dumps(line) + "\n").encode()
+    os.write(_REAL_STDOUT if _REAL_STDOUT is not None else 1, data)
+
+
+_REAL_STDOUT = None
+
+
 def main():
+    global _REAL_STDOUT
+    sys.stdout.flush()
+    _REAL_STDOUT = os.dup(1)
+    os.dup2(2, 1)
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
