@@ -45,7 +45,7 @@ _SIGNATURES = {
     "fox_bwd_delta": (c_int, [c_int, c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, _T4P, _T4P, _F]),
     "fox_dq_convert": (c_int, [c_int, c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, _F, c_float, _T4P]),
     "fox_attn_fwd": (c_int, [c_int, c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, c_int64, _T4P, _T4P, _T4P,
-                             _F, _F, _F, c_float, _T4P, _F, _F]),
+                             _F, _F, _F, c_float, _T4P, _F, _F, _F]),
     "fox_attn_bwd": (c_int, [c_int, c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, c_int64, _T4P, _T4P, _T4P,
                              _T4P, _F, _F, _F, _F, _F, c_float, _F, _F, _F, _T4P, _T4P, _F]),
     "fox_attn_bwd_noalloc": (c_int, [c_int, c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, c_int64, _T4P, _T4P,

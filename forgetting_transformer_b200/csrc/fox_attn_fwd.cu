@@ -29,6 +29,9 @@ constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 // the reference maximum is only moved when it is off by more than 2^kLazyShift
 constexpr float kLazyShift = 8.0f;
+// A tile whose logits are provably below (reference maximum + this many octaves) skips the maximum pass
+// altogether: p <= 2^shift stays far inside fp32 / bf16 range (fp16 P: 2^14 < 65504).
+constexpr float kSkipShiftBf16 = 32.0f, kSkipShiftFp16 = 14.0f;
 
 struct FwdParams {
   const float* lam;            // (B,H,N) inclusive prefix of the log gates
@@ -40,14 +43,33 @@ struct FwdParams {
   int* status;
   int H, M, N;
   float qk_scale;              // sm_scale * log2(e)
+  const float* k_norm_max;     // (B,H) max_t ||k[b,h,t,:]||_2, or nullptr: lets a tile skip its maximum pass
 };
+
+// How many of every 4 column pairs take the FMA-pipe exponential instead of the ex2 unit (measured best:
+// a quarter at D=64, where four softmax warps share a scheduler, half at D=128 with two).
+#ifndef FOX_POLYQ64
+#define FOX_POLYQ64 1
+#endif
+#ifndef FOX_POLYQ128
+#define FOX_POLYQ128 2
+#endif
+
+// Debug builds with -DFOX_FWD_TRACE record clock64 stamps of CTA (0,0,0), tiles 32..47:
+// trace[(role * 8 + event) * 16 + tile - 32], role = softmax warp index or 8 for the MMA issuer.
+#ifdef FOX_FWD_TRACE
+__device__ long long g_fwd_trace[16 * 8 * 16];
+#define STAMP(role, ev, it) do { if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0 && (it) >= 32 && (it) < 48) g_fwd_trace[((role) * 8 + (ev)) * 16 + (it) - 32] = clock64(); } while (0)
+#else
+#define STAMP(role, ev, it)
+#endif
 
 enum FwdWaitSite {
   kSiteQFull = 11, kSiteKFull = 12, kSiteVFull = 13, kSiteKEmpty = 14, kSiteVEmpty = 15,
   kSiteSFull = 16, kSitePFull = 17, kSiteODone = 18, kSiteDrain = 19, kSiteNegB = 20, kSiteMerge = 21
 };
 
-template <int D, bool kBf16, int BN, int STAGES, int CTAS, bool SPLIT, bool TWOPASS>
+template <int D, bool kBf16, int BN, int STAGES, int CTAS, bool SPLIT, bool PREF>
 __global__ void __launch_bounds__(SPLIT ? 320 : 192, CTAS)
 fox_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                     const __grid_constant__ CUtensorMap tmV, const FwdParams p) {
@@ -68,11 +90,12 @@ fox_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   constexpr int kTmaWarp = 4 * kWG, kMmaWarp = 4 * kWG + 1;
 
   extern __shared__ uint8_t smem_raw[];
-  __shared__ uint64_t bar_q_full, bar_s_full, bar_o_done, bar_merge;
-  __shared__ uint64_t bar_p_full[2];
+  __shared__ uint64_t bar_q_full, bar_o_done, bar_merge;
+  __shared__ uint64_t bar_s_full[2], bar_p_full[2];
   __shared__ uint64_t bar_k_full[STAGES], bar_k_empty[STAGES], bar_v_full[STAGES], bar_v_empty[STAGES];
-  __shared__ uint64_t bar_negb[2];
-  __shared__ __align__(16) float s_negb[2][BN];  // read as float4
+  __shared__ uint64_t bar_negb[2][2];
+  __shared__ __align__(16) float s_negb[2][2][CW];  // [warpgroup][tile parity][column]; read as float4
+  __shared__ float s_nbmax[2][2][4];  // per stager warp: maximum of its 32 staged -b_j
   __shared__ float s_m1[128], s_l1[128];
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
@@ -103,13 +126,14 @@ fox_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   if (tid == 0) {
     abort_flag = 0;
     mbar_init(&bar_q_full, 1);
-    mbar_init(&bar_s_full, 1);
-    mbar_init(&bar_p_full[0], 128);
-    mbar_init(&bar_p_full[1], 128);
+    for (int g = 0; g < 2; ++g) {
+      mbar_init(&bar_s_full[g], 1);
+      mbar_init(&bar_p_full[g], 128);
+      mbar_init(&bar_negb[g][0], 128);
+      mbar_init(&bar_negb[g][1], 128);
+    }
     mbar_init(&bar_o_done, 1);
     mbar_init(&bar_merge, 128);
-    mbar_init(&bar_negb[0], 128);
-    mbar_init(&bar_negb[1], 128);
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&bar_k_full[s], 1);
       mbar_init(&bar_k_empty[s], 1);
@@ -181,36 +205,52 @@ fox_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   } else if (warp == kMmaWarp) {
     // ===================== MMA issuer (whole warp converged, one elected lane issues) =====================
     if (n_tiles > 0) {
-      constexpr uint32_t idQK = umma_idesc(kFmt, 128, BN, 0, 0);
+      // Every softmax warpgroup g has its own chain S_g -> P_g -> O_g += P_g V_g -> S_g(next tile): the S
+      // product is issued per column slice right behind the P V product that frees the slice, so a
+      // warpgroup never waits for the other one.
+      constexpr uint32_t idQK = umma_idesc(kFmt, 128, CW, 0, 0);
       constexpr uint32_t idPV = umma_idesc(kFmt, 128, D, 0, 1);
       // descriptors are built once; the loops only move the start-address field
       const uint64_t dQ = umma_desc_kmajor(smem_u32(sQ));
       const uint64_t dK0 = umma_desc_kmajor(smem_u32(sK));
       const uint64_t dV0 = umma_desc_mnmajor(smem_u32(sV), kSubBytes);
+      auto issue_s = [&](int g, int st) {  // S[:, g CW : (g+1) CW] = Q K[g CW : (g+1) CW, :]^T
+        const uint64_t dK = umma_desc_advance(dK0, st * kTileBytes + g * CW * 128);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk)
+          mma_ss_raw(tbase + g * CW, umma_desc_advance(dQ, (kk >> 2) * 16384 + (kk & 3) * 32),
+                     umma_desc_advance(dK, (kk >> 2) * kSubBytes + (kk & 3) * 32), idQK, kk > 0);
+        tc_commit_raw(&bar_s_full[g]);
+      };
       bool ok = mbar_wait_warp(&bar_q_full, 0, abortp, p.status, kSiteQFull);
+      ok = ok && mbar_wait_warp(&bar_k_full[0], 0, abortp, p.status, kSiteKFull, 0);
+      if (ok) {
+        tc_fence_after();
+        if (elect_one()) {
+#pragma unroll
+          for (int g = 0; g < kWG; ++g) issue_s(g, 0);
+          tc_commit_raw(&bar_k_empty[0]);
+        }
+        __syncwarp();
+      }
       for (int it = 0; it < n_tiles && ok; ++it) {
         const int st = it % STAGES;
         const uint32_t ph = (it / STAGES) & 1;
-        ok = mbar_wait_warp(&bar_k_full[st], ph, abortp, p.status, kSiteKFull, it);
-        if (!ok) break;
-        tc_fence_after();
-        const uint64_t dK = umma_desc_advance(dK0, st * kTileBytes);
-        if (elect_one()) {
-#pragma unroll
-          for (int kk = 0; kk < D / 16; ++kk)
-            mma_ss_raw(tbase, umma_desc_advance(dQ, (kk >> 2) * 16384 + (kk & 3) * 32),
-                       umma_desc_advance(dK, (kk >> 2) * kSubBytes + (kk & 3) * 32), idQK, kk > 0);
-          tc_commit_raw(&bar_s_full);
-          tc_commit_raw(&bar_k_empty[st]);
-        }
-        __syncwarp();
+        const bool more = it + 1 < n_tiles;
+        const int st1 = (it + 1) % STAGES;
         ok = mbar_wait_warp(&bar_v_full[st], ph, abortp, p.status, kSiteVFull, it);
         if (!ok) break;
+        if (more) {
+          ok = mbar_wait_warp(&bar_k_full[st1], ((it + 1) / STAGES) & 1, abortp, p.status, kSiteKFull, it + 1);
+          if (!ok) break;
+        }
         const uint64_t dV = umma_desc_advance(dV0, st * kTileBytes);
 #pragma unroll
         for (int g = 0; g < kWG; ++g) {
+          STAMP(8, g * 3 + 0, it);
           ok = mbar_wait_warp(&bar_p_full[g], it & 1, abortp, p.status, kSitePFull, it);
           if (!ok) break;
+          STAMP(8, g * 3 + 1, it);
           tc_fence_after();
           if (elect_one()) {
             // O_g += P[:, g CW : (g+1) CW] V[g CW : (g+1) CW, :]; the 16-bit P sits at S columns g CW ...
@@ -218,9 +258,14 @@ fox_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             for (int kk = 0; kk < CW / 16; ++kk)
               mma_ts_raw(tbase + kColO + g * D, tbase + g * CW + kk * 8,
                          umma_desc_advance(dV, (g * (CW / 16) + kk) * 2048), idPV, (it > 0 || kk > 0) ? 1u : 0u);
-            if (g == kWG - 1) tc_commit_raw(&bar_v_empty[st]);
+            if (more) issue_s(g, st1);
+            if (g == kWG - 1) {
+              tc_commit_raw(&bar_v_empty[st]);
+              if (more) tc_commit_raw(&bar_k_empty[st1]);
+            }
           }
           __syncwarp();
+          STAMP(8, g * 3 + 2, it);
         }
         if (!ok) break;
       }
@@ -241,107 +286,174 @@ fox_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 
     float m_ref = -INFINITY, l_sum = 0.f;
     bool ok = true;
-    float negb_next = 0.f;
-    const bool stager = (g == 0) && (r < BN);  // these threads stage one -b_j each per tile
+    // the prefix of the next tile's column is fetched one tile ahead and only scaled when it is staged, so
+    // that the global load's latency is not waited for inside the tile
+    float lam_next = 0.f;
+    const bool stager = r < CW;  // these threads stage one -b_j of the warpgroup's slice per tile
     if (n_tiles > 0 && stager) {
-      const int col = (nb_hi - 1) * BN + r;
-      negb_next = col < N ? -lam[col] * kLog2e : 0.f;
+      const int col = (nb_hi - 1) * BN + g * CW + r;
+      lam_next = col < N ? lam[col] : 0.f;
     }
-    for (int it = 0; it < n_tiles; ++it) {
+    // Upper bound of this row's scaled logits q_i.k_j*c <= ||q_i|| max_j||k_j|| c (Cauchy-Schwarz): with the
+    // largest -b_j of a tile it tells, before S is even read, that no logit of the tile can exceed the
+    // reference maximum by more than the skip shift; then the maximum pass over S is not run.
+    const bool dead = !row_ok || (P + row < seq0);  // rows without any valid column never need a maximum
+    float qbound = INFINITY;
+    if (p.k_norm_max != nullptr && n_tiles > 1) {
+      ok = mbar_wait(&bar_q_full, 0, abortp, p.status, kSiteQFull);
+      float ss = 0.f;
+#pragma unroll
+      for (int sub = 0; sub < kSub; ++sub) {
+#pragma unroll
+        for (int ch = 0; ch < 8; ++ch) {
+          const uint4 w = *reinterpret_cast<const uint4*>(sQ + sub * 16384 + r * 128 + ((ch ^ (r & 7)) << 4));
+          const float2 f0 = unpack2<kBf16>(w.x), f1 = unpack2<kBf16>(w.y), f2 = unpack2<kBf16>(w.z), f3 = unpack2<kBf16>(w.w);
+          ss = fmaf(f0.x, f0.x, ss); ss = fmaf(f0.y, f0.y, ss);
+          ss = fmaf(f1.x, f1.x, ss); ss = fmaf(f1.y, f1.y, ss);
+          ss = fmaf(f2.x, f2.x, ss); ss = fmaf(f2.y, f2.y, ss);
+          ss = fmaf(f3.x, f3.x, ss); ss = fmaf(f3.y, f3.y, ss);
+        }
+      }
+      qbound = sqrtf(ss) * p.k_norm_max[bh] * fabsf(p.qk_scale) * 1.0001f + a_i;
+    }
+    constexpr float kSkipShift = kBf16 ? kSkipShiftBf16 : kSkipShiftFp16;
+    constexpr int kPolyQ = (D == 64) ? FOX_POLYQ64 : FOX_POLYQ128;
+    const float2 scale2 = make_float2(p.qk_scale, p.qk_scale);
+    for (int it = 0; it < n_tiles && ok; ++it) {
       const int nb = nb_hi - 1 - it;
       const int col0 = nb * BN + g * CW;  // first column of this thread's slice
-      if (g == 0) {
-        if (stager) s_negb[it & 1][r] = negb_next;
-        mbar_arrive(&bar_negb[it & 1]);
+      STAMP(warp, 0, it);
+      if (stager) {
+        const float negb = -lam_next * kLog2e;
+        s_negb[g][it & 1][r] = negb;
+        float mx = negb;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        if (lane == 0) s_nbmax[g][it & 1][warp & 3] = mx;
       }
-      ok = mbar_wait(&bar_negb[it & 1], (it >> 1) & 1, abortp, p.status, kSiteNegB, it);
-      ok = mbar_wait(&bar_s_full, it & 1, abortp, p.status, kSiteSFull, it) && ok;
+      mbar_arrive(&bar_negb[g][it & 1]);
+      ok = mbar_wait(&bar_negb[g][it & 1], (it >> 1) & 1, abortp, p.status, kSiteNegB, it);
+      ok = mbar_wait(&bar_s_full[g], it & 1, abortp, p.status, kSiteSFull, it) && ok;
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
+      STAMP(warp, 1, it);
       tc_fence_after();
       if (it + 1 < n_tiles && stager) {
-        const int col = (nb - 1) * BN + r;
-        negb_next = -lam[col] * kLog2e;  // nb-1 >= nb_lo >= 0 and this tile lies left of the tail
+        const int col = (nb - 1) * BN + g * CW + r;
+        lam_next = lam[col];  // nb-1 >= nb_lo >= 0 and this tile lies left of the tail
       }
-      // Two passes over this thread's slice of S, 32 columns at a time.  TWOPASS reads S from TMEM in both
-      // (a TMEM load costs ~50 cycles; holding a 64/128-column slice in registers costs spills):
+      // Two passes over this thread's slice of S, 32 columns at a time, in packed two-wide fp32 arithmetic.
+      // Both read S from TMEM (a TMEM load costs ~50 cycles; holding a 64/128-column slice in registers
+      // costs spills):
       //   pass 1: u = s*scale - b_j (masked on boundary tiles), row maximum
-      //   pass 2: the same u again, p = 2^(u + a_i - m), row sum, pack, write back over S
-      const float4* nb4 = reinterpret_cast<const float4*>(&s_negb[it & 1][g * CW]);
+      //   pass 2: p = 2^(s*scale - b_j + a_i - m), row sum, pack, write back over S
+      const float4* nb4 = reinterpret_cast<const float4*>(&s_negb[g][it & 1][0]);
       const bool need_mask = (col0 + CW - 1 > P + mb * kFwdBM) || (col0 < seq0) || (col0 + CW > N);
       // valid columns of this row inside the slice: [c_lo, c_hi]
       const int c_lo = need_mask ? max(seq0 - col0, 0) : 0;
       const int c_hi = need_mask ? (row_ok ? min(min(P + row, N - 1) - col0, CW - 1) : -1) : CW - 1;
-      auto load_u = [&](int ch, float* u) {
-        uint32_t sreg[32];
-        tmem_ld32(tS + ch * 32, sreg);
+      // S chunks of 32 columns go through two register buffers: with PREF the load of chunk ch+1 is issued
+      // before chunk ch is worked on, which hides the TMEM latency at the price of 32 registers
+      uint32_t sbuf[PREF ? 2 : 1][32];
+      auto fetch = [&](int ch) { tmem_ld32(tS + ch * 32, sbuf[PREF ? (ch & 1) : 0]); };
+      auto load_u = [&](int ch, float2* u, const bool with_add, const float2 add) {  // u[16] = 32 columns
+        if (!PREF || ch == 0) fetch(ch);
         tmem_ld_wait();
+        if (PREF && ch + 1 < CW / 32) fetch(ch + 1);
+        const uint32_t* sreg = sbuf[PREF ? (ch & 1) : 0];
 #pragma unroll
         for (int c4 = 0; c4 < 8; ++c4) {
           const float4 nbv = nb4[ch * 8 + c4];
-          u[4 * c4 + 0] = fmaf(__uint_as_float(sreg[4 * c4 + 0]), p.qk_scale, nbv.x);
-          u[4 * c4 + 1] = fmaf(__uint_as_float(sreg[4 * c4 + 1]), p.qk_scale, nbv.y);
-          u[4 * c4 + 2] = fmaf(__uint_as_float(sreg[4 * c4 + 2]), p.qk_scale, nbv.z);
-          u[4 * c4 + 3] = fmaf(__uint_as_float(sreg[4 * c4 + 3]), p.qk_scale, nbv.w);
+          float2 n0 = make_float2(nbv.x, nbv.y), n1 = make_float2(nbv.z, nbv.w);
+          if (with_add) {
+            n0 = __fadd2_rn(n0, add);
+            n1 = __fadd2_rn(n1, add);
+          }
+          u[2 * c4 + 0] = __ffma2_rn(make_float2(__uint_as_float(sreg[4 * c4 + 0]), __uint_as_float(sreg[4 * c4 + 1])), scale2, n0);
+          u[2 * c4 + 1] = __ffma2_rn(make_float2(__uint_as_float(sreg[4 * c4 + 2]), __uint_as_float(sreg[4 * c4 + 3])), scale2, n1);
         }
         if (need_mask) {
 #pragma unroll
-          for (int c = 0; c < 32; ++c) {
-            const int cc = ch * 32 + c;
-            u[c] = (cc >= c_lo && cc <= c_hi) ? u[c] : -INFINITY;
+          for (int c = 0; c < 16; ++c) {
+            const int cc = ch * 32 + 2 * c;
+            u[c].x = (cc >= c_lo && cc <= c_hi) ? u[c].x : -INFINITY;
+            u[c].y = (cc + 1 >= c_lo && cc + 1 <= c_hi) ? u[c].y : -INFINITY;
           }
         }
       };
-      float umax = -INFINITY;
-      float ukeep[TWOPASS ? 1 : CW];  // one-pass form: u stays in registers between the passes
+      float nbmax = s_nbmax[g][it & 1][0];
 #pragma unroll
-      for (int ch = 0; ch < CW / 32; ++ch) {
-        float utmp[32];
-        float* u = TWOPASS ? utmp : &ukeep[TWOPASS ? 0 : ch * 32];
-        load_u(ch, u);
+      for (int w = 1; w < CW / 32; ++w) nbmax = fmaxf(nbmax, s_nbmax[g][it & 1][w]);
+      // (NaN or -inf reference -> false -> the maximum pass runs)
+      const bool skip1 = __all_sync(0xffffffffu, dead || (qbound + nbmax <= m_ref + kSkipShift));
+      if (!skip1) {
+        float umax = -INFINITY;
 #pragma unroll
-        for (int c = 0; c < 32; c += 4) umax = fmaxf(umax, fmaxf(fmaxf(u[c], u[c + 1]), fmaxf(u[c + 2], u[c + 3])));
-      }
-      // ---- running maximum with lazy rescaling ----
-      const float m_new = fmaxf(m_ref, a_i + umax);
-      const bool need = (m_new - m_ref) > kLazyShift;  // false when both are -inf (NaN compare)
-      if (__any_sync(0xffffffffu, need)) {
-        const float alpha = (m_new == -INFINITY) ? 1.f : fast_exp2(m_ref - m_new);
-        l_sum *= alpha;
-        if (it > 0) {
+        for (int ch = 0; ch < CW / 32; ++ch) {
+          float2 u[16];
+          load_u(ch, u, false, make_float2(0.f, 0.f));
 #pragma unroll
-          for (int c = 0; c < D; c += 32) {
-            uint32_t o[32];
-            tmem_ld32(tO + c, o);
-            tmem_ld_wait();
-#pragma unroll
-            for (int j = 0; j < 32; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * alpha);
-            tmem_st32(tO + c, o);
-          }
+          for (int c = 0; c < 16; ++c) umax = fmax3(umax, u[c].x, u[c].y);
         }
-        m_ref = m_new;
+        STAMP(warp, 2, it);
+        // ---- running maximum with lazy rescaling ----
+        const float m_new = fmaxf(m_ref, a_i + umax);
+        const bool need = (m_new - m_ref) > kLazyShift;  // false when both are -inf (NaN compare)
+        if (__any_sync(0xffffffffu, need)) {
+          const float alpha = (m_new == -INFINITY) ? 1.f : fast_exp2(m_ref - m_new);
+          l_sum *= alpha;
+          if (it > 0) {
+            const float2 alpha2 = make_float2(alpha, alpha);
+#pragma unroll
+            for (int c = 0; c < D; c += 32) {
+              uint32_t o[32];
+              tmem_ld32(tO + c, o);
+              tmem_ld_wait();
+#pragma unroll
+              for (int j = 0; j < 32; j += 2) {
+                const float2 t = __fmul2_rn(make_float2(__uint_as_float(o[j]), __uint_as_float(o[j + 1])), alpha2);
+                o[j] = __float_as_uint(t.x);
+                o[j + 1] = __float_as_uint(t.y);
+              }
+              tmem_st32(tO + c, o);
+            }
+          }
+          m_ref = m_new;
+        }
       }
+      STAMP(warp, 3, it);
       const float off = a_i - ((m_ref == -INFINITY) ? 0.f : m_ref);
-      float psum = 0.f;
+      const float2 off2 = make_float2(off, off);
+      float2 psum = make_float2(0.f, 0.f);
 #pragma unroll
       for (int ch = 0; ch < CW / 32; ++ch) {
-        float utmp[32];
-        float* u = TWOPASS ? utmp : &ukeep[TWOPASS ? 0 : ch * 32];
-        if (TWOPASS) load_u(ch, u);
+        float2 u[16];
+        load_u(ch, u, true, off2);
         uint32_t pk[16];
+        if (kPolyQ > 0 && !need_mask) {
+          // kPolyQ of every 4 column pairs take the FMA-pipe exponential instead of the ex2 unit
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const float p0 = fast_exp2(u[2 * j] + off);
-          const float p1 = fast_exp2(u[2 * j + 1] + off);
-          psum += p0 + p1;
-          pk[j] = pack2<kBf16>(p0, p1);
+          for (int j = 0; j < 16; ++j) {
+            const float2 pp = ((j & 3) < kPolyQ) ? poly_exp2_x2(u[j]) : make_float2(fast_exp2(u[j].x), fast_exp2(u[j].y));
+            psum = __fadd2_rn(psum, pp);
+            pk[j] = pack2<kBf16>(pp.x, pp.y);
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const float2 pp = make_float2(fast_exp2(u[j].x), fast_exp2(u[j].y));
+            psum = __fadd2_rn(psum, pp);
+            pk[j] = pack2<kBf16>(pp.x, pp.y);
+          }
         }
         tmem_st16(tS + ch * 16, pk);  // columns already consumed by this thread
       }
-      l_sum += psum;
+      l_sum += psum.x + psum.y;
+      STAMP(warp, 4, it);
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(&bar_p_full[g]);
+      STAMP(warp, 5, it);
     }
 
     // ---- epilogue: merge the streams, O / l -> 16-bit -> global, L = m ln2 + ln l ----
@@ -414,11 +526,18 @@ fox_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   if (warp == kTmaWarp) tmem_dealloc(tbase, kTmemCols);
 }
 
-// Shapes: D=64 -> 128-row KV tiles, two softmax warpgroups with independent streams, S re-read from TMEM;
-// D=128 -> 64-row KV tiles, two stages, one softmax warpgroup.  Tuning hook: 1 = D=64 with one warpgroup.
+// Shapes: D=64 -> 128-row KV tiles in two stages, two softmax warpgroups with independent streams;
+// D=128 -> 128-row KV tiles in a single K and a single V buffer (K is free again once S is computed, V once
+// P V is, so the next tile's copies overlap the softmax), one softmax warpgroup, S chunks prefetched.
+// Tuning hook: 1 = D=64 with one warpgroup, 2 = D=128 with 64-row KV tiles in two stages.
 static int g_fwd_variant = 0;
+#ifdef FOX_FWD_TRACE
+extern "C" int fox_debug_read_fwd_trace(long long* host) {
+  return cudaMemcpyFromSymbol(host, g_fwd_trace, sizeof(g_fwd_trace));
+}
+#endif
 
-template <int D, bool kBf16, int BN, int STAGES, int CTAS, bool SPLIT, bool TWOPASS>
+template <int D, bool kBf16, int BN, int STAGES, int CTAS, bool SPLIT, bool PREF>
 static int launch_fwd(int device, cudaStream_t stream, int64_t B, int64_t H, int64_t M, int64_t N, const fox_tensor4* q,
                       const fox_tensor4* k, const fox_tensor4* v, const FwdParams& prm) {
   CUtensorMap tmQ, tmK, tmV;
@@ -431,7 +550,7 @@ static int launch_fwd(int device, cudaStream_t stream, int64_t B, int64_t H, int
   if ((rc = cached_tmap_4d(&tmK, tk, 2, false, kBf16, 64, BN, true))) return rc;
   if ((rc = cached_tmap_4d(&tmV, tv, 2, false, kBf16, 64, BN, true))) return rc;
   constexpr int smem = 128 * D * 2 + 2 * STAGES * BN * D * 2 + 1024;
-  auto kern = fox_attn_fwd_kernel<D, kBf16, BN, STAGES, CTAS, SPLIT, TWOPASS>;
+  auto kern = fox_attn_fwd_kernel<D, kBf16, BN, STAGES, CTAS, SPLIT, PREF>;
   static bool configured[64] = {};  // per template instance and device
   if (device < 0 || device >= 64) return FOX_ERR_DEVICE;
   if (!configured[device]) {
@@ -450,7 +569,8 @@ extern "C" void fox_debug_set_fwd_variant(int v) { fox::g_fwd_variant = v; }
 extern "C" int fox_attn_fwd(int device, void* stream, int dtype, int64_t B, int64_t H, int64_t M, int64_t N,
                             int64_t D, const fox_tensor4* q, const fox_tensor4* k, const fox_tensor4* v,
                             const float* log_lambda, const int64_t* seq_start, const int64_t* start_index,
-                            float sm_scale, const fox_tensor4* o, float* L, int32_t* status) {
+                            float sm_scale, const fox_tensor4* o, float* L, const float* k_norm_max,
+                            int32_t* status) {
   using namespace fox;
   if (!q || !k || !v || !o || !q->ptr || !k->ptr || !v->ptr || !o->ptr || !log_lambda || !L || !status)
     return FOX_ERR_BAD_ARG;
@@ -469,16 +589,20 @@ extern "C" int fox_attn_fwd(int device, void* stream, int dtype, int64_t B, int6
   prm.status = status;
   prm.H = (int)H; prm.M = (int)M; prm.N = (int)N;
   prm.qk_scale = sm_scale * 1.4426950408889634f;
+  prm.k_norm_max = k_norm_max;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const bool bf = dtype == FOX_DTYPE_BF16;
   const int variant = g_fwd_variant;
   if (D == 64) {
     if (variant == 1)
-      return bf ? launch_fwd<64, true, 128, 2, 2, false, true>(device, st, B, H, M, N, q, k, v, prm)
-                : launch_fwd<64, false, 128, 2, 2, false, true>(device, st, B, H, M, N, q, k, v, prm);
-    return bf ? launch_fwd<64, true, 128, 2, 2, true, true>(device, st, B, H, M, N, q, k, v, prm)
-              : launch_fwd<64, false, 128, 2, 2, true, true>(device, st, B, H, M, N, q, k, v, prm);
+      return bf ? launch_fwd<64, true, 128, 2, 2, false, false>(device, st, B, H, M, N, q, k, v, prm)
+                : launch_fwd<64, false, 128, 2, 2, false, false>(device, st, B, H, M, N, q, k, v, prm);
+    return bf ? launch_fwd<64, true, 128, 2, 2, true, false>(device, st, B, H, M, N, q, k, v, prm)
+              : launch_fwd<64, false, 128, 2, 2, true, false>(device, st, B, H, M, N, q, k, v, prm);
   }
-  return bf ? launch_fwd<128, true, 64, 2, 2, false, false>(device, st, B, H, M, N, q, k, v, prm)
-            : launch_fwd<128, false, 64, 2, 2, false, false>(device, st, B, H, M, N, q, k, v, prm);
+  if (variant == 2)
+    return bf ? launch_fwd<128, true, 64, 2, 2, false, false>(device, st, B, H, M, N, q, k, v, prm)
+              : launch_fwd<128, false, 64, 2, 2, false, false>(device, st, B, H, M, N, q, k, v, prm);
+  return bf ? launch_fwd<128, true, 128, 1, 2, false, true>(device, st, B, H, M, N, q, k, v, prm)
+            : launch_fwd<128, false, 128, 1, 2, false, true>(device, st, B, H, M, N, q, k, v, prm);
 }

@@ -363,6 +363,32 @@ __device__ __forceinline__ float2 unpack2(uint32_t u) {
     return __half22float2(*reinterpret_cast<__half2*>(&u));
   }
 }
+// 2^x for two values on the FMA pipe (no ex2 unit): x = n + f with n = round(x), f in [-0.5, 0.5];
+// 2^f by a cubic (relative error 7.5e-5, below 16-bit rounding), 2^n by adding n to the exponent
+// field.  x is clamped to >= -125 (result 2^-125 instead of a denormal or zero); x must stay below 2^22.
+__device__ __forceinline__ float2 poly_exp2_x2(float2 x) {
+  const float2 magic = make_float2(12582912.f, 12582912.f);  // 1.5 * 2^23: the sum's low mantissa bits hold n
+  x.x = fmaxf(x.x, -125.f);
+  x.y = fmaxf(x.y, -125.f);
+  const float2 xr = __fadd2_rn(x, magic);
+  const float2 n = __fadd2_rn(xr, make_float2(-12582912.f, -12582912.f));
+  const float2 f = __ffma2_rn(n, make_float2(-1.f, -1.f), x);
+  float2 p = __ffma2_rn(make_float2(0.0551716685f, 0.0551716685f), f, make_float2(0.24261114f, 0.24261114f));
+  p = __ffma2_rn(p, f, make_float2(0.693260968f, 0.693260968f));
+  p = __ffma2_rn(p, f, make_float2(0.999928057f, 0.999928057f));
+  float2 r;
+  r.x = __int_as_float(__float_as_int(p.x) + (__float_as_int(xr.x) << 23));
+  r.y = __int_as_float(__float_as_int(p.y) + (__float_as_int(xr.y) << 23));
+  return r;
+}
+
+// three-input maximum (one instruction on sm_100)
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));

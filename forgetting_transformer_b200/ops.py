@@ -78,16 +78,17 @@ def _tma_view(x: torch.Tensor) -> torch.Tensor:
     return x if _lib.tma_ready(x) else x.contiguous()
 
 
-def max_row_norm(x: torch.Tensor) -> torch.Tensor:
+def max_row_norm(x: torch.Tensor, keep_fp32: bool = False) -> torch.Tensor:
     """max_t ||x[b,h,t,:]||_2 in x's dtype, i.e.
-    ``torch.linalg.vector_norm(x, dim=-1).max(dim=-1).values`` (upstream lines 95-96)."""
+    ``torch.linalg.vector_norm(x, dim=-1).max(dim=-1).values`` (upstream lines 95-96);
+    ``keep_fp32`` returns the unrounded fp32 maxima."""
     lib = _lib.load()
     B, H, T, D = x.shape
     x = _tma_view(x)
     out = torch.zeros((B, H), dtype=torch.float32, device=x.device)
     _call("fox_max_row_norm", lib.fox_max_row_norm, x.device.index, _stream(), _lib.dtype_code(x.dtype), B, H, T,
           D, _lib.t4(x), out.data_ptr())
-    return out.to(x.dtype)
+    return out if keep_fp32 else out.to(x.dtype)
 
 
 def log_lambda_cumsum(log_fgate: torch.Tensor, seq_start: Optional[torch.Tensor],
@@ -156,12 +157,15 @@ class ForgettingAttention(torch.autograd.Function):
         with torch.cuda.device(q.device):
             dev = q.device
             q, k, v = _tma_view(q), _tma_view(k), _tma_view(v)
+            # largest key norm per (b,h): the forward kernel's bound that lets most tiles skip the row-maximum pass
+            need_auto = isinstance(adaptive_threshold, str)
+            k_norm_max = max_row_norm(k, keep_fp32=True) if (N >= 8 * FWD_BLOCK[1] or need_auto) else None
 
             if adaptive_threshold is not None:
                 if isinstance(adaptive_threshold, str):
                     assert adaptive_threshold == "auto", f'adaptive_threshold must be either the string "auto", a float, or a Tensor, but got {adaptive_threshold}.'
                     max_q_norm = max_row_norm(q)
-                    max_k_norm = max_row_norm(k)
+                    max_k_norm = k_norm_max.to(k.dtype)
                     logit_upper_bound = max_q_norm * max_k_norm * sm_scale
                     tolerance = -10
                     adaptive_threshold = -(2 * logit_upper_bound + math.log(N)) + tolerance
@@ -192,7 +196,8 @@ class ForgettingAttention(torch.autograd.Function):
             status = _lib.status_buffer(dev)
             _call("fox_attn_fwd", lib.fox_attn_fwd, dev.index, _stream(), _lib.dtype_code(q.dtype), B, H, M, N, D,
                   _lib.t4(q), _lib.t4(k), _lib.t4(v), log_lambda.data_ptr(), _lib.ptr(seq_start),
-                  _lib.ptr(start_index), float(sm_scale), _lib.t4(o), L.data_ptr(), status.data_ptr())
+                  _lib.ptr(start_index), float(sm_scale), _lib.t4(o), L.data_ptr(), _lib.ptr(k_norm_max),
+                  status.data_ptr())
             if _DEBUG_SYNC:
                 _lib.check_status(dev)
 

@@ -100,11 +100,14 @@ int fox_max_row_norm(int device, void* stream, int dtype, int64_t B, int64_t H, 
  * fox_cumsum_fwd.  seq_start (B,) int64 or NULL.  start_index from fox_find_index with
  * FOX_FWD_BLOCK_M/N, or NULL for no pruning.  Writes o (same dtype, caller's strides) and the
  * log-normaliser L (B,H,M) fp32 (natural log; -inf for rows left of seq_start, whose output is
- * 0).  status: int32[4], zero on entry; [0] != 0 after the kernel means a bounded wait ran out. */
+ * 0).  k_norm_max: (B,H) fp32 from fox_max_row_norm(k), or NULL; with it a KV tile whose logits
+ * are provably (Cauchy-Schwarz + the gate prefix) no more than 2^32 (fp16: 2^14) above the row's
+ * running reference skips its row-maximum pass, which changes no result beyond fp32 rounding.
+ * status: int32[4], zero on entry; [0] != 0 after the kernel means a bounded wait ran out. */
 int fox_attn_fwd(int device, void* stream, int dtype, int64_t B, int64_t H, int64_t M, int64_t N, int64_t D,
                  const fox_tensor4* q, const fox_tensor4* k, const fox_tensor4* v, const float* log_lambda,
                  const int64_t* seq_start, const int64_t* start_index, float sm_scale, const fox_tensor4* o,
-                 float* L, int32_t* status);
+                 float* L, const float* k_norm_max, int32_t* status);
 
 /* delta[b,h,m] = sum_d o[b,h,m,d] * d_o[b,h,m,d] in fp32: replaces _bwd_preprocess
  * (forgetting_attention.py:267-277, kernel 902-943). */
