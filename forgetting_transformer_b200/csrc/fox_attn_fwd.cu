@@ -69,16 +69,16 @@ enum FwdWaitSite {
   kSiteSFull = 16, kSitePFull = 17, kSiteODone = 18, kSiteDrain = 19, kSiteNegB = 20, kSiteMerge = 21
 };
 
-template <int D, bool kBf16, int BN, int STAGES, int CTAS, bool SPLIT, bool PREF>
-__global__ void __launch_bounds__(SPLIT ? 320 : 192, CTAS)
+template <int D, bool kBf16, int BN, int STAGES, int CTAS, int NWG, bool PREF>
+__global__ void __launch_bounds__(128 * NWG + 64, CTAS)
 fox_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                     const __grid_constant__ CUtensorMap tmV, const FwdParams p) {
   // KV tiles of BN rows (64 or 128; the pruning grid stays 128 wide, BN = 64 just walks it in halves).
-  // SPLIT: two softmax warpgroups per CTA, each owning half of the tile's columns with its own running
-  // maximum, row sum and O accumulator (two independent online-softmax streams, merged in the epilogue),
-  // so that four softmax warps per scheduler hide each other's ex2 / TMEM latency without any exchange
-  // between the warpgroups inside the loop.
-  constexpr int kWG = SPLIT ? 2 : 1;
+  // NWG softmax warpgroups per CTA, each owning a BN / NWG wide column slice of every tile with its own
+  // running maximum, row sum and O accumulator (independent online-softmax streams, merged in the
+  // epilogue), so that several softmax warps per scheduler hide each other's ex2 / TMEM latency without
+  // any exchange between the warpgroups inside the loop.
+  constexpr int kWG = NWG;
   constexpr int CW = BN / kWG;              // columns per softmax thread
   constexpr int kQBytes = 128 * D * 2;      // Q tile: D/64 swizzled [128][64] sub-tiles
   constexpr int kTileBytes = BN * D * 2;    // K / V tile: D/64 swizzled [BN][64] sub-tiles
@@ -86,17 +86,21 @@ fox_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   constexpr int kSub = D / 64;
   constexpr uint32_t kFmt = kBf16 ? 1u : 0u;
   constexpr uint32_t kColO = BN;            // S (fp32) in columns [0, BN), O_g in [BN + g D, BN + (g+1) D)
-  constexpr uint32_t kTmemCols = (BN + kWG * D <= 128) ? 128 : ((BN + kWG * D <= 256) ? 256 : 512);
+  constexpr uint32_t kTmemCols = (kColO + kWG * D <= 128) ? 128 : ((kColO + kWG * D <= 256) ? 256 : 512);
+  static_assert(kColO + kWG * D <= 512, "TMEM budget");
   constexpr int kTmaWarp = 4 * kWG, kMmaWarp = 4 * kWG + 1;
 
   extern __shared__ uint8_t smem_raw[];
   __shared__ uint64_t bar_q_full, bar_o_done, bar_merge;
-  __shared__ uint64_t bar_s_full[2], bar_p_full[2];
+  __shared__ uint64_t bar_s_full[NWG], bar_p_full[NWG];  // per warpgroup
   __shared__ uint64_t bar_k_full[STAGES], bar_k_empty[STAGES], bar_v_full[STAGES], bar_v_empty[STAGES];
-  __shared__ uint64_t bar_negb[2][2];
-  __shared__ __align__(16) float s_negb[2][2][CW];  // [warpgroup][tile parity][column]; read as float4
-  __shared__ float s_nbmax[2][2][4];  // per stager warp: maximum of its 32 staged -b_j
-  __shared__ float s_m1[128], s_l1[128];
+  // -b_j = -Lambda_j log2(e) of a tile's columns and the maximum over each warpgroup's slice, staged by the
+  // producer warp one tile ahead in a ring of three (slot of tile t is reused for t+3, which the producer
+  // stages only after O += P V of tile t+1 or later has retired, i.e. after every reader of tile t is done)
+  __shared__ uint64_t bar_negb[3];
+  __shared__ __align__(16) float s_negb[3][BN];  // read as float4
+  __shared__ float s_nbmax[3][NWG];
+  __shared__ float s_mg[NWG][128], s_lg[NWG][128];  // every stream's (m, l) for the merge
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
 
@@ -126,14 +130,13 @@ fox_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   if (tid == 0) {
     abort_flag = 0;
     mbar_init(&bar_q_full, 1);
-    for (int g = 0; g < 2; ++g) {
+    for (int g = 0; g < NWG; ++g) {
       mbar_init(&bar_s_full[g], 1);
       mbar_init(&bar_p_full[g], 128);
-      mbar_init(&bar_negb[g][0], 128);
-      mbar_init(&bar_negb[g][1], 128);
     }
+    for (int i = 0; i < 3; ++i) mbar_init(&bar_negb[i], 1);
     mbar_init(&bar_o_done, 1);
-    mbar_init(&bar_merge, 128);
+    mbar_init(&bar_merge, 128 * NWG);
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&bar_k_full[s], 1);
       mbar_init(&bar_k_empty[s], 1);
@@ -165,39 +168,72 @@ fox_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       }
       __syncwarp();
       int issued = 0;
-      for (int it = 0; it < n_tiles; ++it) {
+      // K(it), V(it) per tile, each into stage it % STAGES once the product that read its previous
+      // occupant has retired
+      auto load_kv = [&](bool is_v, int it) -> bool {
         const int nb = nb_hi - 1 - it;
         const int st = it % STAGES;
         const uint32_t ph = (it / STAGES) & 1;
-        if (!mbar_wait_warp(&bar_k_empty[st], ph ^ 1, abortp, p.status, kSiteKEmpty, it)) break;
+        uint64_t* empty = is_v ? &bar_v_empty[st] : &bar_k_empty[st];
+        uint64_t* full = is_v ? &bar_v_full[st] : &bar_k_full[st];
+        STAMP(9, is_v ? 2 : 0, it);
+        if (!mbar_wait_warp(empty, ph ^ 1, abortp, p.status, is_v ? kSiteVEmpty : kSiteKEmpty, it)) return false;
+        STAMP(9, is_v ? 3 : 1, it);
         if (elect_one()) {
-          mbar_expect_tx(&bar_k_full[st], kTileBytes);
+          mbar_expect_tx(full, kTileBytes);
 #pragma unroll
           for (int s = 0; s < kSub; ++s)
-            tma_load_4d(sK + st * kTileBytes + s * kSubBytes, &tmK, &bar_k_full[st], s * 64, nb * BN, h, b);
+            tma_load_4d((is_v ? sV : sK) + st * kTileBytes + s * kSubBytes, is_v ? &tmV : &tmK, full, s * 64, nb * BN, h, b);
         }
         __syncwarp();
-        issued = it * 2 + 1;
-        if (!mbar_wait_warp(&bar_v_empty[st], ph ^ 1, abortp, p.status, kSiteVEmpty, it)) break;
-        if (elect_one()) {
-          mbar_expect_tx(&bar_v_full[st], kTileBytes);
+        return true;
+      };
+      // gate prefixes of a tile's columns: lane l holds columns 4l .. 4l+3 (lanes < BN/4)
+      const float* lam = p.lam + (static_cast<int64_t>(b) * p.H + h) * N;
+      float lamv[4] = {0.f, 0.f, 0.f, 0.f};
+      auto fetch_lam = [&](int it) {
+        const int c0 = (nb_hi - 1 - it) * BN + 4 * lane;
 #pragma unroll
-          for (int s = 0; s < kSub; ++s)
-            tma_load_4d(sV + st * kTileBytes + s * kSubBytes, &tmV, &bar_v_full[st], s * 64, nb * BN, h, b);
-        }
+        for (int e = 0; e < 4; ++e) lamv[e] = (4 * lane < BN && c0 + e < N) ? ldg_f32_here(lam + c0 + e) : 0.f;
+      };
+      auto stage_negb = [&](int it) {  // from lamv, fetched earlier for this tile
+        const int slot = it % 3;
+        float4 nbv = make_float4(-lamv[0] * kLog2e, -lamv[1] * kLog2e, -lamv[2] * kLog2e, -lamv[3] * kLog2e);
+        if (4 * lane < BN) *reinterpret_cast<float4*>(&s_negb[slot][4 * lane]) = nbv;
+        float mx = fmaxf(fmaxf(nbv.x, nbv.y), fmaxf(nbv.z, nbv.w));
+#pragma unroll
+        for (int o = CW / 8; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        if (4 * lane < BN && (4 * lane) % CW == 0) s_nbmax[slot][(4 * lane) / CW] = mx;
         __syncwarp();
-        issued = it * 2 + 2;
+        if (lane == 0) mbar_arrive(&bar_negb[slot]);
+        __syncwarp();
+      };
+      fetch_lam(0);
+      stage_negb(0);
+      if (n_tiles > 1) fetch_lam(1);
+      for (int it = 0; it < n_tiles; ++it) {
+        if (!load_kv(false, it)) break;
+        ++issued;
+        if (!load_kv(true, it)) break;  // waits for O += P V of tile it-STAGES
+        ++issued;
+        if (it + 1 < n_tiles) {
+          stage_negb(it + 1);
+          if (it + 2 < n_tiles) fetch_lam(it + 2);
+        }
       }
       if (*abortp && lane == 0) {
-        // error path only: let the copies already in flight land before the CTA retires
+        // error path only: let the copies already in flight land before the CTA retires (at most 2 STAGES
+        // are outstanding; a wait on a phase that completed earlier returns at once or runs into the limit)
         const long long t0 = clock64();
         while (!mbar_try_wait(&bar_q_full, 0) && clock64() - t0 < 200000000LL) {
         }
-        for (int c = max(issued - 2 * STAGES, 0); c < issued; ++c) {
-          const int it = c >> 1, st = it % STAGES;
+        const int last = (issued + 1) / 2;  // tiles with at least one copy issued
+        for (int it = max(last - STAGES - 1, 0); it < last; ++it) {
+          const int st = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
-          uint64_t* bar = (c & 1) ? &bar_v_full[st] : &bar_k_full[st];
-          while (!mbar_try_wait(bar, ph) && clock64() - t0 < 200000000LL) {
+          while (!mbar_try_wait(&bar_k_full[st], ph) && clock64() - t0 < 200000000LL) {
+          }
+          while (!mbar_try_wait(&bar_v_full[st], ph) && clock64() - t0 < 200000000LL) {
           }
         }
       }
@@ -205,75 +241,77 @@ fox_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   } else if (warp == kMmaWarp) {
     // ===================== MMA issuer (whole warp converged, one elected lane issues) =====================
     if (n_tiles > 0) {
-      // Every softmax warpgroup g has its own chain S_g -> P_g -> O_g += P_g V_g -> S_g(next tile): the S
-      // product is issued per column slice right behind the P V product that frees the slice, so a
-      // warpgroup never waits for the other one.
-      constexpr uint32_t idQK = umma_idesc(kFmt, 128, CW, 0, 0);
       constexpr uint32_t idPV = umma_idesc(kFmt, 128, D, 0, 1);
       // descriptors are built once; the loops only move the start-address field
       const uint64_t dQ = umma_desc_kmajor(smem_u32(sQ));
       const uint64_t dK0 = umma_desc_kmajor(smem_u32(sK));
       const uint64_t dV0 = umma_desc_mnmajor(smem_u32(sV), kSubBytes);
-      auto issue_s = [&](int g, int st) {  // S[:, g CW : (g+1) CW] = Q K[g CW : (g+1) CW, :]^T
-        const uint64_t dK = umma_desc_advance(dK0, st * kTileBytes + g * CW * 128);
-#pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk)
-          mma_ss_raw(tbase + g * CW, umma_desc_advance(dQ, (kk >> 2) * 16384 + (kk & 3) * 32),
-                     umma_desc_advance(dK, (kk >> 2) * kSubBytes + (kk & 3) * 32), idQK, kk > 0);
-        tc_commit_raw(&bar_s_full[g]);
-      };
       bool ok = mbar_wait_warp(&bar_q_full, 0, abortp, p.status, kSiteQFull);
-      ok = ok && mbar_wait_warp(&bar_k_full[0], 0, abortp, p.status, kSiteKFull, 0);
-      if (ok) {
-        tc_fence_after();
-        if (elect_one()) {
+      {
+        // Every softmax warpgroup g has its own chain S_g -> P_g -> O_g += P_g V_g -> S_g(next tile): the S
+        // product is issued per column slice right behind the P V product that frees the slice, so a
+        // warpgroup never waits for the other one.
+        constexpr uint32_t idQK = umma_idesc(kFmt, 128, CW, 0, 0);
+        auto issue_s = [&](int g, int st) {  // S[:, g CW : (g+1) CW] = Q K[g CW : (g+1) CW, :]^T
+          const uint64_t dK = umma_desc_advance(dK0, st * kTileBytes + g * CW * 128);
 #pragma unroll
-          for (int g = 0; g < kWG; ++g) issue_s(g, 0);
-          tc_commit_raw(&bar_k_empty[0]);
-        }
-        __syncwarp();
-      }
-      for (int it = 0; it < n_tiles && ok; ++it) {
-        const int st = it % STAGES;
-        const uint32_t ph = (it / STAGES) & 1;
-        const bool more = it + 1 < n_tiles;
-        const int st1 = (it + 1) % STAGES;
-        ok = mbar_wait_warp(&bar_v_full[st], ph, abortp, p.status, kSiteVFull, it);
-        if (!ok) break;
-        if (more) {
-          ok = mbar_wait_warp(&bar_k_full[st1], ((it + 1) / STAGES) & 1, abortp, p.status, kSiteKFull, it + 1);
-          if (!ok) break;
-        }
-        const uint64_t dV = umma_desc_advance(dV0, st * kTileBytes);
-#pragma unroll
-        for (int g = 0; g < kWG; ++g) {
-          STAMP(8, g * 3 + 0, it);
-          ok = mbar_wait_warp(&bar_p_full[g], it & 1, abortp, p.status, kSitePFull, it);
-          if (!ok) break;
-          STAMP(8, g * 3 + 1, it);
+          for (int kk = 0; kk < D / 16; ++kk)
+            mma_ss_raw(tbase + g * CW, umma_desc_advance(dQ, (kk >> 2) * 16384 + (kk & 3) * 32),
+                       umma_desc_advance(dK, (kk >> 2) * kSubBytes + (kk & 3) * 32), idQK, kk > 0);
+          tc_commit_raw(&bar_s_full[g]);
+        };
+        ok = ok && mbar_wait_warp(&bar_k_full[0], 0, abortp, p.status, kSiteKFull, 0);
+        if (ok) {
           tc_fence_after();
           if (elect_one()) {
-            // O_g += P[:, g CW : (g+1) CW] V[g CW : (g+1) CW, :]; the 16-bit P sits at S columns g CW ...
 #pragma unroll
-            for (int kk = 0; kk < CW / 16; ++kk)
-              mma_ts_raw(tbase + kColO + g * D, tbase + g * CW + kk * 8,
-                         umma_desc_advance(dV, (g * (CW / 16) + kk) * 2048), idPV, (it > 0 || kk > 0) ? 1u : 0u);
-            if (more) issue_s(g, st1);
-            if (g == kWG - 1) {
-              tc_commit_raw(&bar_v_empty[st]);
-              if (more) tc_commit_raw(&bar_k_empty[st1]);
-            }
+            for (int g = 0; g < kWG; ++g) issue_s(g, 0);
+            tc_commit_raw(&bar_k_empty[0]);
           }
           __syncwarp();
-          STAMP(8, g * 3 + 2, it);
         }
-        if (!ok) break;
+        for (int it = 0; it < n_tiles && ok; ++it) {
+          const int st = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          const bool more = it + 1 < n_tiles;
+          const int st1 = (it + 1) % STAGES;
+          ok = mbar_wait_warp(&bar_v_full[st], ph, abortp, p.status, kSiteVFull, it);
+          if (!ok) break;
+          if (more) {
+            ok = mbar_wait_warp(&bar_k_full[st1], ((it + 1) / STAGES) & 1, abortp, p.status, kSiteKFull, it + 1);
+            if (!ok) break;
+          }
+          const uint64_t dV = umma_desc_advance(dV0, st * kTileBytes);
+#pragma unroll
+          for (int g = 0; g < kWG; ++g) {
+            STAMP(8, (g & 1) * 3 + 0, it);
+            ok = mbar_wait_warp(&bar_p_full[g], it & 1, abortp, p.status, kSitePFull, it);
+            if (!ok) break;
+            STAMP(8, (g & 1) * 3 + 1, it);
+            tc_fence_after();
+            if (elect_one()) {
+              // O_g += P[:, g CW : (g+1) CW] V[g CW : (g+1) CW, :]; the 16-bit P sits at S columns g CW ...
+#pragma unroll
+              for (int kk = 0; kk < CW / 16; ++kk)
+                mma_ts_raw(tbase + kColO + g * D, tbase + g * CW + kk * 8,
+                           umma_desc_advance(dV, (g * (CW / 16) + kk) * 2048), idPV, (it > 0 || kk > 0) ? 1u : 0u);
+              if (more) issue_s(g, st1);
+              if (g == kWG - 1) {
+                tc_commit_raw(&bar_v_empty[st]);
+                if (more) tc_commit_raw(&bar_k_empty[st1]);
+              }
+            }
+            __syncwarp();
+            STAMP(8, (g & 1) * 3 + 2, it);
+          }
+          if (!ok) break;
+        }
       }
       if (ok) tc_commit(&bar_o_done);
     }
   } else {
     // ===================== softmax / correction / epilogue =====================
-    const int g = SPLIT ? (warp >> 2) : 0;    // column half owned by this warpgroup
+    const int g = warp >> 2;                  // column slice owned by this warpgroup
     const int r = tid & 127;                  // query row inside the tile == TMEM lane
     const int row = mb * kFwdBM + r;
     const bool row_ok = row < M;
@@ -286,14 +324,6 @@ fox_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 
     float m_ref = -INFINITY, l_sum = 0.f;
     bool ok = true;
-    // the prefix of the next tile's column is fetched one tile ahead and only scaled when it is staged, so
-    // that the global load's latency is not waited for inside the tile
-    float lam_next = 0.f;
-    const bool stager = r < CW;  // these threads stage one -b_j of the warpgroup's slice per tile
-    if (n_tiles > 0 && stager) {
-      const int col = (nb_hi - 1) * BN + g * CW + r;
-      lam_next = col < N ? lam[col] : 0.f;
-    }
     // Upper bound of this row's scaled logits q_i.k_j*c <= ||q_i|| max_j||k_j|| c (Cauchy-Schwarz): with the
     // largest -b_j of a tile it tells, before S is even read, that no logit of the tile can exceed the
     // reference maximum by more than the skip shift; then the maximum pass over S is not run.
@@ -322,32 +352,19 @@ fox_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     for (int it = 0; it < n_tiles && ok; ++it) {
       const int nb = nb_hi - 1 - it;
       const int col0 = nb * BN + g * CW;  // first column of this thread's slice
-      STAMP(warp, 0, it);
-      if (stager) {
-        const float negb = -lam_next * kLog2e;
-        s_negb[g][it & 1][r] = negb;
-        float mx = negb;
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-        if (lane == 0) s_nbmax[g][it & 1][warp & 3] = mx;
-      }
-      mbar_arrive(&bar_negb[g][it & 1]);
-      ok = mbar_wait(&bar_negb[g][it & 1], (it >> 1) & 1, abortp, p.status, kSiteNegB, it);
+      STAMP(warp & 7, 0, it);
+      ok = mbar_wait(&bar_negb[it % 3], (it / 3) & 1, abortp, p.status, kSiteNegB, it);
       ok = mbar_wait(&bar_s_full[g], it & 1, abortp, p.status, kSiteSFull, it) && ok;
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
-      STAMP(warp, 1, it);
+      STAMP(warp & 7, 1, it);
       tc_fence_after();
-      if (it + 1 < n_tiles && stager) {
-        const int col = (nb - 1) * BN + g * CW + r;
-        lam_next = lam[col];  // nb-1 >= nb_lo >= 0 and this tile lies left of the tail
-      }
       // Two passes over this thread's slice of S, 32 columns at a time, in packed two-wide fp32 arithmetic.
       // Both read S from TMEM (a TMEM load costs ~50 cycles; holding a 64/128-column slice in registers
       // costs spills):
       //   pass 1: u = s*scale - b_j (masked on boundary tiles), row maximum
       //   pass 2: p = 2^(s*scale - b_j + a_i - m), row sum, pack, write back over S
-      const float4* nb4 = reinterpret_cast<const float4*>(&s_negb[g][it & 1][0]);
+      const float4* nb4 = reinterpret_cast<const float4*>(&s_negb[it % 3][g * CW]);
       const bool need_mask = (col0 + CW - 1 > P + mb * kFwdBM) || (col0 < seq0) || (col0 + CW > N);
       // valid columns of this row inside the slice: [c_lo, c_hi]
       const int c_lo = need_mask ? max(seq0 - col0, 0) : 0;
@@ -381,9 +398,7 @@ fox_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           }
         }
       };
-      float nbmax = s_nbmax[g][it & 1][0];
-#pragma unroll
-      for (int w = 1; w < CW / 32; ++w) nbmax = fmaxf(nbmax, s_nbmax[g][it & 1][w]);
+      const float nbmax = s_nbmax[it % 3][g];
       // (NaN or -inf reference -> false -> the maximum pass runs)
       const bool skip1 = __all_sync(0xffffffffu, dead || (qbound + nbmax <= m_ref + kSkipShift));
       if (!skip1) {
@@ -395,7 +410,7 @@ fox_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 #pragma unroll
           for (int c = 0; c < 16; ++c) umax = fmax3(umax, u[c].x, u[c].y);
         }
-        STAMP(warp, 2, it);
+        STAMP(warp & 7, 2, it);
         // ---- running maximum with lazy rescaling ----
         const float m_new = fmaxf(m_ref, a_i + umax);
         const bool need = (m_new - m_ref) > kLazyShift;  // false when both are -inf (NaN compare)
@@ -421,7 +436,7 @@ fox_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           m_ref = m_new;
         }
       }
-      STAMP(warp, 3, it);
+      STAMP(warp & 7, 3, it);
       const float off = a_i - ((m_ref == -INFINITY) ? 0.f : m_ref);
       const float2 off2 = make_float2(off, off);
       float2 psum = make_float2(0.f, 0.f);
@@ -449,75 +464,82 @@ fox_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         tmem_st16(tS + ch * 16, pk);  // columns already consumed by this thread
       }
       l_sum += psum.x + psum.y;
-      STAMP(warp, 4, it);
+      STAMP(warp & 7, 4, it);
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(&bar_p_full[g]);
-      STAMP(warp, 5, it);
+      STAMP(warp & 7, 5, it);
     }
 
     // ---- epilogue: merge the streams, O / l -> 16-bit -> global, L = m ln2 + ln l ----
-    if (SPLIT && g == 1) {
-      s_m1[r] = m_ref;
-      s_l1[r] = l_sum;
+    // every warpgroup publishes its (m, l); all of them form the same merge weights and each writes the
+    // 32-column chunks c with (c / 32) % NWG == g
+    if (NWG > 1) {
+      s_mg[g][r] = m_ref;
+      s_lg[g][r] = l_sum;
       mbar_arrive(&bar_merge);
     }
     if (n_tiles > 0 && ok) {
       ok = mbar_wait(&bar_o_done, 0, abortp, p.status, kSiteODone);
       ok = __all_sync(0xffffffffu, ok);
     }
-    if (SPLIT && g == 0 && ok) {
+    if (NWG > 1 && ok) {
       ok = mbar_wait(&bar_merge, 0, abortp, p.status, kSiteMerge);
       ok = __all_sync(0xffffffffu, ok);
     }
-    if (ok && g == 0) {
+    if (ok) {
       tc_fence_after();
-      float w0 = 1.f, w1 = 0.f;
-      if (SPLIT) {
-        const float m1 = s_m1[r], l1 = s_l1[r];
-        const float m = fmaxf(m_ref, m1);
-        w0 = (m_ref == -INFINITY) ? 0.f : fast_exp2(m_ref - m);
-        w1 = (m1 == -INFINITY) ? 0.f : fast_exp2(m1 - m);
-        l_sum = l_sum * w0 + l1 * w1;
+      float w[NWG];
+      w[0] = 1.f;
+      if (NWG > 1) {
+        float m = -INFINITY;
+#pragma unroll
+        for (int q = 0; q < NWG; ++q) m = fmaxf(m, s_mg[q][r]);
+        float l = 0.f;
+#pragma unroll
+        for (int q = 0; q < NWG; ++q) {
+          const float mq = s_mg[q][r];
+          w[q] = (mq == -INFINITY) ? 0.f : fast_exp2(mq - m);
+          l = fmaf(s_lg[q][r], w[q], l);
+        }
+        l_sum = l;
         m_ref = m;
       }
       const bool empty = (n_tiles == 0) || (P + row < seq0) || !(l_sum > 0.f);
       const float inv_l = empty ? 0.f : 1.f / l_sum;
-      w0 *= inv_l;
-      w1 *= inv_l;
+#pragma unroll
+      for (int q = 0; q < NWG; ++q) w[q] *= inv_l;
       uint16_t* orow = reinterpret_cast<uint16_t*>(p.o) + b * p.o_sb + h * p.o_sh + static_cast<int64_t>(row) * p.o_st;
+      const uint32_t tO0 = tbase + lane_base + kColO;
 #pragma unroll
       for (int c = 0; c < D; c += 32) {
+        if ((c / 32) % NWG != g) continue;  // (with more warpgroups than chunks the surplus ones write nothing)
         float o[32];
         if (n_tiles > 0) {
-          uint32_t t0[32];
-          tmem_ld32(tO + c, t0);
-          tmem_ld_wait();
 #pragma unroll
-          for (int j = 0; j < 32; ++j) o[j] = __uint_as_float(t0[j]) * w0;
-          if (SPLIT) {
-            uint32_t t1[32];
-            tmem_ld32(tO + D + c, t1);
+          for (int q = 0; q < NWG; ++q) {
+            uint32_t t0[32];
+            tmem_ld32(tO0 + q * D + c, t0);
             tmem_ld_wait();
 #pragma unroll
-            for (int j = 0; j < 32; ++j) o[j] = fmaf(__uint_as_float(t1[j]), w1, o[j]);
+            for (int j = 0; j < 32; ++j) o[j] = q == 0 ? __uint_as_float(t0[j]) * w[0] : fmaf(__uint_as_float(t0[j]), w[q], o[j]);
           }
         }
         if (row_ok) {
 #pragma unroll
           for (int j = 0; j < 32; j += 8) {
-            uint4 w = make_uint4(0, 0, 0, 0);
+            uint4 wv = make_uint4(0, 0, 0, 0);
             if (!empty) {
-              w.x = pack2<kBf16>(o[j + 0], o[j + 1]);
-              w.y = pack2<kBf16>(o[j + 2], o[j + 3]);
-              w.z = pack2<kBf16>(o[j + 4], o[j + 5]);
-              w.w = pack2<kBf16>(o[j + 6], o[j + 7]);
+              wv.x = pack2<kBf16>(o[j + 0], o[j + 1]);
+              wv.y = pack2<kBf16>(o[j + 2], o[j + 3]);
+              wv.z = pack2<kBf16>(o[j + 4], o[j + 5]);
+              wv.w = pack2<kBf16>(o[j + 6], o[j + 7]);
             }
-            *reinterpret_cast<uint4*>(orow + c + j) = w;
+            *reinterpret_cast<uint4*>(orow + c + j) = wv;
           }
         }
       }
-      if (row_ok) p.L[bh * M + row] = empty ? -INFINITY : m_ref * kLn2 + __logf(l_sum);
+      if (row_ok && g == 0) p.L[bh * M + row] = empty ? -INFINITY : m_ref * kLn2 + __logf(l_sum);
     }
   }
 
@@ -537,8 +559,8 @@ extern "C" int fox_debug_read_fwd_trace(long long* host) {
 }
 #endif
 
-template <int D, bool kBf16, int BN, int STAGES, int CTAS, bool SPLIT, bool PREF>
-static int launch_fwd(int device, cudaStream_t stream, int64_t B, int64_t H, int64_t M, int64_t N, const fox_tensor4* q,
+template <bool kBf16, int D, int BN, int STAGES, int CTAS, int NWG, bool PREF>
+static int launch_fwd_t(int device, cudaStream_t stream, int64_t B, int64_t H, int64_t M, int64_t N, const fox_tensor4* q,
                       const fox_tensor4* k, const fox_tensor4* v, const FwdParams& prm) {
   CUtensorMap tmQ, tmK, tmV;
   Tensor4 tq{q->ptr, B, H, M, D, q->sb, q->sh, q->st};
@@ -550,7 +572,7 @@ static int launch_fwd(int device, cudaStream_t stream, int64_t B, int64_t H, int
   if ((rc = cached_tmap_4d(&tmK, tk, 2, false, kBf16, 64, BN, true))) return rc;
   if ((rc = cached_tmap_4d(&tmV, tv, 2, false, kBf16, 64, BN, true))) return rc;
   constexpr int smem = 128 * D * 2 + 2 * STAGES * BN * D * 2 + 1024;
-  auto kern = fox_attn_fwd_kernel<D, kBf16, BN, STAGES, CTAS, SPLIT, PREF>;
+  auto kern = fox_attn_fwd_kernel<D, kBf16, BN, STAGES, CTAS, NWG, PREF>;
   static bool configured[64] = {};  // per template instance and device
   if (device < 0 || device >= 64) return FOX_ERR_DEVICE;
   if (!configured[device]) {
@@ -558,8 +580,19 @@ static int launch_fwd(int device, cudaStream_t stream, int64_t B, int64_t H, int
     configured[device] = true;
   }
   dim3 grid((unsigned)((M + kFwdBM - 1) / kFwdBM), (unsigned)H, (unsigned)B);
-  kern<<<grid, SPLIT ? 320 : 192, smem, stream>>>(tmQ, tmK, tmV, prm);
+  kern<<<grid, 128 * NWG + 64, smem, stream>>>(tmQ, tmK, tmV, prm);
   return cudaGetLastError() == cudaSuccess ? FOX_OK : FOX_ERR_LAUNCH;
+}
+
+template <int... A>
+static int launch_fwd(int device, cudaStream_t stream, int64_t B, int64_t H, int64_t M, int64_t N, const fox_tensor4* q,
+                      const fox_tensor4* k, const fox_tensor4* v, const FwdParams& prm) {
+  return launch_fwd_t<true, A...>(device, stream, B, H, M, N, q, k, v, prm);
+}
+template <int... A>
+static int launch_fwd_fp16(int device, cudaStream_t stream, int64_t B, int64_t H, int64_t M, int64_t N, const fox_tensor4* q,
+                           const fox_tensor4* k, const fox_tensor4* v, const FwdParams& prm) {
+  return launch_fwd_t<false, A...>(device, stream, B, H, M, N, q, k, v, prm);
 }
 
 }  // namespace fox
@@ -593,16 +626,14 @@ extern "C" int fox_attn_fwd(int device, void* stream, int dtype, int64_t B, int6
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const bool bf = dtype == FOX_DTYPE_BF16;
   const int variant = g_fwd_variant;
+#define FOX_FWD_LAUNCH(...) \
+  (bf ? launch_fwd<__VA_ARGS__>(device, st, B, H, M, N, q, k, v, prm) : launch_fwd_fp16<__VA_ARGS__>(device, st, B, H, M, N, q, k, v, prm))
+  //                 D  BN  STAGES CTAS NWG PREF
   if (D == 64) {
-    if (variant == 1)
-      return bf ? launch_fwd<64, true, 128, 2, 2, false, false>(device, st, B, H, M, N, q, k, v, prm)
-                : launch_fwd<64, false, 128, 2, 2, false, false>(device, st, B, H, M, N, q, k, v, prm);
-    return bf ? launch_fwd<64, true, 128, 2, 2, true, false>(device, st, B, H, M, N, q, k, v, prm)
-              : launch_fwd<64, false, 128, 2, 2, true, false>(device, st, B, H, M, N, q, k, v, prm);
+    if (variant == 1) return FOX_FWD_LAUNCH(64, 128, 2, 2, 1, false);
+    return FOX_FWD_LAUNCH(64, 128, 2, 2, 2, false);
   }
-  if (variant == 2)
-    return bf ? launch_fwd<128, true, 64, 2, 2, false, false>(device, st, B, H, M, N, q, k, v, prm)
-              : launch_fwd<128, false, 64, 2, 2, false, false>(device, st, B, H, M, N, q, k, v, prm);
-  return bf ? launch_fwd<128, true, 128, 1, 2, false, true>(device, st, B, H, M, N, q, k, v, prm)
-            : launch_fwd<128, false, 128, 1, 2, false, true>(device, st, B, H, M, N, q, k, v, prm);
+  if (variant == 2) return FOX_FWD_LAUNCH(128, 64, 2, 2, 1, false);
+  return FOX_FWD_LAUNCH(128, 128, 1, 2, 1, true);
+#undef FOX_FWD_LAUNCH
 }

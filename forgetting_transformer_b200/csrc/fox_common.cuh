@@ -382,6 +382,14 @@ __device__ __forceinline__ float2 poly_exp2_x2(float2 x) {
   return r;
 }
 
+// Read-only global load that stays where it is written: the compiler may sink a plain load down to its
+// first use, which puts the whole memory latency in front of that use; a volatile asm is not moved.
+__device__ __forceinline__ float ldg_f32_here(const float* p) {
+  float v;
+  asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(v) : "l"(p));
+  return v;
+}
+
 // three-input maximum (one instruction on sm_100)
 __device__ __forceinline__ float fmax3(float a, float b, float c) {
   float d;
