@@ -26,6 +26,8 @@
 // same tile appended to Q makes the dK product deliver colsum(dS), the key-side one.
 // Both sums are thus formed from the same rounded dS values and cancel in the reverse
 // prefix sum the way upstream's fp32 sums do.
+#include <type_traits>
+
 #include "fox_common.cuh"
 #include "fox_host.h"
 
@@ -187,63 +189,70 @@ fox_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         }
       }
       __syncwarp();
-      float vec_e[kBwdBM / 32], vec_d[kBwdBM / 32];
-      auto load_vec = [&](int mb_) {
+      // Per-row vectors of a query tile (L_i, Lambda_i, delta_i: lane l holds rows rr*32 + l) are fetched two
+      // tiles ahead into one of two register sets with loads that stay where they are written, and only
+      // combined when they are staged: a global load here sees well over a thousand cycles of latency
+      // while the reductions are in flight, and anything the producer waits for delays every copy behind it.
+      float rawL[2][kBwdBM / 32], rawLam[2][kBwdBM / 32], rawD[2][kBwdBM / 32];
+      auto fetch_vec = [&](int mb_, auto slot_c) {
+        constexpr int slot = decltype(slot_c)::value;
 #pragma unroll
         for (int rr = 0; rr < kBwdBM / 32; ++rr) {
           const int i = mb_ * kBwdBM + rr * 32 + lane;
-          float e = -INFINITY, dl = 0.f;
-          if (i < M) {
-            const float Li = p.L[bh * M + i];
-            e = (Li == -INFINITY) ? -INFINITY : (p.lam[bh * N + P + i] - Li) * kLog2eB;
-            dl = p.delta[bh * M + i];
-          }
-          vec_e[rr] = e;
-          vec_d[rr] = dl;
+          const bool in = i < M;
+          const int ic = in ? i : 0;
+          const float l_ = ldg_f32_here(p.L + bh * M + ic);
+          const float a_ = ldg_f32_here(p.lam + bh * N + P + ic);
+          const float d_ = ldg_f32_here(p.delta + bh * M + ic);
+          rawL[slot][rr] = in ? l_ : -INFINITY;
+          rawLam[slot][rr] = a_;
+          rawD[slot][rr] = in ? d_ : 0.f;
         }
       };
-      load_vec(mb_lo);
       int issued_q = 0, issued_do = 0;
-      for (int it = 0; it < n_tiles; ++it) {
+      auto tile = [&](int it, auto slot_c) -> bool {
+        constexpr int slot = decltype(slot_c)::value;
         const int mb = mb_lo + it;
-        {
-          const int st = it % STQ;
-          const uint32_t ph = (it / STQ) & 1;
-          if (!mbar_wait_warp(&bar_q_empty[st], ph ^ 1, abortp, p.status, kBSiteQEmpty, it)) break;
-          if (elect_one()) {
-            mbar_expect_tx(&bar_q_full[st], kTileBytes);
+        const int st = it % STQ;
+        if (!mbar_wait_warp(&bar_q_empty[st], ((it / STQ) & 1) ^ 1, abortp, p.status, kBSiteQEmpty, it)) return false;
+        if (elect_one()) {
+          mbar_expect_tx(&bar_q_full[st], kTileBytes);
 #pragma unroll
-            for (int s = 0; s < kSub; ++s)
-              tma_load_4d(sQ + st * kTileBytes + s * 16384, &tmQ, &bar_q_full[st], s * 64, mb * kBwdBM, h, b);
-          }
-          __syncwarp();
-          issued_q = it + 1;
-          // per-row vectors of this query tile, same stage as Q (fetched one tile ahead into registers):
-          // e_i = (Lambda_i - L_i) log2 e (-inf for an empty or out-of-range row) and delta_i.  Consumers
-          // reach them through s_full, which the MMA warp commits only after it has seen q_full.
-#pragma unroll
-          for (int rr = 0; rr < kBwdBM / 32; ++rr) {
-            s_e[st][rr * 32 + lane] = vec_e[rr];
-            s_delta[st][rr * 32 + lane] = vec_d[rr];
-          }
-          __syncwarp();
-          if (elect_one()) mbar_arrive(&bar_q_full[st]);
-          __syncwarp();
-          if (it + 1 < n_tiles) load_vec(mb + 1);
+          for (int s = 0; s < kSub; ++s)
+            tma_load_4d(sQ + st * kTileBytes + s * 16384, &tmQ, &bar_q_full[st], s * 64, mb * kBwdBM, h, b);
         }
-        {
-          const int st = it % STDO;
-          const uint32_t ph = (it / STDO) & 1;
-          if (!mbar_wait_warp(&bar_do_empty[st], ph ^ 1, abortp, p.status, kBSiteDOEmpty, it)) break;
-          if (elect_one()) {
-            mbar_expect_tx(&bar_do_full[st], kTileBytes);
+        __syncwarp();
+        issued_q = it + 1;
+        const int sd = it % STDO;
+        if (!mbar_wait_warp(&bar_do_empty[sd], ((it / STDO) & 1) ^ 1, abortp, p.status, kBSiteDOEmpty, it)) return false;
+        if (elect_one()) {
+          mbar_expect_tx(&bar_do_full[sd], kTileBytes);
 #pragma unroll
-            for (int s = 0; s < kSub; ++s)
-              tma_load_4d(sDO + st * kTileBytes + s * 16384, &tmDO, &bar_do_full[st], s * 64, mb * kBwdBM, h, b);
-          }
-          __syncwarp();
-          issued_do = it + 1;
+          for (int s = 0; s < kSub; ++s)
+            tma_load_4d(sDO + sd * kTileBytes + s * 16384, &tmDO, &bar_do_full[sd], s * 64, mb * kBwdBM, h, b);
         }
+        __syncwarp();
+        issued_do = it + 1;
+        // e_i = (Lambda_i - L_i) log2 e (-inf for an empty or out-of-range row) and delta_i go into the Q
+        // stage's vectors.  Consumers reach them through s_full, which the MMA warp commits only after it
+        // has seen q_full.
+#pragma unroll
+        for (int rr = 0; rr < kBwdBM / 32; ++rr) {
+          const float Li = rawL[slot][rr];
+          s_e[st][rr * 32 + lane] = (Li == -INFINITY) ? -INFINITY : (rawLam[slot][rr] - Li) * kLog2eB;
+          s_delta[st][rr * 32 + lane] = rawD[slot][rr];
+        }
+        __syncwarp();
+        if (elect_one()) mbar_arrive(&bar_q_full[st]);
+        __syncwarp();
+        if (it + 2 < n_tiles) fetch_vec(mb + 2, slot_c);
+        return true;
+      };
+      fetch_vec(mb_lo, std::integral_constant<int, 0>{});
+      if (n_tiles > 1) fetch_vec(mb_lo + 1, std::integral_constant<int, 1>{});
+      for (int it = 0; it < n_tiles; it += 2) {
+        if (!tile(it, std::integral_constant<int, 0>{})) break;
+        if (it + 1 < n_tiles && !tile(it + 1, std::integral_constant<int, 1>{})) break;
       }
       if (*abortp && lane == 0) {
         // error path only: let the copies already in flight land before the CTA retires
