@@ -358,6 +358,7 @@ fox_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           for (int kk = 0; kk < 8; ++kk)
             mma_ts_raw(tbase + kColDK, tbase + kColDP + ((kk * 16) / CW) * CW + ((kk * 16) % CW) / 2,
                        umma_desc_advance(bq_mn, kk * 2048), idDK, acc | (kk > 0));
+          tc_commit_raw(&bar_q_empty[it % STQ]);  // dK is the last reader of this Q stage
         }
         __syncwarp();
         // ---- dQ_tile = dS [K | 1] ----
@@ -372,7 +373,6 @@ fox_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             mma_ss_raw(tbase + kColDQ, umma_desc_advance(ads_mn, kk * 2048), umma_desc_advance(dK_mn, kk * 2048),
                        idDQ, kk > 0);
           tc_commit_raw(&bar_dq_full);
-          tc_commit_raw(&bar_q_empty[it % STQ]);
         }
         __syncwarp();
         stamp(0, 4, it);

@@ -20,6 +20,7 @@ from . import _lib
 __all__ = ["forgetting_attention", "ForgettingAttention", "FWD_BLOCK", "BWD_BLOCK"]
 
 # (BLOCK_M, BLOCK_N) of the kernels; pruning indices are defined on this grid.
+_PADDED_HEAD_DIM = 64   # head dims 16 and 32 are zero-padded to this
 FWD_BLOCK = (128, 128)
 BWD_BLOCK = (128, 128)
 
@@ -150,8 +151,12 @@ class ForgettingAttention(torch.autograd.Function):
             assert seq_start.shape == (B,)
         if not q.is_cuda:
             raise _lib.FoxError("forgetting_attention needs CUDA tensors on an sm_100 device; there is no CPU path")
-        if D not in (64, 128):
-            raise _lib.FoxError(f"head dim {D} has no sm_100a kernel yet (64 and 128 are built)")
+        # Head dims 16 and 32 run through the D=64 kernels on zero-padded copies: zero columns change no
+        # dot product, norm or output column, and their gradients are exactly zero and sliced off again.
+        D_in = D
+        if D in (16, 32):
+            q, k, v = [torch.nn.functional.pad(t, (0, _PADDED_HEAD_DIM - D)) for t in (q, k, v)]
+            D = _PADDED_HEAD_DIM
 
         lib = _lib.load()
         with torch.cuda.device(q.device):
@@ -204,10 +209,12 @@ class ForgettingAttention(torch.autograd.Function):
         ctx.save_for_backward(q, k, v, o, L, log_lambda, seq_start, adaptive_threshold)
         ctx.sm_scale = sm_scale
         ctx.has_seq_start = has_seq_start
+        ctx.head_dim = D_in
+        out = o if D_in == D else o[..., :D_in].contiguous()
         if return_log_normalizer or return_start_index:
             ctx.mark_non_differentiable(*[t for t in (L, start_index) if t is not None])
-            return (o, L if return_log_normalizer else None, start_index if return_start_index else None)
-        return o
+            return (out, L if return_log_normalizer else None, start_index if return_start_index else None)
+        return out
 
     @staticmethod
     def backward(ctx, do, *ignored):
@@ -219,6 +226,8 @@ class ForgettingAttention(torch.autograd.Function):
         # the autograd engine runs this on its own thread: select the device explicitly
         with torch.cuda.device(q.device):
             dev = q.device
+            if ctx.head_dim != D:
+                do = torch.nn.functional.pad(do, (0, D - ctx.head_dim))
             do = _tma_view(do)
             code = _lib.dtype_code(q.dtype)
             delta = torch.empty_like(L)
@@ -254,6 +263,8 @@ class ForgettingAttention(torch.autograd.Function):
                   dlam_row.data_ptr(), None, dlog_fgate.data_ptr(), None)
             if _DEBUG_SYNC:
                 _lib.check_status(dev)
+        if ctx.head_dim != D:
+            dq, dk, dv = [t[..., :ctx.head_dim].contiguous() for t in (dq, dk, dv)]
         return dq, dk, dv, dlog_fgate, None, None, None, None, None, None, None, None, None
 
 
@@ -274,7 +285,7 @@ def forgetting_attention(
 
     - q (B, Tq, H, D), k/v (B, Tk, H, D) in fp16/bf16 and log_fgate (B, Tk, H) in
       fp32, or with the H and T axes swapped when ``head_first=True``;
-    - Tq <= Tk, causal, D in {16, 32, 64, 128} (sm_100a kernels exist for 64, 128);
+    - Tq <= Tk, causal, D in {16, 32, 64, 128} (16 and 32 run zero-padded through the D=64 kernels);
     - ``seq_start`` (B,) long: no attention to positions left of it (left padding);
     - ``sm_scale`` defaults to 1/sqrt(D);
     - ``adaptive_threshold``: "auto", a float or a tensor broadcastable to (B, H);

@@ -168,6 +168,22 @@ def test_small_and_ragged_lengths(T, D):
     _close(dlf, r["dlog_fgate"], 2 * ATOL_BF16, RTOL_BF16)
 
 
+@pytest.mark.parametrize("D", [16, 32])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_small_head_dims(D, dtype):
+    """Head dims 16 and 32 of upstream's contract (line 87): same results as the oracle at that D,
+    default sm_scale = 1/sqrt(D), gradients of the input's own shape."""
+    q, k, v, lf, do = _inputs(7 * D, 2, 3, 200, 333, D, dtype)
+    seq = torch.tensor([0, 21])
+    out, dq, dk, dv, dlf = _run(q, k, v, lf, do, seq=seq)
+    assert out.shape == q.shape and dq.shape == q.shape and dk.shape == k.shape and dv.shape == v.shape
+    r = orc.blockwise_fwd_bwd(q, k, v, lf, do, seq_start=seq, low_precision_matmul=False)
+    atol, rtol = (ATOL_BF16, RTOL_BF16) if dtype == torch.bfloat16 else (ATOL_FP16, 0.0)
+    for a, b in [(out, r["out"]), (dq, r["dq"]), (dk, r["dk"]), (dv, r["dv"])]:
+        _close(a, b, atol, rtol)
+    _close(dlf, r["dlog_fgate"], 2 * atol, rtol)
+
+
 def test_seq_start_extremes():
     """seq_start = 0, in the middle of a block, on a block boundary and at the last token."""
     B, H, T, D = 4, 2, 384, 64
