@@ -40,6 +40,9 @@ WORKLOADS = {
     "cfg3": dict(B=2, T=16384, H=24, D=64, mu=4.0, sigma=1.0, seq=True, thr=None, head_scale=False, seed=1003),
     "cfg4": dict(B=4, T=16384, H=16, D=128, mu=-1.0, sigma=1.5, seq=False, thr=None, head_scale=True, seed=1004),
     "cfg4_acp": dict(B=4, T=16384, H=16, D=128, mu=-1.0, sigma=1.5, seq=False, thr="auto", head_scale=True, seed=1004),
+    # attention of the FoX-Pro block shape; at N > 1 GPUs the sequence is split (context parallel, strong scaling)
+    "cfg5_attn": dict(B=1, T=65536, H=24, D=64, mu=5.0, sigma=1.0, seq=False, thr=None, head_scale=False, seed=1005,
+                      context_parallel=True),
     # small cases for profiler captures: inputs (4 x 34 / 67 MB) exceed the 126 MB L2, kernels last a few ms
     "prof_d64": dict(B=2, T=8192, H=16, D=64, mu=4.0, sigma=1.0, seq=True, thr=None, head_scale=False, seed=1005),
     "prof_d128": dict(B=2, T=8192, H=16, D=128, mu=-1.0, sigma=1.5, seq=False, thr=None, head_scale=True, seed=1006),
@@ -49,6 +52,7 @@ DESCR = {
     "cfg3": "long-context FoX-760M layer shape B2 T16384 H24 D64 bf16, gate logits N(4,1), seq_start U[0,2048)",
     "cfg4": "ACP stress shape B4 T16384 H16 D128 bf16, gate logits N(-1,1.5), pruning off",
     "cfg4_acp": "ACP stress shape B4 T16384 H16 D128 bf16, gate logits N(-1,1.5), adaptive_threshold=auto",
+    "cfg5_attn": "attention of the FoX-Pro block shape B1 T65536 H24 D64 bf16, gate logits N(5,1); N>1: context parallel",
     "prof_d64": "profiler-sized case B2 T8192 H16 D64 bf16 (cfg3 distributions)",
     "prof_d128": "profiler-sized case B2 T8192 H16 D128 bf16 (cfg4 distributions, pruning off)",
 }
@@ -227,15 +231,30 @@ def run_ours(args, w, wname):
     host = make_inputs(w, rank, pin=True)
     seq = host["seq_start"]
     flops, pairs = flops_of(w, seq)
+    cp = bool(w.get("context_parallel")) and world > 1
+    if cp:
+        # strong scaling: one sequence, every rank keeps its two zig-zag chunks; per-rank share of the FLOPs
+        from forgetting_transformer_b200 import sharding
+        tc = w["T"] // (2 * world)
+        c0, c1 = sharding.zigzag_chunks(world, rank)
+        for n_ in ("q", "k", "v", "log_fgate", "dout"):
+            t_ = host[n_]
+            host[n_] = torch.cat([t_[:, :, c0 * tc:(c0 + 1) * tc], t_[:, :, c1 * tc:(c1 + 1) * tc]], dim=2).pin_memory()
+        flops = flops / world
     seq_d = None if seq is None else seq.to(dev)
     d = {n: host[n].to(dev, non_blocking=True) for n in ("q", "k", "v", "log_fgate", "dout")}
     q, k, v, lf = [d[n].requires_grad_() for n in ("q", "k", "v", "log_fgate")]
     dout = d["dout"]
     thr = w["thr"]
 
+    def attention(q_, k_, v_, lf_):
+        if cp:
+            return sharding.context_parallel_attention(q_, k_, v_, lf_, adaptive_threshold=thr)
+        return fox.forgetting_attention(q_, k_, v_, lf_, head_first=True, seq_start=seq_d, adaptive_threshold=thr)
+
     def step():
         q.grad = k.grad = v.grad = lf.grad = None
-        out = fox.forgetting_attention(q, k, v, lf, head_first=True, seq_start=seq_d, adaptive_threshold=thr)
+        out = attention(q, k, v, lf)
         out.backward(dout)
         return out
 
@@ -280,7 +299,7 @@ def run_ours(args, w, wname):
         nonlocal outs_host
         dd = {n: host[n].to(dev, non_blocking=True) for n in ("q", "k", "v", "log_fgate", "dout")}
         qq, kk, vv, ll = [dd[n].requires_grad_() for n in ("q", "k", "v", "log_fgate")]
-        out = fox.forgetting_attention(qq, kk, vv, ll, head_first=True, seq_start=seq_d, adaptive_threshold=thr)
+        out = attention(qq, kk, vv, ll)
         out.backward(dd["dout"])
         res = [out.detach(), qq.grad, kk.grad, vv.grad, ll.grad]
         if outs_host is None:
@@ -362,8 +381,9 @@ def run_ours(args, w, wname):
         bwd_n, bwd_ms = kern.get("fox_attn_bwd", (0, float("nan")))
         fwd_n, fwd_ms = kern.get("fox_attn_fwd", (0, float("nan")))
         # executed FLOPs of the dominant kernel (backward: 10 of the 14 per pair)
-        bwd_tf = (10.0 / 14.0) * flops / (bwd_ms * 1e-3) / 1e12
-        fwd_tf = (4.0 / 14.0) * flops / (fwd_ms * 1e-3) / 1e12
+        # (a context-parallel step launches each kernel once per local chunk: FLOPs per step over launches per step)
+        bwd_tf = (10.0 / 14.0) * flops / (bwd_ms * max(bwd_n // args.steps, 1) * 1e-3) / 1e12
+        fwd_tf = (4.0 / 14.0) * flops / (fwd_ms * max(fwd_n // args.steps, 1) * 1e-3) / 1e12
         roof = {
             "kernel": "fox_attn_bwd_kernel", "bound": "tensor", "achieved": bwd_tf,
             "peak": peaks["bf16_sustained"], "unit": "TFLOP/s", "frac": bwd_tf / peaks["bf16_sustained"],
@@ -375,11 +395,14 @@ def run_ours(args, w, wname):
         }
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
-            "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong" if cp else "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": wname, "description": DESCR[wname], "per_gpu_batch": w["B"],
-                       "global_batch": w["B"] * world, "seq_len": w["T"], "heads": w["H"], "head_dim": w["D"],
-                       "sharding": "independent (batch, head) units per rank, no collective",
+                       "global_batch": w["B"] * (1 if cp else world), "seq_len": w["T"], "heads": w["H"],
+                       "head_dim": w["D"],
+                       "sharding": ("context parallel: zig-zag sequence chunks, NCCL all-gather of K, V and log gates, "
+                                    "reduce-scatter of their gradients") if cp else
+                                   "independent (batch, head) units per rank, no collective",
                        "l2": "inputs (>=400 MB per step) larger than the 126 MB L2; no explicit flush",
                        "algorithmic_flops_per_step_per_gpu": flops,
                        "frac_of_bf16_peak": value / world / peaks["bf16"],
