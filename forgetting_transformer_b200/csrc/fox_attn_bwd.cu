@@ -361,6 +361,14 @@ fox_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           tc_commit_raw(&bar_q_empty[it % STQ]);  // dK is the last reader of this Q stage
         }
         __syncwarp();
+        if (!kAliasDQ && it + 1 < n_tiles) {
+          // dP^T(it+1) overwrites dS^T(it), whose only reader in TMEM is dK(it): it goes ahead of dQ(it), so that
+          // a slow drain of the previous dQ tile (the wait below) does not hold up the next tile's phase B
+          stamp(0, 5, it);
+          ok = issue_dP(it + 1);
+          if (!ok) break;
+          stamp(0, 6, it);
+        }
         // ---- dQ_tile = dS [K | 1] ----
         if (it > 0) {
           ok = mbar_wait_warp(&bar_dq_free, (it - 1) & 1, abortp, p.status, kBSiteDqFree, it);
@@ -385,10 +393,12 @@ fox_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             ok = issue_S(it + 1);
             if (!ok) break;
           }
-          stamp(0, 5, it);
-          ok = issue_dP(it + 1);  // overwrites dS^T(it): ordered behind dK(it)
-          if (!ok) break;
-          stamp(0, 6, it);
+          if (kAliasDQ) {
+            stamp(0, 5, it);
+            ok = issue_dP(it + 1);  // overwrites dS^T(it): ordered behind dK(it)
+            if (!ok) break;
+            stamp(0, 6, it);
+          }
         }
       }
       if (ok) tc_commit(&bar_done);
