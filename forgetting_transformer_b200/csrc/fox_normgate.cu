@@ -10,6 +10,10 @@
 //   backward: s = sigmoid(g); xhat = x rstd; dg = dy (xhat w) s (1-s); dy' = dy s;
 //             dw_h += dy' xhat;  dx = (w dy' - xhat mean_d(xhat w dy')) rstd
 //
+// With g == NULL the gate is left out (y = x rstd w_h; no dg): the per-head RMSNorm that the FoX layer
+// applies to q and k ("QK-norm", GroupNorm(num_groups=H, is_rms_norm=True) at
+// modeling_forgetting_transformer.py:264-265, 314-316; Triton kernels at layernorm.py:183-245, 328-423).
+//
 // Layout: x, g, y, dy, dx, dg are contiguous (tokens, G*D) 16-bit arrays, w is
 // (G*D) fp32, rstd is (tokens*G) fp32.  A CTA covers whole tokens: thread
 // (h, sub) owns the 8 consecutive channels [h*D + 8 sub, +8) of every token the
@@ -44,7 +48,7 @@ __device__ __forceinline__ void store8(uint16_t* p, const float* f) {
   *reinterpret_cast<uint4*>(p) = v;
 }
 
-template <bool kBf16>
+template <bool kBf16, bool kGate>
 __global__ void fox_normgate_fwd_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ g,
                                         const float* __restrict__ w, uint16_t* __restrict__ y,
                                         float* __restrict__ rstd, int64_t tokens, int G, int D, float eps) {
@@ -62,7 +66,7 @@ __global__ void fox_normgate_fwd_kernel(const uint16_t* __restrict__ x, const ui
     float xv[8], gv[8];
     if (active) {
       load8<kBf16>(x + t * GD + ch, xv);
-      load8<kBf16>(g + t * GD + ch, gv);
+      if (kGate) load8<kBf16>(g + t * GD + ch, gv);
     } else {
 #pragma unroll
       for (int j = 0; j < 8; ++j) xv[j] = gv[j] = 0.f;
@@ -75,14 +79,14 @@ __global__ void fox_normgate_fwd_kernel(const uint16_t* __restrict__ x, const ui
     if (active) {
       float out[8];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) out[j] = xv[j] * r * wv[j] * sigmoidf_fast(gv[j]);
+      for (int j = 0; j < 8; ++j) out[j] = kGate ? xv[j] * r * wv[j] * sigmoidf_fast(gv[j]) : xv[j] * r * wv[j];
       store8<kBf16>(y + t * GD + ch, out);
       if (sub == 0) rstd[t * G + h] = r;
     }
   }
 }
 
-template <bool kBf16>
+template <bool kBf16, bool kGate>
 __global__ void fox_normgate_bwd_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ g,
                                         const float* __restrict__ w, const float* __restrict__ rstd,
                                         const uint16_t* __restrict__ dy, uint16_t* __restrict__ dx,
@@ -106,7 +110,7 @@ __global__ void fox_normgate_bwd_kernel(const uint16_t* __restrict__ x, const ui
     float r = 0.f;
     if (active) {
       load8<kBf16>(x + t * GD + ch, xv);
-      load8<kBf16>(g + t * GD + ch, gv);
+      if (kGate) load8<kBf16>(g + t * GD + ch, gv);
       load8<kBf16>(dy + t * GD + ch, dyv);
       r = rstd[t * G + h];
     } else {
@@ -117,7 +121,7 @@ __global__ void fox_normgate_bwd_kernel(const uint16_t* __restrict__ x, const ui
     float c1 = 0.f;
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
-      const float s = sigmoidf_fast(gv[j]);
+      const float s = kGate ? sigmoidf_fast(gv[j]) : 1.f;
       xhat[j] = xv[j] * r;
       const float yv = xhat[j] * wv[j];
       dgv[j] = dyv[j] * yv * s * (1.f - s);
@@ -133,7 +137,7 @@ __global__ void fox_normgate_bwd_kernel(const uint16_t* __restrict__ x, const ui
 #pragma unroll
       for (int j = 0; j < 8; ++j) dxv[j] = (wdy[j] - xhat[j] * c1) * r;
       store8<kBf16>(dx + t * GD + ch, dxv);
-      store8<kBf16>(dg + t * GD + ch, dgv);
+      if (kGate) store8<kBf16>(dg + t * GD + ch, dgv);
     }
   }
   if (active) {
@@ -154,7 +158,7 @@ using namespace fox;
 
 extern "C" int fox_normgate_fwd(int device, void* stream, int dtype, int64_t tokens, int64_t G, int64_t D,
                                 const void* x, const void* g, const float* w, float eps, void* y, float* rstd) {
-  if (!x || !g || !w || !y || !rstd || tokens <= 0 || G <= 0) return FOX_ERR_BAD_ARG;
+  if (!x || !w || !y || !rstd || tokens <= 0 || G <= 0) return FOX_ERR_BAD_ARG;
   if (D % 8 || D < 8 || D > 256 || (D & (D - 1))) return FOX_ERR_HEAD_DIM;
   const int threads = normgate_threads(G, D);
   if (threads > 1024) return FOX_ERR_TOO_LARGE;
@@ -162,20 +166,24 @@ extern "C" int fox_normgate_fwd(int device, void* stream, int dtype, int64_t tok
     return FOX_ERR_ALIGNMENT;
   if (cudaSetDevice(device) != cudaSuccess) return FOX_ERR_DEVICE;
   const int64_t grid = tokens < 148 * 16 ? tokens : 148 * 16;
-  if (dtype == FOX_DTYPE_BF16)
-    fox_normgate_fwd_kernel<true><<<(unsigned)grid, threads, 0, (cudaStream_t)stream>>>(
-        (const uint16_t*)x, (const uint16_t*)g, w, (uint16_t*)y, rstd, tokens, (int)G, (int)D, eps);
-  else
-    fox_normgate_fwd_kernel<false><<<(unsigned)grid, threads, 0, (cudaStream_t)stream>>>(
-        (const uint16_t*)x, (const uint16_t*)g, w, (uint16_t*)y, rstd, tokens, (int)G, (int)D, eps);
+#define FOX_NG_FWD(BF, GATE)                                                                      \
+  fox_normgate_fwd_kernel<BF, GATE><<<(unsigned)grid, threads, 0, (cudaStream_t)stream>>>(          \
+      (const uint16_t*)x, (const uint16_t*)g, w, (uint16_t*)y, rstd, tokens, (int)G, (int)D, eps)
+  if (dtype == FOX_DTYPE_BF16) {
+    if (g) FOX_NG_FWD(true, true); else FOX_NG_FWD(true, false);
+  } else {
+    if (g) FOX_NG_FWD(false, true); else FOX_NG_FWD(false, false);
+  }
+#undef FOX_NG_FWD
   return cudaGetLastError() == cudaSuccess ? FOX_OK : FOX_ERR_LAUNCH;
 }
 
 extern "C" int fox_normgate_bwd(int device, void* stream, int dtype, int64_t tokens, int64_t G, int64_t D,
                                 const void* x, const void* g, const float* w, const float* rstd, const void* dy,
                                 void* dx, void* dg, float* dw_partial, int64_t n_partials) {
-  if (!x || !g || !w || !rstd || !dy || !dx || !dg || !dw_partial || tokens <= 0 || G <= 0 || n_partials <= 0)
+  if (!x || !w || !rstd || !dy || !dx || !dw_partial || tokens <= 0 || G <= 0 || n_partials <= 0)
     return FOX_ERR_BAD_ARG;
+  if ((g == nullptr) != (dg == nullptr)) return FOX_ERR_BAD_ARG;
   if (D % 8 || D < 8 || D > 256 || (D & (D - 1))) return FOX_ERR_HEAD_DIM;
   const int threads = normgate_threads(G, D);
   if (threads > 1024) return FOX_ERR_TOO_LARGE;
@@ -183,13 +191,15 @@ extern "C" int fox_normgate_bwd(int device, void* stream, int dtype, int64_t tok
        reinterpret_cast<uintptr_t>(dx) | reinterpret_cast<uintptr_t>(dg) | reinterpret_cast<uintptr_t>(dw_partial)) % 16)
     return FOX_ERR_ALIGNMENT;
   if (cudaSetDevice(device) != cudaSuccess) return FOX_ERR_DEVICE;
-  if (dtype == FOX_DTYPE_BF16)
-    fox_normgate_bwd_kernel<true><<<(unsigned)n_partials, threads, 0, (cudaStream_t)stream>>>(
-        (const uint16_t*)x, (const uint16_t*)g, w, rstd, (const uint16_t*)dy, (uint16_t*)dx, (uint16_t*)dg,
-        dw_partial, tokens, (int)G, (int)D);
-  else
-    fox_normgate_bwd_kernel<false><<<(unsigned)n_partials, threads, 0, (cudaStream_t)stream>>>(
-        (const uint16_t*)x, (const uint16_t*)g, w, rstd, (const uint16_t*)dy, (uint16_t*)dx, (uint16_t*)dg,
-        dw_partial, tokens, (int)G, (int)D);
+#define FOX_NG_BWD(BF, GATE)                                                                          \
+  fox_normgate_bwd_kernel<BF, GATE><<<(unsigned)n_partials, threads, 0, (cudaStream_t)stream>>>(        \
+      (const uint16_t*)x, (const uint16_t*)g, w, rstd, (const uint16_t*)dy, (uint16_t*)dx, (uint16_t*)dg, \
+      dw_partial, tokens, (int)G, (int)D)
+  if (dtype == FOX_DTYPE_BF16) {
+    if (g) FOX_NG_BWD(true, true); else FOX_NG_BWD(true, false);
+  } else {
+    if (g) FOX_NG_BWD(false, true); else FOX_NG_BWD(false, false);
+  }
+#undef FOX_NG_BWD
   return cudaGetLastError() == cudaSuccess ? FOX_OK : FOX_ERR_LAUNCH;
 }

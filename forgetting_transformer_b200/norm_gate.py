@@ -18,7 +18,7 @@ import torch.nn as nn
 
 from . import _lib
 
-__all__ = ["group_norm_gated", "FusedGroupNormGated", "GroupRMSNormSigmoidGate"]
+__all__ = ["group_norm_gated", "FusedGroupNormGated", "GroupRMSNormSigmoidGate", "group_norm", "GroupNorm"]
 
 _MAX_PARTIALS = 148 * 8
 
@@ -29,13 +29,14 @@ def _stream() -> int:
 
 class GroupRMSNormSigmoidGate(torch.autograd.Function):
     """y = rmsnorm_per_group(x) * weight * sigmoid(g); saves (x, g, weight, rstd) like
-    upstream's LayerNormGatedFunction (fuse_norm_gate.py:726-822)."""
+    upstream's LayerNormGatedFunction (fuse_norm_gate.py:726-822).  ``g=None`` leaves the gate
+    out: upstream's LayerNormFunction (layernorm.py:523-620) in its per-head RMSNorm use."""
 
     @staticmethod
     def forward(ctx, x, g, weight, num_groups, eps):
         if not x.is_cuda:
             raise _lib.FoxError("group_norm_gated needs CUDA tensors on an sm_100 device; there is no CPU path")
-        assert x.shape == g.shape and x.dtype == g.dtype
+        assert g is None or (x.shape == g.shape and x.dtype == g.dtype)
         assert x.dtype in (torch.float16, torch.bfloat16)
         hidden = x.shape[-1]
         assert hidden % num_groups == 0 and weight.shape == (hidden,)
@@ -44,13 +45,13 @@ class GroupRMSNormSigmoidGate(torch.autograd.Function):
         shape = x.shape
         with torch.cuda.device(x.device):
             x2 = x.reshape(-1, hidden).contiguous()
-            g2 = g.reshape(-1, hidden).contiguous()
+            g2 = None if g is None else g.reshape(-1, hidden).contiguous()
             w32 = weight.detach().float().contiguous()
             tokens = x2.shape[0]
             y = torch.empty_like(x2)
             rstd = torch.empty(tokens * num_groups, dtype=torch.float32, device=x.device)
             _lib.check(lib.fox_normgate_fwd(x.device.index, _stream(), _lib.dtype_code(x.dtype), tokens,
-                                            num_groups, D, x2.data_ptr(), g2.data_ptr(), w32.data_ptr(),
+                                            num_groups, D, x2.data_ptr(), _lib.ptr(g2), w32.data_ptr(),
                                             float(eps), y.data_ptr(), rstd.data_ptr()), "fox_normgate_fwd")
         ctx.save_for_backward(x2, g2, w32, rstd)
         ctx.shape = shape
@@ -69,15 +70,15 @@ class GroupRMSNormSigmoidGate(torch.autograd.Function):
         with torch.cuda.device(x2.device):
             dy2 = dy.reshape(-1, hidden).contiguous()
             dx = torch.empty_like(x2)
-            dg = torch.empty_like(g2)
+            dg = None if g2 is None else torch.empty_like(g2)
             n_part = min(tokens, _MAX_PARTIALS)
             dw_partial = torch.empty((n_part, hidden), dtype=torch.float32, device=x2.device)
             _lib.check(lib.fox_normgate_bwd(x2.device.index, _stream(), _lib.dtype_code(x2.dtype), tokens, G, D,
-                                            x2.data_ptr(), g2.data_ptr(), w32.data_ptr(), rstd.data_ptr(),
-                                            dy2.data_ptr(), dx.data_ptr(), dg.data_ptr(), dw_partial.data_ptr(),
+                                            x2.data_ptr(), _lib.ptr(g2), w32.data_ptr(), rstd.data_ptr(),
+                                            dy2.data_ptr(), dx.data_ptr(), _lib.ptr(dg), dw_partial.data_ptr(),
                                             n_part), "fox_normgate_bwd")
             dw = dw_partial.sum(0).to(ctx.w_dtype)
-        return dx.reshape(ctx.shape), dg.reshape(ctx.shape), dw, None, None
+        return dx.reshape(ctx.shape), None if dg is None else dg.reshape(ctx.shape), dw, None, None
 
 
 def group_norm_gated(x, g, weight, bias=None, activation: str = "swish", residual=None, eps: float = 1e-5,
@@ -129,3 +130,51 @@ class FusedGroupNormGated(nn.Module):
         return group_norm_gated(x, g, self.weight, self.bias, self.activation, residual=residual, eps=self.eps,
                                 prenorm=prenorm, residual_in_fp32=residual_in_fp32,
                                 is_rms_norm=self.is_rms_norm, num_groups=self.num_groups)
+
+
+def group_norm(x, weight, bias=None, residual=None, eps: float = 1e-5, prenorm: bool = False,
+               residual_in_fp32: bool = False, is_rms_norm: bool = False, num_groups: int = 1):
+    """Same argument list as upstream's ``group_norm`` / ``group_norm_fn`` (layernorm.py:706-792):
+    the FoX layer's QK-norm is ``is_rms_norm=True`` with a weight and nothing else."""
+    if bias is not None or residual is not None or prenorm or not is_rms_norm:
+        raise NotImplementedError(
+            "only the QK-norm configuration is built: is_rms_norm=True, no bias, no residual, prenorm=False")
+    if weight is None:
+        raise NotImplementedError("elementwise_affine=False is not built")
+    return GroupRMSNormSigmoidGate.apply(x, None, weight, num_groups, eps)
+
+
+class GroupNorm(nn.Module):
+    """Drop-in for upstream's ``GroupNorm`` (layernorm.py:993-1051) as the FoX layer builds it for
+    q and k (modeling_forgetting_transformer.py:264-265): per-head RMSNorm with a weight."""
+
+    def __init__(self, num_groups: int, hidden_size: int, elementwise_affine: bool = True, bias: bool = False,
+                 eps: float = 1e-5, is_rms_norm: bool = False, device=None, dtype=None):
+        super().__init__()
+        if hidden_size % num_groups != 0:
+            raise ValueError("num_channels must be divisible by num_groups")
+        if bias:
+            raise NotImplementedError("bias=True is not built")
+        self.num_groups = num_groups
+        self.hidden_size = hidden_size
+        self.elementwise_affine = elementwise_affine
+        self.eps = eps
+        self.is_rms_norm = is_rms_norm
+        if elementwise_affine:
+            self.weight = nn.Parameter(torch.empty(hidden_size, device=device, dtype=dtype))
+        else:
+            self.register_parameter("weight", None)
+        self.register_parameter("bias", None)
+        self.reset_parameters()
+
+    def reset_parameters(self):
+        if self.elementwise_affine:
+            nn.init.ones_(self.weight)
+
+    def extra_repr(self) -> str:
+        return f"{self.num_groups}, {self.hidden_size}, is_rms_norm={self.is_rms_norm}, eps={self.eps}"
+
+    def forward(self, x, residual=None, prenorm=False, residual_in_fp32=False):
+        return group_norm(x, self.weight, self.bias, residual=residual, eps=self.eps, prenorm=prenorm,
+                          residual_in_fp32=residual_in_fp32, is_rms_norm=self.is_rms_norm,
+                          num_groups=self.num_groups)

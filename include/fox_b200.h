@@ -134,16 +134,40 @@ int fox_dq_convert(int device, void* stream, int dtype, int64_t B, int64_t H, in
 /* Fused per-head RMSNorm + sigmoid gate, forward: y = x * rstd * w_h * sigmoid(g) with
  * rstd = (mean_d x^2 + eps)^-1/2 per (token, head).  Replaces layer_norm_gated_fwd
  * (fuse_norm_gate.py:539-617, kernel 132-206) for is_rms_norm, activation "sigmoid", no
- * bias/residual.  x, g, y: contiguous (tokens, G*D) 16-bit; w: (G*D) fp32; rstd: (tokens*G) fp32. */
+ * bias/residual.  x, g, y: contiguous (tokens, G*D) 16-bit; w: (G*D) fp32; rstd: (tokens*G) fp32.
+ * g == NULL leaves the gate out (y = x * rstd * w_h): the per-head RMSNorm the FoX layer applies
+ * to q and k (GroupNorm(num_groups=H, is_rms_norm=True), modeling_forgetting_transformer.py:264-265,
+ * 314-316; layer_norm_fwd of layernorm.py:248-325, kernel 183-245). */
 int fox_normgate_fwd(int device, void* stream, int dtype, int64_t tokens, int64_t G, int64_t D, const void* x,
                      const void* g, const float* w, float eps, void* y, float* rstd);
 
 /* Backward of the above: dx, dg (16-bit) and per-CTA partial weight gradients dw_partial
  * (n_partials, G*D) fp32, fully written, to be summed over axis 0 by the caller.  Replaces
- * layer_norm_gated_bwd (fuse_norm_gate.py:620-723, kernel 309-421). */
+ * layer_norm_gated_bwd (fuse_norm_gate.py:620-723, kernel 309-421).  g and dg both NULL: backward
+ * of the ungated per-head RMSNorm (layer_norm_bwd, layernorm.py:426-520, kernel 328-423). */
 int fox_normgate_bwd(int device, void* stream, int dtype, int64_t tokens, int64_t G, int64_t D, const void* x,
                      const void* g, const float* w, const float* rstd, const void* dy, void* dx, void* dg,
                      float* dw_partial, int64_t n_partials);
+
+/* Data-dependent token shift, forward: out[b,t,h,:] = x[b,t,h,:] * curr[b,t,h] + x[b,t-1,h,:] *
+ * prev[b,t,h] with x[b,-1] = 0, products in fp32, rounded once.  Replaces shift_fwd_kernel
+ * (token_shift.py:21-80; TokenShift.forward 164-195), which ShiftLinear calls as
+ * token_shift(x, alpha, 1 - alpha) (modeling_forgetting_transformer.py:82).  x, out: (B,T,H,D)
+ * 16-bit, unit stride on D, D in {16,32,64,128}, element strides (x_sb, x_st, x_sh) shared by both,
+ * multiples of 8, 16-byte aligned bases; prev_weight, curr_weight: (B,T,H) fp32 sharing
+ * (w_sb, w_st, w_sh). */
+int fox_token_shift_fwd(int device, void* stream, int dtype, int64_t B, int64_t T, int64_t H, int64_t D,
+                        const void* x, int64_t x_sb, int64_t x_st, int64_t x_sh, const float* prev_weight,
+                        const float* curr_weight, int64_t w_sb, int64_t w_st, int64_t w_sh, void* out);
+
+/* Backward of the above (shift_bwd_kernel, token_shift.py:82-157; TokenShift.backward 198-235):
+ * dx[b,t,h,:] = dout[b,t,h,:] * curr[b,t,h] + dout[b,t+1,h,:] * prev[b,t+1,h];
+ * dcurr[b,t,h] = sum_d dout * x[b,t];  dprev[b,t,h] = sum_d dout * x[b,t-1].  dout, dx share x's
+ * strides; dprev_weight, dcurr_weight are fp32 with the weights' strides, fully written. */
+int fox_token_shift_bwd(int device, void* stream, int dtype, int64_t B, int64_t T, int64_t H, int64_t D,
+                        const void* x, int64_t x_sb, int64_t x_st, int64_t x_sh, const float* prev_weight,
+                        const float* curr_weight, int64_t w_sb, int64_t w_st, int64_t w_sh, const void* dout,
+                        void* dx, float* dprev_weight, float* dcurr_weight);
 
 /* Backward attention that allocates nothing (no counterpart upstream, where torch allocates
  * every buffer).  For hosts that cannot obtain device memory at call time -- the GPU was

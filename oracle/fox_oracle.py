@@ -310,3 +310,46 @@ def group_rmsnorm_gated_fwd_bwd(x, g, weight, dy, num_groups, eps=1e-6):
     y = group_rmsnorm_gated(x, g, weight, num_groups, eps)
     y.backward(dy)
     return y.detach(), x.grad, g.grad, weight.grad
+
+
+def group_rmsnorm(x: torch.Tensor, weight: torch.Tensor, num_groups: int, eps: float = 1e-5,
+                  upcast: bool = True) -> torch.Tensor:
+    """y = rmsnorm_per_group(x) * weight, cast back to x.dtype: group_norm_ref with
+    is_rms_norm=True, no bias, no residual (layernorm.py:77-110), the FoX layer's QK-norm."""
+    dtype = x.dtype
+    if upcast:
+        x, weight = x.float(), weight.float()
+    shp = x.shape
+    xg = x.reshape(*shp[:-1], num_groups, shp[-1] // num_groups)
+    rstd = 1 / torch.sqrt(xg.square().mean(dim=-1, keepdim=True) + eps)
+    return (xg * rstd * weight.reshape(num_groups, -1)).reshape(shp).to(dtype)
+
+
+def group_rmsnorm_fwd_bwd(x, weight, dy, num_groups, eps=1e-5):
+    x, weight = [t.detach().clone().requires_grad_() for t in (x, weight)]
+    y = group_rmsnorm(x, weight, num_groups, eps)
+    y.backward(dy)
+    return y.detach(), x.grad, weight.grad
+
+
+def token_shift(x: torch.Tensor, prev_weight: torch.Tensor, curr_weight: torch.Tensor) -> torch.Tensor:
+    """out[b,t,h,:] = x[b,t,h,:] curr[b,t,h] + x[b,t-1,h,:] prev[b,t,h] (x[b,-1] = 0), products in fp32,
+    one rounding to x.dtype: the arithmetic of shift_fwd_kernel (token_shift.py:66-67)."""
+    xf = x.float()
+    x_prev = torch.nn.functional.pad(xf, (0, 0, 0, 0, 1, 0))[:, :-1]
+    out = xf * curr_weight.float()[..., None] + x_prev * prev_weight.float()[..., None]
+    return out.to(x.dtype)
+
+
+def token_shift_fwd_bwd(x, prev_weight, curr_weight, dout):
+    """Gradients with the kernel's roundings (token_shift.py:138-144): dx rounded to x.dtype from fp32
+    products; weight gradients summed in fp32 from the 16-bit dout and x."""
+    out = token_shift(x, prev_weight, curr_weight)
+    df, xf = dout.float(), x.float()
+    d_next = torch.nn.functional.pad(df, (0, 0, 0, 0, 0, 1))[:, 1:]
+    p_next = torch.nn.functional.pad(prev_weight.float(), (0, 0, 0, 1))[:, 1:]
+    dx = (df * curr_weight.float()[..., None] + d_next * p_next[..., None]).to(x.dtype)
+    x_prev = torch.nn.functional.pad(xf, (0, 0, 0, 0, 1, 0))[:, :-1]
+    dcurr = (df * xf).sum(-1)
+    dprev = (df * x_prev).sum(-1)
+    return out, dx, dprev, dcurr

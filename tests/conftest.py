@@ -17,8 +17,19 @@ def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (sm_100a); run with -m gpu on a B200")
 
 
+GLUE_GOLDEN = "glue_refs"  # norms and token shift (tests/golden/make_golden_glue.py); the rest are attention cases
+
+
 def golden_names():
-    return sorted(os.path.splitext(os.path.basename(p))[0] for p in glob.glob(os.path.join(GOLDEN_DIR, "*.npz")))
+    names = sorted(os.path.splitext(os.path.basename(p))[0] for p in glob.glob(os.path.join(GOLDEN_DIR, "*.npz")))
+    return [n for n in names if n != GLUE_GOLDEN]
+
+
+def load_glue_golden():
+    """Fixture produced by tests/golden/make_golden_glue.py: upstream's reference norm functions on CPU and
+    its token-shift Triton kernels in Triton's CPU interpreter (fp16)."""
+    z = np.load(os.path.join(GOLDEN_DIR, GLUE_GOLDEN + ".npz"))
+    return {k: (torch.from_numpy(np.ascontiguousarray(z[k])) if z[k].ndim else z[k].item()) for k in z.files}
 
 
 def load_golden(name):

@@ -23,7 +23,8 @@ def _declared_symbols():
 def test_header_declares_the_expected_entry_points():
     syms = _declared_symbols()
     for s in ["fox_attn_fwd", "fox_attn_bwd", "fox_cumsum_fwd", "fox_revcumsum", "fox_find_index",
-              "fox_max_row_norm", "fox_bwd_delta", "fox_dq_convert", "fox_normgate_fwd", "fox_normgate_bwd"]:
+              "fox_max_row_norm", "fox_bwd_delta", "fox_dq_convert", "fox_normgate_fwd", "fox_normgate_bwd",
+              "fox_token_shift_fwd", "fox_token_shift_bwd"]:
         assert s in syms
 
 

@@ -149,3 +149,24 @@ def test_norm_gate_reference_math():
     xg = x.view(2, 5, 4, 64)
     ref = (xg / xg.pow(2).mean(-1, keepdim=True).add(1e-6).sqrt()).reshape(2, 5, -1) * w * torch.sigmoid(gate)
     assert torch.allclose(y, ref, atol=1e-5)
+
+
+def test_glue_oracles_against_upstream_references():
+    """Per-head RMSNorm with and without the gate against upstream's reference functions, token shift
+    against upstream's own kernels (tests/golden/glue_refs.npz)."""
+    from conftest import load_glue_golden
+    z = load_glue_golden()
+    G = int(z["ng_groups"])
+    y, dx, dg, dw = orc.group_rmsnorm_gated_fwd_bwd(z["ng_x"], z["ng_g"], z["ng_w"], z["ng_dy"], G, z["ng_eps"])
+    # upstream's reference function evaluates sigmoid(g) in g's 16-bit dtype, its kernel (and the oracle) in
+    # fp32: outputs may differ by one fp16 ulp
+    assert _err(y, z["ng_y"]) < 2e-3
+    assert _err(dx, z["ng_dx"]) < 2e-3 and _err(dg, z["ng_dg"]) < 2e-3
+    assert _err(dw, z["ng_dw"]) < 1e-3 * z["ng_dw"].abs().max()  # sums of 74 such terms
+    y, dx, dw = orc.group_rmsnorm_fwd_bwd(z["ng_x"], z["ng_w"], z["ng_dy"], G, z["qk_eps"])
+    assert torch.equal(y, z["qk_y"])
+    assert _err(dx, z["qk_dx"]) < 2e-3
+    assert _err(dw, z["qk_dw"]) < 1e-4 * z["qk_dw"].abs().max()
+    out, dx, dprev, dcurr = orc.token_shift_fwd_bwd(z["ts_x"], z["ts_prev"], z["ts_curr"], z["ts_dout"])
+    assert torch.equal(out, z["ts_out"]) and torch.equal(dx, z["ts_dx"])
+    assert _err(dprev, z["ts_dprev"]) < 1e-4 and _err(dcurr, z["ts_dcurr"]) < 1e-4
