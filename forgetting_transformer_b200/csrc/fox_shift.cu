@@ -10,8 +10,9 @@
 //             dcurr[b,t,h] = sum_d dout[b,t,h,d] x[b,t,h,d];  dprev[b,t,h] = sum_d dout[b,t,h,d] x[b,t-1,h,d]
 //
 // x, out, dout, dx: (B,T,H,D) 16-bit, unit stride on D, arbitrary element strides on B, T, H (all four share
-// them, as upstream asserts); prev, curr, dprev, dcurr: (B,T,H) fp32 sharing one set of strides.  Products
-// are formed in fp32 and rounded once, as upstream does.  Thread = 8 channels of one (b,t,h) row; the D/8
+// them, as upstream asserts); prev, curr, dprev, dcurr: (B,T,H) fp32 sharing one set of strides.  The two
+// products and their sum are separate fp32 operations (no fused multiply-add) and the result is rounded once,
+// which reproduces upstream's kernels in Triton's interpreter bit for bit.  Thread = 8 channels of one (b,t,h) row; the D/8
 // lanes of a row are neighbours in a warp, so the two weight gradients are a shuffle reduction.
 #include "fox_common.cuh"
 #include "fox_host.h"
@@ -69,7 +70,7 @@ fox_token_shift_fwd_kernel(const uint16_t* __restrict__ x, const float* __restri
     }
     const float cw = curr[wo], pw = prev[wo];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) o[j] = xv[j] * cw + xp[j] * pw;
+    for (int j = 0; j < 8; ++j) o[j] = __fadd_rn(__fmul_rn(xv[j], cw), __fmul_rn(xp[j], pw));  // two products, one sum: no contraction
     shift_store8<kBf16>(out + xo, o);
   }
 }
@@ -114,7 +115,7 @@ fox_token_shift_bwd_kernel(const uint16_t* __restrict__ x, const float* __restri
     float sc = 0.f, sp = 0.f;
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
-      o[j] = dv[j] * cw + dn[j] * pw_next;
+      o[j] = __fadd_rn(__fmul_rn(dv[j], cw), __fmul_rn(dn[j], pw_next));
       sc = fmaf(dv[j], xv[j], sc);
       sp = fmaf(dv[j], xp[j], sp);
     }
