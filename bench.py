@@ -460,12 +460,12 @@ def run_ours(args, w, wname):
 # DRAM bytes (read + write) of one backward-kernel launch from an ncu capture, per workload;
 # filled from profiles/ (None = not captured).
 TRAFFIC_BYTES_PER_LAUNCH = {
-    # backward kernel: 263.4 MB measured on prof_d64 (profiles/attn_bwd_kernel_prof_d64_d128.md); the traffic is
+    # backward kernel: 265.6 MB measured on prof_d64 (profiles/attn_bwd_kernel_prof_d64_d128.md); the traffic is
     # per-row (inputs once, outputs once, dQ workspace once), cfg3 has 3x the rows
-    "cfg3": 3 * 263.4e6,
-    "prof_d64": 263.4e6,
-    "prof_d128": 635.5e6,
-    "cfg4": 4 * 635.5e6,
+    "cfg3": 3 * 265.6e6,
+    "prof_d64": 265.6e6,
+    "prof_d128": 632.8e6,
+    "cfg4": 4 * 632.8e6,
 }
 
 
