@@ -1,9 +1,9 @@
 """B200-native (sm_100a) Forgetting Attention: a drop-in for
 ``forgetting_transformer.forgetting_attention`` and the FoX-Pro fused
 RMSNorm + output gate, backed by hand-written CUDA kernels behind a C ABI."""
-from .norm_gate import FusedGroupNormGated, GroupNorm, group_norm, group_norm_gated  # noqa: F401
+from .norm_gate import FusedGroupNormGated, GroupNorm, RMSNorm, group_norm, group_norm_gated, rms_norm  # noqa: F401
 from .ops import ForgettingAttention, forgetting_attention  # noqa: F401
 from .token_shift import TokenShift, token_shift  # noqa: F401
 
 __all__ = ["forgetting_attention", "ForgettingAttention", "FusedGroupNormGated", "group_norm_gated", "GroupNorm",
-           "group_norm", "TokenShift", "token_shift"]
+           "group_norm", "RMSNorm", "rms_norm", "TokenShift", "token_shift"]

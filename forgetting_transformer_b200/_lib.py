@@ -53,6 +53,8 @@ _SIGNATURES = {
     "fox_noalloc_scratch_floats": (c_int64, []),
     "fox_normgate_fwd": (c_int, [c_int, c_void_p, c_int, c_int64, c_int64, c_int64, _F, _F, _F, c_float, _F, _F]),
     "fox_normgate_bwd": (c_int, [c_int, c_void_p, c_int, c_int64, c_int64, c_int64, _F, _F, _F, _F, _F, _F, _F, _F, c_int64]),
+    "fox_rmsnorm_fwd": (c_int, [c_int, c_void_p, c_int, c_int64, c_int64, _F, _F, _F, c_float, _F, _F, _F]),
+    "fox_rmsnorm_bwd": (c_int, [c_int, c_void_p, c_int, c_int64, c_int64, _F, _F, _F, _F, _F, _F, _F, c_int64]),
     "fox_token_shift_fwd": (c_int, [c_int, c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, _F, c_int64, c_int64,
                                     c_int64, _F, _F, c_int64, c_int64, c_int64, _F]),
     "fox_token_shift_bwd": (c_int, [c_int, c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, _F, c_int64, c_int64,

@@ -18,7 +18,8 @@ import torch.nn as nn
 
 from . import _lib
 
-__all__ = ["group_norm_gated", "FusedGroupNormGated", "GroupRMSNormSigmoidGate", "group_norm", "GroupNorm"]
+__all__ = ["group_norm_gated", "FusedGroupNormGated", "GroupRMSNormSigmoidGate", "group_norm", "GroupNorm",
+           "rms_norm", "RMSNorm", "RowRMSNorm"]
 
 _MAX_PARTIALS = 148 * 8
 
@@ -178,3 +179,99 @@ class GroupNorm(nn.Module):
         return group_norm(x, self.weight, self.bias, residual=residual, eps=self.eps, prenorm=prenorm,
                           residual_in_fp32=residual_in_fp32, is_rms_norm=self.is_rms_norm,
                           num_groups=self.num_groups)
+
+
+class RowRMSNorm(torch.autograd.Function):
+    """y = rmsnorm(x + residual) * weight over the last axis, optionally also returning the sum
+    (prenorm); upstream's LayerNormFunction with is_rms_norm=True (layernorm.py:523-620)."""
+
+    @staticmethod
+    def forward(ctx, x, weight, residual, eps, prenorm):
+        if not x.is_cuda:
+            raise _lib.FoxError("rms_norm needs CUDA tensors on an sm_100 device; there is no CPU path")
+        assert x.dtype in (torch.float16, torch.bfloat16)
+        hidden = x.shape[-1]
+        assert weight.shape == (hidden,)
+        assert residual is None or (residual.shape == x.shape and residual.dtype == x.dtype)
+        lib = _lib.load()
+        shape = x.shape
+        with torch.cuda.device(x.device):
+            x2 = x.reshape(-1, hidden).contiguous()
+            r2 = None if residual is None else residual.reshape(-1, hidden).contiguous()
+            w32 = weight.detach().float().contiguous()
+            rows = x2.shape[0]
+            y = torch.empty_like(x2)
+            z = None if r2 is None else torch.empty_like(x2)   # residual_out; without a residual z is x itself
+            rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
+            _lib.check(lib.fox_rmsnorm_fwd(x.device.index, _stream(), _lib.dtype_code(x.dtype), rows, hidden,
+                                           x2.data_ptr(), _lib.ptr(r2), w32.data_ptr(), float(eps), y.data_ptr(),
+                                           _lib.ptr(z), rstd.data_ptr()), "fox_rmsnorm_fwd")
+        zs = x2 if z is None else z
+        ctx.save_for_backward(zs, w32, rstd)
+        ctx.shape, ctx.w_dtype = shape, weight.dtype
+        ctx.has_residual, ctx.prenorm = residual is not None, prenorm
+        y = y.reshape(shape)
+        if not prenorm:
+            return y
+        return y, zs.reshape(shape)
+
+    @staticmethod
+    def backward(ctx, dy, *args):
+        zs, w32, rstd = ctx.saved_tensors
+        rows, hidden = zs.shape
+        lib = _lib.load()
+        dres_in = args[0] if (ctx.prenorm and len(args) > 0) else None
+        with torch.cuda.device(zs.device):
+            dy2 = dy.reshape(-1, hidden).contiguous()
+            dr2 = None if dres_in is None else dres_in.reshape(-1, hidden).to(zs.dtype).contiguous()
+            dx = torch.empty_like(zs)
+            n_part = min((rows + 7) // 8, _MAX_PARTIALS)
+            dw_partial = torch.empty((n_part, hidden), dtype=torch.float32, device=zs.device)
+            _lib.check(lib.fox_rmsnorm_bwd(zs.device.index, _stream(), _lib.dtype_code(zs.dtype), rows, hidden,
+                                           zs.data_ptr(), w32.data_ptr(), rstd.data_ptr(), dy2.data_ptr(),
+                                           _lib.ptr(dr2), dx.data_ptr(), dw_partial.data_ptr(), n_part),
+                       "fox_rmsnorm_bwd")
+            dw = dw_partial.sum(0).to(ctx.w_dtype)
+        dx = dx.reshape(ctx.shape)
+        return dx, dw, (dx if ctx.has_residual else None), None, None
+
+
+def rms_norm(x, weight, bias=None, residual=None, eps: float = 1e-5, prenorm: bool = False,
+             residual_in_fp32: bool = False):
+    """Same argument list as upstream's ``rms_norm`` (layernorm.py:841-859)."""
+    if bias is not None or residual_in_fp32:
+        raise NotImplementedError("only the FoX block's configuration is built: no bias, residual in the input dtype")
+    if weight is None:
+        raise NotImplementedError("elementwise_affine=False is not built")
+    return RowRMSNorm.apply(x, weight, residual, eps, prenorm)
+
+
+class RMSNorm(nn.Module):
+    """Drop-in for upstream's ``RMSNorm`` (layernorm.py:1054-1101) as the FoX block builds it
+    (attn_norm, mlp_norm: a weight, no bias)."""
+
+    def __init__(self, hidden_size: int, elementwise_affine: bool = True, bias: bool = False, eps: float = 1e-5,
+                 device=None, dtype=None):
+        super().__init__()
+        if bias:
+            raise NotImplementedError("bias=True is not built")
+        self.hidden_size = hidden_size
+        self.elementwise_affine = elementwise_affine
+        self.eps = eps
+        if elementwise_affine:
+            self.weight = nn.Parameter(torch.empty(hidden_size, device=device, dtype=dtype))
+        else:
+            self.register_parameter("weight", None)
+        self.register_parameter("bias", None)
+        self.reset_parameters()
+
+    def reset_parameters(self):
+        if self.elementwise_affine:
+            nn.init.ones_(self.weight)
+
+    def extra_repr(self) -> str:
+        return f"{self.hidden_size}, eps={self.eps}"
+
+    def forward(self, x, residual=None, prenorm=False, residual_in_fp32=False):
+        return rms_norm(x, self.weight, self.bias, residual=residual, eps=self.eps, prenorm=prenorm,
+                        residual_in_fp32=residual_in_fp32)

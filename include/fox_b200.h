@@ -149,6 +149,25 @@ int fox_normgate_bwd(int device, void* stream, int dtype, int64_t tokens, int64_
                      const void* g, const float* w, const float* rstd, const void* dy, void* dx, void* dg,
                      float* dw_partial, int64_t n_partials);
 
+/* Row-wise RMSNorm with optional residual add, forward: z = x + residual (fp32; residual may be
+ * NULL), residual_out = z rounded to the input dtype (may be NULL), rstd = (mean z^2 + eps)^-1/2,
+ * y = z * rstd * w.  Replaces layer_norm_fwd with IS_RMS_NORM, a weight, no bias (layernorm.py:
+ * 426-470, kernel 248-325) as RMSNorm.forward reaches it (layernorm.py:1092-1101): the FoX block's
+ * attn_norm(x) and mlp_norm(x, residual, prenorm=True) (modeling_forgetting_transformer.py:565, 580).
+ * x, residual, y, residual_out: contiguous (rows, hidden) 16-bit; w (hidden) fp32; rstd (rows) fp32;
+ * hidden in 256 * {1,2,3,4,5,6,8}, else FOX_ERR_HEAD_DIM. */
+int fox_rmsnorm_fwd(int device, void* stream, int dtype, int64_t rows, int64_t hidden, const void* x,
+                    const void* residual, const float* w, float eps, void* y, void* residual_out, float* rstd);
+
+/* Backward of the above (layer_norm_bwd, layernorm.py:473-520, kernel 328-423): z = the saved
+ * residual_out (or x when there was no residual); dx = (w dy - xhat mean(xhat w dy)) rstd +
+ * dresidual_in (may be NULL; the gradient that reached residual_out), which is also the gradient of
+ * the residual input; dw_partial (n_partials, hidden) fp32 per-CTA partials, fully written, to be
+ * summed over axis 0 by the caller. */
+int fox_rmsnorm_bwd(int device, void* stream, int dtype, int64_t rows, int64_t hidden, const void* z,
+                    const float* w, const float* rstd, const void* dy, const void* dresidual_in, void* dx,
+                    float* dw_partial, int64_t n_partials);
+
 /* Data-dependent token shift, forward: out[b,t,h,:] = x[b,t,h,:] * curr[b,t,h] + x[b,t-1,h,:] *
  * prev[b,t,h] with x[b,-1] = 0, products in fp32, rounded once.  Replaces shift_fwd_kernel
  * (token_shift.py:21-80; TokenShift.forward 164-195), which ShiftLinear calls as

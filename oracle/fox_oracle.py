@@ -353,3 +353,27 @@ def token_shift_fwd_bwd(x, prev_weight, curr_weight, dout):
     dcurr = (df * xf).sum(-1)
     dprev = (df * x_prev).sum(-1)
     return out, dx, dprev, dcurr
+
+
+def rms_norm(x, weight, residual=None, eps: float = 1e-5, prenorm: bool = False):
+    """Row-wise RMSNorm with optional residual add as upstream's kernel computes it (layernorm.py:287-313):
+    the sum x + residual is formed and normalised in fp32, its rounded copy is what prenorm returns."""
+    z = x.float() if residual is None else x.float() + residual.float()
+    rstd = 1 / torch.sqrt(z.square().mean(dim=-1, keepdim=True) + eps)
+    y = (z * rstd * weight.float()).to(x.dtype)
+    return (y, z.to(x.dtype)) if prenorm else y
+
+
+def rms_norm_fwd_bwd(x, weight, residual, dy, dres, eps=1e-5):
+    """Gradients as upstream's backward forms them (layernorm.py:380-416): from the saved, rounded sum."""
+    y, zs = rms_norm(x, weight, residual, eps, prenorm=True)
+    z = zs.float()
+    rstd = 1 / torch.sqrt(z.square().mean(dim=-1, keepdim=True) + eps)
+    xhat = z * rstd
+    wdy = weight.float() * dy.float()
+    c1 = (xhat * wdy).mean(dim=-1, keepdim=True)
+    dx = (wdy - xhat * c1) * rstd
+    if dres is not None:
+        dx = dx + dres.float()
+    dw = (dy.float() * xhat).reshape(-1, x.shape[-1]).sum(0)
+    return y, zs, dx.to(x.dtype), dw

@@ -9,6 +9,8 @@ $FOX_REFERENCE_SRC (default /root/reference/src):
 * norms: upstream's pure-PyTorch references ``group_norm_gated_ref`` (fuse_norm_gate.py:18-53) and
   ``group_norm_ref`` (layernorm.py:77-110), called on CPU with upcast=True in the FoX layer's
   configuration (is_rms_norm, sigmoid gate, weight, no bias); gradients by autograd through them.
+* row RMSNorm with residual (the block's input norms): ``rms_norm_ref`` (layernorm.py:53-74), upcast=True,
+  prenorm=True, gradients by autograd with a gradient flowing into both outputs.
 * token shift: upstream's own Triton kernels (token_shift.py:21-157) in Triton's CPU interpreter, fp16,
   called through ``token_shift`` exactly as ShiftLinear does (alpha, 1 - alpha).  The kernels carry an
   autotuner, which needs a GPU to time its candidates; the generator pins the one tuned parameter
@@ -26,7 +28,7 @@ REF = os.environ.get("FOX_REFERENCE_SRC", "/root/reference/src")
 sys.path.insert(0, REF)
 sys.dont_write_bytecode = True
 from forgetting_transformer.model.forgetting_transformer.fuse_norm_gate import group_norm_gated_ref  # noqa: E402
-from forgetting_transformer.model.forgetting_transformer.layernorm import group_norm_ref  # noqa: E402
+from forgetting_transformer.model.forgetting_transformer.layernorm import group_norm_ref, rms_norm_ref  # noqa: E402
 from forgetting_transformer.model.forgetting_transformer.token_shift import token_shift  # noqa: E402
 
 import forgetting_transformer.model.forgetting_transformer.token_shift as ts_mod  # noqa: E402
@@ -69,6 +71,19 @@ def main():
     y = group_norm_ref(xx, ww, None, num_groups=G, eps=1e-5, is_rms_norm=True, upcast=True)
     y.backward(dy)
     rec.update(qk_y=y.detach().numpy(), qk_dx=xx.grad.numpy(), qk_dw=ww.grad.numpy(), qk_eps=np.float64(1e-5))
+    # ---- row RMSNorm with residual, prenorm: (B, T, hidden) ----
+    Bn, Tn, Hn = 2, 19, 768
+    x = torch.randn(Bn, Tn, Hn, generator=g).half()
+    res = torch.randn(Bn, Tn, Hn, generator=g).half()
+    w = torch.rand(Hn, generator=g) + 0.5
+    dy = torch.randn(Bn, Tn, Hn, generator=g).half()
+    dres = torch.randn(Bn, Tn, Hn, generator=g).half()
+    xx, rr, ww = [t.clone().requires_grad_() for t in (x, res, w)]
+    y, z = rms_norm_ref(xx, ww, None, residual=rr, eps=1e-5, prenorm=True, upcast=True)
+    torch.autograd.backward([y, z], [dy, dres.float()])
+    rec.update(rn_x=x.numpy(), rn_res=res.numpy(), rn_w=w.numpy(), rn_dy=dy.numpy(), rn_dres=dres.numpy(),
+               rn_y=y.detach().numpy(), rn_z=z.detach().numpy(), rn_dx=xx.grad.numpy(), rn_dr=rr.grad.numpy(),
+               rn_dw=ww.grad.numpy(), rn_eps=np.float64(1e-5))
     # ---- token shift: (B, T, H, D), weights (B, T, H) fp32 ----
     B, T, H, D = 2, 70, 3, 32
     x = torch.randn(B, T, H, D, generator=g).half()

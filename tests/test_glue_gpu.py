@@ -54,6 +54,49 @@ def test_norms_against_upstream_reference_outputs():
     assert _err(wc.grad, z["qk_dw"]) / z["qk_dw"].abs().max().item() < 1e-2
 
 
+@pytest.mark.parametrize("rows,hidden", [(1, 256), (37, 768), (1000, 1536), (64, 2048)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("with_residual", [False, True])
+def test_row_rms_norm_fwd_bwd(rows, hidden, dtype, with_residual):
+    g = torch.Generator().manual_seed(rows + hidden)
+    x = torch.randn(2, rows, hidden, generator=g).to(dtype)
+    res = torch.randn(2, rows, hidden, generator=g).to(dtype) if with_residual else None
+    w = torch.rand(hidden, generator=g) + 0.5
+    dy = torch.randn(2, rows, hidden, generator=g).to(dtype)
+    dres = torch.randn(2, rows, hidden, generator=g).to(dtype) if with_residual else None
+    m = fox.RMSNorm(hidden).cuda()
+    with torch.no_grad():
+        m.weight.copy_(w)
+    xc = x.cuda().requires_grad_()
+    if with_residual:                      # the block's mlp_norm(hidden_states, residual, True)
+        rc = res.cuda().requires_grad_()
+        y, z = m(xc, rc, True)
+        torch.autograd.backward([y, z], [dy.cuda(), dres.cuda()])
+    else:                                  # the block's attn_norm(hidden_states)
+        y = m(xc)
+        y.backward(dy.cuda())
+    ry, rz, rdx, rdw = orc.rms_norm_fwd_bwd(x, w, res, dy, dres, 1e-5)
+    # one ulp of the 16-bit type at the tensor's largest magnitude (x + residual reaches 6-8)
+    tol = (2.0 ** -7 if dtype == torch.bfloat16 else 2.0 ** -10)
+    assert y.dtype == dtype and _err(y, ry) <= tol * max(1.0, ry.abs().max().item())
+    assert _err(xc.grad, rdx) <= 2 * tol * max(1.0, rdx.abs().max().item())
+    if with_residual:
+        assert torch.equal(z.cpu(), rz) and torch.equal(rc.grad, xc.grad)
+    assert _err(m.weight.grad, rdw) / rdw.abs().max().item() < 2e-2
+
+
+def test_row_rms_norm_against_upstream_reference_outputs():
+    z = load_glue_golden()
+    x, res, w = z["rn_x"].cuda().requires_grad_(), z["rn_res"].cuda().requires_grad_(), z["rn_w"].cuda().requires_grad_()
+    y, zs = fox.rms_norm(x, w, None, residual=res, eps=z["rn_eps"], prenorm=True)
+    torch.autograd.backward([y, zs], [z["rn_dy"].cuda(), z["rn_dres"].cuda()])
+    assert _err(y, z["rn_y"]) < 2e-3 and torch.equal(zs.cpu(), z["rn_z"].to(zs.dtype))
+    assert _err(x.grad, z["rn_dx"]) < 8e-3 and _err(res.grad, z["rn_dr"]) < 8e-3
+    assert _err(w.grad, z["rn_dw"]) / z["rn_dw"].abs().max().item() < 1e-2
+    with pytest.raises(_lib.FoxError):
+        fox.rms_norm(torch.randn(4, 384).half().cuda(), torch.ones(384).cuda())   # 384 is not a built row length
+
+
 def test_token_shift_bit_exact_against_upstream_kernel_outputs():
     z = load_glue_golden()
     x = z["ts_x"].cuda().requires_grad_()

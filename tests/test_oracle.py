@@ -170,3 +170,9 @@ def test_glue_oracles_against_upstream_references():
     out, dx, dprev, dcurr = orc.token_shift_fwd_bwd(z["ts_x"], z["ts_prev"], z["ts_curr"], z["ts_dout"])
     assert torch.equal(out, z["ts_out"]) and torch.equal(dx, z["ts_dx"])
     assert _err(dprev, z["ts_dprev"]) < 1e-4 and _err(dcurr, z["ts_dcurr"]) < 1e-4
+    # row RMSNorm with residual, prenorm (upstream's reference keeps the sum in fp32; the kernel and the oracle
+    # return it rounded to the input dtype, and differentiate through the rounded copy)
+    y, zs, dx, dw = orc.rms_norm_fwd_bwd(z["rn_x"], z["rn_w"], z["rn_res"], z["rn_dy"], z["rn_dres"], z["rn_eps"])
+    assert torch.equal(y, z["rn_y"]) and torch.equal(zs, z["rn_z"].to(zs.dtype))
+    assert _err(dx, z["rn_dx"]) < 4e-3 and _err(dx, z["rn_dr"]) < 4e-3
+    assert _err(dw, z["rn_dw"]) < 2e-3 * z["rn_dw"].abs().max()
