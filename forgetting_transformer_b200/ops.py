@@ -303,3 +303,38 @@ def forgetting_attention(
     if not head_first:
         out = out.permute(0, 2, 1, 3)
     return out
+
+
+# ---- the FoX layer's glue in front of the operator (modeling_forgetting_transformer.py:366-396) ----
+
+def seq_start_from_attention_mask(attention_mask: torch.Tensor) -> torch.Tensor:
+    """``seq_start = T - attention_mask.sum(-1)`` for a left-padded (B, T) mask (upstream lines 392-396)."""
+    assert attention_mask.dim() == 2
+    return attention_mask.shape[-1] - attention_mask.sum(dim=-1)
+
+
+def acp_threshold_from_qk_norm(q_norm_weight: torch.Tensor, k_norm_weight: torch.Tensor, num_heads: int,
+                               head_dim: int, seq_len: int, log_pruning_tolerance: float,
+                               share_param_across_head: bool = False) -> torch.Tensor:
+    """Pruning threshold of a layer with QK-norm: after a per-head RMSNorm ||q|| <= max|w_q| sqrt(D), so
+    the logit bound max|w_q| max|w_k| sqrt(D) needs no pass over the data (upstream lines 371-381).
+    Returns a scalar (shared weights) or a (num_heads,) tensor for ``adaptive_threshold``."""
+    with torch.no_grad():
+        if share_param_across_head:
+            assert q_norm_weight.size() == k_norm_weight.size() == (head_dim,)
+            bound = q_norm_weight.abs().max() * k_norm_weight.abs().max() * math.sqrt(head_dim)
+        else:
+            assert q_norm_weight.size() == k_norm_weight.size() == (num_heads * head_dim,)
+            bound = (q_norm_weight.view(num_heads, head_dim).abs().max(dim=-1).values
+                     * k_norm_weight.view(num_heads, head_dim).abs().max(dim=-1).values * math.sqrt(head_dim))
+        return -(2 * bound + math.log(seq_len)) + log_pruning_tolerance
+
+
+def acp_threshold_from_data(q: torch.Tensor, k: torch.Tensor, log_pruning_tolerance: float) -> torch.Tensor:
+    """Pruning threshold of a layer without QK-norm, from the largest row norms of head-first q, k
+    (upstream lines 383-387); (B, H) tensor for ``adaptive_threshold``.  The norms come from
+    ``fox_max_row_norm`` in the input dtype, as ``torch.linalg.vector_norm(...).max(...)`` gives them."""
+    with torch.no_grad():
+        D, T = q.shape[-1], k.shape[2]
+        bound = max_row_norm(q) * max_row_norm(k) / math.sqrt(D)
+        return -(2 * bound + math.log(T)) + log_pruning_tolerance

@@ -111,3 +111,21 @@ def test_signature_matches_upstream():
         assert sig.parameters[n].kind is inspect.Parameter.KEYWORD_ONLY
     assert sig.parameters["head_first"].default is False
     assert sig.parameters["seq_start"].default is None
+
+
+def test_layer_glue_expressions():
+    """The layer-side helpers restate upstream's expressions (modeling_forgetting_transformer.py:371-396)."""
+    import math
+    import forgetting_transformer_b200 as fox
+    mask = torch.tensor([[0, 0, 1, 1, 1], [1, 1, 1, 1, 1]])
+    assert fox.seq_start_from_attention_mask(mask).tolist() == [2, 0]
+    g = torch.Generator().manual_seed(0)
+    H, D, T, tol = 3, 64, 1000, -10.0
+    wq, wk = torch.randn(H * D, generator=g), torch.randn(H * D, generator=g)
+    thr = fox.acp_threshold_from_qk_norm(wq, wk, H, D, T, tol)
+    ref = -(2 * wq.view(H, D).abs().max(-1).values * wk.view(H, D).abs().max(-1).values * math.sqrt(D)
+            + math.log(T)) + tol
+    assert thr.shape == (H,) and torch.equal(thr, ref)
+    ws = fox.acp_threshold_from_qk_norm(wq[:D], wk[:D], H, D, T, tol, share_param_across_head=True)
+    assert ws.dim() == 0 and ws.item() == (-(2 * wq[:D].abs().max() * wk[:D].abs().max() * math.sqrt(D)
+                                              + math.log(T)) + tol).item()

@@ -280,6 +280,38 @@ def test_auto_threshold_identical_to_upstream_expression():
         assert torch.equal(thr, orc.auto_threshold(q, k, 0.125))
 
 
+def test_host_streamed_steps_equal_direct_calls():
+    """The stream-pipelined host-buffer path returns, step by step, what direct calls return."""
+    from forgetting_transformer_b200.host_pipeline import HostStreamedAttention
+    seq = torch.tensor([0, 50]).cuda()
+    pipe = HostStreamedAttention(torch.device("cuda", torch.cuda.current_device()), seq_start=seq)
+    steps = []
+    for i in range(5):                       # more steps than buffer sets
+        q, k, v, lf, do = _inputs(40 + i, 2, 2, 384, 384, 64, torch.bfloat16)
+        host = {n: t.pin_memory() for n, t in dict(q=q, k=k, v=v, log_fgate=lf, dout=do).items()}
+        hout, ev = pipe.submit(host)
+        ev.synchronize()
+        steps.append((host, {n: t.clone() for n, t in hout.items()}))
+    pipe.finish()
+    for host, got in steps:
+        qq, kk, vv, ll = [host[n].cuda().requires_grad_() for n in ("q", "k", "v", "log_fgate")]
+        out = fox.forgetting_attention(qq, kk, vv, ll, head_first=True, seq_start=seq)
+        out.backward(host["dout"].cuda())
+        assert torch.equal(got["out"], out.detach().cpu()) and torch.equal(got["dk"], kk.grad.cpu())
+        assert torch.equal(got["dv"], vv.grad.cpu())
+        # dq and dlog_fgate come out of fp32 atomics whose order varies from run to run
+        _close(got["dq"], qq.grad, 1e-2, 1e-2)
+        _close(got["dlog_fgate"], ll.grad, 1e-2, 1e-2)
+
+
+def test_layer_threshold_from_data_matches_auto():
+    """acp_threshold_from_data with tolerance -10 is the operator's own "auto" threshold (OPS:95-102)."""
+    q, k, v, lf, do = _inputs(5, 2, 3, 300, 300, 64, torch.bfloat16)
+    thr = fox.acp_threshold_from_data(q.cuda(), k.cuda(), -10.0)
+    ref = orc.auto_threshold(q, k, 1 / math.sqrt(64))
+    assert thr.shape == (2, 3) and torch.equal(thr.float().cpu(), ref.float())
+
+
 def test_pruned_attention_matches_block_oracle():
     """Strong decay + "auto": most KV blocks are pruned; outputs and gradients match the
     oracle that skips exactly the blocks named by the index arrays."""
