@@ -1,9 +1,9 @@
 """Generates the golden fixtures in this directory from the upstream project itself.
 
 Run once, in a container that has the upstream checkout (read-only) at
-$FOX_REFERENCE_SRC (default /root/reference/src):
+$FOX_REFERENCE_SRC (the directory that holds the ``forgetting_transformer`` package):
 
-    TRITON_INTERPRET=1 python tests/golden/make_golden.py
+    FOX_REFERENCE_SRC=<upstream>/src TRITON_INTERPRET=1 python tests/golden/make_golden.py
 
 It imports upstream's ``forgetting_transformer.ops.forgetting_attention`` and runs
 its *own Triton kernels* in Triton's CPU interpreter (fp16 -- the interpreter has no
@@ -20,7 +20,7 @@ os.environ.setdefault("TRITON_INTERPRET", "1")
 import numpy as np
 import torch
 
-REF = os.environ.get("FOX_REFERENCE_SRC", "/root/reference/src")
+REF = os.environ["FOX_REFERENCE_SRC"]
 sys.path.insert(0, REF)
 sys.dont_write_bytecode = True
 import forgetting_transformer.ops.forgetting_attention as ops  # noqa: E402

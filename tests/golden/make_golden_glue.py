@@ -2,9 +2,9 @@
 without the sigmoid gate, token shift) from the upstream project itself.
 
 Run once, in a container that has the upstream checkout (read-only) at
-$FOX_REFERENCE_SRC (default /root/reference/src):
+$FOX_REFERENCE_SRC (the directory that holds the ``forgetting_transformer`` package):
 
-    TRITON_INTERPRET=1 python tests/golden/make_golden_glue.py
+    FOX_REFERENCE_SRC=<upstream>/src TRITON_INTERPRET=1 python tests/golden/make_golden_glue.py
 
 * norms: upstream's pure-PyTorch references ``group_norm_gated_ref`` (fuse_norm_gate.py:18-53) and
   ``group_norm_ref`` (layernorm.py:77-110), called on CPU with upcast=True in the FoX layer's
@@ -24,7 +24,7 @@ os.environ.setdefault("TRITON_INTERPRET", "1")
 import numpy as np
 import torch
 
-REF = os.environ.get("FOX_REFERENCE_SRC", "/root/reference/src")
+REF = os.environ["FOX_REFERENCE_SRC"]
 sys.path.insert(0, REF)
 sys.dont_write_bytecode = True
 from forgetting_transformer.model.forgetting_transformer.fuse_norm_gate import group_norm_gated_ref  # noqa: E402
