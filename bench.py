@@ -393,6 +393,35 @@ def run_ours(args, w, wname):
                                    "fwd_gbs": (4 * n_el + 8 * tokens * G) / (f_ms * 1e-3) / 1e9,
                                    "bwd_gbs": (6 * n_el + 16 * tokens * G) / (b_ms * 1e-3) / 1e9}
 
+    # ---- the FoX-Pro block of config 5 around the attention (single GPU): Linear layers are cuBLAS, the rest
+    #      this library's kernels; reported beside the attention-only numbers, not as the metric ----
+    block = None
+    if world == 1 and wname == "cfg5_attn" and not args.no_e2e:
+        hidden, inter = w["H"] * w["D"], 4096
+        blk = fox.FoxProBlock(hidden, w["H"], inter, fgate_bias=5.0).to(dev).to(torch.bfloat16)
+        xb = torch.randn(w["B"], w["T"], hidden, device=dev, dtype=torch.bfloat16).requires_grad_()
+        dyb = torch.randn(w["B"], w["T"], hidden, device=dev, dtype=torch.bfloat16)
+        for _ in range(2):
+            blk(xb).backward(dyb)
+        torch.cuda.synchronize()
+        n_blk = 3
+        with ops.KernelTimer() as btimer:
+            e0.record()
+            for _ in range(n_blk):
+                blk(xb).backward(dyb)
+            e1.record()
+            torch.cuda.synchronize()
+        bk = btimer.summary()
+        ms_blk = e0.elapsed_time(e1) / n_blk
+        tokens_b = w["B"] * w["T"]
+        lin_flops = 6.0 * tokens_b * (5 * hidden * hidden + 3 * hidden * inter + 3 * hidden * w["H"])
+        block = {"shape": f"B{w['B']} T{w['T']} hidden {hidden}, {w['H']} heads, SwiGLU {inter}, bf16 weights",
+                 "ms_per_step": ms_blk,
+                 "attention_kernels_ms": sum(v_[1] * v_[0] / n_blk for k_, v_ in bk.items()),
+                 "attention_flops": flops, "linear_flops": lin_flops,
+                 "tflops_total": (flops + lin_flops) / (ms_blk * 1e-3) / 1e12}
+        del blk, xb, dyb
+
     if rank == 0:
         peaks = load_peaks()
         bwd_n, bwd_ms = kern.get("fox_attn_bwd", (0, float("nan")))
@@ -432,6 +461,8 @@ def run_ours(args, w, wname):
         }
         if acp is not None:
             line["acp"] = acp
+        if block is not None:
+            line["fox_pro_block"] = block
         if normgate is not None:
             normgate["frac_of_hbm_peak_fwd"] = normgate["fwd_gbs"] / peaks["hbm_gbs"]
             line["normgate"] = normgate

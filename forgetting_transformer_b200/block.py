@@ -1,0 +1,150 @@
+"""The FoX-Pro block (attention layer + SwiGLU MLP) composed from this package's operators.
+
+Mirrors the data flow of upstream's ``ForgettingAttentionLayer`` / ``ForgettingTransformerMLP`` /
+``ForgettingTransformerBlock`` (modeling_forgetting_transformer.py:98-430, 467-516, 519-622) in the "Pro"
+configuration: output gate + output norm, per-head QK-norm, data-dependent K and V token shift, full forget
+gate, no rotary embedding, training path only (no cache).  The matrix products are ``nn.Linear`` (cuBLAS);
+everything between them is a kernel of this library:
+
+    x -> RMSNorm -> q_proj, ShiftLinear(k), ShiftLinear(v), fgate_proj, ogate_proj
+      -> per-head RMSNorm(q), RMSNorm(k) -> forgetting_attention(log sigmoid(fgate))
+      -> per-head RMSNorm * sigmoid(ogate) -> o_proj -> (+ residual, RMSNorm with prenorm) -> SwiGLU MLP -> +
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from .norm_gate import FusedGroupNormGated, GroupNorm, RMSNorm
+from .ops import acp_threshold_from_qk_norm, forgetting_attention, seq_start_from_attention_mask
+from .token_shift import token_shift
+
+__all__ = ["ShiftLinear", "FoxProAttentionLayer", "FoxMLP", "FoxProBlock"]
+
+
+class ShiftLinear(nn.Module):
+    """Linear projection followed by the data-dependent token shift (upstream lines 44-95, T > 1 branch)."""
+
+    def __init__(self, input_dim: int, output_dim: int, num_heads: int, bias: bool = False, shift_bias: bool = False):
+        super().__init__()
+        assert output_dim % num_heads == 0
+        self.num_heads = num_heads
+        self.linear = nn.Linear(input_dim, output_dim, bias=bias)
+        self.shift_proj = nn.Linear(input_dim, num_heads, bias=shift_bias)
+
+    def forward(self, x: torch.Tensor, attention_mask: Optional[torch.Tensor] = None) -> torch.Tensor:
+        B, T, _ = x.shape
+        out = self.linear(x)
+        alpha = torch.sigmoid(self.shift_proj(x).float())
+        out_per_head = out.view(B, T, self.num_heads, -1)
+        if attention_mask is not None:
+            out_per_head = torch.where(attention_mask[:, :, None, None].bool(), out_per_head, 0.0)
+        return token_shift(out_per_head, alpha, 1.0 - alpha).to(out.dtype).reshape(B, T, -1)
+
+
+class FoxProAttentionLayer(nn.Module):
+
+    def __init__(self, hidden_size: int, num_heads: int, norm_eps: float = 1e-6, qk_norm: bool = True,
+                 use_k_shift: bool = True, use_v_shift: bool = True, fgate_bias: float = 0.0,
+                 log_pruning_tolerance: Optional[float] = None, initializer_range: float = 0.02):
+        super().__init__()
+        assert hidden_size % num_heads == 0
+        self.hidden_size, self.num_heads, self.head_dim = hidden_size, num_heads, hidden_size // num_heads
+        self.q_proj = nn.Linear(hidden_size, hidden_size, bias=False)
+        self.k_proj = (ShiftLinear(hidden_size, hidden_size, num_heads) if use_k_shift
+                       else nn.Linear(hidden_size, hidden_size, bias=False))
+        self.v_proj = (ShiftLinear(hidden_size, hidden_size, num_heads) if use_v_shift
+                       else nn.Linear(hidden_size, hidden_size, bias=False))
+        self.use_k_shift, self.use_v_shift = use_k_shift, use_v_shift
+        self.o_proj = nn.Linear(hidden_size, hidden_size, bias=False)
+        self.fgate_proj = nn.Linear(hidden_size, num_heads, bias=True)
+        self.ogate_proj = nn.Linear(hidden_size, hidden_size, bias=False)
+        self.output_norm = FusedGroupNormGated(num_groups=num_heads, hidden_size=hidden_size, eps=norm_eps,
+                                               activation="sigmoid", is_rms_norm=True)
+        self.qk_norm = qk_norm
+        if qk_norm:
+            self.q_norm = GroupNorm(num_groups=num_heads, hidden_size=hidden_size, is_rms_norm=True)
+            self.k_norm = GroupNorm(num_groups=num_heads, hidden_size=hidden_size, is_rms_norm=True)
+        self.log_pruning_tolerance = log_pruning_tolerance
+        for m in self.modules():
+            if isinstance(m, nn.Linear):
+                nn.init.normal_(m.weight, mean=0.0, std=initializer_range)
+                if m.bias is not None:
+                    nn.init.zeros_(m.bias)
+        with torch.no_grad():
+            self.fgate_proj.bias.fill_(fgate_bias)
+
+    def forward(self, hidden_states: torch.Tensor, attention_mask: Optional[torch.Tensor] = None) -> torch.Tensor:
+        dtype = torch.get_autocast_dtype("cuda") if torch.is_autocast_enabled("cuda") else hidden_states.dtype
+        hidden_states = hidden_states.to(dtype)
+        B, T, _ = hidden_states.shape
+        H, D = self.num_heads, self.head_dim
+        q = self.q_proj(hidden_states)
+        k = self.k_proj(hidden_states, attention_mask) if self.use_k_shift else self.k_proj(hidden_states)
+        v = self.v_proj(hidden_states, attention_mask) if self.use_v_shift else self.v_proj(hidden_states)
+        if self.qk_norm:
+            q = self.q_norm(q).to(q.dtype)
+            k = self.k_norm(k).to(k.dtype)
+        fgate_logit = self.fgate_proj(hidden_states).transpose(1, 2)               # (B, H, T)
+        log_fgate = F.logsigmoid(fgate_logit.float())
+        q, k, v = [t.view(B, T, H, D).transpose(1, 2) for t in (q, k, v)]          # head-first views
+        thr = None
+        if self.log_pruning_tolerance is not None:
+            assert self.qk_norm, "the closed-form threshold needs QK-norm"
+            thr = acp_threshold_from_qk_norm(self.q_norm.weight, self.k_norm.weight, H, D, T,
+                                             self.log_pruning_tolerance)
+        seq_start = None if attention_mask is None else seq_start_from_attention_mask(attention_mask)
+        o = forgetting_attention(q, k, v, log_fgate, head_first=True, seq_start=seq_start,
+                                 sm_scale=1 / math.sqrt(D), adaptive_threshold=thr)
+        o = o.transpose(1, 2).reshape(B, T, self.hidden_size)
+        o = self.output_norm(o, self.ogate_proj(hidden_states))
+        return self.o_proj(o)
+
+
+class FoxMLP(nn.Module):
+    """SwiGLU MLP (upstream lines 467-516): down_proj(silu(gate) * y) with [gate, y] = gate_proj(x)."""
+
+    def __init__(self, hidden_size: int, intermediate_size: int, initializer_range: float = 0.02):
+        super().__init__()
+        self.gate_proj = nn.Linear(hidden_size, intermediate_size * 2, bias=False)
+        self.down_proj = nn.Linear(intermediate_size, hidden_size, bias=False)
+        for m in (self.gate_proj, self.down_proj):
+            nn.init.normal_(m.weight, mean=0.0, std=initializer_range)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        gate, y = self.gate_proj(x).chunk(2, -1)
+        return self.down_proj(F.silu(gate) * y)
+
+
+class FoxProBlock(nn.Module):
+    """attn_norm -> attention -> (residual add + mlp_norm, prenorm) -> MLP -> residual add (upstream lines 552-622)."""
+
+    def __init__(self, hidden_size: int = 1536, num_heads: int = 24, intermediate_size: int = 4096,
+                 norm_eps: float = 1e-6, fgate_bias: float = 0.0, log_pruning_tolerance: Optional[float] = None):
+        super().__init__()
+        self.attn_norm = RMSNorm(hidden_size, eps=norm_eps)
+        self.attn = FoxProAttentionLayer(hidden_size, num_heads, norm_eps=norm_eps, fgate_bias=fgate_bias,
+                                         log_pruning_tolerance=log_pruning_tolerance)
+        self.mlp_norm = RMSNorm(hidden_size, eps=norm_eps)
+        self.mlp = FoxMLP(hidden_size, intermediate_size)
+
+    def forward(self, hidden_states: torch.Tensor, attention_mask: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """hidden_states (B, T, hidden) in fp16/bf16 (the residual stream is kept in that dtype here)."""
+        residual = hidden_states
+        hidden_states = self.attn(self.attn_norm(hidden_states), attention_mask)
+        hidden_states, residual = self.mlp_norm(hidden_states, residual, True)
+        return residual + self.mlp(hidden_states)
+
+    def oracle_weights(self) -> dict:
+        """The block's weights under the names the CPU oracle's restatement of the block uses."""
+        a = self.attn
+        return {"attn_norm": self.attn_norm.weight, "q": a.q_proj.weight, "k": a.k_proj.linear.weight,
+                "k_shift": a.k_proj.shift_proj.weight, "v": a.v_proj.linear.weight,
+                "v_shift": a.v_proj.shift_proj.weight, "q_norm": a.q_norm.weight, "k_norm": a.k_norm.weight,
+                "fgate_w": a.fgate_proj.weight, "fgate_b": a.fgate_proj.bias, "ogate": a.ogate_proj.weight,
+                "out_norm": a.output_norm.weight, "o": a.o_proj.weight, "mlp_norm": self.mlp_norm.weight,
+                "gate": self.mlp.gate_proj.weight, "down": self.mlp.down_proj.weight}

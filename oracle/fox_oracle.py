@@ -377,3 +377,39 @@ def rms_norm_fwd_bwd(x, weight, residual, dy, dres, eps=1e-5):
         dx = dx + dres.float()
     dw = (dy.float() * xhat).reshape(-1, x.shape[-1]).sum(0)
     return y, zs, dx.to(x.dtype), dw
+
+
+def fox_pro_block(x, weights: dict, num_heads: int, eps: float = 1e-6, attention_mask=None):
+    """fp32 restatement of the FoX-Pro block's data flow (modeling_forgetting_transformer.py:44-95,
+    300-430, 505-516, 565-588) from a dict of weights: attn_norm, q, k, k_shift, v, v_shift, q_norm, k_norm,
+    fgate_w, fgate_b, ogate, out_norm, o, mlp_norm, gate, down.  Every operator is this module's own
+    reference; the matrix products are plain fp32 matmuls."""
+    W = {n: t.float() for n, t in weights.items()}
+    x = x.float()
+    B, T, C = x.shape
+    H, D = num_heads, C // num_heads
+    residual = x
+    h = rms_norm(x, W["attn_norm"], None, eps)
+    q = h @ W["q"].T
+
+    def shifted(w, w_shift):
+        out = (h @ w.T).view(B, T, H, D)
+        alpha = torch.sigmoid(h @ w_shift.T)
+        if attention_mask is not None:
+            out = torch.where(attention_mask[:, :, None, None].bool(), out, 0.0)
+        return token_shift(out, alpha, 1.0 - alpha).reshape(B, T, C)
+
+    k = shifted(W["k"], W["k_shift"])
+    v = shifted(W["v"], W["v_shift"])
+    q = group_rmsnorm(q, W["q_norm"], H, 1e-5)
+    k = group_rmsnorm(k, W["k_norm"], H, 1e-5)
+    log_fgate = torch.nn.functional.logsigmoid(h @ W["fgate_w"].T + W["fgate_b"]).transpose(1, 2)
+    qh, kh, vh = [t.view(B, T, H, D).transpose(1, 2) for t in (q, k, v)]
+    seq_start = None if attention_mask is None else attention_mask.shape[-1] - attention_mask.sum(-1)
+    o = dense_forgetting_attention(qh, kh, vh, log_fgate, seq_start=seq_start, sm_scale=1 / math.sqrt(D))
+    o = o.transpose(1, 2).reshape(B, T, C)
+    o = group_rmsnorm_gated(o, h @ W["ogate"].T, W["out_norm"], H, eps)
+    attn_out = o @ W["o"].T
+    h2, residual = rms_norm(attn_out, W["mlp_norm"], residual, eps, prenorm=True)
+    gate, y = (h2 @ W["gate"].T).chunk(2, -1)
+    return residual + (torch.nn.functional.silu(gate) * y) @ W["down"].T

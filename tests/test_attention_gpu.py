@@ -211,6 +211,19 @@ def test_seq_len_q_shorter_than_kv():
     _close(dlf, r["dlog_fgate"], 2 * ATOL_BF16, RTOL_BF16)
 
 
+@pytest.mark.parametrize("N,D", [(777, 64), (1, 64), (4099, 128)])
+def test_single_query_decode_step(N, D):
+    """One new token against a cache of N keys (generation, OPS:148-153): seqlen_q = 1 goes through the
+    same kernels; forward output and, for completeness, the gradients."""
+    q, k, v, lf, do = _inputs(N + D, 2, 3, 1, N, D, torch.bfloat16, mu=2.0)
+    seq = torch.tensor([0, min(5, N - 1)])
+    out, dq, dk, dv, dlf = _run(q, k, v, lf, do, seq)
+    r = orc.blockwise_fwd_bwd(q, k, v, lf, do, seq, low_precision_matmul=False)
+    for a, b in [(out, r["out"]), (dq, r["dq"]), (dk, r["dk"]), (dv, r["dv"])]:
+        _close(a, b, ATOL_BF16, RTOL_BF16)
+    _close(dlf, r["dlog_fgate"], 2 * ATOL_BF16, RTOL_BF16)
+
+
 def test_layout_b_t_h_d_views_and_output_strides():
     """head_first=False hands the kernels permuted views; the output keeps q's layout."""
     B, T, H, D = 2, 320, 3, 64

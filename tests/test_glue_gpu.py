@@ -138,3 +138,37 @@ def test_token_shift_contract():
         fox.token_shift(x.cuda(), w.cuda(), w.cuda())          # D not in {16, 32, 64, 128}
     with pytest.raises(_lib.FoxError):
         fox.token_shift(torch.randn(1, 4, 2, 16).half(), w, w)  # no CPU path
+
+
+@pytest.mark.parametrize("with_mask", [False, True])
+def test_fox_pro_block_against_oracle(with_mask):
+    """The block composed from the package's operators against the oracle's fp32 restatement of its data
+    flow, same weights: output and input gradient."""
+    torch.manual_seed(3)
+    B, T, C, H, I = 2, 300, 256, 4, 512
+    blk = fox.FoxProBlock(C, H, I, fgate_bias=2.0).cuda().to(torch.bfloat16)
+    with torch.no_grad():                       # non-trivial norm weights
+        for m in (blk.attn_norm, blk.mlp_norm, blk.attn.q_norm, blk.attn.k_norm, blk.attn.output_norm):
+            m.weight.uniform_(0.5, 1.5)
+        for lin in (blk.attn.q_proj, blk.attn.k_proj.linear, blk.attn.v_proj.linear, blk.attn.o_proj,
+                    blk.attn.ogate_proj, blk.mlp.gate_proj, blk.mlp.down_proj):
+            lin.weight.normal_(0, 0.08)
+    x = torch.randn(B, T, C, device="cuda").to(torch.bfloat16).requires_grad_()
+    mask = None
+    if with_mask:
+        mask = torch.ones(B, T, dtype=torch.long, device="cuda")
+        mask[1, :17] = 0                        # left padding
+    y = blk(x, mask)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    xr = x.detach().float().cpu().requires_grad_()
+    w = {n: t.detach().float().cpu() for n, t in blk.oracle_weights().items()}
+    yr = orc.fox_pro_block(xr, w, H, eps=1e-6, attention_mask=None if mask is None else mask.cpu())
+    yr.backward(dy.float().cpu())
+    valid = slice(None) if mask is None else mask.bool().cpu()
+    scale = yr.detach().abs().max().item()
+    assert (y.detach().float().cpu() - yr.detach())[valid].abs().max().item() < 3e-2 * scale
+    gscale = xr.grad.abs().max().item()
+    assert (x.grad.float().cpu() - xr.grad)[valid].abs().max().item() < 5e-2 * gscale
