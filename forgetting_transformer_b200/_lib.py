@@ -55,6 +55,9 @@ _SIGNATURES = {
     "fox_normgate_bwd": (c_int, [c_int, c_void_p, c_int, c_int64, c_int64, c_int64, _F, _F, _F, _F, _F, _F, _F, _F, c_int64]),
     "fox_rmsnorm_fwd": (c_int, [c_int, c_void_p, c_int, c_int64, c_int64, _F, _F, _F, c_float, _F, _F, _F]),
     "fox_rmsnorm_bwd": (c_int, [c_int, c_void_p, c_int, c_int64, c_int64, _F, _F, _F, _F, _F, _F, _F, c_int64]),
+    "fox_swiglu_fwd": (c_int, [c_int, c_void_p, c_int, c_int64, c_int64, _F, c_int64, _F, c_int64, _F, c_int64]),
+    "fox_swiglu_bwd": (c_int, [c_int, c_void_p, c_int, c_int64, c_int64, _F, c_int64, _F, c_int64, _F, c_int64, _F,
+                               c_int64, _F, c_int64, _F, c_int64]),
     "fox_token_shift_fwd": (c_int, [c_int, c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, _F, c_int64, c_int64,
                                     c_int64, _F, _F, c_int64, c_int64, c_int64, _F]),
     "fox_token_shift_bwd": (c_int, [c_int, c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, _F, c_int64, c_int64,

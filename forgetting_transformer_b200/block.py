@@ -3,7 +3,7 @@
 Mirrors the data flow of upstream's ``ForgettingAttentionLayer`` / ``ForgettingTransformerMLP`` /
 ``ForgettingTransformerBlock`` (modeling_forgetting_transformer.py:98-430, 467-516, 519-622) in the "Pro"
 configuration: output gate + output norm, per-head QK-norm, data-dependent K and V token shift, full forget
-gate, no rotary embedding, training path only (no cache).  The matrix products are ``nn.Linear`` (cuBLAS);
+gate, no rotary embedding, training path only (no cache).  The matrix products are ``nn.Linear`` / ``F.linear`` (cuBLAS);
 everything between them is a kernel of this library:
 
     x -> RMSNorm -> q_proj, ShiftLinear(k), ShiftLinear(v), fgate_proj, ogate_proj
@@ -21,6 +21,7 @@ import torch.nn.functional as F
 
 from .norm_gate import FusedGroupNormGated, GroupNorm, RMSNorm
 from .ops import acp_threshold_from_qk_norm, forgetting_attention, seq_start_from_attention_mask
+from .glu import swiglu_linear_packed
 from .token_shift import token_shift
 
 __all__ = ["ShiftLinear", "FoxProAttentionLayer", "FoxMLP", "FoxProBlock"]
@@ -116,8 +117,7 @@ class FoxMLP(nn.Module):
             nn.init.normal_(m.weight, mean=0.0, std=initializer_range)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        gate, y = self.gate_proj(x).chunk(2, -1)
-        return self.down_proj(F.silu(gate) * y)
+        return swiglu_linear_packed(self.gate_proj(x), self.down_proj.weight, self.down_proj.bias)
 
 
 class FoxProBlock(nn.Module):

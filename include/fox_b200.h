@@ -168,6 +168,20 @@ int fox_rmsnorm_bwd(int device, void* stream, int dtype, int64_t rows, int64_t h
                     const float* w, const float* rstd, const void* dy, const void* dresidual_in, void* dx,
                     float* dw_partial, int64_t n_partials);
 
+/* SwiGLU, forward: z = x * sigmoid(x) * y elementwise in fp32, rounded once.  Replaces swiglu_fwd
+ * (glu_linear.py:64-68; SwiGLUFunction / SwiGLULinearFunction 95-146) of ForgettingTransformerMLP
+ * (modeling_forgetting_transformer.py:505-516).  x, y, z: (rows, cols) 16-bit, unit inner stride, own
+ * row strides in elements (multiples of 8, >= cols): the halves of a packed projection are read in place. */
+int fox_swiglu_fwd(int device, void* stream, int dtype, int64_t rows, int64_t cols, const void* x,
+                   int64_t x_row_stride, const void* y, int64_t y_row_stride, void* z, int64_t z_row_stride);
+
+/* Backward of the above (swiglu_bwd / swiglu_bwd_with_output, glu_linear.py:70-86): s = sigmoid(x);
+ * dx = s (1 + x (1 - s)) g y; dy = x s g; z (may be NULL) = x s y again for the weight gradient of the
+ * linear layer behind it. */
+int fox_swiglu_bwd(int device, void* stream, int dtype, int64_t rows, int64_t cols, const void* x,
+                   int64_t x_row_stride, const void* y, int64_t y_row_stride, const void* g, int64_t g_row_stride,
+                   void* dx, int64_t dx_row_stride, void* dy, int64_t dy_row_stride, void* z, int64_t z_row_stride);
+
 /* Data-dependent token shift, forward: out[b,t,h,:] = x[b,t,h,:] * curr[b,t,h] + x[b,t-1,h,:] *
  * prev[b,t,h] with x[b,-1] = 0, products in fp32, rounded once.  Replaces shift_fwd_kernel
  * (token_shift.py:21-80; TokenShift.forward 164-195), which ShiftLinear calls as

@@ -413,3 +413,18 @@ def fox_pro_block(x, weights: dict, num_heads: int, eps: float = 1e-6, attention
     h2, residual = rms_norm(attn_out, W["mlp_norm"], residual, eps, prenorm=True)
     gate, y = (h2 @ W["gate"].T).chunk(2, -1)
     return residual + (torch.nn.functional.silu(gate) * y) @ W["down"].T
+
+
+def swiglu(x: torch.Tensor, y: torch.Tensor) -> torch.Tensor:
+    """z = x sigmoid(x) y in fp32, one rounding (glu_linear.py:64-68)."""
+    xf = x.float()
+    return (xf * y.float() / (1.0 + torch.exp(-xf))).to(x.dtype)
+
+
+def swiglu_bwd(x, y, g):
+    """dx, dy, z with upstream's expressions (glu_linear.py:78-86)."""
+    xf, yf, gf = x.float(), y.float(), g.float()
+    s = 1.0 / (1.0 + torch.exp(-xf))
+    dx = s * (1 + xf * (1.0 - s)) * gf * yf
+    dy = xf * s * gf
+    return dx.to(x.dtype), dy.to(x.dtype), (xf * s * yf).to(x.dtype)

@@ -172,3 +172,37 @@ def test_fox_pro_block_against_oracle(with_mask):
     assert (y.detach().float().cpu() - yr.detach())[valid].abs().max().item() < 3e-2 * scale
     gscale = xr.grad.abs().max().item()
     assert (x.grad.float().cpu() - xr.grad)[valid].abs().max().item() < 5e-2 * gscale
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_swiglu_and_swiglu_linear(dtype):
+    """SwiGLU kernels against upstream's expressions (glu_linear.py:64-86), in place on the halves of a
+    packed projection, and the linear-fused forms against autograd through the eager composition."""
+    g = torch.Generator().manual_seed(9)
+    rows, inter, out_dim = 333, 256, 96
+    xy = (torch.randn(3, rows, 2 * inter, generator=g) * 2).to(dtype).cuda()
+    x, y = xy.chunk(2, -1)
+    gout = torch.randn(3, rows, inter, generator=g).to(dtype).cuda()
+    xr, yr = x.detach().clone().requires_grad_(), y.detach().clone().requires_grad_()
+    z = fox.swiglu(xr, yr)
+    z.backward(gout)
+    rdx, rdy, rz = orc.swiglu_bwd(x.cpu(), y.cpu(), gout.cpu())
+    ulp = 2.0 ** -7 if dtype == torch.bfloat16 else 2.0 ** -10
+    for a, b in ((z, rz), (xr.grad, rdx), (yr.grad, rdy)):          # __expf vs exp: at most one ulp apart
+        assert _err(a, b) <= ulp * max(1.0, b.abs().max().item())
+    w = (torch.randn(out_dim, inter, generator=g) * 0.1).to(dtype).cuda().requires_grad_()
+    xy1 = xy.detach().clone().requires_grad_()
+    out = fox.swiglu_linear_packed(xy1, w, None)
+    dout = torch.randn_like(out)
+    out.backward(dout)
+    xy2, w2 = xy.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+    a_, b_ = xy2.chunk(2, -1)
+    ref = torch.nn.functional.linear(torch.nn.functional.silu(a_) * b_, w2)
+    ref.backward(dout.float())
+    assert _err(out, ref) < 3e-2 * ref.abs().max().item()
+    assert _err(xy1.grad, xy2.grad) < 3e-2 * xy2.grad.abs().max().item()
+    assert _err(w.grad, w2.grad) < 3e-2 * w2.grad.abs().max().item()
+    x3, y3, w3 = x.detach().clone().requires_grad_(), y.detach().clone().requires_grad_(), w.detach().clone().requires_grad_()
+    out3 = fox.swiglu_linear(x3, y3, w3, None)
+    out3.backward(dout)
+    assert torch.equal(out3, out) and torch.equal(torch.cat([x3.grad, y3.grad], -1), xy1.grad)
