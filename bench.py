@@ -421,6 +421,25 @@ def run_ours(args, w, wname):
                  "attention_flops": flops, "linear_flops": lin_flops,
                  "tflops_total": (flops + lin_flops) / (ms_blk * 1e-3) / 1e12}
         del blk, xb, dyb
+        # generation step on the same cache: one query row against all N keys (split-KV decode kernels), beside
+        # the same call through the general forward kernel (what a call with gradients enabled takes)
+        q1 = q.detach()[:, :, -1:, :].contiguous()
+        def dec_step(grad):
+            with torch.set_grad_enabled(grad):
+                qq_ = q1.requires_grad_(grad)
+                return fox.forgetting_attention(qq_, k.detach(), v.detach(), lf.detach(), head_first=True)
+        times = {}
+        for name_, grad in (("decode_kernels_ms", False), ("general_kernel_ms", True)):
+            for _ in range(3):
+                dec_step(grad)
+            e0.record()
+            for _ in range(20):
+                dec_step(grad)
+            e1.record()
+            torch.cuda.synchronize()
+            times[name_] = e0.elapsed_time(e1) / 20
+        kv_bytes = 2 * k.numel() * k.element_size()
+        block["decode_step"] = dict(times, keys=w["T"], kv_gbs_decode_incl_prefix_sum=kv_bytes / (times["decode_kernels_ms"] * 1e-3) / 1e9)
 
     if rank == 0:
         peaks = load_peaks()

@@ -46,6 +46,9 @@ _SIGNATURES = {
     "fox_dq_convert": (c_int, [c_int, c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, _F, c_float, _T4P]),
     "fox_attn_fwd": (c_int, [c_int, c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, c_int64, _T4P, _T4P, _T4P,
                              _F, _F, _F, c_float, _T4P, _F, _F, _F]),
+    "fox_attn_decode": (c_int, [c_int, c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, _T4P, _T4P, _T4P, _F, _F, _F,
+                                c_float, _T4P, _F, _F, c_int64]),
+    "fox_attn_decode_workspace_floats": (c_int64, [c_int64, c_int64, c_int64, c_int64]),
     "fox_attn_bwd": (c_int, [c_int, c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, c_int64, _T4P, _T4P, _T4P,
                              _T4P, _F, _F, _F, _F, _F, c_float, _F, _F, _F, _T4P, _T4P, _F]),
     "fox_attn_bwd_noalloc": (c_int, [c_int, c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, c_int64, _T4P, _T4P,

@@ -164,7 +164,7 @@ class ForgettingAttention(torch.autograd.Function):
             q, k, v = _tma_view(q), _tma_view(k), _tma_view(v)
             # largest key norm per (b,h): the forward kernel's bound that lets most tiles skip the row-maximum pass
             need_auto = isinstance(adaptive_threshold, str)
-            k_norm_max = max_row_norm(k, keep_fp32=True) if (N >= 8 * FWD_BLOCK[1] or need_auto) else None
+            k_norm_max = max_row_norm(k, keep_fp32=True) if ((N >= 8 * FWD_BLOCK[1] and M > 1) or need_auto) else None
 
             if adaptive_threshold is not None:
                 if isinstance(adaptive_threshold, str):
@@ -198,6 +198,18 @@ class ForgettingAttention(torch.autograd.Function):
             if not _lib.tma_ready(o):
                 o = torch.empty(q.shape, dtype=q.dtype, device=dev)
             L = torch.empty((B, H, M), device=dev, dtype=torch.float32)
+            if M == 1 and not any(ctx.needs_input_grad[:4]):
+                # generation step: one query row against the cache, no gradients -> split-KV kernels
+                splits = max(1, min((N + 511) // 512, (4 * 148 + B * H - 1) // (B * H), 256))
+                work = torch.empty(lib.fox_attn_decode_workspace_floats(B, H, D, splits), device=dev,
+                                   dtype=torch.float32)
+                _call("fox_attn_decode", lib.fox_attn_decode, dev.index, _stream(), _lib.dtype_code(q.dtype), B, H, N,
+                      D, _lib.t4(q), _lib.t4(k), _lib.t4(v), log_lambda.data_ptr(), _lib.ptr(seq_start),
+                      _lib.ptr(start_index), float(sm_scale), _lib.t4(o), L.data_ptr(), work.data_ptr(), splits)
+                out = o if D_in == D else o[..., :D_in].contiguous()
+                if return_log_normalizer or return_start_index:
+                    return (out, L if return_log_normalizer else None, start_index if return_start_index else None)
+                return out
             status = _lib.status_buffer(dev)
             _call("fox_attn_fwd", lib.fox_attn_fwd, dev.index, _stream(), _lib.dtype_code(q.dtype), B, H, M, N, D,
                   _lib.t4(q), _lib.t4(k), _lib.t4(v), log_lambda.data_ptr(), _lib.ptr(seq_start),

@@ -109,6 +109,19 @@ int fox_attn_fwd(int device, void* stream, int dtype, int64_t B, int64_t H, int6
                  const int64_t* seq_start, const int64_t* start_index, float sm_scale, const fox_tensor4* o,
                  float* L, const float* k_norm_max, int32_t* status);
 
+/* Forward attention for ONE query row per (b,h) -- a generation step against a cache of N keys, the
+ * seqlen_q = 1 case of the same upstream kernel (forgetting_attention.py:148-153, 591-693; cache:
+ * fgate_cache.py:77-116).  The keys are split over `splits` CTAs per (b,h) that reduce their slice to a
+ * partial (max, sum, out) triple; a second kernel merges the triples.  q, o: (B,H,1,D); k, v: (B,H,N,D),
+ * 16-bit, unit inner stride, element strides multiples of 8, 16-byte aligned bases; D in {64,128};
+ * log_lambda (B,H,N) from fox_cumsum_fwd; seq_start (B,) or NULL; start_index (B,H,1) or NULL; L (B,H,1)
+ * fp32; workspace: fox_attn_decode_workspace_floats(B,H,D,splits) floats, fully overwritten. */
+int fox_attn_decode(int device, void* stream, int dtype, int64_t B, int64_t H, int64_t N, int64_t D,
+                    const fox_tensor4* q, const fox_tensor4* k, const fox_tensor4* v, const float* log_lambda,
+                    const int64_t* seq_start, const int64_t* start_index, float sm_scale, const fox_tensor4* o,
+                    float* L, float* workspace, int64_t splits);
+int64_t fox_attn_decode_workspace_floats(int64_t B, int64_t H, int64_t D, int64_t splits);
+
 /* delta[b,h,m] = sum_d o[b,h,m,d] * d_o[b,h,m,d] in fp32: replaces _bwd_preprocess
  * (forgetting_attention.py:267-277, kernel 902-943). */
 int fox_bwd_delta(int device, void* stream, int dtype, int64_t B, int64_t H, int64_t M, int64_t D,

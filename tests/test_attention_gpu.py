@@ -224,6 +224,31 @@ def test_single_query_decode_step(N, D):
     _close(dlf, r["dlog_fgate"], 2 * ATOL_BF16, RTOL_BF16)
 
 
+@pytest.mark.parametrize("N,D,dtype", [(1, 64, torch.bfloat16), (777, 64, torch.bfloat16), (5000, 128, torch.float16),
+                                       (20000, 64, torch.bfloat16)])
+@pytest.mark.parametrize("thr", [None, -15.0])
+def test_decode_kernels_match_the_general_forward(N, D, dtype, thr):
+    """Without gradients a single-query call takes the split-KV decode kernels; with gradients enabled the
+    same call goes through the general forward kernel.  Both against the fp32 oracle and each other."""
+    q, k, v, lf, _ = _inputs(N + D, 2, 5, 1, N, D, dtype, mu=3.0)
+    seq = torch.tensor([0, min(9, N - 1)])
+    qc, kc, vc, lc, sc = q.cuda(), k.cuda(), v.cuda(), lf.cuda(), seq.cuda()
+    with torch.no_grad():
+        out_d, L_d, si_d = ops.ForgettingAttention.apply(qc, kc, vc, lc, sc, True, None, thr, True, thr is not None,
+                                                         None, False, False)
+    out_g, L_g, _ = ops.ForgettingAttention.apply(qc.requires_grad_(), kc, vc, lc, sc, True, None, thr, True, False,
+                                                  None, False, False)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    ref = orc.dense_forgetting_attention(q.float(), k.float(), v.float(), lf, seq_start=seq)
+    tol = ATOL_BF16 if dtype == torch.bfloat16 else ATOL_FP16
+    if thr is None:
+        _close(out_d, ref, tol)
+    _close(out_d, out_g.detach(), tol)
+    assert (L_d - L_g).abs().max().item() < 1e-3
+    assert out_d.shape == q.shape and out_d.dtype == dtype
+
+
 def test_layout_b_t_h_d_views_and_output_strides():
     """head_first=False hands the kernels permuted views; the output keeps q's layout."""
     B, T, H, D = 2, 320, 3, 64
