@@ -7,13 +7,14 @@
 //
 // One CTA = one (batch, head, 128-row query tile); two CTAs share an SM so that
 // one CTA's softmax overlaps the other's matrix products.
-//   warps 0-3 : softmax / correction / epilogue, thread t owns query row t and
-//               TMEM lane t (no cross-thread reductions)
-//   warp 4    : TMA producer (one elected lane)
-//   warp 5    : tcgen05.mma issuer (one elected lane)
-// TMEM (256 columns): S = Q K^T fp32 in columns [0,128); the probabilities are
-// written back over S as packed 16-bit pairs (columns [0,64)) and consumed as the
-// TMEM A operand of P V; O accumulates in columns [128, 128+D).
+//   warps 0 .. 4 NWG-1 : NWG softmax warpgroups; warpgroup g owns a BN / NWG wide column slice of every KV
+//                        tile with its own running maximum, row sum and O accumulator; thread t of a
+//                        warpgroup owns query row t and TMEM lane t (no cross-thread reductions)
+//   next warp          : TMA producer (one elected lane); also stages the tile's gate prefixes
+//   last warp          : tcgen05.mma issuer (one elected lane)
+// TMEM: S = Q K^T fp32 in columns [0,BN); each slice's probabilities are written back over the slice's own
+// S columns as packed 16-bit pairs and consumed as the TMEM A operand of P V; O_g accumulates in columns
+// [BN + g D, BN + (g+1) D).  D = 64: BN = 128, NWG = 2 (256 columns); D = 128: BN = 128, NWG = 1 (256 columns).
 //
 // KV tiles are visited from the diagonal leftwards: with forget gates the
 // largest logits sit next to the diagonal, so the running row maximum is found
