@@ -20,7 +20,8 @@
 //   dV += P^T dO ; dK += dS^T Q                          (TMEM x smem)
 //   dQ_i = dS [K | 1]                                    (smem x smem, fresh accumulator)
 // The tensor pipe and the compute warps overlap: while phase B(i) runs the pipe does
-// dV(i) and S(i+1); while phase A(i+1) runs it does dK(i), dQ(i), dP(i+1).
+// dV(i) and S(i+1); while phase A(i+1) runs it does dK(i), dP(i+1), dQ(i) (D = 128, where the dQ
+// accumulator has to share columns with S^T / dP^T: dK(i), dQ(i), drain, S(i+1), dP(i+1)).
 // A 16-column "ones" tile appended (through the descriptor's leading offset) to K makes
 // the dQ product also deliver rowsum(dS), the query-side log-gate gradient; at D=64 the
 // same tile appended to Q makes the dK product deliver colsum(dS), the key-side one.
