@@ -458,6 +458,20 @@ def run_ours(args, w, wname):
             "fwd_kernel": {"achieved": fwd_tf, "frac": fwd_tf / peaks["bf16_sustained"], "ms_per_launch": fwd_ms},
             "all_kernels_ms": {k_: round(v_[1], 4) for k_, v_ in kern.items()},
         }
+        if thr is None and not cp:
+            # what actually bounds the one-pass backward: every (KV tile, query tile) pair add-reduces a 128 x D
+            # fp32 dQ partial into L2, whose reduction rate is chip-wide (~1.54 KB/clk = 3.03 TB/s at 1965 MHz,
+            # measured with a stand-alone probe on this pool; not part of MEASURED_PEAKS.json)
+            nT = (w["T"] + 127) // 128
+            pairs_t = 0
+            for b_ in range(w["B"]):
+                s0 = 0 if seq is None else int(seq[b_])
+                j0 = max((s0 - 1) // 128, 0) if s0 > 0 else 0
+                pairs_t += sum(nT - j for j in range(j0, nT))
+            red_bytes = float(pairs_t) * w["H"] * 128 * w["D"] * 4
+            roof["l2_reduction"] = {"bytes_per_launch": red_bytes, "achieved_gbs": red_bytes / (bwd_ms * 1e-3) / 1e9,
+                                    "probe_peak_gbs": 3030.0,
+                                    "frac": red_bytes / (bwd_ms * 1e-3) / 1e9 / 3030.0}
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong" if cp else "weak",
