@@ -51,6 +51,8 @@ _SIGNATURES = {
     "fox_attn_decode_workspace_floats": (c_int64, [c_int64, c_int64, c_int64, c_int64]),
     "fox_attn_bwd": (c_int, [c_int, c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, c_int64, _T4P, _T4P, _T4P,
                              _T4P, _F, _F, _F, _F, _F, c_float, _F, _F, _F, _T4P, _T4P, _F]),
+    "fox_attn_bwd_dq": (c_int, [c_int, c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, c_int64, _T4P, _T4P, _T4P,
+                                _T4P, _F, _F, _F, _F, _F, c_float, _T4P, _F, _F]),
     "fox_attn_bwd_noalloc": (c_int, [c_int, c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, c_int64, _T4P, _T4P,
                                      _T4P, _T4P, _F, _F, _F, _F, _F, c_float, _T4P, _T4P, _T4P, _F, _F, _F]),
     "fox_noalloc_scratch_floats": (c_int64, []),

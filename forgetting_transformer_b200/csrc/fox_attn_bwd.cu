@@ -66,7 +66,7 @@ __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float 
                : "memory");
 }
 
-template <int D, bool kBf16, bool kTrace, int kCWG>
+template <int D, bool kBf16, bool kTrace, int kCWG, bool kNoDQ>
 __global__ void __launch_bounds__((4 * kCWG + 6) * 32, 1)
 fox_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                     const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
@@ -74,7 +74,9 @@ fox_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   constexpr int kTileBytes = 128 * D * 2;
   constexpr int kSub = D / 64;
   constexpr uint32_t kFmt = kBf16 ? 1u : 0u;
-  constexpr bool kAliasDQ = (D == 128);     // dQ accumulator shares columns with S^T / dP^T
+  // kNoDQ: dK, dV and the key-side gate gradient only (dQ comes from fox_attn_bwd_dq_kernel): no dQ product, no
+  // drain, no reductions, and at D = 128 no sharing of TMEM columns
+  constexpr bool kAliasDQ = (D == 128) && !kNoDQ;  // dQ accumulator shares columns with S^T / dP^T
   constexpr bool kColsumMMA = (D == 64);    // colsum(dS) from the dK product
   constexpr int STQ = 2;
   constexpr int STDO = (D == 64) ? 2 : 1;
@@ -88,7 +90,7 @@ fox_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   constexpr int kNdq = D + 16;
   constexpr uint32_t kColS = 0, kColDP = 128, kColDK = 256, kColDV = 256 + kNdk;
   constexpr uint32_t kColDQ = kAliasDQ ? 0 : kColDV + D;
-  static_assert(kAliasDQ || kColDQ + kNdq <= 512, "TMEM budget");
+  static_assert(kAliasDQ || kNoDQ || kColDQ + kNdq <= 512, "TMEM budget");
 
   // 1024-byte aligned by declaration: at D=128 the tiles use all but 3 KiB of the 227 KiB a CTA may
   // have, so there is no room for a manual alignment slack.
@@ -371,12 +373,12 @@ fox_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           stamp(0, 6, it);
         }
         // ---- dQ_tile = dS [K | 1] ----
-        if (it > 0) {
+        if (!kNoDQ && it > 0) {
           ok = mbar_wait_warp(&bar_dq_free, (it - 1) & 1, abortp, p.status, kBSiteDqFree, it);
           if (!ok) break;
           tc_fence_after();
         }
-        if (elect_one()) {
+        if (!kNoDQ && elect_one()) {
 #pragma unroll
           for (int kk = 0; kk < 8; ++kk)
             mma_ss_raw(tbase + kColDQ, umma_desc_advance(ads_mn, kk * 2048), umma_desc_advance(dK_mn, kk * 2048),
@@ -410,7 +412,7 @@ fox_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     const int r = quarter * 32 + lane;  // query row inside the tile == TMEM lane
     const uint32_t tDQ = tbase + (static_cast<uint32_t>(quarter * 32) << 16) + kColDQ;
     bool ok = true;
-    for (int it = 0; it < n_tiles; ++it) {
+    for (int it = 0; it < (kNoDQ ? 0 : n_tiles); ++it) {
       if (warp == kDrainWarp0) stamp(1, 0, it);
       ok = mbar_wait_warp(&bar_dq_full, it & 1, abortp, p.status, kBSiteDq, it);
       if (!ok) break;
@@ -557,14 +559,14 @@ fox_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         }
         tmem_st16(tDP + g * CW + ch * 16, dsk);
 #pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
+        for (int q4 = 0; q4 < (kNoDQ ? 0 : 4); ++q4) {  // (dS in shared memory only feeds the dQ product)
           const int cj = ((col0 & 63) >> 3) + q4;
           *reinterpret_cast<uint4*>(dbuf + (col0 >> 6) * 16384 + ((cj ^ (r & 7)) << 4)) =
               make_uint4(dsk[q4 * 4], dsk[q4 * 4 + 1], dsk[q4 * 4 + 2], dsk[q4 * 4 + 3]);
         }
       }
       tmem_st_wait();
-      fence_proxy_async_smem();
+      if (!kNoDQ) fence_proxy_async_smem();
       tc_fence_before();
       mbar_arrive(&bar_ds_done);
       if (warp < 8) stamp(6 + warp, 3, it);
@@ -661,18 +663,21 @@ static int launch_bwd(int device, cudaStream_t stream, int64_t B, int64_t H, int
   if ((rc = cached_tmap_4d(&tmDO, tdo, 2, false, kBf16, 64, 128, true))) return rc;
   CUtensorMap tmDQ;
   Tensor4 tdq{prm.dq_accum, B, H, M, D, H * M * D, M * D, D};
-  if ((rc = cached_tmap_4d(&tmDQ, tdq, 4, true, false, 32, 128, true))) return rc;
+  if (prm.dq_accum == nullptr) tmDQ = tmQ;  // unused by the kernel without a dQ product
+  else if ((rc = cached_tmap_4d(&tmDQ, tdq, 4, true, false, 32, 128, true))) return rc;
   constexpr int kStQ = 2, kStDO = (D == 64) ? 2 : 1, kDsBufs = (D == 64) ? 2 : 1;
   constexpr int kStageSub = (D == 64) ? 2 : 1;
   constexpr int smem = (2 + kStQ + kStDO) * 128 * D * 2 + kDsBufs * 32768 + 16384 + kStageSub * 16384;
   static_assert(smem + 3072 <= 232448, "shared memory budget (tiles + static barriers/vectors rounded to 1 KiB)");
   const bool tracing = prm.trace != nullptr;
   constexpr int kCWG = 4;  // compute warpgroups per CTA (2 was measured no faster at D=64 and slower at D=128)
-  auto kern = tracing ? fox_attn_bwd_kernel<D, kBf16, true, kCWG> : fox_attn_bwd_kernel<D, kBf16, false, kCWG>;
+  const bool nodq = prm.dq_accum == nullptr;
+  auto kern = tracing ? fox_attn_bwd_kernel<D, kBf16, true, kCWG, false>
+                      : (nodq ? fox_attn_bwd_kernel<D, kBf16, false, kCWG, true> : fox_attn_bwd_kernel<D, kBf16, false, kCWG, false>);
   const int threads = (4 * kCWG + 6) * 32;
-  static bool configured[2][64] = {};
+  static bool configured[3][64] = {};
   if (device < 0 || device >= 64) return FOX_ERR_DEVICE;
-  const int slot = tracing ? 1 : 0;
+  const int slot = tracing ? 1 : (nodq ? 2 : 0);
   if (!configured[slot][device]) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return FOX_ERR_LAUNCH;
     configured[slot][device] = true;
@@ -694,7 +699,7 @@ extern "C" int fox_attn_bwd(int device, void* stream, int dtype, int64_t B, int6
                             const fox_tensor4* dv, int32_t* status) {
   using namespace fox;
   if (!q || !k || !v || !d_o || !dk || !dv || !q->ptr || !k->ptr || !v->ptr || !d_o->ptr || !dk->ptr || !dv->ptr ||
-      !log_lambda || !L || !delta || !dq_accum_zeroed || !dlam_row_zeroed || !dlam_col || !status)
+      !log_lambda || !L || !delta || ((dq_accum_zeroed == nullptr) != (dlam_row_zeroed == nullptr)) || !dlam_col || !status)
     return FOX_ERR_BAD_ARG;
   if (B <= 0 || H <= 0 || M <= 0 || N <= 0 || M > N || H > 65535 || B > 65535) return FOX_ERR_BAD_ARG;
   if (D != 64 && D != 128) return FOX_ERR_HEAD_DIM;

@@ -21,6 +21,7 @@ __all__ = ["forgetting_attention", "ForgettingAttention", "FWD_BLOCK", "BWD_BLOC
 
 # (BLOCK_M, BLOCK_N) of the kernels; pruning indices are defined on this grid.
 _PADDED_HEAD_DIM = 64   # head dims 16 and 32 are zero-padded to this
+_TWO_KERNEL_BACKWARD_D128 = os.environ.get("FOX_B200_ONE_PASS_BWD", "0") != "1"
 FWD_BLOCK = (128, 128)
 BWD_BLOCK = (128, 128)
 
@@ -258,12 +259,35 @@ class ForgettingAttention(torch.autograd.Function):
                 dv = torch.empty(v.shape, dtype=v.dtype, device=dev)
             if not _lib.tma_ready(dq):
                 dq = torch.empty(q.shape, dtype=q.dtype, device=dev)
+            dlam_col = torch.empty((B, H, N), dtype=torch.float32, device=dev)
+            status = _lib.status_buffer(dev)
+            if D == 128 and _TWO_KERNEL_BACKWARD_D128:
+                # key side (dk, dv, column sums) without a dQ product, query side as its own kernel: no fp32
+                # dQ partials to add-reduce into L2, which is what bounds the one-pass kernel at this head dim
+                start_index = None
+                if adaptive_threshold is not None:
+                    start_index, _ = find_index(log_lambda, adaptive_threshold, M, *BWD_BLOCK)
+                dlam_row = torch.empty((B, H, M), dtype=torch.float32, device=dev)
+                _call("fox_attn_bwd", lib.fox_attn_bwd, dev.index, _stream(), code, B, H, M, N, D, _lib.t4(q),
+                      _lib.t4(k), _lib.t4(v), _lib.t4(do), log_lambda.data_ptr(), L.data_ptr(), delta.data_ptr(),
+                      _lib.ptr(seq_start), _lib.ptr(end_index), float(sm_scale), None, None,
+                      dlam_col.data_ptr(), _lib.t4(dk), _lib.t4(dv), status.data_ptr())
+                _call("fox_attn_bwd_dq", lib.fox_attn_bwd_dq, dev.index, _stream(), code, B, H, M, N, D, _lib.t4(q),
+                      _lib.t4(k), _lib.t4(v), _lib.t4(do), log_lambda.data_ptr(), L.data_ptr(), delta.data_ptr(),
+                      _lib.ptr(seq_start), _lib.ptr(start_index), float(sm_scale), _lib.t4(dq), dlam_row.data_ptr(),
+                      status.data_ptr())
+                dlog_fgate = torch.empty((B, H, N), dtype=torch.float32, device=dev)
+                _call("fox_revcumsum", lib.fox_revcumsum, dev.index, _stream(), B, H, M, N, dlam_col.data_ptr(),
+                      dlam_row.data_ptr(), None, dlog_fgate.data_ptr(), None)
+                if _DEBUG_SYNC:
+                    _lib.check_status(dev)
+                if ctx.head_dim != D:
+                    dq, dk, dv = [t[..., :ctx.head_dim].contiguous() for t in (dq, dk, dv)]
+                return dq, dk, dv, dlog_fgate, None, None, None, None, None, None, None, None, None
             # scratch: fp32 dQ accumulator and the query-side log-gate gradient (both reduced into)
             scratch = torch.zeros(B * H * M * (D + 1), dtype=torch.float32, device=dev)
             dq_accum = scratch[: B * H * M * D]
             dlam_row = scratch[B * H * M * D:]
-            dlam_col = torch.empty((B, H, N), dtype=torch.float32, device=dev)
-            status = _lib.status_buffer(dev)
             _call("fox_attn_bwd", lib.fox_attn_bwd, dev.index, _stream(), code, B, H, M, N, D, _lib.t4(q),
                   _lib.t4(k), _lib.t4(v), _lib.t4(do), log_lambda.data_ptr(), L.data_ptr(), delta.data_ptr(),
                   _lib.ptr(seq_start), _lib.ptr(end_index), float(sm_scale), dq_accum.data_ptr(),

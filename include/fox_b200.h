@@ -131,6 +131,7 @@ int fox_bwd_delta(int device, void* stream, int dtype, int64_t B, int64_t H, int
  * (forgetting_attention.py:313-334, 366-386; kernels 956-1143, 1156-1344).  end_index from
  * fox_find_index with FOX_BWD_BLOCK_M/N, or NULL.  Outputs: dk, dv (input dtype, caller's
  * strides, zero left of seq_start); dlam_col (B,H,N) fp32 = -sum_i dS_ij, fully written;
+ * dq_accum_zeroed and dlam_row_zeroed may both be NULL: key side only (see fox_attn_bwd_dq);
  * and two caller-provided scratch arrays that must be zero on entry and are reduced into:
  * dq_accum (B,H,M,D) fp32 = sum_j dS_ij k_j (unscaled) and dlam_row (B,H,M) fp32 = sum_j dS_ij. */
 int fox_attn_bwd(int device, void* stream, int dtype, int64_t B, int64_t H, int64_t M, int64_t N, int64_t D,
@@ -138,6 +139,18 @@ int fox_attn_bwd(int device, void* stream, int dtype, int64_t B, int64_t H, int6
                  const float* log_lambda, const float* L, const float* delta, const int64_t* seq_start,
                  const int64_t* end_index, float sm_scale, float* dq_accum_zeroed, float* dlam_row_zeroed,
                  float* dlam_col, const fox_tensor4* dk, const fox_tensor4* dv, int32_t* status);
+
+/* Query side of the backward as a kernel of its own: dq (input dtype, caller's strides, fully written) and
+ * dlam_row (B,H,M) fp32 = sum_j dS_ij, fully written.  Replaces the _bwd_q_kernel launch
+ * (forgetting_attention.py:366-386; kernel 1156-1344); start_index from fox_find_index with
+ * FOX_BWD_BLOCK_M/N, or NULL.  Used together with fox_attn_bwd called with dq_accum_zeroed = dlam_row_zeroed =
+ * NULL (key side only: dk, dv, dlam_col): at D = 128 recomputing S and dP costs less than add-reducing the
+ * one-pass kernel's fp32 dQ partials into L2. */
+int fox_attn_bwd_dq(int device, void* stream, int dtype, int64_t B, int64_t H, int64_t M, int64_t N, int64_t D,
+                    const fox_tensor4* q, const fox_tensor4* k, const fox_tensor4* v, const fox_tensor4* d_o,
+                    const float* log_lambda, const float* L, const float* delta, const int64_t* seq_start,
+                    const int64_t* start_index, float sm_scale, const fox_tensor4* dq, float* dlam_row,
+                    int32_t* status);
 
 /* dq = dq_accum * scale, fp32 -> input dtype with the caller's strides (the `dq *= sm_scale`
  * and store of forgetting_attention.py:1333-1343). */

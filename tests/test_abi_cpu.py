@@ -25,7 +25,7 @@ def test_header_declares_the_expected_entry_points():
     for s in ["fox_attn_fwd", "fox_attn_bwd", "fox_cumsum_fwd", "fox_revcumsum", "fox_find_index",
               "fox_max_row_norm", "fox_bwd_delta", "fox_dq_convert", "fox_normgate_fwd", "fox_normgate_bwd",
               "fox_token_shift_fwd", "fox_token_shift_bwd", "fox_rmsnorm_fwd", "fox_rmsnorm_bwd",
-              "fox_swiglu_fwd", "fox_swiglu_bwd", "fox_attn_decode"]:
+              "fox_swiglu_fwd", "fox_swiglu_bwd", "fox_attn_decode", "fox_attn_bwd_dq"]:
         assert s in syms
 
 
