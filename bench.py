@@ -449,16 +449,40 @@ def run_ours(args, w, wname):
         # (a context-parallel step launches each kernel once per local chunk: FLOPs per step over launches per step)
         bwd_tf = (10.0 / 14.0) * flops / (bwd_ms * max(bwd_n // args.steps, 1) * 1e-3) / 1e12
         fwd_tf = (4.0 / 14.0) * flops / (fwd_ms * max(fwd_n // args.steps, 1) * 1e-3) / 1e12
+        dq_n, dq_ms = kern.get("fox_attn_bwd_dq", (0, float("nan")))
+        two_kernel = dq_n > 0
+        bwd_kernel_name = "fox_attn_bwd_kernel"
+        if two_kernel:
+            # head dim 128: the backward is a key-side kernel (S, dP, dV, dK: 8 of the 14 FLOPs per pair) and a
+            # query-side kernel (S and dP recomputed, dQ: 6 per pair executed, 2 of them algorithmic). The roofline
+            # entry is the longer of the two with the FLOPs it executes; the pair's algorithmic rate is beside it.
+            per = max(bwd_n // args.steps, 1)
+            key_tf = (8.0 / 14.0) * flops / (bwd_ms * per * 1e-3) / 1e12
+            qry_tf = (6.0 / 14.0) * flops / (dq_ms * max(dq_n // args.steps, 1) * 1e-3) / 1e12
+            pair_tf = (10.0 / 14.0) * flops / ((bwd_ms + dq_ms) * per * 1e-3) / 1e12
+            two = {"key_side": {"kernel": "fox_attn_bwd_kernel<no dQ>", "ms_per_launch": bwd_ms, "executed_tflops": key_tf,
+                                "frac": key_tf / peaks["bf16_sustained"]},
+                   "query_side": {"kernel": "fox_attn_bwd_dq_kernel", "ms_per_launch": dq_ms, "executed_tflops": qry_tf,
+                                  "frac": qry_tf / peaks["bf16_sustained"]},
+                   "algorithmic_tflops_of_the_pair": pair_tf,
+                   "algorithmic_frac_of_the_pair": pair_tf / peaks["bf16_sustained"]}
+            if dq_ms > bwd_ms:
+                bwd_kernel_name, bwd_tf, bwd_ms, bwd_n = "fox_attn_bwd_dq_kernel", qry_tf, dq_ms, dq_n
+            else:
+                bwd_kernel_name, bwd_tf = "fox_attn_bwd_kernel<no dQ>", key_tf
         roof = {
-            "kernel": "fox_attn_bwd_kernel", "bound": "tensor", "achieved": bwd_tf,
+            "kernel": bwd_kernel_name, "bound": "tensor", "achieved": bwd_tf,
             "peak": peaks["bf16_sustained"], "unit": "TFLOP/s", "frac": bwd_tf / peaks["bf16_sustained"],
             "peak_kind": f"bf16_tflops_sustained of {peaks['source']} (kernel timed inside the stepping loop)",
-            "frac_of_burst_peak": bwd_tf / peaks["bf16"], "traffic": TRAFFIC_BYTES_PER_LAUNCH.get(wname),
+            "frac_of_burst_peak": bwd_tf / peaks["bf16"],
+            "traffic": TRAFFIC_BYTES_PER_LAUNCH.get((wname, bwd_kernel_name), TRAFFIC_BYTES_PER_LAUNCH.get(wname)),
             "ms_per_launch": bwd_ms, "launches": bwd_n,
             "fwd_kernel": {"achieved": fwd_tf, "frac": fwd_tf / peaks["bf16_sustained"], "ms_per_launch": fwd_ms},
             "all_kernels_ms": {k_: round(v_[1], 4) for k_, v_ in kern.items()},
         }
-        if thr is None and not cp:
+        if two_kernel:
+            roof["backward_two_kernels"] = two
+        if thr is None and not cp and not two_kernel:
             # what actually bounds the one-pass backward: every (KV tile, query tile) pair add-reduces a 128 x D
             # fp32 dQ partial into L2, whose reduction rate is chip-wide (~1.54 KB/clk = 3.03 TB/s at 1965 MHz,
             # measured with a stand-alone probe on this pool; not part of MEASURED_PEAKS.json)

@@ -308,7 +308,7 @@ fox_attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
           const uint32_t d01 = pack2<kBf16>(ds01.x, ds01.y), d23 = pack2<kBf16>(ds23.x, ds23.y);
           pk[2 * c4] = d01;
           pk[2 * c4 + 1] = d23;
-          rowsum2 = __fadd2_rn(rowsum2, __fadd2_rn(unpack2<kBf16>(d01), unpack2<kBf16>(d23)));
+          rowsum2 = __fadd2_rn(rowsum2, __fadd2_rn(ds01, ds23));   // fp32 values, as the key-side kernel's column sums
         }
         tmem_st16(tS + ch * 16, pk);
       }

@@ -21,7 +21,8 @@ __all__ = ["forgetting_attention", "ForgettingAttention", "FWD_BLOCK", "BWD_BLOC
 
 # (BLOCK_M, BLOCK_N) of the kernels; pruning indices are defined on this grid.
 _PADDED_HEAD_DIM = 64   # head dims 16 and 32 are zero-padded to this
-_TWO_KERNEL_BACKWARD_D128 = os.environ.get("FOX_B200_ONE_PASS_BWD", "0") != "1"
+# head dims whose backward runs as a key-side and a query-side kernel instead of the one-pass kernel
+_TWO_KERNEL_BACKWARD_DIMS = set() if os.environ.get("FOX_B200_ONE_PASS_BWD", "0") == "1" else {128}
 FWD_BLOCK = (128, 128)
 BWD_BLOCK = (128, 128)
 
@@ -261,7 +262,7 @@ class ForgettingAttention(torch.autograd.Function):
                 dq = torch.empty(q.shape, dtype=q.dtype, device=dev)
             dlam_col = torch.empty((B, H, N), dtype=torch.float32, device=dev)
             status = _lib.status_buffer(dev)
-            if D == 128 and _TWO_KERNEL_BACKWARD_D128:
+            if D in _TWO_KERNEL_BACKWARD_DIMS:
                 # key side (dk, dv, column sums) without a dQ product, query side as its own kernel: no fp32
                 # dQ partials to add-reduce into L2, which is what bounds the one-pass kernel at this head dim
                 start_index = None

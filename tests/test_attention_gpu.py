@@ -184,6 +184,26 @@ def test_small_head_dims(D, dtype):
     _close(dlf, r["dlog_fgate"], 2 * atol, rtol)
 
 
+@pytest.mark.parametrize("D", [64, 128])
+@pytest.mark.parametrize("two_kernel", [True, False])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_backward_formulations(D, two_kernel, dtype, monkeypatch):
+    """The backward exists as one pass over (KV tile, query tile) pairs and as a key-side kernel plus a
+    query-side kernel (upstream's split, forgetting_attention.py:956-1344); both forms at both head dims, with
+    seqlen_q < seqlen_k, seq_start and pruning, against the same oracle and with upstream's 1e-2 on the gate
+    gradient (the two halves of the gate gradient come from different kernels in the second form)."""
+    monkeypatch.setattr(ops, "_TWO_KERNEL_BACKWARD_DIMS", {64, 128} if two_kernel else set())
+    q, k, v, lf, do = _inputs(91 + D, 2, 2, 640, 1100, D, dtype, mu=2.0, std=0.5)
+    seq = torch.tensor([0, 333])
+    for thr in (None, -12.0):
+        out, dq, dk, dv, dlf = _run(q, k, v, lf, do, seq=seq, sm_scale=0.5, thr=thr)
+        ro, rdq, rdk, rdv, rdl = orc.dense_fwd_bwd(q.float(), k.float(), v.float(), lf, do.float(), seq, 0.5)
+        atol, rtol = (ATOL_BF16, RTOL_BF16) if dtype == torch.bfloat16 else (ATOL_FP16, 0.0)
+        for a, b in [(out, ro), (dq, rdq), (dk, rdk), (dv, rdv)]:
+            _close(a, b, atol, rtol)
+        _close(dlf, rdl, atol, rtol)
+
+
 def test_seq_start_extremes():
     """seq_start = 0, in the middle of a block, on a block boundary and at the last token."""
     B, H, T, D = 4, 2, 384, 64
