@@ -548,8 +548,14 @@ TRAFFIC_BYTES_PER_LAUNCH = {
     # per-row (inputs once, outputs once, dQ workspace once), cfg3 has 3x the rows
     "cfg3": 3 * 265.6e6,
     "prof_d64": 265.6e6,
+    # head dim 128, one-pass kernel (FOX_B200_ONE_PASS_BWD=1)
     "prof_d128": 632.8e6,
     "cfg4": 4 * 632.8e6,
+    # head dim 128, the kernel pair (profiles/attn_bwd_two_kernels_prof_d128.md); cfg4 has 4x the rows of prof_d128
+    ("prof_d128", "fox_attn_bwd_kernel<no dQ>"): 380.5e6,
+    ("prof_d128", "fox_attn_bwd_dq_kernel"): 323.3e6,
+    ("cfg4", "fox_attn_bwd_kernel<no dQ>"): 4 * 380.5e6,
+    ("cfg4", "fox_attn_bwd_dq_kernel"): 4 * 323.3e6,
 }
 
 

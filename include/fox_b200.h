@@ -131,7 +131,9 @@ int fox_bwd_delta(int device, void* stream, int dtype, int64_t B, int64_t H, int
  * (forgetting_attention.py:313-334, 366-386; kernels 956-1143, 1156-1344).  end_index from
  * fox_find_index with FOX_BWD_BLOCK_M/N, or NULL.  Outputs: dk, dv (input dtype, caller's
  * strides, zero left of seq_start); dlam_col (B,H,N) fp32 = -sum_i dS_ij, fully written;
- * dq_accum_zeroed and dlam_row_zeroed may both be NULL: key side only (see fox_attn_bwd_dq);
+ * dq_accum_zeroed and dlam_row_zeroed may both be NULL: key side only (see fox_attn_bwd_dq; dlam_col is then the
+ * sum of the fp32 dS values, as fox_attn_bwd_dq's dlam_row, instead of the 16-bit-rounded ones both sums of the
+ * one-pass form are built from);
  * and two caller-provided scratch arrays that must be zero on entry and are reduced into:
  * dq_accum (B,H,M,D) fp32 = sum_j dS_ij k_j (unscaled) and dlam_row (B,H,M) fp32 = sum_j dS_ij. */
 int fox_attn_bwd(int device, void* stream, int dtype, int64_t B, int64_t H, int64_t M, int64_t N, int64_t D,
