@@ -7,7 +7,7 @@
 //
 // One CTA = one (batch, head, 128-row query tile), two CTAs per SM, same roles as the forward kernel:
 //   warps 0-3 : thread t owns query row t (TMEM lane t): p = 2^(s c + e_i - b_j), dS = p (dP - delta_i),
-//               16-bit dS written over S, running rowsum(dS) (from the rounded values, like the key side's colsum)
+//               16-bit dS written over S, running rowsum(dS) (of the fp32 values, like the key side's colsum)
 //   warp 4    : TMA producer (Q, dO once; K, V tiles of 64 rows; also stages the tile's gate prefixes)
 //   warp 5    : tcgen05.mma issuer: S = Q K^T, dP = dO V^T (smem x smem), dQ += dS K (TMEM x smem)
 // TMEM (256 columns): S fp32 [0,64), dP fp32 [64,128), dQ fp32 [128, 128 + D).
@@ -36,7 +36,7 @@ struct DqParams {
 };
 
 #ifdef FOX_DQ_TRACE
-__device__ long long g_dq_trace[8 * 8 * 16];
+__device__ long long g_dq_trace[24 * 8 * 16];
 #define DQSTAMP(role, ev, it) do { if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0 && (it) >= 32 && (it) < 48) g_dq_trace[((role) * 8 + (ev)) * 16 + (it) - 32] = clock64(); } while (0)
 extern "C" int fox_debug_read_dq_trace(long long* host) { return cudaMemcpyFromSymbol(host, g_dq_trace, sizeof(g_dq_trace)); }
 #else
@@ -356,6 +356,373 @@ fox_attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
   if (warp == kTmaWarp) tmem_dealloc(tbase, kTmemCols);
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// Pipelined form for D = 128: one CTA per SM, 128-row KV tiles, four elementwise warpgroups (thread = query row x
+// 32 of the tile's 128 columns; four warps on every scheduler), S double-buffered in TMEM so that the products of
+// the next tile run under the elementwise passes of this one:
+//   issuer, tile t:  S(t+1) = Q K(t+1)^T | wait dS(t) | dP(t+1) = dO V(t+1)^T | dQ += dS(t) K(t)
+//   elementwise, t:  phase A: wait S(t):  p = 2^(s c + e_i - b_j) kept in registers
+//                    phase B: wait dP(t): dS = p (dP - delta_i) -> 16 bit over the warpgroup's own S columns
+// TMEM (512 columns): S [0,128) and [128,256), dP [256,384), dQ [384,512).  Shared memory: Q, dO resident (64 KB),
+// K in three stages (read by S(t) and, two tiles of products later, by dQ(t)), V in one.
+// A 128-column S / dP product re-reads Q / dO from shared memory once per 128 columns instead of once per 64.
+constexpr int kDq2BN = 128;
+enum Dq2WaitSite { kDq2SiteQ = 51, kDq2SiteK = 52, kDq2SiteV = 53, kDq2SiteKE = 54, kDq2SiteVE = 55, kDq2SiteS = 56,
+                   kDq2SiteDP = 57, kDq2SiteDS = 58, kDq2SiteDone = 59, kDq2SiteNegB = 60, kDq2SiteRow = 61 };
+
+template <int D, bool kBf16>
+__global__ void __launch_bounds__(576, 1)
+fox_attn_bwd_dq2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                        const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
+                        const DqParams p) {
+  static_assert(D == 128, "pipelined query-side kernel: D = 128");
+  constexpr int BN = kDq2BN;
+  constexpr int kWG = 4, CW = BN / kWG;          // 32 columns of every tile per warpgroup
+  constexpr int kKS = 3;                         // K stages
+  constexpr int kQBytes = 128 * D * 2;
+  constexpr int kTileBytes = BN * D * 2;
+  constexpr int kSubBytes = BN * 128;            // one [128 rows][64 x 16 bit] sub-tile
+  constexpr int kSub = D / 64;
+  constexpr uint32_t kFmt = kBf16 ? 1u : 0u;
+  constexpr uint32_t kColS = 0, kColDP = 2 * BN, kColDQ = 3 * BN;
+  constexpr uint32_t kTmemCols = 512;
+  constexpr int kTmaWarp = 4 * kWG, kMmaWarp = 4 * kWG + 1;
+
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  __shared__ uint64_t bar_q_full, bar_k_full[kKS], bar_k_empty[kKS], bar_v_full, bar_v_empty, bar_s_full[2], bar_dp_full,
+      bar_ds_full, bar_done, bar_rowsum;
+  __shared__ uint64_t bar_negb[3];
+  __shared__ __align__(16) float s_negb[3][BN];
+  __shared__ float s_rowsum[kWG - 1][128];
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag;
+
+  uint8_t* sQ = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint8_t* sDO = sQ + kQBytes;
+  uint8_t* sK = sDO + kQBytes;
+  uint8_t* sV = sK + kKS * kTileBytes;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int mb = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);  // heavy tiles first
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int M = p.M, N = p.N, P = N - M;
+  const int64_t bh = static_cast<int64_t>(b) * p.H + h;
+
+  const int hi = min(N, P + (mb + 1) * kDqBM);
+  const int seq0 = p.seq_start ? static_cast<int>(p.seq_start[b]) : 0;
+  int lo = min(seq0, hi);
+  if (p.start_index) {
+    const int64_t si = p.start_index[bh * gridDim.x + mb];
+    lo = max(lo, static_cast<int>(si < static_cast<int64_t>(hi) ? si : static_cast<int64_t>(hi)));
+  }
+  const int nb_lo = lo / BN;
+  const int nb_hi = (hi + BN - 1) / BN;
+  const int n_tiles = max(nb_hi - nb_lo, 0);
+
+  if (tid == 0) {
+    abort_flag = 0;
+    mbar_init(&bar_q_full, 1);
+    for (int i = 0; i < kKS; ++i) {
+      mbar_init(&bar_k_full[i], 1);
+      mbar_init(&bar_k_empty[i], 1);
+    }
+    mbar_init(&bar_v_full, 1);
+    mbar_init(&bar_v_empty, 1);
+    mbar_init(&bar_s_full[0], 1);
+    mbar_init(&bar_s_full[1], 1);
+    mbar_init(&bar_dp_full, 1);
+    mbar_init(&bar_ds_full, 128 * kWG);
+    mbar_init(&bar_done, 1);
+    mbar_init(&bar_rowsum, 128 * (kWG - 1));
+    for (int i = 0; i < 3; ++i) mbar_init(&bar_negb[i], 1);
+    mbar_fence_init();
+  }
+  if (warp == kTmaWarp) {
+    tmem_alloc(&tmem_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tbase = tmem_slot;
+  volatile int* abortp = &abort_flag;
+
+  if (warp == kTmaWarp) {
+    // ===================== TMA producer =====================
+    if (n_tiles > 0) {
+      if (elect_one()) {
+        tma_prefetch_desc(&tmQ);
+        tma_prefetch_desc(&tmK);
+        tma_prefetch_desc(&tmV);
+        tma_prefetch_desc(&tmDO);
+        mbar_expect_tx(&bar_q_full, 2 * kQBytes);
+#pragma unroll
+        for (int s = 0; s < kSub; ++s) {
+          tma_load_4d(sQ + s * 16384, &tmQ, &bar_q_full, s * 64, mb * kDqBM, h, b);
+          tma_load_4d(sDO + s * 16384, &tmDO, &bar_q_full, s * 64, mb * kDqBM, h, b);
+        }
+      }
+      __syncwarp();
+      const float* lam = p.lam + bh * N;
+      float lamv[4] = {0.f, 0.f, 0.f, 0.f};   // lane l holds columns 4l .. 4l+3 of a tile
+      auto fetch_lam = [&](int it) {
+        const int c0 = (nb_hi - 1 - it) * BN + 4 * lane;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) lamv[e] = (c0 + e < N) ? ldg_f32_here(lam + c0 + e) : 0.f;
+      };
+      auto stage_negb = [&](int it) {
+        const int slot = it % 3;
+        *reinterpret_cast<float4*>(&s_negb[slot][4 * lane]) =
+            make_float4(-lamv[0] * kDqLog2e, -lamv[1] * kDqLog2e, -lamv[2] * kDqLog2e, -lamv[3] * kDqLog2e);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bar_negb[slot]);
+        __syncwarp();
+      };
+      fetch_lam(0);
+      stage_negb(0);
+      if (n_tiles > 1) fetch_lam(1);
+      int issued_k = 0, issued_v = 0;
+      for (int it = 0; it < n_tiles; ++it) {
+        const int nb = nb_hi - 1 - it;
+        const int ks = it % kKS;
+        if (!mbar_wait_warp(&bar_k_empty[ks], ((it / kKS) & 1) ^ 1, abortp, p.status, kDq2SiteKE, it)) break;
+        if (elect_one()) {
+          mbar_expect_tx(&bar_k_full[ks], kTileBytes);
+#pragma unroll
+          for (int s = 0; s < kSub; ++s)
+            tma_load_4d(sK + ks * kTileBytes + s * kSubBytes, &tmK, &bar_k_full[ks], s * 64, nb * BN, h, b);
+        }
+        __syncwarp();
+        issued_k = it + 1;
+        if (!mbar_wait_warp(&bar_v_empty, (it & 1) ^ 1, abortp, p.status, kDq2SiteVE, it)) break;  // dP(it-1) done
+        if (elect_one()) {
+          mbar_expect_tx(&bar_v_full, kTileBytes);
+#pragma unroll
+          for (int s = 0; s < kSub; ++s) tma_load_4d(sV + s * kSubBytes, &tmV, &bar_v_full, s * 64, nb * BN, h, b);
+        }
+        __syncwarp();
+        issued_v = it + 1;
+        if (it + 1 < n_tiles) {   // (the slot of tile it+1 was last read for tile it-2: dP(it-1) done => phase A(it-2) done)
+          stage_negb(it + 1);
+          if (it + 2 < n_tiles) fetch_lam(it + 2);
+        }
+      }
+      if (*abortp && lane == 0) {
+        // error path only: let the copies already in flight land before the CTA retires
+        const long long t0 = clock64();
+        while (!mbar_try_wait(&bar_q_full, 0) && clock64() - t0 < 200000000LL) {
+        }
+        for (int c = max(issued_k - kKS, 0); c < issued_k; ++c)
+          while (!mbar_try_wait(&bar_k_full[c % kKS], (c / kKS) & 1) && clock64() - t0 < 200000000LL) {
+          }
+        if (issued_v > 0)
+          while (!mbar_try_wait(&bar_v_full, (issued_v - 1) & 1) && clock64() - t0 < 200000000LL) {
+          }
+      }
+    }
+  } else if (warp == kMmaWarp) {
+    // ===================== MMA issuer =====================
+    if (n_tiles > 0) {
+      constexpr uint32_t idS = umma_idesc(kFmt, 128, BN, 0, 0);
+      constexpr uint32_t idDQ = umma_idesc(kFmt, 128, D, 0, 1);
+      const uint64_t dQd = umma_desc_kmajor(smem_u32(sQ));
+      const uint64_t dDOd = umma_desc_kmajor(smem_u32(sDO));
+      const uint64_t dKk = umma_desc_kmajor(smem_u32(sK));
+      const uint64_t dVk = umma_desc_kmajor(smem_u32(sV));
+      const uint64_t dKmn = umma_desc_mnmajor(smem_u32(sK), kSubBytes);
+      auto issue_s = [&](int t) {      // S(t) -> buffer t & 1
+        if (elect_one()) {
+          const uint64_t dK_s = umma_desc_advance(dKk, (t % kKS) * kTileBytes);
+#pragma unroll
+          for (int kk = 0; kk < D / 16; ++kk) {
+            const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
+            mma_ss_raw(tbase + kColS + (t & 1) * BN, umma_desc_advance(dQd, off), umma_desc_advance(dK_s, off), idS, kk > 0);
+          }
+          tc_commit_raw(&bar_s_full[t & 1]);
+        }
+        __syncwarp();
+      };
+      auto issue_dp = [&]() {
+        if (elect_one()) {
+#pragma unroll
+          for (int kk = 0; kk < D / 16; ++kk) {
+            const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
+            mma_ss_raw(tbase + kColDP, umma_desc_advance(dDOd, off), umma_desc_advance(dVk, off), idS, kk > 0);
+          }
+          tc_commit_raw(&bar_dp_full);
+          tc_commit_raw(&bar_v_empty);
+        }
+        __syncwarp();
+      };
+      bool ok = mbar_wait_warp(&bar_q_full, 0, abortp, p.status, kDq2SiteQ);
+      if (ok) ok = mbar_wait_warp(&bar_k_full[0], 0, abortp, p.status, kDq2SiteK, 0);
+      if (ok) {
+        tc_fence_after();
+        issue_s(0);
+        ok = mbar_wait_warp(&bar_v_full, 0, abortp, p.status, kDq2SiteV, 0);
+      }
+      if (ok) {
+        tc_fence_after();
+        issue_dp();
+      }
+      for (int it = 0; it < n_tiles && ok; ++it) {
+        DQSTAMP(17, 0, it);
+        if (it + 1 < n_tiles) {
+          ok = mbar_wait_warp(&bar_k_full[(it + 1) % kKS], ((it + 1) / kKS) & 1, abortp, p.status, kDq2SiteK, it + 1);
+          if (!ok) break;
+          tc_fence_after();
+          issue_s(it + 1);
+        }
+        DQSTAMP(17, 1, it);
+        ok = mbar_wait_warp(&bar_ds_full, it & 1, abortp, p.status, kDq2SiteDS, it);
+        if (!ok) break;
+        DQSTAMP(17, 2, it);
+        if (it + 1 < n_tiles) {
+          ok = mbar_wait_warp(&bar_v_full, (it + 1) & 1, abortp, p.status, kDq2SiteV, it + 1);
+          if (!ok) break;
+          tc_fence_after();
+          issue_dp();
+        }
+        tc_fence_after();
+        if (elect_one()) {
+          // dQ += dS(it) K(it); warpgroup g's 16-bit dS sits in the first 16 of its own 32 S columns
+          const uint64_t dKmn_s = umma_desc_advance(dKmn, (it % kKS) * kTileBytes);
+          const uint32_t tA = tbase + kColS + (it & 1) * BN;
+#pragma unroll
+          for (int kk = 0; kk < BN / 16; ++kk)
+            mma_ts_raw(tbase + kColDQ, tA + (kk >> 1) * CW + (kk & 1) * 8, umma_desc_advance(dKmn_s, kk * 2048), idDQ,
+                       (it > 0 || kk > 0) ? 1u : 0u);
+          tc_commit_raw(&bar_k_empty[it % kKS]);
+        }
+        __syncwarp();
+        DQSTAMP(17, 3, it);
+      }
+      if (ok) tc_commit(&bar_done);
+    }
+  } else {
+    // ===================== elementwise / epilogue =====================
+    const int g = warp >> 2;
+    const int r = tid & 127;
+    const int row = mb * kDqBM + r;
+    const bool row_ok = row < M;
+    float e_i = -INFINITY, delta_i = 0.f;
+    if (row_ok) {
+      const float Li = p.L[bh * M + row];
+      e_i = (Li == -INFINITY) ? -INFINITY : (p.lam[bh * N + P + row] - Li) * kDqLog2e;
+      delta_i = p.delta[bh * M + row];
+    }
+    const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const uint32_t tDP = tbase + lane_base + kColDP + g * CW, tDQ = tbase + lane_base + kColDQ;
+    const float2 scale2 = make_float2(p.qk_scale, p.qk_scale);
+    const float2 e2 = make_float2(e_i, e_i);
+    const float2 nd2 = make_float2(-delta_i, -delta_i);
+    float2 rowsum2 = make_float2(0.f, 0.f);
+    bool ok = true;
+    for (int it = 0; it < n_tiles; ++it) {
+      const int nb = nb_hi - 1 - it;
+      const int col0 = nb * BN;
+      const uint32_t tS = tbase + lane_base + kColS + (it & 1) * BN + g * CW;
+      // ---------------- phase A: p ----------------
+      DQSTAMP(warp, 0, it);
+      ok = mbar_wait(&bar_negb[it % 3], (it / 3) & 1, abortp, p.status, kDq2SiteNegB, it);
+      ok = mbar_wait(&bar_s_full[it & 1], (it >> 1) & 1, abortp, p.status, kDq2SiteS, it) && ok;
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      DQSTAMP(warp, 1, it);
+      tc_fence_after();
+      uint32_t sreg[32];
+      float2 pf[16];
+      tmem_ld32(tS, sreg);
+      tmem_ld_wait();
+      const float4* nb4 = reinterpret_cast<const float4*>(&s_negb[it % 3][g * CW]);
+      const bool need_mask = (col0 + BN - 1 > P + mb * kDqBM) || (col0 < seq0) || (col0 + BN > N);
+      const int c_lo = need_mask ? max(seq0 - col0, 0) : 0;
+      const int c_hi = need_mask ? (row_ok ? min(min(P + row, N - 1) - col0, BN - 1) : -1) : BN - 1;
+#pragma unroll
+      for (int c4 = 0; c4 < 8; ++c4) {
+        const float4 nbv = nb4[c4];
+        float2 x01 = __ffma2_rn(make_float2(__uint_as_float(sreg[4 * c4]), __uint_as_float(sreg[4 * c4 + 1])), scale2,
+                                __fadd2_rn(make_float2(nbv.x, nbv.y), e2));
+        float2 x23 = __ffma2_rn(make_float2(__uint_as_float(sreg[4 * c4 + 2]), __uint_as_float(sreg[4 * c4 + 3])), scale2,
+                                __fadd2_rn(make_float2(nbv.z, nbv.w), e2));
+        if (need_mask) {
+          const int cc = g * CW + 4 * c4;
+          x01.x = (cc >= c_lo && cc <= c_hi) ? x01.x : -INFINITY;
+          x01.y = (cc + 1 >= c_lo && cc + 1 <= c_hi) ? x01.y : -INFINITY;
+          x23.x = (cc + 2 >= c_lo && cc + 2 <= c_hi) ? x23.x : -INFINITY;
+          x23.y = (cc + 3 >= c_lo && cc + 3 <= c_hi) ? x23.y : -INFINITY;
+        }
+        pf[2 * c4] = make_float2(fast_exp2(x01.x), fast_exp2(x01.y));
+        pf[2 * c4 + 1] = make_float2(fast_exp2(x23.x), fast_exp2(x23.y));
+      }
+      DQSTAMP(warp, 2, it);
+      // ---------------- phase B: dS ----------------
+      ok = mbar_wait(&bar_dp_full, it & 1, abortp, p.status, kDq2SiteDP, it);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      DQSTAMP(warp, 3, it);
+      tc_fence_after();
+      uint32_t pk[16];
+      tmem_ld32(tDP, sreg);
+      tmem_ld_wait();
+#pragma unroll
+      for (int c2 = 0; c2 < 16; ++c2) {
+        const float2 ds = __fmul2_rn(pf[c2], __fadd2_rn(make_float2(__uint_as_float(sreg[2 * c2]), __uint_as_float(sreg[2 * c2 + 1])), nd2));
+        pk[c2] = pack2<kBf16>(ds.x, ds.y);
+        rowsum2 = __fadd2_rn(rowsum2, ds);   // fp32 values, as the key-side kernel's column sums
+      }
+      tmem_st16(tS, pk);
+      tmem_st_wait();
+      tc_fence_before();
+      mbar_arrive(&bar_ds_full);
+      DQSTAMP(warp, 4, it);
+    }
+    // ---- epilogue: dQ * sm_scale -> 16-bit -> global (each warpgroup a quarter of the columns); rowsum(dS) ----
+    if (g > 0) {
+      s_rowsum[g - 1][r] = rowsum2.x + rowsum2.y;
+      mbar_arrive(&bar_rowsum);
+    } else {
+      ok = mbar_wait(&bar_rowsum, 0, abortp, p.status, kDq2SiteRow) && ok;
+      ok = __all_sync(0xffffffffu, ok);
+    }
+    if (n_tiles > 0 && ok) {
+      ok = mbar_wait(&bar_done, 0, abortp, p.status, kDq2SiteDone);
+      ok = __all_sync(0xffffffffu, ok);
+    }
+    if (ok) {
+      tc_fence_after();
+      constexpr int kCols = D / kWG;   // 32
+      uint16_t* orow = reinterpret_cast<uint16_t*>(p.dq) + b * p.dq_sb + h * p.dq_sh + static_cast<int64_t>(row) * p.dq_st + g * kCols;
+      uint32_t t0[32];
+      if (n_tiles > 0) {
+        tmem_ld32(tDQ + g * kCols, t0);
+        tmem_ld_wait();
+      }
+      if (row_ok) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 8) {
+          uint4 w = make_uint4(0, 0, 0, 0);
+          if (n_tiles > 0) {
+            w.x = pack2<kBf16>(__uint_as_float(t0[j + 0]) * p.sm_scale, __uint_as_float(t0[j + 1]) * p.sm_scale);
+            w.y = pack2<kBf16>(__uint_as_float(t0[j + 2]) * p.sm_scale, __uint_as_float(t0[j + 3]) * p.sm_scale);
+            w.z = pack2<kBf16>(__uint_as_float(t0[j + 4]) * p.sm_scale, __uint_as_float(t0[j + 5]) * p.sm_scale);
+            w.w = pack2<kBf16>(__uint_as_float(t0[j + 6]) * p.sm_scale, __uint_as_float(t0[j + 7]) * p.sm_scale);
+          }
+          *reinterpret_cast<uint4*>(orow + j) = w;
+        }
+      }
+      if (g == 0 && row_ok)
+        p.dlam_row[bh * M + row] = (rowsum2.x + rowsum2.y) + (s_rowsum[0][r] + s_rowsum[1][r]) + s_rowsum[2][r];
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == kTmaWarp) tmem_dealloc(tbase, kTmemCols);
+}
+
+static int g_dq_variant = 1;   // 0: two CTAs per SM, 64-column tiles; 1: pipelined form at D = 128
+
 template <int D, bool kBf16>
 static int launch_dq(int device, cudaStream_t stream, int64_t B, int64_t H, int64_t M, int64_t N, const fox_tensor4* q,
                      const fox_tensor4* k, const fox_tensor4* v, const fox_tensor4* d_o, const DqParams& prm) {
@@ -384,7 +751,38 @@ static int launch_dq(int device, cudaStream_t stream, int64_t B, int64_t H, int6
   return cudaGetLastError() == cudaSuccess ? FOX_OK : FOX_ERR_LAUNCH;
 }
 
+template <int D, bool kBf16>
+static int launch_dq2(int device, cudaStream_t stream, int64_t B, int64_t H, int64_t M, int64_t N, const fox_tensor4* q,
+                      const fox_tensor4* k, const fox_tensor4* v, const fox_tensor4* d_o, const DqParams& prm) {
+  CUtensorMap tmQ, tmK, tmV, tmDO;
+  Tensor4 tq{q->ptr, B, H, M, D, q->sb, q->sh, q->st};
+  Tensor4 tk{k->ptr, B, H, N, D, k->sb, k->sh, k->st};
+  Tensor4 tv{v->ptr, B, H, N, D, v->sb, v->sh, v->st};
+  Tensor4 tdo{d_o->ptr, B, H, M, D, d_o->sb, d_o->sh, d_o->st};
+  if (!tma_compatible(tq, 2) || !tma_compatible(tk, 2) || !tma_compatible(tv, 2) || !tma_compatible(tdo, 2))
+    return FOX_ERR_ALIGNMENT;
+  int rc;
+  if ((rc = cached_tmap_4d(&tmQ, tq, 2, false, kBf16, 64, 128, true))) return rc;
+  if ((rc = cached_tmap_4d(&tmDO, tdo, 2, false, kBf16, 64, 128, true))) return rc;
+  if ((rc = cached_tmap_4d(&tmK, tk, 2, false, kBf16, 64, kDq2BN, true))) return rc;
+  if ((rc = cached_tmap_4d(&tmV, tv, 2, false, kBf16, 64, kDq2BN, true))) return rc;
+  constexpr int smem = 2 * 128 * D * 2 + 4 * kDq2BN * D * 2 + 1024;
+  auto kern = fox_attn_bwd_dq2_kernel<D, kBf16>;
+  static bool configured[64] = {};
+  if (device < 0 || device >= 64) return FOX_ERR_DEVICE;
+  if (!configured[device]) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return FOX_ERR_LAUNCH;
+    configured[device] = true;
+  }
+  dim3 grid((unsigned)((M + kDqBM - 1) / kDqBM), (unsigned)H, (unsigned)B);
+  kern<<<grid, 576, smem, stream>>>(tmQ, tmK, tmV, tmDO, prm);
+  return cudaGetLastError() == cudaSuccess ? FOX_OK : FOX_ERR_LAUNCH;
+}
+
 }  // namespace fox
+
+// Debug hook: 0 selects the two-CTA form at every head dim, 1 (default) the pipelined form at D = 128.
+extern "C" void fox_debug_set_dq_variant(int v) { fox::g_dq_variant = v; }
 
 extern "C" int fox_attn_bwd_dq(int device, void* stream, int dtype, int64_t B, int64_t H, int64_t M, int64_t N, int64_t D,
                                const fox_tensor4* q, const fox_tensor4* k, const fox_tensor4* v, const fox_tensor4* d_o,
@@ -412,5 +810,7 @@ extern "C" int fox_attn_bwd_dq(int device, void* stream, int dtype, int64_t B, i
   const bool bf = dtype == FOX_DTYPE_BF16;
   if (D == 64)
     return bf ? launch_dq<64, true>(device, st, B, H, M, N, q, k, v, d_o, prm) : launch_dq<64, false>(device, st, B, H, M, N, q, k, v, d_o, prm);
+  if (g_dq_variant == 1)
+    return bf ? launch_dq2<128, true>(device, st, B, H, M, N, q, k, v, d_o, prm) : launch_dq2<128, false>(device, st, B, H, M, N, q, k, v, d_o, prm);
   return bf ? launch_dq<128, true>(device, st, B, H, M, N, q, k, v, d_o, prm) : launch_dq<128, false>(device, st, B, H, M, N, q, k, v, d_o, prm);
 }
