@@ -462,12 +462,12 @@ def run_ours(args, w, wname):
             pair_tf = (10.0 / 14.0) * flops / ((bwd_ms + dq_ms) * per * 1e-3) / 1e12
             two = {"key_side": {"kernel": "fox_attn_bwd_kernel<no dQ>", "ms_per_launch": bwd_ms, "executed_tflops": key_tf,
                                 "frac": key_tf / peaks["bf16_sustained"]},
-                   "query_side": {"kernel": "fox_attn_bwd_dq_kernel", "ms_per_launch": dq_ms, "executed_tflops": qry_tf,
+                   "query_side": {"kernel": "fox_attn_bwd_dq2_kernel", "ms_per_launch": dq_ms, "executed_tflops": qry_tf,
                                   "frac": qry_tf / peaks["bf16_sustained"]},
                    "algorithmic_tflops_of_the_pair": pair_tf,
                    "algorithmic_frac_of_the_pair": pair_tf / peaks["bf16_sustained"]}
             if dq_ms > bwd_ms:
-                bwd_kernel_name, bwd_tf, bwd_ms, bwd_n = "fox_attn_bwd_dq_kernel", qry_tf, dq_ms, dq_n
+                bwd_kernel_name, bwd_tf, bwd_ms, bwd_n = "fox_attn_bwd_dq2_kernel", qry_tf, dq_ms, dq_n
             else:
                 bwd_kernel_name, bwd_tf = "fox_attn_bwd_kernel<no dQ>", key_tf
         roof = {
@@ -552,10 +552,10 @@ TRAFFIC_BYTES_PER_LAUNCH = {
     "prof_d128": 632.8e6,
     "cfg4": 4 * 632.8e6,
     # head dim 128, the kernel pair (profiles/attn_bwd_two_kernels_prof_d128.md); cfg4 has 4x the rows of prof_d128
-    ("prof_d128", "fox_attn_bwd_kernel<no dQ>"): 380.5e6,
-    ("prof_d128", "fox_attn_bwd_dq_kernel"): 323.3e6,
-    ("cfg4", "fox_attn_bwd_kernel<no dQ>"): 4 * 380.5e6,
-    ("cfg4", "fox_attn_bwd_dq_kernel"): 4 * 323.3e6,
+    ("prof_d128", "fox_attn_bwd_kernel<no dQ>"): 380.1e6,
+    ("prof_d128", "fox_attn_bwd_dq2_kernel"): 325.3e6,
+    ("cfg4", "fox_attn_bwd_kernel<no dQ>"): 4 * 380.1e6,
+    ("cfg4", "fox_attn_bwd_dq2_kernel"): 4 * 325.3e6,
 }
 
 

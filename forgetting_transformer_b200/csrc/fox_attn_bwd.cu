@@ -676,12 +676,12 @@ static int launch_bwd(int device, cudaStream_t stream, int64_t B, int64_t H, int
   const bool tracing = prm.trace != nullptr;
   constexpr int kCWG = 4;  // compute warpgroups per CTA (2 was measured no faster at D=64 and slower at D=128)
   const bool nodq = prm.dq_accum == nullptr;
-  auto kern = tracing ? fox_attn_bwd_kernel<D, kBf16, true, kCWG, false>
+  auto kern = tracing ? (nodq ? fox_attn_bwd_kernel<D, kBf16, true, kCWG, true> : fox_attn_bwd_kernel<D, kBf16, true, kCWG, false>)
                       : (nodq ? fox_attn_bwd_kernel<D, kBf16, false, kCWG, true> : fox_attn_bwd_kernel<D, kBf16, false, kCWG, false>);
   const int threads = (4 * kCWG + 6) * 32;
-  static bool configured[3][64] = {};
+  static bool configured[4][64] = {};
   if (device < 0 || device >= 64) return FOX_ERR_DEVICE;
-  const int slot = tracing ? 1 : (nodq ? 2 : 0);
+  const int slot = tracing ? (nodq ? 3 : 1) : (nodq ? 2 : 0);
   if (!configured[slot][device]) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return FOX_ERR_LAUNCH;
     configured[slot][device] = true;
