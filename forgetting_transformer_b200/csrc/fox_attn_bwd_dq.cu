@@ -5,7 +5,9 @@
 // backward kernel's dQ partials (64 KB of fp32 per tile pair, add-reduced into L2 at the L2's chip-wide rate)
 // cost more than recomputing S and dP: there the key side runs without a dQ product and this kernel owns dQ.
 //
-// One CTA = one (batch, head, 128-row query tile), two CTAs per SM, same roles as the forward kernel:
+// Two kernels: fox_attn_bwd_dq2_kernel (further down; D = 128, one CTA per SM, 128-column tiles, products of the
+// next tile under the elementwise passes of this one) and the first form, which serves D = 64:
+// one CTA = one (batch, head, 128-row query tile), two CTAs per SM, same roles as the forward kernel:
 //   warps 0-3 : thread t owns query row t (TMEM lane t): p = 2^(s c + e_i - b_j), dS = p (dP - delta_i),
 //               16-bit dS written over S, running rowsum(dS) (of the fp32 values, like the key side's colsum)
 //   warp 4    : TMA producer (Q, dO once; K, V tiles of 64 rows; also stages the tile's gate prefixes)
