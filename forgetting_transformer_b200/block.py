@@ -3,7 +3,7 @@
 Mirrors the data flow of upstream's ``ForgettingAttentionLayer`` / ``ForgettingTransformerMLP`` /
 ``ForgettingTransformerBlock`` (modeling_forgetting_transformer.py:98-430, 467-516, 519-622) in the "Pro"
 configuration: output gate + output norm, per-head QK-norm, data-dependent K and V token shift, full forget
-gate, no rotary embedding, training path only (no cache).  The matrix products are ``nn.Linear`` / ``F.linear`` (cuBLAS);
+gate, no rotary embedding; training path and, with an ``FgateCache``, the prefill / generation path.  The matrix products are ``nn.Linear`` / ``F.linear`` (cuBLAS);
 everything between them is a kernel of this library:
 
     x -> RMSNorm -> q_proj, ShiftLinear(k), ShiftLinear(v), fgate_proj, ogate_proj
@@ -28,7 +28,9 @@ __all__ = ["ShiftLinear", "FoxProAttentionLayer", "FoxMLP", "FoxProBlock"]
 
 
 class ShiftLinear(nn.Module):
-    """Linear projection followed by the data-dependent token shift (upstream lines 44-95, T > 1 branch)."""
+    """Linear projection followed by the data-dependent token shift (upstream lines 44-95): a sequence goes
+    through the token-shift kernel, a single generated token is mixed with the cached projection of the token
+    before it.  ``shift_state`` (B, output_dim), when given, is overwritten with the last token's projection."""
 
     def __init__(self, input_dim: int, output_dim: int, num_heads: int, bias: bool = False, shift_bias: bool = False):
         super().__init__()
@@ -37,14 +39,24 @@ class ShiftLinear(nn.Module):
         self.linear = nn.Linear(input_dim, output_dim, bias=bias)
         self.shift_proj = nn.Linear(input_dim, num_heads, bias=shift_bias)
 
-    def forward(self, x: torch.Tensor, attention_mask: Optional[torch.Tensor] = None) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, attention_mask: Optional[torch.Tensor] = None,
+                shift_state: Optional[torch.Tensor] = None) -> torch.Tensor:
         B, T, _ = x.shape
         out = self.linear(x)
         alpha = torch.sigmoid(self.shift_proj(x).float())
         out_per_head = out.view(B, T, self.num_heads, -1)
-        if attention_mask is not None:
-            out_per_head = torch.where(attention_mask[:, :, None, None].bool(), out_per_head, 0.0)
-        return token_shift(out_per_head, alpha, 1.0 - alpha).to(out.dtype).reshape(B, T, -1)
+        if T > 1:
+            if attention_mask is not None:
+                out_per_head = torch.where(attention_mask[:, :, None, None].bool(), out_per_head, 0.0)
+            result = token_shift(out_per_head, alpha, 1.0 - alpha)
+        else:
+            assert shift_state is not None, "a single token needs the projection of the token before it"
+            prev = shift_state.view(B, 1, self.num_heads, -1)
+            a = alpha[..., None]
+            result = a * prev.float() + (1.0 - a) * out_per_head.float()      # fp32, as upstream's weight_sum
+        if shift_state is not None:
+            shift_state.copy_(out[:, -1, :])
+        return result.to(out.dtype).reshape(B, T, -1)
 
 
 class FoxProAttentionLayer(nn.Module):
@@ -79,26 +91,50 @@ class FoxProAttentionLayer(nn.Module):
         with torch.no_grad():
             self.fgate_proj.bias.fill_(fgate_bias)
 
-    def forward(self, hidden_states: torch.Tensor, attention_mask: Optional[torch.Tensor] = None) -> torch.Tensor:
+    def init_shift_state(self, batch_size: int) -> dict:
+        """Zero K / V shift states of one sequence batch (upstream's ``init_shift_state``): the projection of
+        the token before the first one."""
+        w = self.q_proj.weight
+        z = lambda: torch.zeros(batch_size, self.hidden_size, dtype=w.dtype, device=w.device)
+        return {"key_shift": z(), "value_shift": z()}
+
+    def forward(self, hidden_states: torch.Tensor, attention_mask: Optional[torch.Tensor] = None,
+                past_key_values=None, layer_idx: int = 0) -> torch.Tensor:
+        """With ``past_key_values`` (an ``FgateCache`` whose shift states were registered with
+        ``update_shift_cache``) the layer appends its keys, values and log gates to the cache and attends over
+        the whole history (upstream lines 296-362); a single new token takes the split-KV generation kernels."""
         dtype = torch.get_autocast_dtype("cuda") if torch.is_autocast_enabled("cuda") else hidden_states.dtype
         hidden_states = hidden_states.to(dtype)
         B, T, _ = hidden_states.shape
         H, D = self.num_heads, self.head_dim
+        k_state = v_state = None
+        if past_key_values is not None:
+            k_state = past_key_values.key_shift_cache[layer_idx]
+            v_state = past_key_values.value_shift_cache[layer_idx]
+        step_mask = attention_mask
+        if attention_mask is not None and attention_mask.shape[1] != T:
+            step_mask = attention_mask[:, -T:]          # the mask covers the history, the shift only this call
         q = self.q_proj(hidden_states)
-        k = self.k_proj(hidden_states, attention_mask) if self.use_k_shift else self.k_proj(hidden_states)
-        v = self.v_proj(hidden_states, attention_mask) if self.use_v_shift else self.v_proj(hidden_states)
+        k = self.k_proj(hidden_states, step_mask, k_state) if self.use_k_shift else self.k_proj(hidden_states)
+        v = self.v_proj(hidden_states, step_mask, v_state) if self.use_v_shift else self.v_proj(hidden_states)
         if self.qk_norm:
             q = self.q_norm(q).to(q.dtype)
             k = self.k_norm(k).to(k.dtype)
         fgate_logit = self.fgate_proj(hidden_states).transpose(1, 2)               # (B, H, T)
         log_fgate = F.logsigmoid(fgate_logit.float())
         q, k, v = [t.view(B, T, H, D).transpose(1, 2) for t in (q, k, v)]          # head-first views
+        if past_key_values is not None:
+            k, v, log_fgate = past_key_values.update(k, v, log_fgate, layer_idx)
+        N = log_fgate.shape[-1]
         thr = None
         if self.log_pruning_tolerance is not None:
             assert self.qk_norm, "the closed-form threshold needs QK-norm"
-            thr = acp_threshold_from_qk_norm(self.q_norm.weight, self.k_norm.weight, H, D, T,
+            thr = acp_threshold_from_qk_norm(self.q_norm.weight, self.k_norm.weight, H, D, N,
                                              self.log_pruning_tolerance)
-        seq_start = None if attention_mask is None else seq_start_from_attention_mask(attention_mask)
+        seq_start = None
+        if attention_mask is not None:
+            assert attention_mask.shape == (B, N), ((B, N), tuple(attention_mask.shape))
+            seq_start = seq_start_from_attention_mask(attention_mask)
         o = forgetting_attention(q, k, v, log_fgate, head_first=True, seq_start=seq_start,
                                  sm_scale=1 / math.sqrt(D), adaptive_threshold=thr)
         o = o.transpose(1, 2).reshape(B, T, self.hidden_size)
@@ -132,10 +168,11 @@ class FoxProBlock(nn.Module):
         self.mlp_norm = RMSNorm(hidden_size, eps=norm_eps)
         self.mlp = FoxMLP(hidden_size, intermediate_size)
 
-    def forward(self, hidden_states: torch.Tensor, attention_mask: Optional[torch.Tensor] = None) -> torch.Tensor:
+    def forward(self, hidden_states: torch.Tensor, attention_mask: Optional[torch.Tensor] = None,
+                past_key_values=None, layer_idx: int = 0) -> torch.Tensor:
         """hidden_states (B, T, hidden) in fp16/bf16 (the residual stream is kept in that dtype here)."""
         residual = hidden_states
-        hidden_states = self.attn(self.attn_norm(hidden_states), attention_mask)
+        hidden_states = self.attn(self.attn_norm(hidden_states), attention_mask, past_key_values, layer_idx)
         hidden_states, residual = self.mlp_norm(hidden_states, residual, True)
         return residual + self.mlp(hidden_states)
 

@@ -206,3 +206,46 @@ def test_swiglu_and_swiglu_linear(dtype):
     out3 = fox.swiglu_linear(x3, y3, w3, None)
     out3.backward(dout)
     assert torch.equal(out3, out) and torch.equal(torch.cat([x3.grad, y3.grad], -1), xy1.grad)
+
+
+@pytest.mark.parametrize("with_mask", [False, True])
+def test_generation_with_cache_matches_full_forward(with_mask):
+    """Prefill of T0 tokens followed by single-token steps through ``FgateCache`` (in-place growth, the
+    ShiftLinear single-token branch of modeling_forgetting_transformer.py:83-86, the split-KV generation
+    kernels) against the oracle's restatement of the block on the whole sequence, and against the block's own
+    full-sequence forward."""
+    torch.manual_seed(5)
+    B, T0, steps, C, H, I = 2, 150, 6, 256, 4, 512
+    T = T0 + steps
+    blk = fox.FoxProBlock(C, H, I, fgate_bias=2.0).cuda().to(torch.bfloat16)
+    with torch.no_grad():
+        for m in (blk.attn_norm, blk.mlp_norm, blk.attn.q_norm, blk.attn.k_norm, blk.attn.output_norm):
+            m.weight.uniform_(0.5, 1.5)
+        for lin in (blk.attn.q_proj, blk.attn.k_proj.linear, blk.attn.v_proj.linear, blk.attn.o_proj,
+                    blk.attn.ogate_proj, blk.mlp.gate_proj, blk.mlp.down_proj):
+            lin.weight.normal_(0, 0.08)
+    x = torch.randn(B, T, C, device="cuda").to(torch.bfloat16)
+    mask = None
+    if with_mask:
+        mask = torch.ones(B, T, dtype=torch.long, device="cuda")
+        mask[1, :9] = 0                         # left padding
+    cache = fox.FgateCache(granule=128)
+    st = blk.attn.init_shift_state(B)
+    cache.update_shift_cache(st["key_shift"], st["value_shift"], 0)
+    with torch.no_grad():
+        full = blk(x, mask)
+        outs = [blk(x[:, :T0], None if mask is None else mask[:, :T0], cache, 0)]
+        ptr = cache[0][0].data_ptr()
+        for t in range(T0, T):
+            outs.append(blk(x[:, t:t + 1], None if mask is None else mask[:, :t + 1], cache, 0))
+        gen = torch.cat(outs, dim=1)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    assert cache.get_seq_length() == T and cache.capacity(0) == 256
+    assert cache[0][0].data_ptr() == ptr        # the steps wrote in place
+    w = {n: t.detach().float().cpu() for n, t in blk.oracle_weights().items()}
+    yr = orc.fox_pro_block(x.float().cpu(), w, H, eps=1e-6, attention_mask=None if mask is None else mask.cpu())
+    valid = slice(None) if mask is None else mask.bool().cpu()
+    scale = yr.abs().max().item()
+    assert (gen.float().cpu() - yr)[valid].abs().max().item() < 3e-2 * scale
+    assert (gen.float().cpu() - full.float().cpu())[valid].abs().max().item() < 3e-2 * scale
