@@ -321,6 +321,29 @@ def run_ours(args, w, wname):
         e2e_val = world * flops / (float(t2.item()) / n_e2e * 1e-3) / 1e12
         del pipe
 
+    # ---- launch-bound shapes: the same step replayed from CUDA graphs (forward graph + backward graph) ----
+    graphed = None
+    if world == 1 and ms_per_step < 1.0 and not args.no_e2e:
+        gq, gk, gv, gl = [t.detach().clone().requires_grad_() for t in (q, k, v, lf)]
+        gf = fox.make_graphed(gq, gk, gv, gl, head_first=True, seq_start=seq_d, adaptive_threshold=thr)
+
+        def gstep():
+            gq.grad = gk.grad = gv.grad = gl.grad = None
+            gf(gq, gk, gv, gl).backward(dout)
+
+        for _ in range(5):
+            gstep()
+        barrier()
+        n_g = max(args.steps, 50)
+        e0.record()
+        for _ in range(n_g):
+            gstep()
+        e1.record()
+        barrier()
+        ms_g = e0.elapsed_time(e1) / n_g
+        graphed = {"ms_per_step": ms_g, "value": flops / (ms_g * 1e-3) / 1e12, "unit": UNIT, "steps": n_g,
+                   "speedup_over_eager_launches": ms_per_step / ms_g}
+
     # ---- pruning statistics and dense comparison (ACP workloads) ----
     acp = None
     if thr is not None:
@@ -516,6 +539,8 @@ def run_ours(args, w, wname):
             "gpu_launches": launches,
             "clocks": clocks,
         }
+        if graphed is not None:
+            line["cuda_graph"] = graphed
         if acp is not None:
             line["acp"] = acp
         if block is not None:

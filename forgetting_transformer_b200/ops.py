@@ -176,7 +176,10 @@ class ForgettingAttention(torch.autograd.Function):
                     logit_upper_bound = max_q_norm * max_k_norm * sm_scale
                     tolerance = -10
                     adaptive_threshold = -(2 * logit_upper_bound + math.log(N)) + tolerance
-                adaptive_threshold = torch.as_tensor(adaptive_threshold, dtype=torch.float, device=dev)
+                if isinstance(adaptive_threshold, torch.Tensor):
+                    adaptive_threshold = adaptive_threshold.to(dtype=torch.float, device=dev)
+                else:   # a fill kernel instead of a host-to-device copy: legal inside CUDA-graph capture
+                    adaptive_threshold = torch.full((), float(adaptive_threshold), dtype=torch.float, device=dev)
                 try:
                     adaptive_threshold = torch.broadcast_to(adaptive_threshold, (B, H))
                 except RuntimeError:
