@@ -476,14 +476,14 @@ def run_ours(args, w, wname):
         two_kernel = dq_n > 0
         bwd_kernel_name = "fox_attn_bwd_kernel"
         if two_kernel:
-            # head dim 128: the backward is a key-side kernel (S, dP, dV, dK: 8 of the 14 FLOPs per pair) and a
+            # head dim 128: the backward is a key-side kernel (S^T, dP^T, dV, dK: 8 of the 14 FLOPs per pair) and a
             # query-side kernel (S and dP recomputed, dQ: 6 per pair executed, 2 of them algorithmic). The roofline
             # entry is the longer of the two with the FLOPs it executes; the pair's algorithmic rate is beside it.
             per = max(bwd_n // args.steps, 1)
             key_tf = (8.0 / 14.0) * flops / (bwd_ms * per * 1e-3) / 1e12
             qry_tf = (6.0 / 14.0) * flops / (dq_ms * max(dq_n // args.steps, 1) * 1e-3) / 1e12
             pair_tf = (10.0 / 14.0) * flops / ((bwd_ms + dq_ms) * per * 1e-3) / 1e12
-            two = {"key_side": {"kernel": "fox_attn_bwd_kernel<no dQ>", "ms_per_launch": bwd_ms, "executed_tflops": key_tf,
+            two = {"key_side": {"kernel": "fox_attn_bwd_kv_kernel", "ms_per_launch": bwd_ms, "executed_tflops": key_tf,
                                 "frac": key_tf / peaks["bf16_sustained"]},
                    "query_side": {"kernel": "fox_attn_bwd_dq2_kernel", "ms_per_launch": dq_ms, "executed_tflops": qry_tf,
                                   "frac": qry_tf / peaks["bf16_sustained"]},
@@ -492,7 +492,7 @@ def run_ours(args, w, wname):
             if dq_ms > bwd_ms:
                 bwd_kernel_name, bwd_tf, bwd_ms, bwd_n = "fox_attn_bwd_dq2_kernel", qry_tf, dq_ms, dq_n
             else:
-                bwd_kernel_name, bwd_tf = "fox_attn_bwd_kernel<no dQ>", key_tf
+                bwd_kernel_name, bwd_tf = "fox_attn_bwd_kv_kernel", key_tf
         roof = {
             "kernel": bwd_kernel_name, "bound": "tensor", "achieved": bwd_tf,
             "peak": peaks["bf16_sustained"], "unit": "TFLOP/s", "frac": bwd_tf / peaks["bf16_sustained"],
@@ -577,9 +577,9 @@ TRAFFIC_BYTES_PER_LAUNCH = {
     "prof_d128": 632.8e6,
     "cfg4": 4 * 632.8e6,
     # head dim 128, the kernel pair (profiles/attn_bwd_two_kernels_prof_d128.md); cfg4 has 4x the rows of prof_d128
-    ("prof_d128", "fox_attn_bwd_kernel<no dQ>"): 380.1e6,
+    ("prof_d128", "fox_attn_bwd_kv_kernel"): 380.1e6,
     ("prof_d128", "fox_attn_bwd_dq2_kernel"): 325.3e6,
-    ("cfg4", "fox_attn_bwd_kernel<no dQ>"): 4 * 380.1e6,
+    ("cfg4", "fox_attn_bwd_kv_kernel"): 4 * 380.1e6,
     ("cfg4", "fox_attn_bwd_dq2_kernel"): 4 * 325.3e6,
 }
 
