@@ -302,7 +302,7 @@ def run_ours(args, w, wname):
     if not args.no_e2e:
         pipe = HostStreamedAttention(dev, seq_start=seq_d, adaptive_threshold=thr,
                                      attention=(lambda q_, k_, v_, lf_: attention(q_, k_, v_, lf_)) if cp else None)
-        for _ in range(3):
+        for _ in range(args.e2e_warmup):
             pipe.submit(host)
         pipe.finish()
         barrier()
@@ -607,6 +607,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg (profiler runs)")
+    ap.add_argument("--e2e-warmup", type=int, default=3, help="untimed host-to-host steps before the end-to-end leg")
     args = ap.parse_args()
     w = WORKLOADS[args.workload]
     if args.impl == "reference":
