@@ -111,7 +111,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   return false;
 }
 
-// Warp-collective form: every lane waits, the verdict is made uniform so the warp stays converged.
+// Warp-collective form: every lane waits, the outcome is made uniform so the warp stays converged.
 __device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
                                                int* status, int site, int detail = 0) {
   const bool ok = mbar_wait<false>(bar, parity, abort_flag, status, site, detail);
