@@ -226,6 +226,9 @@ class ForgettingAttention(torch.autograd.Function):
         ctx.save_for_backward(q, k, v, o, L, log_lambda, seq_start, adaptive_threshold)
         ctx.sm_scale = sm_scale
         ctx.has_seq_start = has_seq_start
+        # the query-side backward kernel prunes by the same array when the two block grids agree (not an input or
+        # output of the function, so it is kept on ctx rather than through save_for_backward)
+        ctx.start_index = start_index if FWD_BLOCK == BWD_BLOCK else None
         ctx.head_dim = D_in
         out = o if D_in == D else o[..., :D_in].contiguous()
         if return_log_normalizer or return_start_index:
@@ -270,7 +273,9 @@ class ForgettingAttention(torch.autograd.Function):
                 # dQ partials to add-reduce into L2, which is what bounds the one-pass kernel at this head dim
                 start_index = None
                 if adaptive_threshold is not None:
-                    start_index, _ = find_index(log_lambda, adaptive_threshold, M, *BWD_BLOCK)
+                    start_index = ctx.start_index
+                    if start_index is None:
+                        start_index, _ = find_index(log_lambda, adaptive_threshold, M, *BWD_BLOCK)
                 dlam_row = torch.empty((B, H, M), dtype=torch.float32, device=dev)
                 _call("fox_attn_bwd", lib.fox_attn_bwd, dev.index, _stream(), code, B, H, M, N, D, _lib.t4(q),
                       _lib.t4(k), _lib.t4(v), _lib.t4(do), log_lambda.data_ptr(), L.data_ptr(), delta.data_ptr(),
