@@ -694,16 +694,16 @@ static int launch_bwd(int device, cudaStream_t stream, int64_t B, int64_t H, int
 }  // namespace fox
 
 namespace fox {
-// fox_attn_bwd_kv.cu: the key side at D = 128 with P^T and dS^T both written in phase B
-int launch_bwd_kv_d128(int device, cudaStream_t stream, bool bf16, int64_t B, int64_t H, int64_t M, int64_t N,
+// fox_attn_bwd_kv.cu: the key side with P^T and dS^T both written in phase B
+int launch_bwd_kv(int device, cudaStream_t stream, bool bf16, int D, int64_t B, int64_t H, int64_t M, int64_t N,
                        const fox_tensor4* q, const fox_tensor4* k, const fox_tensor4* v, const fox_tensor4* d_o,
                        const float* log_lambda, const float* L, const float* delta, const int64_t* seq_start,
                        const int64_t* end_index, float sm_scale, float* dlam_col, const fox_tensor4* dk,
                        const fox_tensor4* dv, int32_t* status);
-static int g_kv_variant = 1;   // 0: the general kernel without its dQ product; 1: the D = 128 key-side kernel
+static int g_kv_variant = 1;   // 0: the general kernel without its dQ product; 1: the key-side kernel
 }  // namespace fox
 
-// Debug hook: which kernel serves a key-side-only call (dq_accum_zeroed == NULL) at D = 128.
+// Debug hook: which kernel serves a key-side-only call (dq_accum_zeroed == NULL).
 extern "C" void fox_debug_set_kv_variant(int v) { fox::g_kv_variant = v; }
 
 extern "C" void fox_debug_set_bwd_trace(void* device_buffer) { fox::g_bwd_trace = static_cast<long long*>(device_buffer); }
@@ -741,9 +741,9 @@ extern "C" int fox_attn_bwd(int device, void* stream, int dtype, int64_t B, int6
   prm.qk_scale = sm_scale * 1.4426950408889634f;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const bool bf = dtype == FOX_DTYPE_BF16;
-  if (D == 128 && dq_accum_zeroed == nullptr && g_kv_variant == 1 && g_bwd_trace == nullptr)
-    return launch_bwd_kv_d128(device, st, bf, B, H, M, N, q, k, v, d_o, log_lambda, L, delta, seq_start, end_index,
-                              sm_scale, dlam_col, dk, dv, status);
+  if (dq_accum_zeroed == nullptr && g_kv_variant == 1 && g_bwd_trace == nullptr)
+    return launch_bwd_kv(device, st, bf, (int)D, B, H, M, N, q, k, v, d_o, log_lambda, L, delta, seq_start, end_index,
+                         sm_scale, dlam_col, dk, dv, status);
   if (D == 64)
     return bf ? launch_bwd<64, true>(device, st, B, H, M, N, q, k, v, d_o, prm)
               : launch_bwd<64, false>(device, st, B, H, M, N, q, k, v, d_o, prm);

@@ -5,8 +5,8 @@
 // backward kernel's dQ partials (64 KB of fp32 per tile pair, add-reduced into L2 at the L2's chip-wide rate)
 // cost more than recomputing S and dP: there the key side runs without a dQ product and this kernel owns dQ.
 //
-// Two kernels: fox_attn_bwd_dq2_kernel (further down; D = 128, one CTA per SM, 128-column tiles, products of the
-// next tile under the elementwise passes of this one) and the first form, which serves D = 64:
+// Two kernels: fox_attn_bwd_dq2_kernel (further down; one CTA per SM, 128-column tiles, products of the
+// next tile under the elementwise passes of this one), the default, and the first form (debug hook):
 // one CTA = one (batch, head, 128-row query tile), two CTAs per SM, same roles as the forward kernel:
 //   warps 0-3 : thread t owns query row t (TMEM lane t): p = 2^(s c + e_i - b_j), dS = p (dP - delta_i),
 //               16-bit dS written over S, running rowsum(dS) (of the fp32 values, like the key side's colsum)
@@ -359,7 +359,7 @@ fox_attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
 }
 
 // ---------------------------------------------------------------------------------------------------------------
-// Pipelined form for D = 128: one CTA per SM, 128-row KV tiles, four elementwise warpgroups (thread = query row x
+// Pipelined form: one CTA per SM, 128-row KV tiles, four elementwise warpgroups (thread = query row x
 // 32 of the tile's 128 columns; four warps on every scheduler), S double-buffered in TMEM so that the products of
 // the next tile run under the elementwise passes of this one:
 //   issuer, tile t:  S(t+1) = Q K(t+1)^T | wait dS(t) | dP(t+1) = dO V(t+1)^T | dQ += dS(t) K(t)
@@ -377,7 +377,7 @@ __global__ void __launch_bounds__(576, 1)
 fox_attn_bwd_dq2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                         const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
                         const DqParams p) {
-  static_assert(D == 128, "pipelined query-side kernel: D = 128");
+  static_assert(D == 64 || D == 128, "head dim");
   constexpr int BN = kDq2BN;
   constexpr int kWG = 4, CW = BN / kWG;          // 32 columns of every tile per warpgroup
   constexpr int kKS = 3;                         // K stages
@@ -693,16 +693,16 @@ fox_attn_bwd_dq2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
     }
     if (ok) {
       tc_fence_after();
-      constexpr int kCols = D / kWG;   // 32
+      constexpr int kCols = D / kWG;   // 32 or 16
       uint16_t* orow = reinterpret_cast<uint16_t*>(p.dq) + b * p.dq_sb + h * p.dq_sh + static_cast<int64_t>(row) * p.dq_st + g * kCols;
-      uint32_t t0[32];
+      uint32_t t0[kCols];
       if (n_tiles > 0) {
-        tmem_ld32(tDQ + g * kCols, t0);
+        if constexpr (kCols == 32) tmem_ld32(tDQ + g * kCols, t0); else tmem_ld16(tDQ + g * kCols, t0);
         tmem_ld_wait();
       }
       if (row_ok) {
 #pragma unroll
-        for (int j = 0; j < 32; j += 8) {
+        for (int j = 0; j < kCols; j += 8) {
           uint4 w = make_uint4(0, 0, 0, 0);
           if (n_tiles > 0) {
             w.x = pack2<kBf16>(__uint_as_float(t0[j + 0]) * p.sm_scale, __uint_as_float(t0[j + 1]) * p.sm_scale);
@@ -723,7 +723,7 @@ fox_attn_bwd_dq2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
   if (warp == kTmaWarp) tmem_dealloc(tbase, kTmemCols);
 }
 
-static int g_dq_variant = 1;   // 0: two CTAs per SM, 64-column tiles; 1: pipelined form at D = 128
+static int g_dq_variant = 1;   // 0: two CTAs per SM, 64-column tiles; 1: pipelined form
 
 template <int D, bool kBf16>
 static int launch_dq(int device, cudaStream_t stream, int64_t B, int64_t H, int64_t M, int64_t N, const fox_tensor4* q,
@@ -810,8 +810,11 @@ extern "C" int fox_attn_bwd_dq(int device, void* stream, int dtype, int64_t B, i
   prm.sm_scale = sm_scale;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const bool bf = dtype == FOX_DTYPE_BF16;
-  if (D == 64)
+  if (D == 64) {
+    if (g_dq_variant == 1)
+      return bf ? launch_dq2<64, true>(device, st, B, H, M, N, q, k, v, d_o, prm) : launch_dq2<64, false>(device, st, B, H, M, N, q, k, v, d_o, prm);
     return bf ? launch_dq<64, true>(device, st, B, H, M, N, q, k, v, d_o, prm) : launch_dq<64, false>(device, st, B, H, M, N, q, k, v, d_o, prm);
+  }
   if (g_dq_variant == 1)
     return bf ? launch_dq2<128, true>(device, st, B, H, M, N, q, k, v, d_o, prm) : launch_dq2<128, false>(device, st, B, H, M, N, q, k, v, d_o, prm);
   return bf ? launch_dq<128, true>(device, st, B, H, M, N, q, k, v, d_o, prm) : launch_dq<128, false>(device, st, B, H, M, N, q, k, v, d_o, prm);

@@ -1,4 +1,4 @@
-// Forgetting Attention backward, key side at D = 128: dK, dV and the key-side log-gate gradient.
+// Forgetting Attention backward, key side: dK, dV and the key-side log-gate gradient.
 //
 // Stands in for upstream's Triton `_bwd_kv_kernel`
 // (src/forgetting_transformer/ops/forgetting_attention.py:956-1147).  Used together with the query-side kernel
@@ -53,11 +53,11 @@ extern "C" int fox_debug_read_kv_trace(long long* host) { return cudaMemcpyFromS
 enum KvWaitSite { kKvSiteQ = 71, kKvSiteDO = 72, kKvSiteQE = 73, kKvSiteDOE = 74, kKvSiteS = 75, kKvSiteDP = 76,
                   kKvSiteP = 77, kKvSiteDS = 78, kKvSiteDone = 79, kKvSiteVec = 80, kKvSiteCol = 81, kKvSiteKV = 82 };
 
-template <bool kBf16>
+template <int D, bool kBf16>
 __global__ void __launch_bounds__(576, 1)
 fox_attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                        const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO, const KvParams p) {
-  constexpr int D = 128;
+  static_assert(D == 64 || D == 128, "head dim");
   constexpr int BM = kKvBM;                      // query rows per tile
   constexpr int kWG = 4, CW = BM / kWG;          // 32 query columns of every tile per warpgroup
   constexpr int kSt = 2;                         // Q and dO stages
@@ -404,7 +404,8 @@ fox_attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     if (ok) {
       tc_fence_after();
       // warpgroups 0, 1 write the halves of dK, 2 and 3 those of dV
-      const int which = g >> 1, part_c = (g & 1) * 64;
+      constexpr int kHalf = D / 2;   // columns of dK or dV per warpgroup
+      const int which = g >> 1, part_c = (g & 1) * kHalf;
       const bool keep = j_ok && n_tiles > 0;
       const uint32_t tcol = tbase + lane_base + (which == 0 ? kColDK : kColDV) + part_c;
       const float sc = which == 0 ? p.sm_scale : 1.f;
@@ -412,7 +413,7 @@ fox_attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
           ? reinterpret_cast<uint16_t*>(p.dk) + b * p.dk_sb + h * p.dk_sh + static_cast<int64_t>(j) * p.dk_st
           : reinterpret_cast<uint16_t*>(p.dv) + b * p.dv_sb + h * p.dv_sh + static_cast<int64_t>(j) * p.dv_st) + part_c;
 #pragma unroll
-      for (int c = 0; c < 64; c += 32) {
+      for (int c = 0; c < kHalf; c += 32) {
         uint32_t t0[32];
         if (n_tiles > 0) {
           tmem_ld32(tcol + c, t0);
@@ -441,10 +442,9 @@ fox_attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
   if (warp == kTmaWarp) tmem_dealloc(tbase, kTmemCols);
 }
 
-template <bool kBf16>
+template <int D, bool kBf16>
 static int launch_kv(int device, cudaStream_t stream, int64_t B, int64_t H, int64_t M, int64_t N, const fox_tensor4* q,
                      const fox_tensor4* k, const fox_tensor4* v, const fox_tensor4* d_o, const KvParams& prm) {
-  constexpr int D = 128;
   CUtensorMap tmQ, tmK, tmV, tmDO;
   Tensor4 tq{q->ptr, B, H, M, D, q->sb, q->sh, q->st};
   Tensor4 tk{k->ptr, B, H, N, D, k->sb, k->sh, k->st};
@@ -458,7 +458,7 @@ static int launch_kv(int device, cudaStream_t stream, int64_t B, int64_t H, int6
   if ((rc = cached_tmap_4d(&tmK, tk, 2, false, kBf16, 64, kKvBN, true))) return rc;
   if ((rc = cached_tmap_4d(&tmV, tv, 2, false, kBf16, 64, kKvBN, true))) return rc;
   constexpr int smem = (2 * 2 + 2) * 128 * D * 2 + 1024;   // Q, dO in two stages each, K, V
-  auto kern = fox_attn_bwd_kv_kernel<kBf16>;
+  auto kern = fox_attn_bwd_kv_kernel<D, kBf16>;
   static bool configured[64] = {};
   if (device < 0 || device >= 64) return FOX_ERR_DEVICE;
   if (!configured[device]) {
@@ -470,8 +470,8 @@ static int launch_kv(int device, cudaStream_t stream, int64_t B, int64_t H, int6
   return cudaGetLastError() == cudaSuccess ? FOX_OK : FOX_ERR_LAUNCH;
 }
 
-// Key side at D = 128 (dk, dv, dlam_col); arguments as fox_attn_bwd's, already validated there.
-int launch_bwd_kv_d128(int device, cudaStream_t stream, bool bf16, int64_t B, int64_t H, int64_t M, int64_t N,
+// Key side (dk, dv, dlam_col); arguments as fox_attn_bwd's, already validated there.
+int launch_bwd_kv(int device, cudaStream_t stream, bool bf16, int D, int64_t B, int64_t H, int64_t M, int64_t N,
                        const fox_tensor4* q, const fox_tensor4* k, const fox_tensor4* v, const fox_tensor4* d_o,
                        const float* log_lambda, const float* L, const float* delta, const int64_t* seq_start,
                        const int64_t* end_index, float sm_scale, float* dlam_col, const fox_tensor4* dk,
@@ -485,8 +485,11 @@ int launch_bwd_kv_d128(int device, cudaStream_t stream, bool bf16, int64_t B, in
   prm.H = (int)H; prm.M = (int)M; prm.N = (int)N;
   prm.sm_scale = sm_scale;
   prm.qk_scale = sm_scale * kKvLog2e;
-  return bf16 ? launch_kv<true>(device, stream, B, H, M, N, q, k, v, d_o, prm)
-              : launch_kv<false>(device, stream, B, H, M, N, q, k, v, d_o, prm);
+  if (D == 64)
+    return bf16 ? launch_kv<64, true>(device, stream, B, H, M, N, q, k, v, d_o, prm)
+                : launch_kv<64, false>(device, stream, B, H, M, N, q, k, v, d_o, prm);
+  return bf16 ? launch_kv<128, true>(device, stream, B, H, M, N, q, k, v, d_o, prm)
+              : launch_kv<128, false>(device, stream, B, H, M, N, q, k, v, d_o, prm);
 }
 
 }  // namespace fox
