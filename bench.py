@@ -382,36 +382,41 @@ def run_ours(args, w, wname):
         x = torch.randn(1, tokens, G * Dh, device=dev, dtype=torch.bfloat16).requires_grad_()
         gate = torch.randn(1, tokens, G * Dh, device=dev, dtype=torch.bfloat16).requires_grad_()
         dy = torch.randn(1, tokens, G * Dh, device=dev, dtype=torch.bfloat16)
-        for _ in range(3):
-            m(x, gate).backward(dy)
         ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
-        tf = tb = 0.0
-        for _ in range(10):
-            ev[0].record(); y = m(x, gate); ev[1].record(); y.backward(dy); ev[2].record()
-            torch.cuda.synchronize()
-            tf += ev[0].elapsed_time(ev[1]); tb += ev[1].elapsed_time(ev[2])
-        n_el = tokens * G * Dh
-        normgate = {"shape": "tokens 65536 x 24 heads x 64", "fwd_ms": tf / 10, "bwd_ms": tb / 10,
-                    "fwd_gbs": (6 * n_el + 4 * tokens * G) / (tf / 10 * 1e-3) / 1e9,
-                    "bwd_gbs_incl_host_dw_sum": (10 * n_el + 4 * tokens * G) / (tb / 10 * 1e-3) / 1e9}
-        # the other two HBM-bound operators of the FoX-Pro layer: per-head RMSNorm of q / k, token shift of k / v
-        def timed(fwd_fn, grad):
+
+        def timed(fwd_fn, grad, leaves, n_it=10):
+            """Mean device time of n_it forwards queued back to back, then of their n_it backwards (queued, so
+            that the host's launch latency is not inside the timed intervals of these 0.1-0.4 ms kernels)."""
             for _ in range(3):
                 fwd_fn().backward(grad)
-            a = b_ = 0.0
-            for _ in range(10):
-                ev[0].record(); o_ = fwd_fn(); ev[1].record(); o_.backward(grad); ev[2].record()
-                torch.cuda.synchronize()
-                a += ev[0].elapsed_time(ev[1]); b_ += ev[1].elapsed_time(ev[2])
-            return a / 10, b_ / 10
+            outs = [fwd_fn() for _ in range(n_it)]   # untimed: lets the caching allocator grow to n_it live outputs
+            del outs
+            torch.cuda.synchronize()
+            ev[0].record()
+            outs = [fwd_fn() for _ in range(n_it)]
+            ev[1].record()
+            for o_ in outs:
+                for leaf in leaves:        # no gradient accumulation kernels inside the timed interval
+                    leaf.grad = None
+                o_.backward(grad)
+            ev[2].record()
+            torch.cuda.synchronize()
+            return ev[0].elapsed_time(ev[1]) / n_it, ev[1].elapsed_time(ev[2]) / n_it
+
+        tf, tb = timed(lambda: m(x, gate), dy, (x, gate, m.weight))
+        n_el = tokens * G * Dh
+        normgate = {"shape": "tokens 65536 x 24 heads x 64", "fwd_ms": tf, "bwd_ms": tb,
+                    "fwd_gbs": (6 * n_el + 4 * tokens * G) / (tf * 1e-3) / 1e9,
+                    "bwd_gbs_incl_host_dw_sum": (10 * n_el + 4 * tokens * G) / (tb * 1e-3) / 1e9}
+        # the other two HBM-bound operators of the FoX-Pro layer: per-head RMSNorm of q / k, token shift of k / v
         qkn = fox.GroupNorm(G, G * Dh, is_rms_norm=True).to(dev)
-        f_ms, b_ms = timed(lambda: qkn(x), dy)
+        f_ms, b_ms = timed(lambda: qkn(x), dy, (x, qkn.weight))
         normgate["qk_norm"] = {"fwd_ms": f_ms, "bwd_ms": b_ms,
                                "fwd_gbs": (4 * n_el + 4 * tokens * G) / (f_ms * 1e-3) / 1e9,
                                "bwd_gbs_incl_host_dw_sum": (6 * n_el + 4 * tokens * G) / (b_ms * 1e-3) / 1e9}
         x4 = x.detach().view(1, tokens, G, Dh).requires_grad_()
         alpha = torch.rand(1, tokens, G, device=dev).requires_grad_()
-        f_ms, b_ms = timed(lambda: fox.token_shift(x4, alpha, 1.0 - alpha), dy.view(1, tokens, G, Dh))
+        f_ms, b_ms = timed(lambda: fox.token_shift(x4, alpha, 1.0 - alpha), dy.view(1, tokens, G, Dh), (x4, alpha))
         normgate["token_shift"] = {"fwd_ms_incl_1_minus_alpha": f_ms, "bwd_ms": b_ms,
                                    "fwd_gbs": (4 * n_el + 8 * tokens * G) / (f_ms * 1e-3) / 1e9,
                                    "bwd_gbs": (6 * n_el + 16 * tokens * G) / (b_ms * 1e-3) / 1e9}

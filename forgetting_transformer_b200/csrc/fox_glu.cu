@@ -49,7 +49,7 @@ fox_swiglu_fwd_kernel(const uint16_t* __restrict__ x, int64_t x_sr, const uint16
     glu_load8<kBf16>(x + r * x_sr + c, xv);
     glu_load8<kBf16>(y + r * y_sr + c, yv);
 #pragma unroll
-    for (int j = 0; j < 8; ++j) o[j] = xv[j] * yv[j] / (1.0f + __expf(-xv[j]));
+    for (int j = 0; j < 8; ++j) o[j] = __fdividef(xv[j] * yv[j], 1.0f + __expf(-xv[j]));   // approximate reciprocal: 2 ulp in fp32
     glu_store8<kBf16>(z + r * z_sr + c, o);
   }
 }
@@ -70,7 +70,7 @@ fox_swiglu_bwd_kernel(const uint16_t* __restrict__ x, int64_t x_sr, const uint16
     glu_load8<kBf16>(g + r * g_sr + c, gv);
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
-      const float s = 1.0f / (1.0f + __expf(-xv[j]));
+      const float s = __fdividef(1.0f, 1.0f + __expf(-xv[j]));
       const float sw = xv[j] * s;
       ox[j] = s * (1.0f + xv[j] * (1.0f - s)) * gv[j] * yv[j];
       oy[j] = sw * gv[j];
