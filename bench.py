@@ -417,6 +417,19 @@ def run_ours(args, w, wname):
         x4 = x.detach().view(1, tokens, G, Dh).requires_grad_()
         alpha = torch.rand(1, tokens, G, device=dev).requires_grad_()
         f_ms, b_ms = timed(lambda: fox.token_shift(x4, alpha, 1.0 - alpha), dy.view(1, tokens, G, Dh), (x4, alpha))
+        # the block's input norm (row RMSNorm, hidden 1536) and the MLP's SwiGLU (65536 x 4096 per half)
+        rn = fox.RMSNorm(G * Dh, eps=1e-6).to(dev)
+        f2, b2 = timed(lambda: rn(x), dy, (x, rn.weight))
+        normgate["row_rms_norm"] = {"fwd_ms": f2, "bwd_ms": b2, "fwd_gbs": 4 * n_el / (f2 * 1e-3) / 1e9,
+                                    "bwd_gbs_incl_host_dw_sum": 6 * n_el / (b2 * 1e-3) / 1e9}
+        gx = torch.randn(tokens, 4096, device=dev, dtype=torch.bfloat16).requires_grad_()
+        gy = torch.randn(tokens, 4096, device=dev, dtype=torch.bfloat16).requires_grad_()
+        gdz = torch.randn(tokens, 4096, device=dev, dtype=torch.bfloat16)
+        f3, b3 = timed(lambda: fox.swiglu(gx, gy), gdz, (gx, gy))
+        n_g = tokens * 4096
+        normgate["swiglu"] = {"fwd_ms": f3, "bwd_ms": b3, "fwd_gbs": 6 * n_g / (f3 * 1e-3) / 1e9,
+                              "bwd_gbs": 10 * n_g / (b3 * 1e-3) / 1e9}
+        del gx, gy, gdz
         normgate["token_shift"] = {"fwd_ms_incl_1_minus_alpha": f_ms, "bwd_ms": b_ms,
                                    "fwd_gbs": (4 * n_el + 8 * tokens * G) / (f_ms * 1e-3) / 1e9,
                                    "bwd_gbs": (6 * n_el + 16 * tokens * G) / (b_ms * 1e-3) / 1e9}
