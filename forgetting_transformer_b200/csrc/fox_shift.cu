@@ -57,7 +57,11 @@ fox_token_shift_fwd_kernel(const uint16_t* __restrict__ x, const float* __restri
   const int64_t n_rows = p.B * p.T * p.H;
   for (int64_t row = static_cast<int64_t>(blockIdx.x) * rows_per_block + threadIdx.x / lanes; row < n_rows;
        row += static_cast<int64_t>(gridDim.x) * rows_per_block) {
-    const int64_t h = row % p.H, t = (row / p.H) % p.T, b = row / (p.H * p.T);
+    // (b, t, h) of the row with 32-bit divisions (the launcher rejects more than 2^31 rows): 64-bit ones cost
+    // more instructions than the row's arithmetic
+    const uint32_t r32 = static_cast<uint32_t>(row), H32 = static_cast<uint32_t>(p.H), T32 = static_cast<uint32_t>(p.T);
+    const uint32_t q32 = r32 / H32;
+    const int64_t h = r32 - q32 * H32, b = q32 / T32, t = q32 - static_cast<uint32_t>(b) * T32;
     const int64_t xo = b * p.x_sb + t * p.x_st + h * p.x_sh + sub * 8;
     const int64_t wo = b * p.w_sb + t * p.w_st + h * p.w_sh;
     float xv[8], xp[8], o[8];
@@ -91,7 +95,9 @@ fox_token_shift_bwd_kernel(const uint16_t* __restrict__ x, const float* __restri
     const int64_t row = (it * gridDim.x + blockIdx.x) * rows_per_block + threadIdx.x / lanes;
     const bool in = row < n_rows;
     const int64_t rc = in ? row : 0;
-    const int64_t h = rc % p.H, t = (rc / p.H) % p.T, b = rc / (p.H * p.T);
+    const uint32_t r32 = static_cast<uint32_t>(rc), H32 = static_cast<uint32_t>(p.H), T32 = static_cast<uint32_t>(p.T);
+    const uint32_t q32 = r32 / H32;
+    const int64_t h = r32 - q32 * H32, b = q32 / T32, t = q32 - static_cast<uint32_t>(b) * T32;
     const int64_t xo = b * p.x_sb + t * p.x_st + h * p.x_sh + sub * 8;
     const int64_t wo = b * p.w_sb + t * p.w_st + h * p.w_sh;
     float xv[8], xp[8], dv[8], dn[8], o[8];
@@ -136,6 +142,7 @@ fox_token_shift_bwd_kernel(const uint16_t* __restrict__ x, const float* __restri
 static int shift_check(int64_t B, int64_t T, int64_t H, int64_t D, int64_t x_sb, int64_t x_st, int64_t x_sh,
                        std::initializer_list<const void*> ptrs16) {
   if (B <= 0 || T <= 0 || H <= 0) return FOX_ERR_BAD_ARG;
+  if (B * T > (int64_t{1} << 31) / H) return FOX_ERR_TOO_LARGE;              // rows are indexed with 32 bits
   if (D != 16 && D != 32 && D != 64 && D != 128) return FOX_ERR_HEAD_DIM;  // token_shift.py:166
   if (x_sb % 8 || x_st % 8 || x_sh % 8) return FOX_ERR_ALIGNMENT;           // 16-byte rows
   for (const void* q : ptrs16)
