@@ -192,21 +192,32 @@ fox_max_row_norm_kernel(const uint16_t* __restrict__ x, int64_t sb, int64_t sh, 
   const uint16_t* base = x + b * sb + h * sh;
   float best = 0.f;
   // every lane runs the same number of iterations (the shuffles below need the full warp)
-  for (int t0 = blockIdx.x * rows_per_block; t0 < T; t0 += gridDim.x * rows_per_block) {
-    const int t = t0 + r_in;
-    uint4 v = make_uint4(0, 0, 0, 0);
-    if (t < T) v = *reinterpret_cast<const uint4*>(base + static_cast<int64_t>(t) * st + sub * 8);
-    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-    float acc = 0.f;
+  // four rows per iteration with their loads issued first; the maximum is taken over the squared norms and the
+  // square root once at the end (sqrt is monotone and correctly rounded: same result as the maximum of the roots)
+  constexpr int kU = 4;
+  for (int t0 = blockIdx.x * rows_per_block; t0 < T; t0 += kU * gridDim.x * rows_per_block) {
+    uint4 v[kU];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const float2 f = unpack2<kBf16>(w[j]);
-      acc = fmaf(f.x, f.x, acc);
-      acc = fmaf(f.y, f.y, acc);
+    for (int u = 0; u < kU; ++u) {
+      const int t = t0 + u * gridDim.x * rows_per_block + r_in;
+      v[u] = make_uint4(0, 0, 0, 0);
+      if (t < T) v[u] = *reinterpret_cast<const uint4*>(base + static_cast<int64_t>(t) * st + sub * 8);
     }
-    for (int o = lanes_per_row / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-    best = fmaxf(best, sqrtf(acc));
+#pragma unroll
+    for (int u = 0; u < kU; ++u) {
+      const uint32_t w[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+      float acc = 0.f;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = unpack2<kBf16>(w[j]);
+        acc = fmaf(f.x, f.x, acc);
+        acc = fmaf(f.y, f.y, acc);
+      }
+      for (int o = lanes_per_row / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+      best = fmaxf(best, acc);
+    }
   }
+  best = sqrtf(best);
   for (int o = 16; o > 0; o >>= 1) best = fmaxf(best, __shfl_xor_sync(0xffffffffu, best, o));
   if ((threadIdx.x & 31) == 0) atomicMax(reinterpret_cast<int*>(out + bh), __float_as_int(best));
 }
