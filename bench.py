@@ -180,12 +180,18 @@ def cpu_sample(w, threads, rows=None):
                        f"PyTorch fwd+autograd bwd in {chunk}-row chunks")
 
 
+def cpu_rows(w):
+    """Query rows of the CPU sample: every row of the unit up to T = 16384 (seconds per sample), the last 4096
+    beyond.  The reference arm and the cpu_baseline leg of the GPU arm time the same sample."""
+    return None if w["T"] <= 16384 else 4096
+
+
 def run_reference(args, w, wname):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     threads = os.cpu_count() or 1
-    rows = min(w["T"], 2048)
+    rows = cpu_rows(w)
     for _ in range(args.warmup):
         cpu_sample(w, threads, rows)
     times = []
@@ -208,6 +214,80 @@ def run_reference(args, w, wname):
     _emit(line)
 
 
+# --------------------------------------------------------------------------- upstream's Triton operator
+# Block configurations tried for upstream's three kernels, (BLOCK_M, BLOCK_N, num_stages, num_warps) as
+# (forward, key side of the backward, query side of the backward) by head dim.  Upstream's own table stops at
+# sm_90 and raises on sm_100; its config functions are documented as overridable
+# (src/forgetting_transformer/ops/forgetting_attention.py:459, 799).  First row: upstream's H100 entries
+# (lines 467-472, 855-859, 882-886).
+UPSTREAM_CONFIGS = {
+    64: [("h100_rows", (128, 64, 3, 8), (128, 64, 3, 4), (128, 128, 4, 8)),
+         ("all_128x128", (128, 128, 2, 8), (128, 128, 2, 8), (128, 128, 2, 8)),
+         ("narrow_kv", (128, 64, 3, 4), (64, 64, 3, 4), (128, 64, 3, 4))],
+    128: [("h100_rows", (128, 128, 2, 8), (64, 64, 2, 4), (128, 128, 2, 8)),
+          ("all_128x128", (128, 128, 2, 8), (128, 128, 2, 8), (128, 128, 2, 8)),
+          ("narrow_kv", (128, 64, 2, 8), (64, 128, 2, 8), (128, 64, 2, 8))],
+}
+
+
+def find_upstream():
+    """Upstream's operator module, from $FOX_REFERENCE_SRC (directory holding its ``forgetting_transformer``
+    package) or ``baseline/_ref`` of this checkout (pip install --target; git-ignored); None when absent."""
+    import importlib
+    for cand in (os.environ.get("FOX_REFERENCE_SRC"), os.path.join(ROOT, "baseline", "_ref")):
+        if cand and os.path.isdir(os.path.join(cand, "forgetting_transformer")):
+            if cand not in sys.path:
+                sys.path.insert(0, cand)
+            sys.dont_write_bytecode = True
+            return importlib.import_module("forgetting_transformer.ops.forgetting_attention")
+    return None
+
+
+def time_upstream_triton(q, k, v, lf, dout, seq_d, thr, flops, n_configs, steps):
+    """fwd + bwd of upstream's Triton operator on the same device tensors, CUDA-event timed like our own step,
+    for the first ``n_configs`` rows of UPSTREAM_CONFIGS; returns the record for the JSON line (the best row's
+    ms per step and TFLOP/s, every row's time, or the reason it could not run)."""
+    try:
+        up = find_upstream()
+        if up is None:
+            return {"unavailable": "no copy of the upstream package (FOX_REFERENCE_SRC or baseline/_ref)"}
+        D = q.shape[-1]
+        rows = {}
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        for name, fwd, kv, qs in UPSTREAM_CONFIGS[D][:n_configs]:
+            up.get_fwd_config = lambda *a, _c=fwd: _c
+            up.get_bwd_kv_config = lambda *a, _c=kv: _c
+            up.get_bwd_q_config = lambda *a, _c=qs: _c
+            try:
+                def ustep():
+                    q.grad = k.grad = v.grad = lf.grad = None
+                    up.forgetting_attention(q, k, v, lf, head_first=True, seq_start=seq_d,
+                                            adaptive_threshold=thr).backward(dout)
+                for _ in range(2):
+                    ustep()
+                torch.cuda.synchronize()
+                e0.record()
+                for _ in range(steps):
+                    ustep()
+                e1.record()
+                torch.cuda.synchronize()
+                rows[name] = e0.elapsed_time(e1) / steps
+            except Exception as exc:  # a configuration that does not fit (shared memory) or does not compile
+                rows[name] = f"{type(exc).__name__}: {str(exc)[:200]}"
+        q.grad = k.grad = v.grad = lf.grad = None
+        timed = {n: t for n, t in rows.items() if isinstance(t, float)}
+        if not timed:
+            return {"unavailable": "no block configuration ran", "configs": rows}
+        best = min(timed, key=timed.get)
+        import triton
+        return {"ms_per_step": timed[best], "tflops": flops / (timed[best] * 1e-3) / 1e12, "best_config": best,
+                "config_table": {n: dict(zip(("fwd", "bwd_kv", "bwd_q"), c)) for n, *c in UPSTREAM_CONFIGS[D][:n_configs]},
+                "ms_per_step_by_config": rows, "steps": steps, "triton": triton.__version__,
+                "note": "upstream's Triton kernels, block-size hooks overridden (they raise on sm_100), same tensors"}
+    except Exception as exc:
+        return {"unavailable": f"{type(exc).__name__}: {str(exc)[:300]}"}
+
+
 # --------------------------------------------------------------------------- GPU arm
 def run_ours(args, w, wname):
     import torch.distributed as dist
@@ -222,9 +302,6 @@ def run_ours(args, w, wname):
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
-        # NCCL prints its version banner on stdout at NCCL_DEBUG=VERSION/INFO; stdout carries the JSON line only
-        if os.environ.get("NCCL_DEBUG", "").upper() in ("VERSION", "INFO", "TRACE"):
-            os.environ["NCCL_DEBUG"] = "WARN"
         dist.init_process_group("nccl", device_id=dev)
     _lib.load()
 
@@ -343,6 +420,14 @@ def run_ours(args, w, wname):
         ms_g = e0.elapsed_time(e1) / n_g
         graphed = {"ms_per_step": ms_g, "value": flops / (ms_g * 1e-3) / 1e12, "unit": UNIT, "steps": n_g,
                    "speedup_over_eager_launches": ms_per_step / ms_g}
+
+    # ---- upstream's Triton operator on the same tensors (single GPU, not context parallel) ----
+    upstream = None
+    if world == 1 and not cp and args.upstream_configs > 0:
+        upstream = time_upstream_triton(q, k, v, lf, dout, seq_d, thr, flops, args.upstream_configs,
+                                        max(3, min(args.steps, 5)))
+        if "ms_per_step" in upstream:
+            upstream["speedup_vs_upstream_triton"] = upstream["ms_per_step"] / ms_per_step
 
     # ---- pruning statistics and dense comparison (ACP workloads) ----
     acp = None
@@ -557,6 +642,8 @@ def run_ours(args, w, wname):
             "gpu_launches": launches,
             "clocks": clocks,
         }
+        if upstream is not None:
+            line["upstream_triton"] = upstream
         if graphed is not None:
             line["cuda_graph"] = graphed
         if acp is not None:
@@ -575,7 +662,7 @@ def run_ours(args, w, wname):
                 aux[name] = {"ms": kern[name][1], "gbs": bytes_ / (kern[name][1] * 1e-3) / 1e9}
         line["hbm_kernels"] = aux
         if world == 1 and not args.no_cpu:
-            dt, fl, desc = cpu_sample(w, os.cpu_count() or 1)
+            dt, fl, desc = cpu_sample(w, os.cpu_count() or 1, cpu_rows(w))
             line["cpu_baseline"] = {"value": fl / dt / 1e12, "unit": UNIT, "cores": os.cpu_count() or 1,
                                     "kind": "port", "sample": desc, "seconds": dt}
         _emit(line)
@@ -584,17 +671,17 @@ def run_ours(args, w, wname):
         dist.destroy_process_group()
 
 
-# DRAM bytes (read + write) of one backward-kernel launch from an ncu capture, per workload;
-# filled from profiles/ (None = not captured).
+# DRAM bytes (read + write) of one backward-kernel launch from an ncu capture of the profiler-sized cases,
+# per workload (None = not captured).
 TRAFFIC_BYTES_PER_LAUNCH = {
-    # backward kernel: 265.6 MB measured on prof_d64 (profiles/attn_bwd_kernel_prof_d64_d128.md); the traffic is
-    # per-row (inputs once, outputs once, dQ workspace once), cfg3 has 3x the rows
+    # backward kernel: 265.6 MB measured on prof_d64; the traffic is per-row (inputs once, outputs once, dQ
+    # workspace once), cfg3 has 3x the rows
     "cfg3": 3 * 265.6e6,
     "prof_d64": 265.6e6,
     # head dim 128, one-pass kernel (FOX_B200_ONE_PASS_BWD=1)
     "prof_d128": 632.8e6,
     "cfg4": 4 * 632.8e6,
-    # head dim 128, the kernel pair (profiles/attn_bwd_two_kernels_prof_d128.md); cfg4 has 4x the rows of prof_d128
+    # head dim 128, the kernel pair; cfg4 has 4x the rows of prof_d128
     ("prof_d128", "fox_attn_bwd_kv_kernel"): 380.1e6,
     ("prof_d128", "fox_attn_bwd_dq2_kernel"): 325.3e6,
     ("cfg4", "fox_attn_bwd_kv_kernel"): 4 * 380.1e6,
@@ -626,6 +713,8 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg (profiler runs)")
     ap.add_argument("--e2e-warmup", type=int, default=3, help="untimed host-to-host steps before the end-to-end leg")
+    ap.add_argument("--upstream-configs", type=int, default=2,
+                    help="rows of UPSTREAM_CONFIGS to time upstream's Triton operator with (0: skip that leg)")
     args = ap.parse_args()
     w = WORKLOADS[args.workload]
     if args.impl == "reference":

@@ -9,8 +9,9 @@ from .token_shift import TokenShift, token_shift  # noqa: F401
 from .block import FoxMLP, FoxProAttentionLayer, FoxProBlock, ShiftLinear  # noqa: F401
 from .cache import FgateCache  # noqa: F401
 from .graphs import make_graphed  # noqa: F401
+from ._lib import FoxError, check_status  # noqa: F401
 
 __all__ = ["forgetting_attention", "ForgettingAttention", "FusedGroupNormGated", "group_norm_gated", "GroupNorm",
            "group_norm", "RMSNorm", "rms_norm", "TokenShift", "token_shift", "acp_threshold_from_qk_norm",
            "acp_threshold_from_data", "seq_start_from_attention_mask", "FoxProBlock", "FoxProAttentionLayer", "FoxMLP",
-           "ShiftLinear", "FgateCache", "make_graphed", "swiglu", "swiglu_linear", "swiglu_linear_packed"]
+           "ShiftLinear", "FgateCache", "make_graphed", "swiglu", "swiglu_linear", "swiglu_linear_packed", "check_status", "FoxError"]

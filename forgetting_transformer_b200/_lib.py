@@ -18,7 +18,7 @@ from . import build as _build
 _ERRORS = {
     -1: "FOX_ERR_BAD_ARG", -2: "FOX_ERR_HEAD_DIM", -3: "FOX_ERR_ALIGNMENT", -4: "FOX_ERR_DRIVER",
     -5: "FOX_ERR_TENSORMAP", -6: "FOX_ERR_LAUNCH", -7: "FOX_ERR_DEVICE", -8: "FOX_ERR_TOO_LARGE",
-    -9: "FOX_ERR_THRESHOLD",
+    -9: "FOX_ERR_THRESHOLD", -10: "FOX_ERR_NO_MEMORY",
 }
 
 FOX_DTYPE_FP16, FOX_DTYPE_BF16 = 0, 1
@@ -148,6 +148,40 @@ def status_buffer(device: torch.device) -> torch.Tensor:
         buf = torch.zeros(4, dtype=torch.int32, device=device)
         _status[key] = buf
     return buf
+
+
+_readback = {}   # device ordinal -> (pinned int32[4], event of the last queued copy)
+
+
+def queue_status_readback(device: torch.device) -> None:
+    """Queue, on the current stream, a copy of the device's status words to pinned host memory (no
+    synchronisation); ``poll_status`` looks at it once it has landed.  Skipped while a CUDA graph is being
+    captured."""
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    buf = _status.get(key)
+    if buf is None or torch.cuda.is_current_stream_capturing():
+        return
+    slot = _readback.get(key)
+    if slot is None:
+        slot = (torch.zeros(4, dtype=torch.int32).pin_memory(), torch.cuda.Event())
+        _readback[key] = slot
+    slot[0].copy_(buf, non_blocking=True)
+    slot[1].record()
+
+
+def poll_status(device: torch.device) -> None:
+    """Non-synchronising check: raises FoxError when the last status readback that has completed shows that a
+    bounded wait inside a kernel ran out (the results of that step are incomplete)."""
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    slot = _readback.get(key)
+    if slot is None or torch.cuda.is_current_stream_capturing() or not slot[1].query():
+        return
+    vals = slot[0].tolist()
+    if vals[0] != 0:
+        slot[0].zero_()
+        _status[key].zero_()
+        raise FoxError(f"kernel wait timed out in an earlier step: site={vals[0]} cta={vals[1]} thread={vals[2]} "
+                       f"detail={vals[3]}")
 
 
 def check_status(device=None) -> None:

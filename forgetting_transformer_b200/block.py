@@ -175,13 +175,3 @@ class FoxProBlock(nn.Module):
         hidden_states = self.attn(self.attn_norm(hidden_states), attention_mask, past_key_values, layer_idx)
         hidden_states, residual = self.mlp_norm(hidden_states, residual, True)
         return residual + self.mlp(hidden_states)
-
-    def oracle_weights(self) -> dict:
-        """The block's weights under the names the CPU oracle's restatement of the block uses."""
-        a = self.attn
-        return {"attn_norm": self.attn_norm.weight, "q": a.q_proj.weight, "k": a.k_proj.linear.weight,
-                "k_shift": a.k_proj.shift_proj.weight, "v": a.v_proj.linear.weight,
-                "v_shift": a.v_proj.shift_proj.weight, "q_norm": a.q_norm.weight, "k_norm": a.k_norm.weight,
-                "fgate_w": a.fgate_proj.weight, "fgate_b": a.fgate_proj.bias, "ogate": a.ogate_proj.weight,
-                "out_norm": a.output_norm.weight, "o": a.o_proj.weight, "mlp_norm": self.mlp_norm.weight,
-                "gate": self.mlp.gate_proj.weight, "down": self.mlp.down_proj.weight}

@@ -646,8 +646,10 @@ fox_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   if (warp == kTmaWarp) tmem_dealloc(tbase, kTmemCols);
 }
 
-// Debug hook: when set, the next backward launches record clock64 stamps of CTA (0,0,0).
+#ifdef FOX_DEBUG
+// Debug builds (-DFOX_DEBUG) only: when set, the next backward launches record clock64 stamps of CTA (0,0,0).
 static long long* g_bwd_trace = nullptr;
+#endif
 
 template <int D, bool kBf16>
 static int launch_bwd(int device, cudaStream_t stream, int64_t B, int64_t H, int64_t M, int64_t N,
@@ -673,11 +675,19 @@ static int launch_bwd(int device, cudaStream_t stream, int64_t B, int64_t H, int
   constexpr int kStageSub = (D == 64) ? 2 : 1;
   constexpr int smem = (2 + kStQ + kStDO) * 128 * D * 2 + kDsBufs * 32768 + 16384 + kStageSub * 16384;
   static_assert(smem + 3072 <= 232448, "shared memory budget (tiles + static barriers/vectors rounded to 1 KiB)");
-  const bool tracing = prm.trace != nullptr;
   constexpr int kCWG = 4;  // compute warpgroups per CTA (2 was measured no faster at D=64 and slower at D=128)
+#ifdef FOX_DEBUG
+  // debug builds also carry the traced instances and the form without a dQ product (the key side before
+  // fox_attn_bwd_kv_kernel replaced it)
+  const bool tracing = prm.trace != nullptr;
   const bool nodq = prm.dq_accum == nullptr;
   auto kern = tracing ? (nodq ? fox_attn_bwd_kernel<D, kBf16, true, kCWG, true> : fox_attn_bwd_kernel<D, kBf16, true, kCWG, false>)
                       : (nodq ? fox_attn_bwd_kernel<D, kBf16, false, kCWG, true> : fox_attn_bwd_kernel<D, kBf16, false, kCWG, false>);
+#else
+  constexpr bool tracing = false, nodq = false;
+  if (prm.dq_accum == nullptr) return FOX_ERR_BAD_ARG;   // key-side-only calls go to fox_attn_bwd_kv_kernel
+  auto kern = fox_attn_bwd_kernel<D, kBf16, false, kCWG, false>;
+#endif
   const int threads = (4 * kCWG + 6) * 32;
   static bool configured[4][64] = {};
   if (device < 0 || device >= 64) return FOX_ERR_DEVICE;
@@ -700,13 +710,16 @@ int launch_bwd_kv(int device, cudaStream_t stream, bool bf16, int D, int64_t B, 
                        const float* log_lambda, const float* L, const float* delta, const int64_t* seq_start,
                        const int64_t* end_index, float sm_scale, float* dlam_col, const fox_tensor4* dk,
                        const fox_tensor4* dv, int32_t* status);
+#ifdef FOX_DEBUG
 static int g_kv_variant = 1;   // 0: the general kernel without its dQ product; 1: the key-side kernel
+#endif
 }  // namespace fox
 
-// Debug hook: which kernel serves a key-side-only call (dq_accum_zeroed == NULL).
+#ifdef FOX_DEBUG
+// Debug builds only: which kernel serves a key-side-only call (dq_accum_zeroed == NULL), and the trace buffer.
 extern "C" void fox_debug_set_kv_variant(int v) { fox::g_kv_variant = v; }
-
 extern "C" void fox_debug_set_bwd_trace(void* device_buffer) { fox::g_bwd_trace = static_cast<long long*>(device_buffer); }
+#endif
 
 extern "C" int fox_attn_bwd(int device, void* stream, int dtype, int64_t B, int64_t H, int64_t M, int64_t N,
                             int64_t D, const fox_tensor4* q, const fox_tensor4* k, const fox_tensor4* v,
@@ -719,6 +732,7 @@ extern "C" int fox_attn_bwd(int device, void* stream, int dtype, int64_t B, int6
       !log_lambda || !L || !delta || ((dq_accum_zeroed == nullptr) != (dlam_row_zeroed == nullptr)) || !dlam_col || !status)
     return FOX_ERR_BAD_ARG;
   if (B <= 0 || H <= 0 || M <= 0 || N <= 0 || M > N || H > 65535 || B > 65535) return FOX_ERR_BAD_ARG;
+  if (N > 2147483647LL) return FOX_ERR_TOO_LARGE;   // row indices are 32-bit inside the kernels (M <= N)
   if (D != 64 && D != 128) return FOX_ERR_HEAD_DIM;
   if (dtype != FOX_DTYPE_BF16 && dtype != FOX_DTYPE_FP16) return FOX_ERR_BAD_ARG;
   const fox_tensor4* outs[2] = {dk, dv};
@@ -735,13 +749,22 @@ extern "C" int fox_attn_bwd(int device, void* stream, int dtype, int64_t B, int6
   prm.dk = dk->ptr; prm.dk_sb = dk->sb; prm.dk_sh = dk->sh; prm.dk_st = dk->st;
   prm.dv = dv->ptr; prm.dv_sb = dv->sb; prm.dv_sh = dv->sh; prm.dv_st = dv->st;
   prm.status = status;
+#ifdef FOX_DEBUG
   prm.trace = g_bwd_trace;
+#else
+  prm.trace = nullptr;
+#endif
   prm.H = (int)H; prm.M = (int)M; prm.N = (int)N;
   prm.sm_scale = sm_scale;
   prm.qk_scale = sm_scale * 1.4426950408889634f;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const bool bf = dtype == FOX_DTYPE_BF16;
-  if (dq_accum_zeroed == nullptr && g_kv_variant == 1 && g_bwd_trace == nullptr)
+#ifdef FOX_DEBUG
+  const bool key_side_kernel = dq_accum_zeroed == nullptr && g_kv_variant == 1 && g_bwd_trace == nullptr;
+#else
+  const bool key_side_kernel = dq_accum_zeroed == nullptr;
+#endif
+  if (key_side_kernel)
     return launch_bwd_kv(device, st, bf, (int)D, B, H, M, N, q, k, v, d_o, log_lambda, L, delta, seq_start, end_index,
                          sm_scale, dlam_col, dk, dv, status);
   if (D == 64)

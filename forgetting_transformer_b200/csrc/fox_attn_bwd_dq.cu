@@ -45,6 +45,7 @@ extern "C" int fox_debug_read_dq_trace(long long* host) { return cudaMemcpyFromS
 #define DQSTAMP(role, ev, it)
 #endif
 
+#ifdef FOX_DEBUG   // the first form is kept in debug builds only
 enum DqWaitSite { kDqSiteQ = 41, kDqSiteK = 42, kDqSiteV = 43, kDqSiteKE = 44, kDqSiteVE = 45, kDqSiteS = 46,
                   kDqSiteDS = 47, kDqSiteDone = 48, kDqSiteNegB = 49 };
 
@@ -357,6 +358,8 @@ fox_attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
   __syncthreads();
   if (warp == kTmaWarp) tmem_dealloc(tbase, kTmemCols);
 }
+
+#endif  // FOX_DEBUG
 
 // ---------------------------------------------------------------------------------------------------------------
 // Pipelined form: one CTA per SM, 128-row KV tiles, four elementwise warpgroups (thread = query row x
@@ -723,6 +726,7 @@ fox_attn_bwd_dq2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
   if (warp == kTmaWarp) tmem_dealloc(tbase, kTmemCols);
 }
 
+#ifdef FOX_DEBUG
 static int g_dq_variant = 1;   // 0: two CTAs per SM, 64-column tiles; 1: pipelined form
 
 template <int D, bool kBf16>
@@ -752,6 +756,8 @@ static int launch_dq(int device, cudaStream_t stream, int64_t B, int64_t H, int6
   kern<<<grid, 192, smem, stream>>>(tmQ, tmK, tmV, tmDO, prm);
   return cudaGetLastError() == cudaSuccess ? FOX_OK : FOX_ERR_LAUNCH;
 }
+
+#endif  // FOX_DEBUG
 
 template <int D, bool kBf16>
 static int launch_dq2(int device, cudaStream_t stream, int64_t B, int64_t H, int64_t M, int64_t N, const fox_tensor4* q,
@@ -783,8 +789,10 @@ static int launch_dq2(int device, cudaStream_t stream, int64_t B, int64_t H, int
 
 }  // namespace fox
 
-// Debug hook: 0 selects the two-CTA form at every head dim, 1 (default) the pipelined form at D = 128.
+#ifdef FOX_DEBUG
+// Debug builds only: 0 selects the two-CTA form at every head dim, 1 (default) the pipelined form.
 extern "C" void fox_debug_set_dq_variant(int v) { fox::g_dq_variant = v; }
+#endif
 
 extern "C" int fox_attn_bwd_dq(int device, void* stream, int dtype, int64_t B, int64_t H, int64_t M, int64_t N, int64_t D,
                                const fox_tensor4* q, const fox_tensor4* k, const fox_tensor4* v, const fox_tensor4* d_o,
@@ -796,6 +804,7 @@ extern "C" int fox_attn_bwd_dq(int device, void* stream, int dtype, int64_t B, i
       !delta || !dlam_row || !status)
     return FOX_ERR_BAD_ARG;
   if (B <= 0 || H <= 0 || M <= 0 || N <= 0 || M > N || H > 65535 || B > 65535) return FOX_ERR_BAD_ARG;
+  if (N > 2147483647LL) return FOX_ERR_TOO_LARGE;   // row indices are 32-bit inside the kernels (M <= N)
   if (D != 64 && D != 128) return FOX_ERR_HEAD_DIM;
   if (dtype != FOX_DTYPE_BF16 && dtype != FOX_DTYPE_FP16) return FOX_ERR_BAD_ARG;
   if (reinterpret_cast<uintptr_t>(dq->ptr) % 16 || (dq->sb * 2) % 16 || (dq->sh * 2) % 16 || (dq->st * 2) % 16)
@@ -810,12 +819,14 @@ extern "C" int fox_attn_bwd_dq(int device, void* stream, int dtype, int64_t B, i
   prm.sm_scale = sm_scale;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const bool bf = dtype == FOX_DTYPE_BF16;
-  if (D == 64) {
-    if (g_dq_variant == 1)
-      return bf ? launch_dq2<64, true>(device, st, B, H, M, N, q, k, v, d_o, prm) : launch_dq2<64, false>(device, st, B, H, M, N, q, k, v, d_o, prm);
-    return bf ? launch_dq<64, true>(device, st, B, H, M, N, q, k, v, d_o, prm) : launch_dq<64, false>(device, st, B, H, M, N, q, k, v, d_o, prm);
+#ifdef FOX_DEBUG
+  if (g_dq_variant != 1) {
+    if (D == 64)
+      return bf ? launch_dq<64, true>(device, st, B, H, M, N, q, k, v, d_o, prm) : launch_dq<64, false>(device, st, B, H, M, N, q, k, v, d_o, prm);
+    return bf ? launch_dq<128, true>(device, st, B, H, M, N, q, k, v, d_o, prm) : launch_dq<128, false>(device, st, B, H, M, N, q, k, v, d_o, prm);
   }
-  if (g_dq_variant == 1)
-    return bf ? launch_dq2<128, true>(device, st, B, H, M, N, q, k, v, d_o, prm) : launch_dq2<128, false>(device, st, B, H, M, N, q, k, v, d_o, prm);
-  return bf ? launch_dq<128, true>(device, st, B, H, M, N, q, k, v, d_o, prm) : launch_dq<128, false>(device, st, B, H, M, N, q, k, v, d_o, prm);
+#endif
+  if (D == 64)
+    return bf ? launch_dq2<64, true>(device, st, B, H, M, N, q, k, v, d_o, prm) : launch_dq2<64, false>(device, st, B, H, M, N, q, k, v, d_o, prm);
+  return bf ? launch_dq2<128, true>(device, st, B, H, M, N, q, k, v, d_o, prm) : launch_dq2<128, false>(device, st, B, H, M, N, q, k, v, d_o, prm);
 }

@@ -552,8 +552,10 @@ fox_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 // Shapes: D=64 -> 128-row KV tiles in two stages, two softmax warpgroups with independent streams;
 // D=128 -> 128-row KV tiles in a single K and a single V buffer (K is free again once S is computed, V once
 // P V is, so the next tile's copies overlap the softmax), one softmax warpgroup, S chunks prefetched.
-// Tuning hook: 1 = D=64 with one warpgroup, 2 = D=128 with 64-row KV tiles in two stages.
+#ifdef FOX_DEBUG
+// Debug builds (-DFOX_DEBUG) only, tuning hook: 1 = D=64 with one warpgroup, 2 = D=128 with 64-row KV tiles in two stages.
 static int g_fwd_variant = 0;
+#endif
 #ifdef FOX_FWD_TRACE
 extern "C" int fox_debug_read_fwd_trace(long long* host) {
   return cudaMemcpyFromSymbol(host, g_fwd_trace, sizeof(g_fwd_trace));
@@ -598,7 +600,9 @@ static int launch_fwd_fp16(int device, cudaStream_t stream, int64_t B, int64_t H
 
 }  // namespace fox
 
+#ifdef FOX_DEBUG
 extern "C" void fox_debug_set_fwd_variant(int v) { fox::g_fwd_variant = v; }
+#endif
 
 extern "C" int fox_attn_fwd(int device, void* stream, int dtype, int64_t B, int64_t H, int64_t M, int64_t N,
                             int64_t D, const fox_tensor4* q, const fox_tensor4* k, const fox_tensor4* v,
@@ -609,6 +613,7 @@ extern "C" int fox_attn_fwd(int device, void* stream, int dtype, int64_t B, int6
   if (!q || !k || !v || !o || !q->ptr || !k->ptr || !v->ptr || !o->ptr || !log_lambda || !L || !status)
     return FOX_ERR_BAD_ARG;
   if (B <= 0 || H <= 0 || M <= 0 || N <= 0 || M > N || H > 65535 || B > 65535) return FOX_ERR_BAD_ARG;
+  if (N > 2147483647LL) return FOX_ERR_TOO_LARGE;   // row indices are 32-bit inside the kernels (M <= N)
   if (D != 64 && D != 128) return FOX_ERR_HEAD_DIM;
   if (dtype != FOX_DTYPE_BF16 && dtype != FOX_DTYPE_FP16) return FOX_ERR_BAD_ARG;
   if (reinterpret_cast<uintptr_t>(o->ptr) % 16 || (o->sb * 2) % 16 || (o->sh * 2) % 16 || (o->st * 2) % 16)
@@ -626,15 +631,17 @@ extern "C" int fox_attn_fwd(int device, void* stream, int dtype, int64_t B, int6
   prm.k_norm_max = k_norm_max;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const bool bf = dtype == FOX_DTYPE_BF16;
+#ifdef FOX_DEBUG
   const int variant = g_fwd_variant;
+#endif
 #define FOX_FWD_LAUNCH(...) \
   (bf ? launch_fwd<__VA_ARGS__>(device, st, B, H, M, N, q, k, v, prm) : launch_fwd_fp16<__VA_ARGS__>(device, st, B, H, M, N, q, k, v, prm))
   //                 D  BN  STAGES CTAS NWG PREF
-  if (D == 64) {
-    if (variant == 1) return FOX_FWD_LAUNCH(64, 128, 2, 2, 1, false);
-    return FOX_FWD_LAUNCH(64, 128, 2, 2, 2, false);
-  }
-  if (variant == 2) return FOX_FWD_LAUNCH(128, 64, 2, 2, 1, false);
+#ifdef FOX_DEBUG
+  if (D == 64 && variant == 1) return FOX_FWD_LAUNCH(64, 128, 2, 2, 1, false);
+  if (D == 128 && variant == 2) return FOX_FWD_LAUNCH(128, 64, 2, 2, 1, false);
+#endif
+  if (D == 64) return FOX_FWD_LAUNCH(64, 128, 2, 2, 2, false);
   return FOX_FWD_LAUNCH(128, 128, 1, 2, 1, true);
 #undef FOX_FWD_LAUNCH
 }

@@ -10,8 +10,18 @@
 // library image, and exposes one entry point that uses it.
 //
 // Consequences of a single fixed array, all of which the caller has to know:
-//  * every GPU that loads the library holds kScratchFloats * 4 bytes (64 MiB)
-//    until the process exits, whether or not this entry point is ever called;
+//  * a GPU holds the array's kScratchFloats * 4 bytes (64 MiB) from the moment the
+//    CUDA runtime loads this file's module on it until the process exits.  With the
+//    runtime's default lazy module loading that moment is the FIRST CALL of this
+//    entry point on the device (the address look-up below), and that first call
+//    therefore does obtain device memory and may serialise the device once: make
+//    it at start-up, on every device that will use the entry point, BEFORE the
+//    host's arena takes the rest of the GPU, with any small valid problem.  With
+//    CUDA_MODULE_LOADING=EAGER in the environment the array is placed when the
+//    library's first CUDA call initialises the device, and every GPU that uses
+//    the library holds it whether or not this entry point is ever called.  If the
+//    device has no room for the array any more, the call returns
+//    FOX_ERR_NO_MEMORY;
 //  * B*H*M*(D+1) must not exceed kScratchFloats, larger problems are refused
 //    with FOX_ERR_TOO_LARGE (use fox_attn_bwd with your own scratch);
 //  * all calls on one device share the array and it keeps whatever the last call
@@ -45,7 +55,12 @@ static int scratch_for_device(int device, float** out) {
   if (!g_scratch_ptr[device]) {
     if (cudaSetDevice(device) != cudaSuccess) return FOX_ERR_DEVICE;
     void* p = nullptr;
-    if (cudaGetSymbolAddress(&p, fox_scratch) != cudaSuccess || !p) return FOX_ERR_DEVICE;
+    const cudaError_t err = cudaGetSymbolAddress(&p, fox_scratch);
+    if (err == cudaErrorMemoryAllocation) {   // loading the module found no room for the array
+      (void)cudaGetLastError();
+      return FOX_ERR_NO_MEMORY;
+    }
+    if (err != cudaSuccess || !p) return FOX_ERR_DEVICE;
     g_scratch_ptr[device] = static_cast<float*>(p);
   }
   *out = g_scratch_ptr[device];
@@ -63,8 +78,14 @@ extern "C" int fox_attn_bwd_noalloc(int device, void* stream, int dtype, int64_t
                                     float sm_scale, const fox_tensor4* dq, const fox_tensor4* dk,
                                     const fox_tensor4* dv, float* dlam_col, float* dlog_fgate, int32_t* status) {
   using namespace fox;
-  if (B <= 0 || H <= 0 || M <= 0 || N <= 0 || M > N || D <= 0 || !dq || !dlam_col || !dlog_fgate)
+  if (B <= 0 || H <= 0 || M <= 0 || N <= 0 || M > N || !dq || !dq->ptr || !dlam_col || !dlog_fgate || !status)
     return FOX_ERR_BAD_ARG;
+  // the same range checks fox_attn_bwd makes, before any product of the sizes is formed or anything is queued
+  if (B > 65535 || H > 65535) return FOX_ERR_BAD_ARG;
+  if (D != 64 && D != 128) return FOX_ERR_HEAD_DIM;
+  if (dtype != FOX_DTYPE_BF16 && dtype != FOX_DTYPE_FP16) return FOX_ERR_BAD_ARG;
+  if (N > 2147483647LL) return FOX_ERR_TOO_LARGE;
+  if (M > kScratchFloats) return FOX_ERR_TOO_LARGE;   // (keeps B*H*M*(D+1) below 2^63)
   const int64_t rows = B * H * M;
   const int64_t need = rows * (D + 1);
   if (need > kScratchFloats) return FOX_ERR_TOO_LARGE;  // B*H*M*(D+1) floats do not fit the fixed array

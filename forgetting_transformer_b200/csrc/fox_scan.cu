@@ -326,6 +326,7 @@ extern "C" int fox_find_index(int device, void* stream, int64_t B, int64_t H, in
 extern "C" int fox_max_row_norm(int device, void* stream, int dtype, int64_t B, int64_t H, int64_t T, int64_t D,
                                 const fox_tensor4* x, float* out_zeroed) {
   if (!x || !out_zeroed || B <= 0 || H <= 0 || T <= 0) return FOX_ERR_BAD_ARG;
+  if (B > 65535 || H > 65535 || B * H > 65535) return FOX_ERR_TOO_LARGE;   // (b, h) is the grid's y index
   if (!head_dim_ok(D)) return FOX_ERR_HEAD_DIM;
   if (!aligned16(x)) return FOX_ERR_ALIGNMENT;
   if (cudaSetDevice(device) != cudaSuccess) return FOX_ERR_DEVICE;
@@ -343,6 +344,7 @@ extern "C" int fox_max_row_norm(int device, void* stream, int dtype, int64_t B, 
 extern "C" int fox_bwd_delta(int device, void* stream, int dtype, int64_t B, int64_t H, int64_t M, int64_t D,
                              const fox_tensor4* o, const fox_tensor4* d_o, float* delta) {
   if (!o || !d_o || !delta || B <= 0 || H <= 0 || M <= 0) return FOX_ERR_BAD_ARG;
+  if (B > 65535 || H > 65535 || B * H > 65535) return FOX_ERR_TOO_LARGE;   // (b, h) is the grid's y index
   if (!head_dim_ok(D)) return FOX_ERR_HEAD_DIM;
   if (!aligned16(o) || !aligned16(d_o)) return FOX_ERR_ALIGNMENT;
   if (cudaSetDevice(device) != cudaSuccess) return FOX_ERR_DEVICE;
@@ -358,6 +360,7 @@ extern "C" int fox_bwd_delta(int device, void* stream, int dtype, int64_t B, int
 extern "C" int fox_dq_convert(int device, void* stream, int dtype, int64_t B, int64_t H, int64_t M, int64_t D,
                               const float* dq_accum, float scale, const fox_tensor4* dq) {
   if (!dq_accum || !dq || B <= 0 || H <= 0 || M <= 0) return FOX_ERR_BAD_ARG;
+  if (B > 65535 || H > 65535 || B * H > 65535) return FOX_ERR_TOO_LARGE;   // (b, h) is the grid's y index
   if (!head_dim_ok(D)) return FOX_ERR_HEAD_DIM;
   if (!aligned16(dq)) return FOX_ERR_ALIGNMENT;
   if (cudaSetDevice(device) != cudaSuccess) return FOX_ERR_DEVICE;

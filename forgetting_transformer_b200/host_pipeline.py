@@ -53,7 +53,11 @@ class HostStreamedAttention:
         dev = self.dev_in[slot]
         # ---- stage 1: host -> device, once the step that last used this slot has been computed ----
         with torch.cuda.stream(self.s_in):
-            if not first_use:
+            if first_use:
+                # the buffers were just allocated on the compute stream: a block the allocator recycled may
+                # still be read by kernels queued there
+                self.s_in.wait_stream(self.s_compute)
+            else:
                 self.s_in.wait_event(self.ev_compute[slot])
             for n in _IN:
                 dev[n].copy_(host[n], non_blocking=True)

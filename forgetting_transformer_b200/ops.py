@@ -163,6 +163,7 @@ class ForgettingAttention(torch.autograd.Function):
         lib = _lib.load()
         with torch.cuda.device(q.device):
             dev = q.device
+            _lib.poll_status(dev)   # did a kernel of an earlier step give up on a wait? (no synchronisation)
             q, k, v = _tma_view(q), _tma_view(k), _tma_view(v)
             # largest key norm per (b,h): the forward kernel's bound that lets most tiles skip the row-maximum pass
             need_auto = isinstance(adaptive_threshold, str)
@@ -288,6 +289,7 @@ class ForgettingAttention(torch.autograd.Function):
                 dlog_fgate = torch.empty((B, H, N), dtype=torch.float32, device=dev)
                 _call("fox_revcumsum", lib.fox_revcumsum, dev.index, _stream(), B, H, M, N, dlam_col.data_ptr(),
                       dlam_row.data_ptr(), None, dlog_fgate.data_ptr(), None)
+                _lib.queue_status_readback(dev)
                 if _DEBUG_SYNC:
                     _lib.check_status(dev)
                 if ctx.head_dim != D:
@@ -306,6 +308,7 @@ class ForgettingAttention(torch.autograd.Function):
             dlog_fgate = torch.empty((B, H, N), dtype=torch.float32, device=dev)
             _call("fox_revcumsum", lib.fox_revcumsum, dev.index, _stream(), B, H, M, N, dlam_col.data_ptr(),
                   dlam_row.data_ptr(), None, dlog_fgate.data_ptr(), None)
+            _lib.queue_status_readback(dev)
             if _DEBUG_SYNC:
                 _lib.check_status(dev)
         if ctx.head_dim != D:

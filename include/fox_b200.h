@@ -42,6 +42,7 @@ extern "C" {
 #define FOX_ERR_DEVICE (-7)       /* cudaSetDevice failed / not an sm_100 device       */
 #define FOX_ERR_TOO_LARGE (-8)    /* size beyond a documented maximum                  */
 #define FOX_ERR_THRESHOLD (-9)    /* reserved                                          */
+#define FOX_ERR_NO_MEMORY (-10)   /* the device could not hold the library's fixed scratch array */
 
 #define FOX_DTYPE_FP16 0
 #define FOX_DTYPE_BF16 1
@@ -234,12 +235,16 @@ int fox_token_shift_bwd(int device, void* stream, int dtype, int64_t B, int64_t 
  * every buffer).  For hosts that cannot obtain device memory at call time -- the GPU was
  * handed to their own arena at start-up, or their thread may not make a call that serialises
  * the device as cudaMalloc/cudaFree do.  Same inputs as fox_attn_bwd; the fp32 dQ / query-side
- * gate-gradient scratch lives in a fixed 64 MiB array inside the library (held by every GPU
- * that loads it), so B*H*M*(D+1) must be <= fox_noalloc_scratch_floats() (2^24), else
- * FOX_ERR_TOO_LARGE.  Also finishes the job: writes dq (input dtype), dk, dv, dlam_col (B,H,N)
- * and dlog_fgate (B,H,N) fp32.  The scratch is shared by all calls on a device and is cleared
- * on `stream` at the start of each call: calls that overlap on the GPU race.  The first call on
- * a device resolves the array's address; make it before any stream capture. */
+ * gate-gradient scratch lives in a fixed 64 MiB array inside the library, so B*H*M*(D+1) must
+ * be <= fox_noalloc_scratch_floats() (2^24), else FOX_ERR_TOO_LARGE.  Also finishes the job:
+ * writes dq (input dtype), dk, dv, dlam_col (B,H,N) and dlog_fgate (B,H,N) fp32.  The scratch is
+ * shared by all calls on a device and is cleared on `stream` at the start of each call: calls
+ * that overlap on the GPU race.  The FIRST call on a device resolves the array's address, and
+ * under the CUDA runtime's default lazy module loading it is also the moment the device obtains
+ * the 64 MiB (from then until exit): make that call at start-up, before the host's arena takes
+ * the rest of the GPU and before any stream capture, or run with CUDA_MODULE_LOADING=EAGER so
+ * that the array is placed when the library first touches the device.  FOX_ERR_NO_MEMORY: the
+ * device had no room left for the array. */
 int fox_attn_bwd_noalloc(int device, void* stream, int dtype, int64_t B, int64_t H, int64_t M, int64_t N,
                          int64_t D, const fox_tensor4* q, const fox_tensor4* k, const fox_tensor4* v,
                          const fox_tensor4* d_o, const float* log_lambda, const float* L, const float* delta,

@@ -91,7 +91,7 @@ def dense_forgetting_attention(
         attention_mask = torch.arange(N, device=dev) < seq_start[:, None, None, None]
         p = torch.where(attention_mask, float("-inf"), p)
     p = torch.softmax(p.float(), dim=-1).to(q.dtype)
-    p = torch.nan_to_num(p, nan=0.0) if False else torch.where(torch.isnan(p), torch.zeros_like(p), p)
+    p = torch.where(torch.isnan(p), torch.zeros_like(p), p)   # rows with no visible key
     return torch.matmul(p, v)
 
 
@@ -272,6 +272,85 @@ def blockwise_fwd_bwd(
         dv = dv * colmask[..., None]
     return dict(out=out_lp, L=L, delta=delta, dq=dq.to(dt), dk=dk.to(dt), dv=dv.to(dt), dlog_lambda=dlam,
                 dlog_fgate=reverse_cumsum(dlam), log_lambda=lam)
+
+
+def chunked_fwd_bwd(q, k, v, log_fgate, dout, seq_start=None, sm_scale=None, start_index=None, end_index=None,
+                    BM=128, BN=128, row_chunk=1024):
+    """``blockwise_fwd_bwd`` for sequences too long to hold (M, N) matrices: the same formulas (OPS:505-693,
+    956-1344) evaluated over chunks of ``row_chunk`` query rows with explicit gradients, in one pass for
+    both the reference arithmetic (probabilities and dS rounded to the input dtype before their products,
+    delta from the rounded output) and the unrounded fp32 path.  Pruning index arrays act on (BM, BN) tiles as
+    in ``_tile_masks``; ``seq_start`` and pruning are not combined here.  M <= N.
+
+    Returns (rounded, fp32): two dicts with out, L, dq, dk, dv, dlog_fgate (out / dq / dk / dv of ``rounded``
+    in the input dtype)."""
+    B, H, M, D = q.shape
+    N = k.shape[2]
+    P = N - M
+    assert row_chunk % BM == 0 and not (seq_start is not None and (start_index is not None or end_index is not None))
+    if sm_scale is None:
+        sm_scale = 1.0 / math.sqrt(D)
+    dt = q.dtype
+    qf, kf, vf, dof = q.float(), k.float(), v.float(), dout.float()
+    lam = log_lambda(log_fgate, seq_start)
+    cols = torch.arange(N)
+    si = None if start_index is None else torch.as_tensor(start_index)
+    ei = None if end_index is None else torch.clamp(torch.as_tensor(end_index), max=M)
+    res = []
+    for rounded in (True, False):
+        res.append(dict(out=torch.zeros(B, H, M, D), L=torch.zeros(B, H, M), dq=torch.zeros(B, H, M, D),
+                        dk=torch.zeros(B, H, N, D), dv=torch.zeros(B, H, N, D), dlam=torch.zeros(B, H, N)))
+    for r0 in range(0, M, row_chunk):
+        r1 = min(M, r0 + row_chunk)
+        n1 = P + r1                                   # keys a row of this chunk may see
+        rows = torch.arange(r0, r1)
+        s = torch.matmul(qf[:, :, r0:r1], kf[:, :, :n1].transpose(2, 3)) * sm_scale
+        s += lam[:, :, P + r0:P + r1, None] - lam[:, :, None, :n1]
+        elem = ((P + rows)[:, None] >= cols[None, :n1])[None, None].expand(B, H, r1 - r0, n1)
+        if seq_start is not None:
+            elem = elem & (cols[None, None, None, :n1] >= seq_start[:, None, None, None])
+        fwd_keep = kv_keep = None
+        if si is not None:
+            lo_rows = ((si // BN) * BN)[..., rows // BM]                       # (B,H,rows)
+            fwd_keep = cols[None, None, None, :n1] >= lo_rows[..., None]
+        if ei is not None:
+            hi_cols = ei[..., cols[:n1] // BN]                                 # (B,H,n1)
+            kv_keep = ((rows // BM) * BM)[None, None, :, None] < hi_cols[:, :, None, :]
+        neg = torch.tensor(float("-inf"))
+        s_f = torch.where(elem if fwd_keep is None else (elem & fwd_keep), s, neg)
+        L = torch.logsumexp(s_f, dim=-1)
+        empty = torch.isinf(L)
+        Lz = torch.where(empty, torch.zeros_like(L), L)
+        p_f = torch.where(torch.isinf(s_f), torch.zeros_like(s_f), torch.exp(s_f - Lz[..., None]))
+        p = torch.where(elem & ~empty[..., None], torch.exp(s - Lz[..., None]), torch.zeros_like(s))
+        del s, s_f
+        dp = torch.matmul(dof[:, :, r0:r1], vf[:, :, :n1].transpose(2, 3))
+        for rounded, acc in zip((True, False), res):
+            lp = (lambda x: x.to(dt).float()) if rounded else (lambda x: x)
+            out = torch.matmul(lp(p_f), vf[:, :, :n1])
+            out_used = lp(out)
+            delta = (out_used * dof[:, :, r0:r1]).sum(-1)
+            ds = p * (dp - delta[..., None])
+            p_kv, ds_kv = (p, ds) if kv_keep is None else (p * kv_keep, ds * kv_keep)
+            ds_q = ds if fwd_keep is None else ds * fwd_keep
+            acc["out"][:, :, r0:r1] = out_used
+            acc["L"][:, :, r0:r1] = L
+            acc["dv"][:, :, :n1] += torch.matmul(lp(p_kv).transpose(2, 3), dof[:, :, r0:r1])
+            acc["dk"][:, :, :n1] += torch.matmul(lp(ds_kv).transpose(2, 3), qf[:, :, r0:r1]) * sm_scale
+            acc["dq"][:, :, r0:r1] = torch.matmul(lp(ds_q), kf[:, :, :n1]) * sm_scale
+            acc["dlam"][:, :, :n1] -= ds_kv.sum(dim=2)
+            acc["dlam"][:, :, P + r0:P + r1] += ds_q.sum(dim=3)
+            del ds, ds_q, ds_kv, p_kv, out
+    for rounded, acc in zip((True, False), res):
+        if seq_start is not None:
+            colmask = (cols[None, None, :] >= seq_start[:, None, None])[..., None]
+            acc["dk"] *= colmask
+            acc["dv"] *= colmask
+        acc["dlog_fgate"] = reverse_cumsum(acc.pop("dlam"))
+        if rounded:
+            for n_ in ("out", "dq", "dk", "dv"):
+                acc[n_] = acc[n_].to(dt)
+    return res[0], res[1]
 
 
 def pruned_tile_fraction(start_index: np.ndarray, M: int, N: int, BM: int, BN: int,

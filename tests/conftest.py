@@ -17,12 +17,28 @@ def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (sm_100a); run with -m gpu on a B200")
 
 
-GLUE_GOLDEN = "glue_refs"  # norms and token shift (tests/golden/make_golden_glue.py); the rest are attention cases
+GLUE_GOLDEN = "glue_refs"  # norms and token shift (tests/golden/make_golden_glue.py)
+INDEX_GOLDEN = "index_scans"  # pruning index arrays of upstream's scan kernels (tests/golden/make_golden_index.py)
+# every other .npz is an attention case
 
 
 def golden_names():
     names = sorted(os.path.splitext(os.path.basename(p))[0] for p in glob.glob(os.path.join(GOLDEN_DIR, "*.npz")))
-    return [n for n in names if n != GLUE_GOLDEN]
+    return [n for n in names if n not in (GLUE_GOLDEN, INDEX_GOLDEN)]
+
+
+def load_index_golden():
+    """Fixture produced by tests/golden/make_golden_index.py: upstream's _find_start_index_kernel and
+    _find_end_index_kernel launched directly (Triton's CPU interpreter) on torch.cumsum prefix sums.
+    Returns {case: dict(shape=(B,H,M,N,BM,BN), log_fgate, threshold, start_index, end_index)}."""
+    z = np.load(os.path.join(GOLDEN_DIR, INDEX_GOLDEN + ".npz"))
+    cases = {}
+    for key in z.files:
+        case, field = key.split("/")
+        cases.setdefault(case, {})[field] = z[key]
+    for rec in cases.values():
+        rec["shape"] = tuple(int(x) for x in rec["shape"])
+    return cases
 
 
 def load_glue_golden():
@@ -54,3 +70,24 @@ def golden(request):
     rec = load_golden(request.param)
     rec["name"] = request.param
     return rec
+
+
+def upstream_ops():
+    """The upstream project's own operator module (forgetting_transformer.ops.forgetting_attention) for
+    head-to-head GPU tests, or None when no copy is installed.  Looked for in $FOX_REFERENCE_SRC (the directory
+    holding the ``forgetting_transformer`` package), then in ``baseline/_ref`` of this checkout (where
+    ``pip install --target baseline/_ref <upstream>`` puts it; git-ignored).  Its three block-size hooks, which
+    upstream documents as overridable and which raise on sm_100, are pinned to 128 x 128 tiles so that the
+    pruning index arrays of both sides live on the same grid."""
+    import importlib
+    for cand in (os.environ.get("FOX_REFERENCE_SRC"), os.path.join(ROOT, "baseline", "_ref")):
+        if cand and os.path.isdir(os.path.join(cand, "forgetting_transformer")):
+            if cand not in sys.path:
+                sys.path.insert(0, cand)
+            sys.dont_write_bytecode = True
+            mod = importlib.import_module("forgetting_transformer.ops.forgetting_attention")
+            mod.get_fwd_config = lambda B, H, M, N, D, causal: (128, 128, 2, 8)
+            mod.get_bwd_kv_config = lambda B, H, M, N, D, causal: (128, 128, 2, 8)
+            mod.get_bwd_q_config = lambda B, H, M, N, D, causal: (128, 128, 2, 8)
+            return mod
+    return None

@@ -38,6 +38,15 @@ def test_library_builds_and_exports_every_declared_symbol():
     assert b"sm_100a" in lib.fox_version()
 
 
+def test_library_exports_nothing_beyond_the_header():
+    """The default build exports exactly the declared C ABI: no debug switches, no process-global hooks."""
+    import subprocess
+    path = build.build()
+    out = subprocess.run(["nm", "-D", "--defined-only", path], capture_output=True, text=True, check=True).stdout
+    exported = {line.split()[-1] for line in out.splitlines() if line.split()[-1].startswith("fox_")}
+    assert exported == set(_declared_symbols()), exported ^ set(_declared_symbols())
+
+
 def test_python_bindings_cover_every_declared_symbol():
     assert set(_declared_symbols()) <= set(_lib._SIGNATURES)
 

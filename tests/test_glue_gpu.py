@@ -13,6 +13,17 @@ from oracle import fox_oracle as orc
 pytestmark = pytest.mark.gpu
 
 
+def _oracle_weights(blk) -> dict:
+    """The block's weights under the names the CPU oracle's restatement of the block uses."""
+    a = blk.attn
+    return {"attn_norm": blk.attn_norm.weight, "q": a.q_proj.weight, "k": a.k_proj.linear.weight,
+            "k_shift": a.k_proj.shift_proj.weight, "v": a.v_proj.linear.weight,
+            "v_shift": a.v_proj.shift_proj.weight, "q_norm": a.q_norm.weight, "k_norm": a.k_norm.weight,
+            "fgate_w": a.fgate_proj.weight, "fgate_b": a.fgate_proj.bias, "ogate": a.ogate_proj.weight,
+            "out_norm": a.output_norm.weight, "o": a.o_proj.weight, "mlp_norm": blk.mlp_norm.weight,
+            "gate": blk.mlp.gate_proj.weight, "down": blk.mlp.down_proj.weight}
+
+
 def _err(a, b):
     return (a.float().cpu() - b.float().cpu()).abs().max().item()
 
@@ -164,7 +175,7 @@ def test_fox_pro_block_against_oracle(with_mask):
     torch.cuda.synchronize()
     _lib.check_status()
     xr = x.detach().float().cpu().requires_grad_()
-    w = {n: t.detach().float().cpu() for n, t in blk.oracle_weights().items()}
+    w = {n: t.detach().float().cpu() for n, t in _oracle_weights(blk).items()}
     yr = orc.fox_pro_block(xr, w, H, eps=1e-6, attention_mask=None if mask is None else mask.cpu())
     yr.backward(dy.float().cpu())
     valid = slice(None) if mask is None else mask.bool().cpu()
@@ -243,7 +254,7 @@ def test_generation_with_cache_matches_full_forward(with_mask):
     _lib.check_status()
     assert cache.get_seq_length() == T and cache.capacity(0) == 256
     assert cache[0][0].data_ptr() == ptr        # the steps wrote in place
-    w = {n: t.detach().float().cpu() for n, t in blk.oracle_weights().items()}
+    w = {n: t.detach().float().cpu() for n, t in _oracle_weights(blk).items()}
     yr = orc.fox_pro_block(x.float().cpu(), w, H, eps=1e-6, attention_mask=None if mask is None else mask.cpu())
     valid = slice(None) if mask is None else mask.bool().cpu()
     scale = yr.abs().max().item()

@@ -70,6 +70,24 @@ def test_find_start_index_bit_exact(golden):
     assert np.array_equal(si, g["start_index"].numpy())
 
 
+def test_index_scans_bit_exact_against_upstream_scan_kernels():
+    """Both carried scans (start and end index) against the arrays upstream's own scan kernels produced
+    (tests/golden/index_scans.npz): small ragged grids at several block sizes, seqlen_q < seqlen_k, and a
+    full-length T = 16384 case with the pruning stress configuration's gate distribution."""
+    from conftest import load_index_golden
+    cases = load_index_golden()
+    assert "stress_16384_128x128" in cases and len(cases) >= 7
+    for name, c in cases.items():
+        B, H, M, N, bm, bn = c["shape"]
+        lam = torch.cumsum(torch.from_numpy(c["log_fgate"]), dim=-1).numpy()
+        si = orc.find_start_index(lam, c["threshold"], M, N, bm, bn)
+        ei = orc.find_end_index(lam, c["threshold"], M, N, bm, bn)
+        assert np.array_equal(si, c["start_index"]), name
+        assert np.array_equal(ei, c["end_index"]), name
+    stress = cases["stress_16384_128x128"]
+    assert orc.pruned_tile_fraction(stress["start_index"], 16384, 16384, 128, 128) > 0.9
+
+
 def test_some_fixture_actually_prunes():
     from conftest import load_golden
     assert int(load_golden("acp_thr_m10")["start_index"].max()) >= 128

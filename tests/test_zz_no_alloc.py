@@ -24,8 +24,10 @@ ATOL_BF16, RTOL_BF16 = 2e-2, 1e-2
 
 
 def _close(a, b, atol=ATOL_BF16, rtol=RTOL_BF16):
-    err = (a.float() - b.float()).abs().max().item()
-    assert err <= atol or err <= rtol * b.float().abs().max().item(), f"max abs err {err:.3e}"
+    """Every element within atol + rtol * |element of the regular entry point's result|."""
+    err = (a.float() - b.float()).abs()
+    over = err - (atol + rtol * b.float().abs())
+    assert over.max().item() <= 0, f"max abs err {err.max().item():.3e}, {int((over > 0).sum())} elements over the bar"
 
 
 def _noalloc_backward(lib, q, k, v, o, L, lam, do, seq, end_index, sm_scale):
@@ -79,7 +81,7 @@ def test_noalloc_backward_matches_regular_entry_point(B, H, M, N, D, with_seq, t
         _close(dq, qq.grad)
         _close(dk, kk.grad)
         _close(dv, vv.grad)
-        _close(dlf, ll.grad, 2 * ATOL_BF16, RTOL_BF16)
+        _close(dlf, ll.grad)
 
 
 def test_noalloc_refuses_sizes_beyond_the_fixed_array():
