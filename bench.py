@@ -214,6 +214,75 @@ def run_reference(args, w, wname):
     _emit(line)
 
 
+def context_parallel_leg(world, rank, dev, steps=5, warmup=3):
+    """cfg5's attention (B1 T65536 H24 D64), context parallel over all ranks (strong scaling: one sequence),
+    next to the same sequence on rank 0 alone in the same run.  Device-timed, max over ranks.  Returns the
+    record for the JSON line (rank 0) or None."""
+    import torch.distributed as dist
+    import forgetting_transformer_b200 as fox
+    from forgetting_transformer_b200 import _lib, sharding
+    w = WORKLOADS["cfg5_attn"]
+    host = make_inputs(w, rank)
+    flops, _ = flops_of(w, None)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+    def timed(step_fn, n_warm, n):
+        for _ in range(n_warm):
+            step_fn()
+        dist.barrier()
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(n):
+            step_fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / n
+
+    one_gpu_ms = None
+    if rank == 0:      # the whole sequence on one GPU; the other ranks wait at the barrier inside their first timed()
+        full = {n: host[n].to(dev) for n in ("q", "k", "v", "log_fgate", "dout")}
+        fq, fk, fv, fl = [full[n].requires_grad_() for n in ("q", "k", "v", "log_fgate")]
+
+        def one_step():
+            fq.grad = fk.grad = fv.grad = fl.grad = None
+            fox.forgetting_attention(fq, fk, fv, fl, head_first=True).backward(full["dout"])
+
+        for _ in range(2):
+            one_step()
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(3):
+            one_step()
+        e1.record()
+        torch.cuda.synchronize()
+        one_gpu_ms = e0.elapsed_time(e1) / 3
+        del full, fq, fk, fv, fl
+        torch.cuda.empty_cache()
+    tc = w["T"] // (2 * world)
+    c0, c1 = sharding.zigzag_chunks(world, rank)
+    loc = {n: torch.cat([host[n][:, :, c0 * tc:(c0 + 1) * tc], host[n][:, :, c1 * tc:(c1 + 1) * tc]], dim=2).to(dev)
+           for n in ("q", "k", "v", "log_fgate", "dout")}
+    q, k, v, lf = [loc[n].requires_grad_() for n in ("q", "k", "v", "log_fgate")]
+
+    def cp_step():
+        q.grad = k.grad = v.grad = lf.grad = None
+        sharding.context_parallel_attention(q, k, v, lf).backward(loc["dout"])
+
+    ms = timed(cp_step, warmup, steps)
+    _lib.check_status()
+    t = torch.tensor([ms], dtype=torch.float64, device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    if rank != 0:
+        return None
+    return {"workload": "cfg5_attn", "description": DESCR["cfg5_attn"], "scaling": "strong", "n_gpus": world,
+            "ms_per_step": ms, "tflops": flops / (ms * 1e-3) / 1e12, "one_gpu_ms": one_gpu_ms,
+            "one_gpu_tflops": flops / (one_gpu_ms * 1e-3) / 1e12, "speedup": one_gpu_ms / ms,
+            "efficiency": one_gpu_ms / (world * ms), "steps": steps, "warmup": warmup,
+            "exchange": "two waves of NCCL all-gathers of K, V (sequence-major staging) and the log gates, "
+                        "reduce-scatter of their gradients; no collective inside the kernels"}
+
+
 # --------------------------------------------------------------------------- upstream's Triton operator
 # Block configurations tried for upstream's three kernels, (BLOCK_M, BLOCK_N, num_stages, num_warps) as
 # (forward, key side of the backward, query side of the backward) by head dim.  Upstream's own table stops at
@@ -420,6 +489,11 @@ def run_ours(args, w, wname):
         ms_g = e0.elapsed_time(e1) / n_g
         graphed = {"ms_per_step": ms_g, "value": flops / (ms_g * 1e-3) / 1e12, "unit": UNIT, "steps": n_g,
                    "speedup_over_eager_launches": ms_per_step / ms_g}
+
+    # ---- the context-parallel configuration (cfg5's attention) beside the sharded one, whenever N > 1 ----
+    cp_leg = None
+    if world > 1 and not cp and not args.no_cp:
+        cp_leg = context_parallel_leg(world, rank, dev)
 
     # ---- upstream's Triton operator on the same tensors (single GPU, not context parallel) ----
     upstream = None
@@ -629,8 +703,8 @@ def run_ours(args, w, wname):
             "config": {"workload": wname, "description": DESCR[wname], "per_gpu_batch": w["B"],
                        "global_batch": w["B"] * (1 if cp else world), "seq_len": w["T"], "heads": w["H"],
                        "head_dim": w["D"],
-                       "sharding": ("context parallel: zig-zag sequence chunks, NCCL all-gather of K, V and log gates, "
-                                    "reduce-scatter of their gradients") if cp else
+                       "sharding": ("context parallel: zig-zag sequence chunks, two waves of NCCL all-gathers of K, V "
+                                    "and log gates, reduce-scatter of their gradients") if cp else
                                    "independent (batch, head) units per rank, no collective",
                        "l2": "inputs (>=400 MB per step) larger than the 126 MB L2; no explicit flush",
                        "algorithmic_flops_per_step_per_gpu": flops,
@@ -642,6 +716,8 @@ def run_ours(args, w, wname):
             "gpu_launches": launches,
             "clocks": clocks,
         }
+        if cp_leg is not None:
+            line["context_parallel"] = cp_leg
         if upstream is not None:
             line["upstream_triton"] = upstream
         if graphed is not None:
@@ -713,6 +789,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg (profiler runs)")
     ap.add_argument("--e2e-warmup", type=int, default=3, help="untimed host-to-host steps before the end-to-end leg")
+    ap.add_argument("--no-cp", action="store_true", help="N > 1: skip the context-parallel leg (cfg5's attention)")
     ap.add_argument("--upstream-configs", type=int, default=2,
                     help="rows of UPSTREAM_CONFIGS to time upstream's Triton operator with (0: skip that leg)")
     args = ap.parse_args()

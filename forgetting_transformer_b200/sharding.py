@@ -10,12 +10,17 @@ Two schemes, neither present upstream (which only knows data-parallel training):
 
 * context parallel for long sequences -- the sequence is cut into 2P chunks and rank r owns
   chunks r and 2P-1-r ("zig-zag": causal work is balanced).  Keys, values and log gates are
-  all-gathered once; each rank then calls the ordinary operator on its query chunk against the
-  key prefix that chunk may attend to -- exactly the operator's ``seqlen_q <= seqlen_k``
-  contract (queries are the last rows) -- and the gradients of the gathered tensors are
-  reduce-scattered back to their owners.  Rows are complete on their owner, so no partial
+  gathered into a sequence-major staging buffer (T, B, H, D) in two waves of asynchronous
+  collectives: the lower halves (chunks 0..P-1, one per rank, landing in natural order), after
+  which a rank's lower query chunk can already run, and the upper halves (chunks P..2P-1),
+  which travel while that first call computes.  Each query chunk is one call of the ordinary
+  operator against the key prefix it may attend to -- exactly the operator's
+  ``seqlen_q <= seqlen_k`` contract (queries are the last rows), reading the staging buffer
+  through strided views, no reordering copies.  Rows are complete on their owner, so no partial
   (max, sum, out) triples have to travel; the log-gate prefix is recomputed from the gathered
-  gates by the operator's own prefix-sum kernel.
+  gates by the operator's own prefix-sum kernel.  Backward: the upper chunk's call first, the
+  reduce-scatter of the upper halves' key / value / gate gradients runs under the lower chunk's
+  backward, the lower halves follow.  Tiles are only ever read from this GPU's own memory.
 """
 from __future__ import annotations
 
@@ -25,7 +30,7 @@ import torch
 import torch.distributed as dist
 
 __all__ = ["unit_slice", "shard_batch_heads", "zigzag_chunks", "ContextParallelAttention",
-           "context_parallel_attention"]
+           "context_parallel_attention", "context_parallel_threshold"]
 
 
 # ----------------------------------------------------------------------------- batch x head
@@ -63,92 +68,177 @@ def zigzag_chunks(world: int, rank: int) -> Tuple[int, int]:
     return rank, 2 * world - 1 - rank
 
 
-class _GatherSeq(torch.autograd.Function):
-    """All-gather along the sequence axis in zig-zag chunk order -> full sequence in natural
-    order; backward reduce-scatters (sums) the gradient back to the chunk owners."""
+def _reduce_scatter(out: torch.Tensor, inp: torch.Tensor, group, async_op: bool):
+    """reduce_scatter_tensor; gloo (CPU tests) has none: all-reduce and keep this rank's slab."""
+    if dist.get_backend(group) == "gloo":
+        dist.all_reduce(inp, group=group)
+        out.copy_(inp.view(dist.get_world_size(group), -1)[dist.get_rank(group)].view_as(out))
+        return None
+    return dist.reduce_scatter_tensor(out, inp, op=dist.ReduceOp.SUM, group=group, async_op=async_op)
+
+
+def _wait(work):
+    if work is not None:
+        work.wait()
+
+
+def _seq_major(x: torch.Tensor) -> torch.Tensor:
+    """(B, H, t, ...) -> contiguous (t, B, H, ...)."""
+    return x.movedim(2, 0).contiguous()
+
+
+def _head_first(x: torch.Tensor) -> torch.Tensor:
+    """View of a sequence-major (t, B, H, ...) buffer as (B, H, t, ...)."""
+    return x.movedim(0, 2)
+
+
+class _ContextParallel(torch.autograd.Function):
+    """Forward and backward of the zig-zag context-parallel attention as one autograd node, so that the
+    collectives, the two operator calls per direction and their overlap are scheduled by hand."""
 
     @staticmethod
-    def forward(ctx, local: torch.Tensor, seq_dim: int, group):
-        world = dist.get_world_size(group)
-        rank = dist.get_rank(group)
-        ctx.seq_dim, ctx.group, ctx.world, ctx.rank = seq_dim, group, world, rank
-        local = local.contiguous()
-        parts = [torch.empty_like(local) for _ in range(world)]
-        dist.all_gather(parts, local, group=group)
-        tc = local.shape[seq_dim] // 2
-        chunks: List[Optional[torch.Tensor]] = [None] * (2 * world)
-        for r, p in enumerate(parts):
-            a, b = zigzag_chunks(world, r)
-            chunks[a] = p.narrow(seq_dim, 0, tc)
-            chunks[b] = p.narrow(seq_dim, tc, tc)
-        return torch.cat(chunks, dim=seq_dim)
+    def forward(ctx, q, k, v, log_fgate, seq_start, sm_scale, threshold, group, attn_fn):
+        world, rank = dist.get_world_size(group), dist.get_rank(group)
+        B, H, t2, D = q.shape
+        tc = t2 // 2
+        P = world
+        T = 2 * P * tc
+        lo_c, hi_c = zigzag_chunks(P, rank)
+        dev, dt = k.device, k.dtype
+        # sequence-major staging: chunk j is the contiguous slab [j*tc, (j+1)*tc)
+        Kf = torch.empty((T, B, H, D), dtype=dt, device=dev)
+        Vf = torch.empty((T, B, H, D), dtype=dt, device=dev)
+        Gf = torch.empty((T, B, H), dtype=log_fgate.dtype, device=dev)
+        up_k = torch.empty((P, tc, B, H, D), dtype=dt, device=dev)
+        up_v = torch.empty((P, tc, B, H, D), dtype=dt, device=dev)
+        g_all = torch.empty((P, 2, tc, B, H), dtype=log_fgate.dtype, device=dev)
+        k_sm, v_sm = _seq_major(k), _seq_major(v)                 # (2tc, B, H, D): lower chunk, upper chunk
+        g_sm = _seq_major(log_fgate).view(2, tc, B, H)
+        # wave 1: gates and the lower halves (rank r owns chunk r: they land in natural order);
+        # wave 2: the upper halves (rank r owns chunk 2P-1-r: reversed afterwards)
+        w_g = dist.all_gather_into_tensor(g_all.view(P * 2, tc, B, H), g_sm, group=group, async_op=True)
+        w_k1 = dist.all_gather_into_tensor(Kf[:P * tc], k_sm[:tc], group=group, async_op=True)
+        w_v1 = dist.all_gather_into_tensor(Vf[:P * tc], v_sm[:tc], group=group, async_op=True)
+        w_k2 = dist.all_gather_into_tensor(up_k.view(P * tc, B, H, D), k_sm[tc:], group=group, async_op=True)
+        w_v2 = dist.all_gather_into_tensor(up_v.view(P * tc, B, H, D), v_sm[tc:], group=group, async_op=True)
+
+        def call(q_c, n):
+            """The operator on one query chunk against keys [0, n), on views of the staging buffers."""
+            leaves = [q_c.detach().requires_grad_(), _head_first(Kf[:n]).detach().requires_grad_(),
+                      _head_first(Vf[:n]).detach().requires_grad_(), _head_first(Gf[:n]).detach().requires_grad_()]
+            ss = None if seq_start is None else torch.clamp(seq_start, max=n)
+            with torch.enable_grad():
+                out = attn_fn(*leaves, head_first=True, seq_start=ss, sm_scale=sm_scale,
+                              adaptive_threshold=threshold)
+            return out, leaves
+
+        _wait(w_g)
+        Gf[:P * tc].view(P, tc, B, H).copy_(g_all[:, 0])
+        Gf[P * tc:].view(P, tc, B, H).copy_(g_all[:, 1].flip(0))
+        _wait(w_k1)
+        _wait(w_v1)
+        n_lo, n_hi = (lo_c + 1) * tc, (hi_c + 1) * tc
+        out_lo, leaves_lo = call(q[:, :, :tc], n_lo)              # runs while wave 2 travels
+        _wait(w_k2)
+        _wait(w_v2)
+        # (written through aliases with their own version counter: the lower call's saved views share the
+        # allocation but cover only rows below P*tc, which stay as they are)
+        Kf.data[P * tc:].view(P, tc, B, H, D).copy_(up_k.flip(0))
+        Vf.data[P * tc:].view(P, tc, B, H, D).copy_(up_v.flip(0))
+        out_hi, leaves_hi = call(q[:, :, tc:], n_hi)
+        ctx.graph = (out_lo, leaves_lo, out_hi, leaves_hi)
+        ctx.geom = (group, P, rank, B, H, D, tc)
+        return torch.cat([out_lo.detach(), out_hi.detach()], dim=2)
 
     @staticmethod
-    def backward(ctx, grad_full: torch.Tensor):
-        world, seq_dim = ctx.world, ctx.seq_dim
-        tc = grad_full.shape[seq_dim] // (2 * world)
-        inputs = []
-        for r in range(world):
-            a, b = zigzag_chunks(world, r)
-            inputs.append(torch.cat([grad_full.narrow(seq_dim, a * tc, tc), grad_full.narrow(seq_dim, b * tc, tc)],
-                                    dim=seq_dim).contiguous())
-        out = torch.empty_like(inputs[ctx.rank])
-        dist.reduce_scatter(out, inputs, op=dist.ReduceOp.SUM, group=ctx.group)
-        return out, None, None
+    def backward(ctx, dout):
+        out_lo, leaves_lo, out_hi, leaves_hi = ctx.graph
+        group, P, rank, B, H, D, tc = ctx.geom
+        ctx.graph = None
+        n_lo, n_hi = leaves_lo[1].shape[2], leaves_hi[1].shape[2]
+        dev = dout.device
+
+        def seq_major_mem(g):
+            """Gradient of a (B, H, n, ...) view of sequence-major memory, as (n, B, H, ...) contiguous."""
+            g = g.movedim(2, 0)
+            return g if g.is_contiguous() else g.contiguous()
+
+        # upper chunk first: only it contributes to the upper halves, whose reduce-scatter then runs
+        # under the lower chunk's backward
+        dq_hi, dk_hi, dv_hi, dg_hi = torch.autograd.grad(out_hi, leaves_hi, dout[:, :, tc:])
+        dk_hi, dv_hi, dg_hi = seq_major_mem(dk_hi), seq_major_mem(dv_hi), seq_major_mem(dg_hi)
+        mine, works = {}, []
+        for name, g_hi in (("k", dk_hi), ("v", dv_hi), ("g", dg_hi)):
+            # slab i of the input belongs to rank i, i.e. to chunk 2P-1-i; this rank saw chunks up to 2P-1-rank
+            tail = g_hi.shape[1:]
+            inp = torch.zeros((P, tc) + tail, dtype=g_hi.dtype, device=dev)
+            inp[rank:].copy_(g_hi[P * tc:].view((P - rank, tc) + tail).flip(0))
+            out = torch.empty((tc,) + tail, dtype=g_hi.dtype, device=dev)
+            works.append(_reduce_scatter(out, inp, group, True))
+            mine[name + "_hi"] = out
+        dq_lo, dk_lo, dv_lo, dg_lo = torch.autograd.grad(out_lo, leaves_lo, dout[:, :, :tc])
+        for name, g_hi, g_lo in (("k", dk_hi, dk_lo), ("v", dv_hi, dv_lo), ("g", dg_hi, dg_lo)):
+            g_hi[:n_lo] += seq_major_mem(g_lo)
+            out = torch.empty((tc,) + g_hi.shape[1:], dtype=g_hi.dtype, device=dev)
+            works.append(_reduce_scatter(out, g_hi[:P * tc], group, True))     # chunk j belongs to rank j
+            mine[name + "_lo"] = out
+        for w in works:
+            _wait(w)
+        dk = _head_first(torch.cat([mine["k_lo"], mine["k_hi"]], dim=0))
+        dv = _head_first(torch.cat([mine["v_lo"], mine["v_hi"]], dim=0))
+        dg = _head_first(torch.cat([mine["g_lo"], mine["g_hi"]], dim=0))
+        dq = torch.cat([dq_lo, dq_hi], dim=2)
+        return dq, dk, dv, dg, None, None, None, None, None
 
 
-def _reduce_scatter_fallback(out, inputs, group):  # gloo has no reduce_scatter: all_reduce + pick
-    stacked = torch.stack(inputs)
-    dist.all_reduce(stacked, group=group)
-    out.copy_(stacked[dist.get_rank(group)])
+def context_parallel_threshold(q, k, sm_scale: float, seq_len: int, group, max_row_norm: Callable,
+                               tolerance: float = -10.0) -> torch.Tensor:
+    """``adaptive_threshold="auto"`` of the unsharded operator for a sharded sequence: the largest row norms
+    of q and k over ALL ranks' rows (all-reduce MAX of the local maxima), rounded to the input dtype as
+    ``torch.linalg.vector_norm`` of a 16-bit tensor rounds them, then upstream's expression
+    (src/forgetting_transformer/ops/forgetting_attention.py:95-102) with the full sequence length."""
+    import math
+    nq, nk = max_row_norm(q).float(), max_row_norm(k).float()
+    both = torch.stack([nq, nk])
+    dist.all_reduce(both, op=dist.ReduceOp.MAX, group=group)
+    bound = both[0].to(q.dtype) * both[1].to(q.dtype) * sm_scale
+    return (-(2 * bound + math.log(seq_len)) + tolerance).float()
 
 
-class _GatherSeqGloo(_GatherSeq):
-    @staticmethod
-    def backward(ctx, grad_full: torch.Tensor):
-        world, seq_dim = ctx.world, ctx.seq_dim
-        tc = grad_full.shape[seq_dim] // (2 * world)
-        inputs = []
-        for r in range(world):
-            a, b = zigzag_chunks(world, r)
-            inputs.append(torch.cat([grad_full.narrow(seq_dim, a * tc, tc), grad_full.narrow(seq_dim, b * tc, tc)],
-                                    dim=seq_dim).contiguous())
-        out = torch.empty_like(inputs[ctx.rank])
-        _reduce_scatter_fallback(out, inputs, ctx.group)
-        return out, None, None
-
-
-def context_parallel_attention(q, k, v, log_fgate, *, group=None, sm_scale: Optional[float] = None,
-                               adaptive_threshold=None, attn_fn: Optional[Callable] = None):
+def context_parallel_attention(q, k, v, log_fgate, *, group=None, seq_start: Optional[torch.Tensor] = None,
+                               sm_scale: Optional[float] = None, adaptive_threshold=None,
+                               attn_fn: Optional[Callable] = None, max_row_norm: Optional[Callable] = None):
     """Head-first forgetting attention over a sequence sharded in zig-zag chunks.
 
     Every rank passes its local shard: q, k, v (B, H, 2*Tc, D) and log_fgate (B, H, 2*Tc), the
     concatenation of its two chunks (``zigzag_chunks``) of a sequence of length 2*world*Tc.
     Returns the local shard of the output, same layout; differentiable (gradients of k, v and
-    log_fgate are summed over ranks and returned to the owners).  ``seq_start`` is not supported
-    here (left padding belongs to the first chunk only; pad on the host instead).
+    log_fgate are summed over ranks and returned to the owners).
 
-    ``attn_fn(q, k, v, log_fgate, head_first=True, sm_scale=..., adaptive_threshold=...)``
-    defaults to the CUDA operator; the CPU tests inject the oracle.
+    ``seq_start`` (B,) counts in positions of the whole sequence (left padding), the same tensor on
+    every rank.  ``adaptive_threshold="auto"`` is evaluated once from the row norms of all ranks, so
+    it is the threshold the unsharded call would use; a float or a (B, H)-broadcastable tensor is
+    passed through.
+
+    ``attn_fn(q, k, v, log_fgate, head_first=True, seq_start=..., sm_scale=..., adaptive_threshold=...)``
+    defaults to the CUDA operator and ``max_row_norm(x) -> (B, H)`` to its row-norm kernel; the CPU
+    tests inject the oracle.
     """
     if attn_fn is None:
         from .ops import forgetting_attention as attn_fn
     group = group if group is not None else dist.group.WORLD
     world = dist.get_world_size(group)
-    rank = dist.get_rank(group)
-    gather = _GatherSeqGloo if dist.get_backend(group) == "gloo" else _GatherSeq
     tc = q.shape[2] // 2
     assert q.shape[2] == 2 * tc and k.shape[2] == 2 * tc and log_fgate.shape[2] == 2 * tc
-    k_full = gather.apply(k, 2, group)
-    v_full = gather.apply(v, 2, group)
-    lf_full = gather.apply(log_fgate, 2, group)
-    outs = []
-    for idx, chunk in enumerate(zigzag_chunks(world, rank)):
-        n = (chunk + 1) * tc  # keys this chunk may see: everything up to and including itself
-        outs.append(attn_fn(q[:, :, idx * tc:(idx + 1) * tc], k_full[:, :, :n], v_full[:, :, :n],
-                            lf_full[:, :, :n], head_first=True, sm_scale=sm_scale,
-                            adaptive_threshold=adaptive_threshold))
-    return torch.cat(outs, dim=2)
+    if sm_scale is None:
+        sm_scale = q.shape[-1] ** -0.5
+    if isinstance(adaptive_threshold, str):
+        assert adaptive_threshold == "auto", f'adaptive_threshold must be either the string "auto", a float, or a Tensor, but got {adaptive_threshold}.'
+        if max_row_norm is None:
+            from .ops import max_row_norm
+        with torch.no_grad():
+            adaptive_threshold = context_parallel_threshold(q, k, sm_scale, 2 * world * tc, group, max_row_norm)
+    return _ContextParallel.apply(q, k, v, log_fgate, seq_start, sm_scale, adaptive_threshold, group, attn_fn)
 
 
 class ContextParallelAttention(torch.nn.Module):
@@ -158,6 +248,7 @@ class ContextParallelAttention(torch.nn.Module):
         super().__init__()
         self.group, self.attn_fn = group, attn_fn
 
-    def forward(self, q, k, v, log_fgate, sm_scale=None, adaptive_threshold=None):
-        return context_parallel_attention(q, k, v, log_fgate, group=self.group, sm_scale=sm_scale,
-                                          adaptive_threshold=adaptive_threshold, attn_fn=self.attn_fn)
+    def forward(self, q, k, v, log_fgate, seq_start=None, sm_scale=None, adaptive_threshold=None):
+        return context_parallel_attention(q, k, v, log_fgate, group=self.group, seq_start=seq_start,
+                                          sm_scale=sm_scale, adaptive_threshold=adaptive_threshold,
+                                          attn_fn=self.attn_fn)

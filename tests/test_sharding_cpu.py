@@ -38,8 +38,15 @@ def test_shard_batch_heads_views_and_metadata():
     assert torch.cat([p[2] for p in pieces]).flatten().tolist() == [-1, -2, -3, -1, -2, -3]
 
 
-def _oracle_attn(q, k, v, lf, head_first=True, sm_scale=None, adaptive_threshold=None):
-    return orc.dense_forgetting_attention(q, k, v, lf, None, sm_scale)
+def _oracle_attn(q, k, v, lf, head_first=True, seq_start=None, sm_scale=None, adaptive_threshold=None):
+    _oracle_attn.thresholds.append(adaptive_threshold)
+    if seq_start is not None:                  # the operator zeroes the gates left of seq_start (OPS:117-125)
+        mask = torch.arange(lf.shape[-1])[None, None, :] < seq_start[:, None, None]
+        lf = torch.where(mask, torch.zeros_like(lf), lf)
+    return orc.dense_forgetting_attention(q, k, v, lf, seq_start, sm_scale)
+
+
+_oracle_attn.thresholds = []
 
 
 def _free_port():
@@ -56,26 +63,40 @@ def _cp_worker(rank, world, port, ret):
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
         torch.manual_seed(0)
-        B, H, D = 1, 2, 16
+        B, H, D = 2, 2, 16
         tc = 8
         T = 2 * world * tc
         q, k, v, do = [torch.randn(B, H, T, D, dtype=torch.float64) for _ in range(4)]
         lf = torch.nn.functional.logsigmoid(torch.randn(B, H, T, dtype=torch.float64))
-        # unsharded reference
-        ro, rdq, rdk, rdv, rdl = orc.dense_fwd_bwd(q, k, v, lf, do)
         a, b = sharding.zigzag_chunks(world, rank)
         idx = torch.cat([torch.arange(a * tc, (a + 1) * tc), torch.arange(b * tc, (b + 1) * tc)])
-        ql, kl, vl, ll = [t.index_select(2, idx).clone().requires_grad_() for t in (q, k, v, lf)]
-        out = sharding.context_parallel_attention(ql, kl, vl, ll, attn_fn=_oracle_attn)
-        out.backward(do.index_select(2, idx))
-        errs = [
-            (out - ro.index_select(2, idx)).abs().max().item(),
-            (ql.grad - rdq.index_select(2, idx)).abs().max().item(),
-            (kl.grad - rdk.index_select(2, idx)).abs().max().item(),
-            (vl.grad - rdv.index_select(2, idx)).abs().max().item(),
-            (ll.grad - rdl.index_select(2, idx)).abs().max().item(),
-        ]
-        ret[rank] = max(errs)
+        worst = 0.0
+        # no padding; left padding inside the first chunk and beyond it (whole lower chunks of rank 0 are empty)
+        for seq in (None, torch.tensor([3, tc + 5])):
+            ro, rdq, rdk, rdv, rdl = orc.dense_fwd_bwd(q, k, v, lf, do, seq, mask_gates=True)
+            ql, kl, vl, ll = [t.index_select(2, idx).clone().requires_grad_() for t in (q, k, v, lf)]
+            out = sharding.context_parallel_attention(ql, kl, vl, ll, seq_start=seq, attn_fn=_oracle_attn)
+            out.backward(do.index_select(2, idx))
+            errs = [
+                (out - ro.index_select(2, idx)).abs().max().item(),
+                (ql.grad - rdq.index_select(2, idx)).abs().max().item(),
+                (kl.grad - rdk.index_select(2, idx)).abs().max().item(),
+                (vl.grad - rdv.index_select(2, idx)).abs().max().item(),
+            ]
+            # left of seq_start the dense formulation's gate gradient is rounding residue only
+            keep = torch.ones(B, H, T, dtype=torch.bool) if seq is None else (
+                torch.arange(T)[None, None, :] >= seq[:, None, None]).expand(B, H, T)
+            errs.append(((ll.grad - rdl.index_select(2, idx)) * keep.index_select(2, idx)).abs().max().item())
+            worst = max(worst, *errs)
+        # "auto": one threshold from the row norms of every rank's rows = the unsharded call's
+        _oracle_attn.thresholds.clear()
+        row_norm_max = lambda x: torch.linalg.vector_norm(x, dim=-1).max(dim=-1).values
+        qb, kb, vb = [t.detach().bfloat16() for t in (ql, kl, vl)]   # the norms are taken in the input dtype
+        sharding.context_parallel_attention(qb, kb, vb, ll.detach().float(), adaptive_threshold="auto",
+                                            attn_fn=_oracle_attn, max_row_norm=row_norm_max)
+        ref_thr = orc.auto_threshold(q.bfloat16(), k.bfloat16(), D ** -0.5)
+        same = all(torch.equal(t.double(), ref_thr.double()) for t in _oracle_attn.thresholds)
+        ret[rank] = (worst, same and len(_oracle_attn.thresholds) == 2)
     finally:
         dist.destroy_process_group()
 
@@ -87,4 +108,5 @@ def test_context_parallel_matches_unsharded_world2():
     ret = mgr.dict()
     mp.spawn(_cp_worker, args=(world, _free_port(), ret), nprocs=world, join=True)
     assert len(ret) == world
-    assert max(ret.values()) < 1e-5  # the dense formulation does its softmax in fp32
+    assert max(w for w, _ in ret.values()) < 1e-5  # the dense formulation does its softmax in fp32
+    assert all(same for _, same in ret.values())

@@ -58,30 +58,35 @@ def _free_port():
 def _cp_worker(rank, world, port, ret):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
     torch.cuda.set_device(rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
     try:
-        B, H, D, tc = 1, 2, 64, 256
+        B, H, D, tc = 2, 2, 64, 256
         T = 2 * world * tc
         q, k, v, lf, do = [t.cuda() for t in _inputs(B, H, T, D, seed=3)]
-        qq, kk, vv, ll = [t.detach().clone().requires_grad_() for t in (q, k, v, lf)]
-        full = fox.forgetting_attention(qq, kk, vv, ll, head_first=True)
-        full.backward(do)
         a, b = sharding.zigzag_chunks(world, rank)
         idx = torch.cat([torch.arange(a * tc, (a + 1) * tc), torch.arange(b * tc, (b + 1) * tc)]).cuda()
-        ql, kl, vl, l_l = [t.index_select(2, idx).contiguous().requires_grad_() for t in (q, k, v, lf)]
-        out = sharding.context_parallel_attention(ql, kl, vl, l_l)
-        out.backward(do.index_select(2, idx).contiguous())
-        torch.cuda.synchronize()
-        _lib.check_status()
-        errs = [
-            (out.float() - full.detach().index_select(2, idx).float()).abs().max().item(),
-            (ql.grad.float() - qq.grad.index_select(2, idx).float()).abs().max().item(),
-            (kl.grad.float() - kk.grad.index_select(2, idx).float()).abs().max().item(),
-            (vl.grad.float() - vv.grad.index_select(2, idx).float()).abs().max().item(),
-            (l_l.grad - ll.grad.index_select(2, idx)).abs().max().item() / max(1.0, ll.grad.abs().max().item()),
-        ]
-        ret[rank] = errs
+        results = {}
+        # plain; left padding inside and beyond the first chunk; pruning with the "auto" threshold
+        for name, seq, thr in (("plain", None, None), ("seq_start", torch.tensor([40, tc + 77]).cuda(), None),
+                               ("auto", None, "auto")):
+            qq, kk, vv, ll = [t.detach().clone().requires_grad_() for t in (q, k, v, lf)]
+            full = fox.forgetting_attention(qq, kk, vv, ll, head_first=True, seq_start=seq, adaptive_threshold=thr)
+            full.backward(do)
+            ql, kl, vl, l_l = [t.index_select(2, idx).contiguous().requires_grad_() for t in (q, k, v, lf)]
+            out = sharding.context_parallel_attention(ql, kl, vl, l_l, seq_start=seq, adaptive_threshold=thr)
+            out.backward(do.index_select(2, idx).contiguous())
+            torch.cuda.synchronize()
+            _lib.check_status()
+            results[name] = [
+                (out.float() - full.detach().index_select(2, idx).float()).abs().max().item(),
+                (ql.grad.float() - qq.grad.index_select(2, idx).float()).abs().max().item(),
+                (kl.grad.float() - kk.grad.index_select(2, idx).float()).abs().max().item(),
+                (vl.grad.float() - vv.grad.index_select(2, idx).float()).abs().max().item(),
+                (l_l.grad - ll.grad.index_select(2, idx)).abs().max().item() / max(1.0, ll.grad.abs().max().item()),
+            ]
+        ret[rank] = results
     finally:
         dist.destroy_process_group()
 
@@ -93,6 +98,8 @@ def test_context_parallel_over_nccl_matches_single_gpu():
     ret = mgr.dict()
     mp.spawn(_cp_worker, args=(world, _free_port(), ret), nprocs=world, join=True)
     assert len(ret) == world
-    for errs in ret.values():
-        # k/v/gate gradients are sums of bf16 partial gradients from two ranks: one more rounding than the full call
-        assert errs[0] < 2e-2 and errs[1] < 3e-2 and errs[2] < 6e-2 and errs[3] < 6e-2 and errs[4] < 3e-2, errs
+    for results in ret.values():
+        for name, errs in results.items():
+            # k/v/gate gradients are sums of bf16 partial gradients from two calls and two ranks: more roundings
+            # than the single call makes
+            assert errs[0] < 2e-2 and errs[1] < 3e-2 and errs[2] < 6e-2 and errs[3] < 6e-2 and errs[4] < 3e-2, (name, errs)
