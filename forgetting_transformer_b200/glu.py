@@ -71,6 +71,16 @@ class SwiGLUFunction(torch.autograd.Function):
         return dx.reshape(ctx.shape), dy.reshape(ctx.shape)
 
 
+def _linear_params(weight, bias):
+    """Under autocast the product runs in the autocast dtype (upstream wraps these functions in
+    custom_fwd / custom_bwd, glu_linear.py:116-119): the parameters are cast once here, so that forward and
+    backward (where autocast is off) multiply in the same dtype; their gradients go back in the parameters' own."""
+    if torch.is_autocast_enabled("cuda"):
+        dt = torch.get_autocast_dtype("cuda")
+        return weight.to(dt), None if bias is None else bias.to(dt)
+    return weight, bias
+
+
 class SwiGLULinearFunction(torch.autograd.Function):
     """(swish(x) * y) W^T + b without keeping the product (glu_linear.py:116-146)."""
 
@@ -80,6 +90,8 @@ class SwiGLULinearFunction(torch.autograd.Function):
         with torch.cuda.device(x.device):
             x2, y2 = _rows(x), _rows(y)
             z = _fwd(x2, y2)
+            ctx.param_dtypes = (weight.dtype, None if bias is None else bias.dtype)
+            weight, bias = _linear_params(weight, bias)
             out = F.linear(z.to(weight.dtype), weight, bias)
         ctx.save_for_backward(x2, y2, weight)
         ctx.linear_bias_is_none = bias is None
@@ -90,12 +102,12 @@ class SwiGLULinearFunction(torch.autograd.Function):
     def backward(ctx, dout, *args):
         x2, y2, weight = ctx.saved_tensors
         with torch.cuda.device(x2.device):
-            dout = dout.reshape(-1, dout.shape[-1])
-            dz = F.linear(dout, weight.t())
+            dout = dout.reshape(-1, dout.shape[-1]).to(weight.dtype)
+            dz = F.linear(dout, weight.t()).to(x2.dtype)
             dx, dy, z = torch.empty_like(dz), torch.empty_like(dz), torch.empty_like(dz)
             _bwd(x2, y2, _rows(dz), dx, dy, z)
-            dlinear_weight = dout.t() @ z
-            dlinear_bias = None if ctx.linear_bias_is_none else dout.sum(0)
+            dlinear_weight = (dout.t() @ z.to(weight.dtype)).to(ctx.param_dtypes[0])
+            dlinear_bias = None if ctx.linear_bias_is_none else dout.sum(0).to(ctx.param_dtypes[1])
         return dx.reshape(ctx.shape), dy.reshape(ctx.shape), dlinear_weight, dlinear_bias
 
 
@@ -111,6 +123,8 @@ class SwiGLULinearPackedFunction(torch.autograd.Function):
         with torch.cuda.device(xy.device):
             p = _rows(xy)
             z = _fwd(p[:, :inter], p[:, inter:])
+            ctx.param_dtypes = (weight.dtype, None if bias is None else bias.dtype)
+            weight, bias = _linear_params(weight, bias)
             out = F.linear(z.to(weight.dtype), weight, bias)
         ctx.save_for_backward(p, weight)
         ctx.linear_bias_is_none = bias is None
@@ -122,13 +136,13 @@ class SwiGLULinearPackedFunction(torch.autograd.Function):
         p, weight = ctx.saved_tensors
         inter = p.shape[1] // 2
         with torch.cuda.device(p.device):
-            dout = dout.reshape(-1, dout.shape[-1])
-            dz = F.linear(dout, weight.t())
+            dout = dout.reshape(-1, dout.shape[-1]).to(weight.dtype)
+            dz = F.linear(dout, weight.t()).to(p.dtype)
             dxy = torch.empty_like(p, memory_format=torch.contiguous_format)
             z = torch.empty_like(dz)
             _bwd(p[:, :inter], p[:, inter:], _rows(dz), dxy[:, :inter], dxy[:, inter:], z)
-            dlinear_weight = dout.t() @ z
-            dlinear_bias = None if ctx.linear_bias_is_none else dout.sum(0)
+            dlinear_weight = (dout.t() @ z.to(weight.dtype)).to(ctx.param_dtypes[0])
+            dlinear_bias = None if ctx.linear_bias_is_none else dout.sum(0).to(ctx.param_dtypes[1])
         return dxy.reshape(ctx.shape), dlinear_weight, dlinear_bias
 
 

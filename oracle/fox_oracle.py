@@ -210,7 +210,7 @@ def blockwise_fwd_bwd(
     q, k, v, log_fgate, dout, seq_start=None, sm_scale=None,
     start_index=None, end_index=None, start_index_bwd=None,
     BM=128, BN=128, bwd_kv_bm=None, bwd_kv_bn=None, bwd_q_bm=None, bwd_q_bn=None,
-    low_precision_matmul=True,
+    low_precision_matmul=True, lam=None, saved_out=None, saved_L=None,
 ):
     """Restatement of the kernels' arithmetic with block pruning (OPS:505-693,
     956-1344): the same formulas as the dense path, but tiles excluded by the
@@ -219,7 +219,14 @@ def blockwise_fwd_bwd(
     Returns dict(out, L, delta, dq, dk, dv, dlog_lambda, dlog_fgate).  All math in
     fp32 on the CPU; when ``low_precision_matmul`` the probabilities and dS are
     rounded to the input dtype before their matmuls as the kernels do
-    (OPS:666, 1101, 1121, 1325)."""
+    (OPS:666, 1101, 1121, 1325).
+
+    The backward is a function of what the forward saved (OPS:207): ``lam`` (the fp32 prefix sum), ``saved_out``
+    (the 16-bit output, which delta is formed from, OPS:902-943) and ``saved_L`` (the log-normaliser the
+    probabilities are recomputed with, OPS:1087, 1300).  When given, they replace the oracle's own values in the
+    backward (and ``lam`` also in the forward), so that a backward kernel can be checked on exactly the inputs it
+    was run on: two correct 16-bit forwards differ in the rounding of ``out`` (which enters every dS through
+    delta) and, for long sequences, in the last bits of the fp32 prefix sum."""
     B, H, M, D = q.shape
     N = k.shape[2]
     P = N - M
@@ -227,7 +234,7 @@ def blockwise_fwd_bwd(
         sm_scale = 1.0 / math.sqrt(D)
     dt = q.dtype
     qf, kf, vf, dof = q.float(), k.float(), v.float(), dout.float()
-    lam = log_lambda(log_fgate, seq_start)
+    lam = log_lambda(log_fgate, seq_start) if lam is None else lam.float()
     s = torch.matmul(qf, kf.transpose(2, 3)) * sm_scale + (lam[..., P:, None] - lam[..., None, :])
     rows = torch.arange(M)
     cols = torch.arange(N)
@@ -251,11 +258,12 @@ def blockwise_fwd_bwd(
 
     out = torch.matmul(lp(p_f), vf)
     out_lp = out.to(dt)
-    delta = (out_lp.float() * dof).sum(-1)
+    delta = ((out_lp if saved_out is None else saved_out).float() * dof).sum(-1)
     # backward: probabilities recomputed from the saved normaliser, no fwd tile mask
-    Lz = torch.where(torch.isinf(L), torch.zeros_like(L), L)
+    Lb = L if saved_L is None else saved_L.float()
+    Lz = torch.where(torch.isinf(Lb), torch.zeros_like(Lb), Lb)
     p = torch.exp(s - Lz[..., None])
-    p = torch.where(elem & ~torch.isinf(L)[..., None], p, torch.zeros_like(p))
+    p = torch.where(elem & ~torch.isinf(Lb)[..., None], p, torch.zeros_like(p))
     dp = torch.matmul(dof, vf.transpose(2, 3))
     ds = p * (dp - delta[..., None])
     p_kv = torch.where(kv_mask, p, torch.zeros_like(p))
@@ -275,12 +283,13 @@ def blockwise_fwd_bwd(
 
 
 def chunked_fwd_bwd(q, k, v, log_fgate, dout, seq_start=None, sm_scale=None, start_index=None, end_index=None,
-                    BM=128, BN=128, row_chunk=1024):
+                    BM=128, BN=128, row_chunk=1024, lam=None, saved_out=None, saved_L=None):
     """``blockwise_fwd_bwd`` for sequences too long to hold (M, N) matrices: the same formulas (OPS:505-693,
     956-1344) evaluated over chunks of ``row_chunk`` query rows with explicit gradients, in one pass for
     both the reference arithmetic (probabilities and dS rounded to the input dtype before their products,
     delta from the rounded output) and the unrounded fp32 path.  Pruning index arrays act on (BM, BN) tiles as
-    in ``_tile_masks``; ``seq_start`` and pruning are not combined here.  M <= N.
+    in ``_tile_masks``; ``seq_start`` and pruning are not combined here.  M <= N.  ``lam``, ``saved_out``,
+    ``saved_L``: as in ``blockwise_fwd_bwd`` (both evaluations then differentiate through the same saved tensors).
 
     Returns (rounded, fp32): two dicts with out, L, dq, dk, dv, dlog_fgate (out / dq / dk / dv of ``rounded``
     in the input dtype)."""
@@ -292,7 +301,7 @@ def chunked_fwd_bwd(q, k, v, log_fgate, dout, seq_start=None, sm_scale=None, sta
         sm_scale = 1.0 / math.sqrt(D)
     dt = q.dtype
     qf, kf, vf, dof = q.float(), k.float(), v.float(), dout.float()
-    lam = log_lambda(log_fgate, seq_start)
+    lam = log_lambda(log_fgate, seq_start) if lam is None else lam.float()
     cols = torch.arange(N)
     si = None if start_index is None else torch.as_tensor(start_index)
     ei = None if end_index is None else torch.clamp(torch.as_tensor(end_index), max=M)
@@ -322,6 +331,10 @@ def chunked_fwd_bwd(q, k, v, log_fgate, dout, seq_start=None, sm_scale=None, sta
         empty = torch.isinf(L)
         Lz = torch.where(empty, torch.zeros_like(L), L)
         p_f = torch.where(torch.isinf(s_f), torch.zeros_like(s_f), torch.exp(s_f - Lz[..., None]))
+        if saved_L is not None:
+            Lb = saved_L[:, :, r0:r1].float()
+            empty = torch.isinf(Lb)
+            Lz = torch.where(empty, torch.zeros_like(Lb), Lb)
         p = torch.where(elem & ~empty[..., None], torch.exp(s - Lz[..., None]), torch.zeros_like(s))
         del s, s_f
         dp = torch.matmul(dof[:, :, r0:r1], vf[:, :, :n1].transpose(2, 3))
@@ -329,7 +342,8 @@ def chunked_fwd_bwd(q, k, v, log_fgate, dout, seq_start=None, sm_scale=None, sta
             lp = (lambda x: x.to(dt).float()) if rounded else (lambda x: x)
             out = torch.matmul(lp(p_f), vf[:, :, :n1])
             out_used = lp(out)
-            delta = (out_used * dof[:, :, r0:r1]).sum(-1)
+            out_bwd = out_used if saved_out is None else saved_out[:, :, r0:r1].float()
+            delta = (out_bwd * dof[:, :, r0:r1]).sum(-1)
             ds = p * (dp - delta[..., None])
             p_kv, ds_kv = (p, ds) if kv_keep is None else (p * kv_keep, ds * kv_keep)
             ds_q = ds if fwd_keep is None else ds * fwd_keep

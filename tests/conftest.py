@@ -86,8 +86,8 @@ def upstream_ops():
                 sys.path.insert(0, cand)
             sys.dont_write_bytecode = True
             mod = importlib.import_module("forgetting_transformer.ops.forgetting_attention")
-            mod.get_fwd_config = lambda B, H, M, N, D, causal: (128, 128, 2, 8)
-            mod.get_bwd_kv_config = lambda B, H, M, N, D, causal: (128, 128, 2, 8)
-            mod.get_bwd_q_config = lambda B, H, M, N, D, causal: (128, 128, 2, 8)
+            # (two pipeline stages of 128 x 128 tiles at head dim 128 exceed the 227 KiB of shared memory)
+            cfg = lambda B, H, M, N, D, causal: (128, 128, 2 if D <= 64 else 1, 8)
+            mod.get_fwd_config = mod.get_bwd_kv_config = mod.get_bwd_q_config = cfg
             return mod
     return None

@@ -9,8 +9,8 @@ one set of weights:
   * upstream's block after the name patch a maintainer would apply (the snippet in INTEGRATION.md), i.e.
     upstream's module code calling this package's operators.
 
-Outputs and input gradients are compared element-wise with the bf16 bar (2e-2 + 1e-2 |ref|), weight gradients
-by their relative error.
+Outputs are compared element-wise with the bf16 bar (2e-2 + 1e-2 |ref|); input and weight gradients, which
+pass through a dozen 16-bit operators on each side, by their relative error in the Frobenius norm.
 """
 import pytest
 import torch
@@ -43,7 +43,10 @@ def _run(block, x, dy, mask, is_upstream):
     for p in block.parameters():
         p.grad = None
     xx = x.clone().requires_grad_()
-    out = block(xx, attention_mask=mask)
+    # upstream's layer computes in the autocast dtype and in fp32 without autocast (lines 289-295): bf16 autocast
+    # over fp32 parameters, as its training configuration runs it (configs/config.py:22)
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        out = block(xx, attention_mask=mask)
     out = out[0] if is_upstream else out
     out.backward(dy)
     torch.cuda.synchronize()
@@ -54,13 +57,14 @@ def _run(block, x, dy, mask, is_upstream):
 def _compare(label, ref, got, valid):
     (ro, rdx, rg), (go, gdx, gg) = ref, got
     v = valid[:, :, None]
-    print(label, "out", round(_bars(go * v, ro * v), 3), "dx", round(_bars(gdx * v, rdx * v), 3), "bars")
+    rel = lambda a, b: ((a.float() - b.float()).norm() / b.float().norm().clamp_min(1e-6)).item()
+    rels = {n: rel(gg[n], rg[n]) for n in rg}
+    print(label, "out", round(_bars(go * v, ro * v), 3), "bars; relative errors: dx", round(rel(gdx * v, rdx * v), 4),
+          "weights, worst", max(rels, key=rels.get), round(max(rels.values()), 4))
     _close(go * v, ro * v, ATOL_BF16, RTOL_BF16, label + " out")
-    _close(gdx * v, rdx * v, ATOL_BF16, RTOL_BF16, label + " dx")
-    for n in rg:
-        a, b = gg[n].float(), rg[n].float()
-        rel = ((a - b).norm() / b.norm().clamp_min(1e-6)).item()
-        assert rel < 3e-2, f"{label} grad of {n}: relative error {rel:.3e}"
+    assert rel(gdx * v, rdx * v) < 2e-2, f"{label} dx: relative error {rel(gdx * v, rdx * v):.3e}"
+    for n, r_ in rels.items():
+        assert r_ < 3e-2, f"{label} grad of {n}: relative error {r_:.3e}"
 
 
 @pytest.mark.parametrize("padded", [False, True])
@@ -69,7 +73,7 @@ def test_block_against_upstream_block_and_through_the_integration_patch(upstream
     torch.manual_seed(5)
     dev = "cuda"
     B, T = 2, 384
-    stock = up_model.ForgettingTransformerBlock(cfg, 0).to(dev).to(torch.bfloat16)
+    stock = up_model.ForgettingTransformerBlock(cfg, 0).to(dev)
     with torch.no_grad():
         for n, p in stock.named_parameters():
             if p.dim() == 2:
@@ -77,7 +81,7 @@ def test_block_against_upstream_block_and_through_the_integration_patch(upstream
             elif n.endswith("norm.weight"):
                 p.uniform_(0.5, 1.5)
         stock.attn.fgate_proj.bias.fill_(3.0)
-    ours = fox.FoxProBlock(HIDDEN, HEADS, INTER).to(dev).to(torch.bfloat16)
+    ours = fox.FoxProBlock(HIDDEN, HEADS, INTER).to(dev)
     assert set(ours.state_dict()) == set(stock.state_dict())
     ours.load_state_dict(stock.state_dict())
     x = torch.randn(B, T, HIDDEN, device=dev).bfloat16()
@@ -103,7 +107,7 @@ def test_block_against_upstream_block_and_through_the_integration_patch(upstream
         ops_mod.forgetting_attention = fox.forgetting_attention
         for n, obj in names.items():
             setattr(up_model, n, obj)
-        patched = up_model.ForgettingTransformerBlock(cfg, 0).to(dev).to(torch.bfloat16)
+        patched = up_model.ForgettingTransformerBlock(cfg, 0).to(dev)
         patched.load_state_dict(stock.state_dict())
         via_patch = _run(patched, x, dy, mask, True)
     finally:
