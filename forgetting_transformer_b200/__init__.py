@@ -10,8 +10,10 @@ from .block import FoxMLP, FoxProAttentionLayer, FoxProBlock, ShiftLinear  # noq
 from .cache import FgateCache  # noqa: F401
 from .graphs import make_graphed  # noqa: F401
 from ._lib import FoxError, check_status  # noqa: F401
+from .cross_entropy import CrossEntropyLossFunction, FusedCrossEntropyLoss, cross_entropy_loss  # noqa: F401
 
 __all__ = ["forgetting_attention", "ForgettingAttention", "FusedGroupNormGated", "group_norm_gated", "GroupNorm",
            "group_norm", "RMSNorm", "rms_norm", "TokenShift", "token_shift", "acp_threshold_from_qk_norm",
            "acp_threshold_from_data", "seq_start_from_attention_mask", "FoxProBlock", "FoxProAttentionLayer", "FoxMLP",
-           "ShiftLinear", "FgateCache", "make_graphed", "swiglu", "swiglu_linear", "swiglu_linear_packed", "check_status", "FoxError"]
+           "ShiftLinear", "FgateCache", "make_graphed", "swiglu", "swiglu_linear", "swiglu_linear_packed", "check_status", "FoxError", "cross_entropy_loss",
+           "CrossEntropyLossFunction", "FusedCrossEntropyLoss"]

@@ -21,7 +21,7 @@ _ERRORS = {
     -9: "FOX_ERR_THRESHOLD", -10: "FOX_ERR_NO_MEMORY",
 }
 
-FOX_DTYPE_FP16, FOX_DTYPE_BF16 = 0, 1
+FOX_DTYPE_FP16, FOX_DTYPE_BF16, FOX_DTYPE_FP32 = 0, 1, 2
 
 
 class FoxError(RuntimeError):
@@ -63,6 +63,10 @@ _SIGNATURES = {
     "fox_swiglu_fwd": (c_int, [c_int, c_void_p, c_int, c_int64, c_int64, _F, c_int64, _F, c_int64, _F, c_int64]),
     "fox_swiglu_bwd": (c_int, [c_int, c_void_p, c_int, c_int64, c_int64, _F, c_int64, _F, c_int64, _F, c_int64, _F,
                                c_int64, _F, c_int64, _F, c_int64]),
+    "fox_cross_entropy_fwd": (c_int, [c_int, c_void_p, c_int, c_int64, c_int64, _F, c_int64, _F, c_float, c_float,
+                                      c_float, c_int64, _F, _F, _F]),
+    "fox_cross_entropy_bwd": (c_int, [c_int, c_void_p, c_int, c_int64, c_int64, _F, c_int64, _F, _F, _F, c_int64,
+                                      c_float, c_float, c_float, c_int64, _F, c_int64]),
     "fox_token_shift_fwd": (c_int, [c_int, c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, _F, c_int64, c_int64,
                                     c_int64, _F, _F, c_int64, c_int64, c_int64, _F]),
     "fox_token_shift_bwd": (c_int, [c_int, c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, _F, c_int64, c_int64,

@@ -13,7 +13,7 @@ import sys
 PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG_DIR, "csrc")
 LIB_PATH = os.path.join(PKG_DIR, "libfox_b200.so")
-SOURCES = ["fox_scan.cu", "fox_attn_fwd.cu", "fox_attn_bwd.cu", "fox_attn_bwd_dq.cu", "fox_attn_bwd_kv.cu", "fox_decode.cu", "fox_normgate.cu", "fox_rmsnorm.cu", "fox_shift.cu", "fox_glu.cu", "fox_noalloc.cu"]
+SOURCES = ["fox_scan.cu", "fox_attn_fwd.cu", "fox_attn_bwd.cu", "fox_attn_bwd_dq.cu", "fox_attn_bwd_kv.cu", "fox_decode.cu", "fox_normgate.cu", "fox_rmsnorm.cu", "fox_shift.cu", "fox_glu.cu", "fox_ce.cu", "fox_noalloc.cu"]
 HEADERS = ["fox_common.cuh", "fox_host.h", os.path.join("..", "..", "include", "fox_b200.h")]
 
 

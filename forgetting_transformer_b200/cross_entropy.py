@@ -1,0 +1,126 @@
+"""Fused cross-entropy loss backed by the sm_100a kernels.
+
+Host-side mirror of upstream's ``CrossEntropyLossFunction`` / ``cross_entropy_loss`` / ``FusedCrossEntropyLoss``
+(src/forgetting_transformer/model/forgetting_transformer/fused_cross_entropy.py:137-401): same arguments,
+defaults and returned (losses, z_losses), label smoothing, logit scale, z-loss, ``ignore_index`` and the
+in-place backward the model's loss uses (modeling_forgetting_transformer.py:877-884).  Tensor parallelism over
+the classes (``process_group``) is not built.  No CPU path.
+"""
+from __future__ import annotations
+
+from typing import Any, Tuple
+
+import torch
+import torch.nn as nn
+
+from . import _lib
+
+__all__ = ["cross_entropy_loss", "CrossEntropyLossFunction", "FusedCrossEntropyLoss"]
+
+_DTYPES = {torch.float16: _lib.FOX_DTYPE_FP16, torch.bfloat16: _lib.FOX_DTYPE_BF16, torch.float32: _lib.FOX_DTYPE_FP32}
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+class CrossEntropyLossFunction(torch.autograd.Function):
+
+    @staticmethod
+    def forward(ctx, logits, target, label_smoothing=0.0, logit_scale=1.0, lse_square_scale=0.0, ignore_index=-100,
+                inplace_backward=False, process_group=None):
+        if process_group is not None:
+            raise NotImplementedError("the class dimension is not split over ranks here (process_group must be None)")
+        if not logits.is_cuda:
+            raise _lib.FoxError("cross_entropy_loss needs CUDA tensors on an sm_100 device; there is no CPU path")
+        n_rows, n_cols = logits.shape
+        assert target.shape == (n_rows,)
+        if logits.dtype not in _DTYPES:
+            raise _lib.FoxError(f"unsupported logits dtype {logits.dtype}")
+        es = logits.element_size()
+        if logits.stride(-1) != 1 or (logits.stride(0) * es) % 16 or logits.data_ptr() % 16:
+            logits = logits.contiguous()
+            if (logits.stride(0) * es) % 16:     # a class count whose rows cannot all start on 16 bytes: pad the stride
+                pad = torch.empty((n_rows, -(-n_cols * es // 16) * 16 // es), dtype=logits.dtype, device=logits.device)
+                pad[:, :n_cols] = logits
+                logits = pad[:, :n_cols]
+        target = target.to(torch.long).contiguous()
+        lib = _lib.load()
+        dev = logits.device
+        with torch.cuda.device(dev):
+            losses = torch.empty(n_rows, dtype=torch.float32, device=dev)
+            z_losses = torch.empty(n_rows, dtype=torch.float32, device=dev)
+            lse = torch.empty(n_rows, dtype=torch.float32, device=dev)
+            _lib.check(lib.fox_cross_entropy_fwd(dev.index, _stream(), _DTYPES[logits.dtype], n_rows, n_cols,
+                                                 logits.data_ptr(), logits.stride(0), target.data_ptr(),
+                                                 float(label_smoothing), float(logit_scale), float(lse_square_scale),
+                                                 int(ignore_index), losses.data_ptr(), z_losses.data_ptr(),
+                                                 lse.data_ptr()), "fox_cross_entropy_fwd")
+        ctx.save_for_backward(logits, lse, target)
+        ctx.mark_non_differentiable(z_losses)
+        ctx.args = (float(label_smoothing), float(logit_scale), float(lse_square_scale), int(ignore_index))
+        ctx.inplace_backward = inplace_backward
+        return losses, z_losses
+
+    @staticmethod
+    def backward(ctx, grad_losses, grad_z_losses):
+        del grad_z_losses  # z_losses are for logging only, as upstream
+        logits, lse, target = ctx.saved_tensors
+        label_smoothing, logit_scale, lse_square_scale, ignore_index = ctx.args
+        n_rows, n_cols = logits.shape
+        dlogits = logits if ctx.inplace_backward else torch.empty_like(logits)
+        grad_losses = grad_losses.float()
+        lib = _lib.load()
+        dev = logits.device
+        with torch.cuda.device(dev):
+            _lib.check(lib.fox_cross_entropy_bwd(dev.index, _stream(), _DTYPES[logits.dtype], n_rows, n_cols,
+                                                 logits.data_ptr(), logits.stride(0), target.data_ptr(),
+                                                 lse.data_ptr(), grad_losses.data_ptr(), grad_losses.stride(0),
+                                                 label_smoothing, logit_scale, lse_square_scale, ignore_index,
+                                                 dlogits.data_ptr(), dlogits.stride(0)), "fox_cross_entropy_bwd")
+        return dlogits, None, None, None, None, None, None, None
+
+
+def cross_entropy_loss(logits: torch.Tensor, target: torch.Tensor, label_smoothing: float = 0.0,
+                       logit_scale: float = 1.0, lse_square_scale: float = 0.0, ignore_index=-100,
+                       inplace_backward: bool = False, process_group=None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """logits (rows, classes), target (rows,) -> (losses, z_losses), both fp32 (rows,); see upstream lines 275-312."""
+    return CrossEntropyLossFunction.apply(logits, target, label_smoothing, logit_scale, lse_square_scale, ignore_index,
+                                          inplace_backward, process_group)
+
+
+class FusedCrossEntropyLoss(nn.Module):
+    """Same constructor and forward contract as upstream's module (lines 315-401)."""
+
+    def __init__(self, ignore_index: int = -100, reduction: str = "mean", label_smoothing: float = 0.0,
+                 logit_scale: float = 1.0, lse_square_scale: float = 0.0, inplace_backward: bool = False,
+                 process_group: Any = None, return_z_loss: bool = False):
+        super().__init__()
+        if reduction not in ["mean", "none", "sum"]:
+            raise NotImplementedError("Only support reduction = 'mean' or 'none' or 'sum'")
+        self.ignore_index = ignore_index
+        self.reduction = reduction
+        self.label_smoothing = label_smoothing
+        self.logit_scale = logit_scale
+        self.lse_square_scale = lse_square_scale
+        self.inplace_backward = inplace_backward
+        self.process_group = process_group
+        self.return_z_loss = return_z_loss
+
+    def forward(self, input, target):
+        assert input.is_cuda and target.is_cuda, "Only support CUDA tensors"
+        loss, z_loss = cross_entropy_loss(input, target, label_smoothing=self.label_smoothing,
+                                          logit_scale=self.logit_scale, lse_square_scale=self.lse_square_scale,
+                                          ignore_index=self.ignore_index, inplace_backward=self.inplace_backward,
+                                          process_group=self.process_group)
+        if self.reduction == "mean":
+            loss = loss.sum() / (target != self.ignore_index).sum()
+        elif self.reduction == "sum":
+            loss = loss.sum()
+        if not self.return_z_loss:
+            return loss
+        if self.reduction == "mean":
+            z_loss = z_loss.sum() / (target != self.ignore_index).sum()
+        elif self.reduction == "sum":
+            z_loss = z_loss.sum()
+        return loss, z_loss

@@ -22,15 +22,22 @@
 // The tensor pipe and the compute warps overlap: while phase B(i) runs the pipe does
 // dV(i) and S(i+1); while phase A(i+1) runs it does dK(i), dP(i+1), dQ(i) (D = 128, where the dQ
 // accumulator has to share columns with S^T / dP^T: dK(i), dQ(i), drain, S(i+1), dP(i+1)).
-// A 16-column "ones" tile appended (through the descriptor's leading offset) to K makes
-// the dQ product also deliver rowsum(dS), the query-side log-gate gradient; at D=64 the
-// same tile appended to Q makes the dK product deliver colsum(dS), the key-side one.
-// Both sums are thus formed from the same rounded dS values and cancel in the reverse
-// prefix sum the way upstream's fp32 sums do.
+// The two halves of the log-gate gradient, colsum(dS) per key and rowsum(dS) per query, are sums of the fp32
+// dS values, as upstream's are (lines 1122, 1326): the column sum is a running sum of the thread that owns
+// the KV row; the row sum of a tile is formed across the 32 lanes of a warp by a transposing reduction
+// (31 shuffles leave lane l with the warp's sum of query column l) after dS has been handed to the tensor
+// pipe, i.e. under the dK / dQ products, and added to the fp32 workspace.  Both halves sum the same values,
+// so they cancel in the reverse prefix sum as upstream's do.  (FOX_BWD_FP32_SUMS=0 builds the earlier form:
+// a 16-column "ones" tile appended to K and Q through the descriptors' leading offset makes the dQ and dK
+// products deliver the sums of the 16-bit dS values, which is free but 2-4e-2 off upstream's gate gradient.)
 #include <type_traits>
 
 #include "fox_common.cuh"
 #include "fox_host.h"
+
+#ifndef FOX_BWD_FP32_SUMS
+#define FOX_BWD_FP32_SUMS 1
+#endif
 
 namespace fox {
 
@@ -77,7 +84,8 @@ fox_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   // kNoDQ: dK, dV and the key-side gate gradient only (dQ comes from fox_attn_bwd_dq_kernel): no dQ product, no
   // drain, no reductions, and at D = 128 no sharing of TMEM columns
   constexpr bool kAliasDQ = (D == 128) && !kNoDQ;  // dQ accumulator shares columns with S^T / dP^T
-  constexpr bool kColsumMMA = (D == 64) && !kNoDQ;    // colsum(dS) from the dK product
+  constexpr bool kFp32Sums = FOX_BWD_FP32_SUMS != 0;            // gate-gradient sums of the fp32 dS values
+  constexpr bool kColsumMMA = (D == 64) && !kNoDQ && !kFp32Sums;  // colsum(dS) from the dK product
   constexpr int STQ = 2;
   constexpr int STDO = (D == 64) ? 2 : 1;
   constexpr int kDsBufs = (D == 64) ? 2 : 1;
@@ -87,7 +95,7 @@ fox_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   constexpr int kTmaWarp = 4 * kCWG, kMmaWarp = 4 * kCWG + 1, kDrainWarp0 = 4 * kCWG + 2;
   constexpr uint32_t kTmemCols = 512;
   constexpr int kNdk = kColsumMMA ? D + 16 : D;
-  constexpr int kNdq = D + 16;
+  constexpr int kNdq = kFp32Sums ? D : D + 16;
   constexpr uint32_t kColS = 0, kColDP = 128, kColDK = 256, kColDV = 256 + kNdk;
   constexpr uint32_t kColDQ = kAliasDQ ? 0 : kColDV + D;
   static_assert(kAliasDQ || kNoDQ || kColDQ + kNdq <= 512, "TMEM budget");
@@ -156,7 +164,7 @@ fox_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     tmem_alloc(&tmem_slot, kTmemCols);
     tmem_relinquish();
   }
-  if (warp < 4) {
+  if (warp < 4 && !kFp32Sums) {
     // "ones" sub-tile: 16-bit 1.0 in columns 0..15 of every row, zero elsewhere
     const uint32_t one2 = kBf16 ? 0x3F803F80u : 0x3C003C00u;
     const uint4 ones = make_uint4(one2, one2, one2, one2), zeros = make_uint4(0, 0, 0, 0);
@@ -196,6 +204,8 @@ fox_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       // tiles ahead into one of two register sets with loads that stay where they are written, and only
       // combined when they are staged: a global load here sees well over a thousand cycles of latency
       // while the reductions are in flight, and anything the producer waits for delays every copy behind it.
+      // (prefixes relative to this KV tile's first key before the scaling by log2(e): see b_j below)
+      const float lam_ref = p.lam[bh * N + min(nb * kBwdBN, N - 1)];
       float rawL[2][kBwdBM / 32], rawLam[2][kBwdBM / 32], rawD[2][kBwdBM / 32];
       auto fetch_vec = [&](int mb_, auto slot_c) {
         constexpr int slot = decltype(slot_c)::value;
@@ -242,7 +252,7 @@ fox_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 #pragma unroll
         for (int rr = 0; rr < kBwdBM / 32; ++rr) {
           const float Li = rawL[slot][rr];
-          s_e[st][rr * 32 + lane] = (Li == -INFINITY) ? -INFINITY : (rawLam[slot][rr] - Li) * kLog2eB;
+          s_e[st][rr * 32 + lane] = (Li == -INFINITY) ? -INFINITY : ((rawLam[slot][rr] - lam_ref) - Li) * kLog2eB;
           s_delta[st][rr * 32 + lane] = rawD[slot][rr];
         }
         __syncwarp();
@@ -423,7 +433,7 @@ fox_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       // 32-column sub-tile into the fp32 workspace (the TMA unit issues the L2 reductions; rows past M
       // are clipped by the tensor map).  The accumulator is released as soon as it has been read.
       uint32_t rs[16];
-      tmem_ld16(tDQ + D, rs);  // rowsum(dS) sits in the column after the dQ columns
+      if (!kFp32Sums) tmem_ld16(tDQ + D, rs);  // rowsum(dS) sits in the column after the dQ columns
 #pragma unroll
       for (int round = 0; round < D / (32 * kStageSub); ++round) {
         const int n_round = it * (D / (32 * kStageSub)) + round;
@@ -465,7 +475,7 @@ fox_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       }
       if (!ok) break;
       if (warp == kDrainWarp0) stamp(1, 2, it);
-      if (i < M) atomicAdd(p.dlam_row + bh * M + i, __uint_as_float(rs[0]));
+      if (!kFp32Sums && i < M) atomicAdd(p.dlam_row + bh * M + i, __uint_as_float(rs[0]));
     }
     if (warp == kDrainWarp0) tma_store_wait_all<0>();
   } else {
@@ -476,7 +486,9 @@ fox_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     const bool j_ok = (j < N) && (j >= seq0);
     const float* lam = p.lam + bh * N;
     // an invalid KV row gets b_j = +inf, i.e. probability 0 everywhere
-    const float b_j = j_ok ? lam[j] * kLog2eB : INFINITY;
+    // Lambda_i - Lambda_j is formed from prefixes relative to the tile's first key: scaling a prefix of -1e4
+    // by log2(e) first would cost an absolute 2e-3 per logit
+    const float b_j = j_ok ? (lam[j] - lam[min(nb * kBwdBN, N - 1)]) * kLog2eB : INFINITY;
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const uint32_t tS = tbase + lane_base + kColS, tDP = tbase + lane_base + kColDP;
     float colsum = 0.f;
@@ -552,10 +564,14 @@ fox_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           const uint32_t d01 = pack2<kBf16>(dsv[0], dsv[1]), d23 = pack2<kBf16>(dsv[2], dsv[3]);
           dsk[c4 * 2] = d01;
           dsk[c4 * 2 + 1] = d23;
-          if constexpr (kNoDQ) {
-            // the row sums come from another kernel's recomputed dS: both sides sum the fp32 values, which agree
-            // to fp32 rounding (the two kernels' 16-bit roundings of them differ on a few percent of the elements)
+          if constexpr (kNoDQ || kFp32Sums) {
+            // fp32 values on both sides (with kNoDQ the row sums come from another kernel's recomputed dS, which
+            // agrees to fp32 rounding; the two kernels' 16-bit roundings differ on a few percent of the elements)
             colsum += (dsv[0] + dsv[1]) + (dsv[2] + dsv[3]);
+            if constexpr (kFp32Sums && !kNoDQ) {
+#pragma unroll
+              for (int e = 0; e < 4; ++e) pf[ch * 32 + c4 * 4 + e] = dsv[e];   // p is no longer needed
+            }
           } else if (!kColsumMMA) {
             const float2 r01 = unpack2<kBf16>(d01), r23 = unpack2<kBf16>(d23);
             colsum += (r01.x + r01.y) + (r23.x + r23.y);
@@ -574,6 +590,27 @@ fox_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       tc_fence_before();
       mbar_arrive(&bar_ds_done);
       if (warp < 8) stamp(6 + warp, 3, it);
+      if constexpr (kFp32Sums && !kNoDQ) {
+        // rowsum(dS) of this warp's 32 KV rows, under the products that now read dS: at the step with lane
+        // distance `off` a lane keeps the half of its columns whose index has that bit as its own lane number
+        // does and receives the partner's sums of them, so lane l ends with the sum of column l
+#pragma unroll
+        for (int ch = 0; ch < CW / 32; ++ch) {
+          float* vsum = &pf[ch * 32];
+#pragma unroll
+          for (int off = 16; off >= 1; off >>= 1) {
+            const bool upper = (lane & off) != 0;
+#pragma unroll
+            for (int c = 0; c < off; ++c) {
+              const float send = upper ? vsum[c] : vsum[c + off];
+              const float keep = upper ? vsum[c + off] : vsum[c];
+              vsum[c] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+            }
+          }
+          const int i = mb * kBwdBM + g * CW + ch * 32 + lane;
+          if (i < M) atomicAdd(p.dlam_row + bh * M + i, vsum[0]);
+        }
+      }
     }
 
     // ---- epilogue: warpgroup 0 writes dK (and the key-side gate gradient), warpgroup 1 writes dV ----

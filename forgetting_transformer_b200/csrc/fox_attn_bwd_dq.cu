@@ -147,7 +147,9 @@ fox_attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       };
       auto stage_negb = [&](int it) {
         const int slot = it % 3;
-        *reinterpret_cast<float2*>(&s_negb[slot][2 * lane]) = make_float2(-lamv[0] * kDqLog2e, -lamv[1] * kDqLog2e);
+        const float lam_ref = lam[min(P + mb * kDqBM, N - 1)];
+        *reinterpret_cast<float2*>(&s_negb[slot][2 * lane]) =
+            make_float2((lam_ref - lamv[0]) * kDqLog2e, (lam_ref - lamv[1]) * kDqLog2e);
         __syncwarp();
         if (lane == 0) mbar_arrive(&bar_negb[slot]);
         __syncwarp();
@@ -260,7 +262,8 @@ fox_attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     float e_i = -INFINITY, delta_i = 0.f;
     if (row_ok) {
       const float Li = p.L[bh * M + row];
-      e_i = (Li == -INFINITY) ? -INFINITY : (p.lam[bh * N + P + row] - Li) * kDqLog2e;
+      e_i = (Li == -INFINITY) ? -INFINITY
+                              : ((p.lam[bh * N + P + row] - p.lam[bh * N + min(P + mb * kDqBM, N - 1)]) - Li) * kDqLog2e;
       delta_i = p.delta[bh * M + row];
     }
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
@@ -469,6 +472,9 @@ fox_attn_bwd_dq2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
       }
       __syncwarp();
       const float* lam = p.lam + bh * N;
+      // Prefixes enter the logits as Lambda_i - Lambda_j; both are taken relative to the prefix of this query
+      // tile's first row before the scaling by log2(e) (a prefix of -1e4 scaled first costs 2e-3 per logit)
+      const float lam_ref = lam[min(P + mb * kDqBM, N - 1)];
       float lamv[4] = {0.f, 0.f, 0.f, 0.f};   // lane l holds columns 4l .. 4l+3 of a tile
       auto fetch_lam = [&](int it) {
         const int c0 = (nb_hi - 1 - it) * BN + 4 * lane;
@@ -478,7 +484,8 @@ fox_attn_bwd_dq2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
       auto stage_negb = [&](int it) {
         const int slot = it % 3;
         *reinterpret_cast<float4*>(&s_negb[slot][4 * lane]) =
-            make_float4(-lamv[0] * kDqLog2e, -lamv[1] * kDqLog2e, -lamv[2] * kDqLog2e, -lamv[3] * kDqLog2e);
+            make_float4((lam_ref - lamv[0]) * kDqLog2e, (lam_ref - lamv[1]) * kDqLog2e,
+                        (lam_ref - lamv[2]) * kDqLog2e, (lam_ref - lamv[3]) * kDqLog2e);
         __syncwarp();
         if (lane == 0) mbar_arrive(&bar_negb[slot]);
         __syncwarp();
@@ -613,7 +620,8 @@ fox_attn_bwd_dq2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
     float e_i = -INFINITY, delta_i = 0.f;
     if (row_ok) {
       const float Li = p.L[bh * M + row];
-      e_i = (Li == -INFINITY) ? -INFINITY : (p.lam[bh * N + P + row] - Li) * kDqLog2e;
+      e_i = (Li == -INFINITY) ? -INFINITY
+                              : ((p.lam[bh * N + P + row] - p.lam[bh * N + min(P + mb * kDqBM, N - 1)]) - Li) * kDqLog2e;
       delta_i = p.delta[bh * M + row];
     }
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;

@@ -152,6 +152,8 @@ fox_attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       const float* lam = p.lam + bh * N + P;
       const float* Lp = p.L + bh * M;
       const float* dl = p.delta + bh * M;
+      // prefixes relative to this KV tile's first key before the scaling by log2(e), as for negb below
+      const float lam_ref = p.lam[bh * N + min(j0, N - 1)];
       float ev[4], dv_[4];   // lane l holds query rows 4l .. 4l+3 of a tile
       auto fetch_vec = [&](int it) {
         const int i0 = (hb_lo + it) * BM + 4 * lane;
@@ -164,7 +166,7 @@ fox_attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
             la = ldg_f32_here(lam + i);
             de = ldg_f32_here(dl + i);
           }
-          ev[e] = (Li == -INFINITY) ? -INFINITY : (la - Li) * kKvLog2e;
+          ev[e] = (Li == -INFINITY) ? -INFINITY : ((la - lam_ref) - Li) * kKvLog2e;
           dv_[e] = de;
         }
       };
@@ -315,7 +317,9 @@ fox_attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     const int j = j0 + r;
     const bool j_ok = j < N && j >= seq0;
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
-    const float negb = j_ok ? -p.lam[bh * N + j] * kKvLog2e : -INFINITY;
+    // Lambda_i - Lambda_j from prefixes relative to the tile's first key: scaling a prefix of -1e4 by log2(e)
+    // first would cost an absolute 2e-3 per logit
+    const float negb = j_ok ? (p.lam[bh * N + min(j0, N - 1)] - p.lam[bh * N + j]) * kKvLog2e : -INFINITY;
     const uint32_t tS = tbase + lane_base + kColS + g * CW, tDP = tbase + lane_base + kColDP + g * CW;
     const float2 scale2 = make_float2(p.qk_scale, p.qk_scale);
     const float2 negb2 = make_float2(negb, negb);

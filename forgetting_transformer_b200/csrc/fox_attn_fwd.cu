@@ -191,6 +191,10 @@ fox_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       };
       // gate prefixes of a tile's columns: lane l holds columns 4l .. 4l+3 (lanes < BN/4)
       const float* lam = p.lam + (static_cast<int64_t>(b) * p.H + h) * N;
+      // Prefixes enter the logits as differences Lambda_i - Lambda_j.  Both are taken relative to the prefix of
+      // this query tile's first row BEFORE the scaling by log2(e): far into a strongly decaying sequence the
+      // prefix reaches -1e4 and beyond, where scaling it first costs an absolute 2e-3 per logit.
+      const float lam_ref = lam[min(P + mb * kFwdBM, N - 1)];
       float lamv[4] = {0.f, 0.f, 0.f, 0.f};
       auto fetch_lam = [&](int it) {
         const int c0 = (nb_hi - 1 - it) * BN + 4 * lane;
@@ -199,7 +203,8 @@ fox_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       };
       auto stage_negb = [&](int it) {  // from lamv, fetched earlier for this tile
         const int slot = it % 3;
-        float4 nbv = make_float4(-lamv[0] * kLog2e, -lamv[1] * kLog2e, -lamv[2] * kLog2e, -lamv[3] * kLog2e);
+        float4 nbv = make_float4((lam_ref - lamv[0]) * kLog2e, (lam_ref - lamv[1]) * kLog2e,
+                                 (lam_ref - lamv[2]) * kLog2e, (lam_ref - lamv[3]) * kLog2e);
         if (4 * lane < BN) *reinterpret_cast<float4*>(&s_negb[slot][4 * lane]) = nbv;
         float mx = fmaxf(fmaxf(nbv.x, nbv.y), fmaxf(nbv.z, nbv.w));
 #pragma unroll
@@ -318,7 +323,7 @@ fox_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     const bool row_ok = row < M;
     const int64_t bh = static_cast<int64_t>(b) * p.H + h;
     const float* lam = p.lam + bh * N;
-    const float a_i = row_ok ? lam[P + row] * kLog2e : 0.f;
+    const float a_i = row_ok ? (lam[P + row] - lam[min(P + mb * kFwdBM, N - 1)]) * kLog2e : 0.f;  // (see the producer)
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const uint32_t tS = tbase + lane_base + g * CW;
     const uint32_t tO = tbase + lane_base + kColO + g * D;

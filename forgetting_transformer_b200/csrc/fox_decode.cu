@@ -72,7 +72,7 @@ fox_decode_partial_kernel(const DecodeParams p) {
     for (int c = 0; c < 8; ++c) dec_load8<kBf16>(qp + c * 8, &qv[c * 8]);
   }
   const float* lam = p.lam + bh * N;
-  const float a = lam[N - 1] * kDecLog2e;
+  const float a = lam[N - 1];   // (the difference of two prefixes is formed before the scaling by log2(e))
   float m = -INFINITY, l = 0.f;
   float acc[64];
 #pragma unroll
@@ -92,7 +92,7 @@ fox_decode_partial_kernel(const DecodeParams p) {
       for (int e = 0; e < 8; ++e) s = fmaf(qv[c * 8 + e], kv[e], s);
     }
     if (TPK == 2) s += __shfl_xor_sync(0xffffffffu, s, 1);
-    const float u = in ? fmaf(s, p.qk_scale, a - lam[jc] * kDecLog2e) : -INFINITY;
+    const float u = in ? fmaf(s, p.qk_scale, (a - lam[jc]) * kDecLog2e) : -INFINITY;
     const float m_new = fmaxf(m, u);
     if (m_new > -INFINITY) {  // (warp-divergent, but only until every lane has seen its first key)
       const float alpha = fast_exp2(m - m_new);   // 0 when m was -inf

@@ -46,6 +46,7 @@ extern "C" {
 
 #define FOX_DTYPE_FP16 0
 #define FOX_DTYPE_BF16 1
+#define FOX_DTYPE_FP32 2          /* accepted by fox_cross_entropy_* only */
 
 typedef struct fox_tensor4 {
   void* ptr;
@@ -210,6 +211,26 @@ int fox_swiglu_fwd(int device, void* stream, int dtype, int64_t rows, int64_t co
 int fox_swiglu_bwd(int device, void* stream, int dtype, int64_t rows, int64_t cols, const void* x,
                    int64_t x_row_stride, const void* y, int64_t y_row_stride, const void* g, int64_t g_row_stride,
                    void* dx, int64_t dx_row_stride, void* dy, int64_t dy_row_stride, void* z, int64_t z_row_stride);
+
+/* Cross-entropy loss per row of a (n_rows, n_cols) logit matrix, forward.  Replaces cross_entropy_fwd_kernel
+ * (fused_cross_entropy.py:24-87) as FusedCrossEntropyLoss launches it for the model's loss
+ * (modeling_forgetting_transformer.py:877-884), without the tensor-parallel class split:
+ * z = logit_scale * logits; lse = log sum exp z; losses = lse - (1 - label_smoothing) z[label]
+ * - label_smoothing * mean(z) + lse_square_scale * lse^2, and 0 where label == ignore_index; z_losses is the
+ * last term alone.  logits: fp32 / bf16 / fp16 (dtype), unit inner stride, row stride in elements, rows 16-byte
+ * aligned; labels int64 (n_rows); losses, z_losses, lse: fp32 (n_rows), fully written. */
+int fox_cross_entropy_fwd(int device, void* stream, int dtype, int64_t n_rows, int64_t n_cols, const void* logits,
+                          int64_t row_stride, const int64_t* labels, float label_smoothing, float logit_scale,
+                          float lse_square_scale, int64_t ignore_index, float* losses, float* z_losses, float* lse);
+
+/* Backward of the above (cross_entropy_bwd_kernel, fused_cross_entropy.py:90-134): dlogits = dloss * logit_scale *
+ * (exp(z - lse) (1 + 2 lse_square_scale lse) - (1 - label_smoothing) [c == label] - label_smoothing / n_cols),
+ * zero rows where label == ignore_index.  dlogits has the logits' dtype and may be the logits buffer itself
+ * (upstream's inplace_backward); dloss: fp32 with element stride dloss_stride. */
+int fox_cross_entropy_bwd(int device, void* stream, int dtype, int64_t n_rows, int64_t n_cols, const void* logits,
+                          int64_t row_stride, const int64_t* labels, const float* lse, const float* dloss,
+                          int64_t dloss_stride, float label_smoothing, float logit_scale, float lse_square_scale,
+                          int64_t ignore_index, void* dlogits, int64_t dlogits_row_stride);
 
 /* Data-dependent token shift, forward: out[b,t,h,:] = x[b,t,h,:] * curr[b,t,h] + x[b,t-1,h,:] *
  * prev[b,t,h] with x[b,-1] = 0, products in fp32, rounded once.  Replaces shift_fwd_kernel

@@ -521,3 +521,29 @@ def swiglu_bwd(x, y, g):
     dx = s * (1 + xf * (1.0 - s)) * gf * yf
     dy = xf * s * gf
     return dx.to(x.dtype), dy.to(x.dtype), (xf * s * yf).to(x.dtype)
+
+
+# --------------------------------------------------------------------------
+# cross-entropy loss (fused_cross_entropy.py:24-134, without the tensor-parallel class split)
+# --------------------------------------------------------------------------
+def cross_entropy(logits: torch.Tensor, target: torch.Tensor, label_smoothing: float = 0.0, logit_scale: float = 1.0,
+                  lse_square_scale: float = 0.0, ignore_index: int = -100):
+    """(losses, z_losses), fp32 (rows,): lse - (1 - eps) z[label] - eps mean(z) + s lse^2 with z = logit_scale *
+    logits in fp32; rows whose label is ``ignore_index`` give 0 (fused_cross_entropy.py:47-87)."""
+    z = logits.float() * logit_scale
+    lse = torch.logsumexp(z, dim=-1)
+    keep = target != ignore_index
+    safe = torch.where(keep, target, torch.zeros_like(target))
+    zlab = z.gather(1, safe[:, None])[:, 0]
+    loss = lse - (1.0 - label_smoothing) * zlab - label_smoothing * z.mean(dim=-1)
+    zl = lse_square_scale * lse * lse
+    zero = torch.zeros_like(loss)
+    return torch.where(keep, loss + zl, zero), torch.where(keep, zl, zero)
+
+
+def cross_entropy_fwd_bwd(logits, target, dloss, **kw):
+    """losses, z_losses and d(sum(losses * dloss)) / dlogits in fp32."""
+    x = logits.detach().float().requires_grad_()
+    losses, zl = cross_entropy(x, target, **kw)
+    (losses * dloss).sum().backward()
+    return losses.detach(), zl.detach(), x.grad

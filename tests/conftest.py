@@ -19,12 +19,24 @@ def pytest_configure(config):
 
 GLUE_GOLDEN = "glue_refs"  # norms and token shift (tests/golden/make_golden_glue.py)
 INDEX_GOLDEN = "index_scans"  # pruning index arrays of upstream's scan kernels (tests/golden/make_golden_index.py)
+CE_GOLDEN = "cross_entropy"  # upstream's fused cross-entropy kernels (tests/golden/make_golden_ce.py)
 # every other .npz is an attention case
 
 
 def golden_names():
     names = sorted(os.path.splitext(os.path.basename(p))[0] for p in glob.glob(os.path.join(GOLDEN_DIR, "*.npz")))
-    return [n for n in names if n not in (GLUE_GOLDEN, INDEX_GOLDEN)]
+    return [n for n in names if n not in (GLUE_GOLDEN, INDEX_GOLDEN, CE_GOLDEN)]
+
+
+def load_ce_golden():
+    """Fixture produced by tests/golden/make_golden_ce.py: upstream's cross_entropy_loss (its Triton kernels in
+    the CPU interpreter).  Returns {case: dict(logits, labels, dloss, losses, z_losses, dlogits, args)}."""
+    z = np.load(os.path.join(GOLDEN_DIR, CE_GOLDEN + ".npz"))
+    cases = {}
+    for key in z.files:
+        case, field = key.split("/")
+        cases.setdefault(case, {})[field] = torch.from_numpy(np.ascontiguousarray(z[key]))
+    return cases
 
 
 def load_index_golden():
@@ -86,8 +98,13 @@ def upstream_ops():
                 sys.path.insert(0, cand)
             sys.dont_write_bytecode = True
             mod = importlib.import_module("forgetting_transformer.ops.forgetting_attention")
-            # (two pipeline stages of 128 x 128 tiles at head dim 128 exceed the 227 KiB of shared memory)
-            cfg = lambda B, H, M, N, D, causal: (128, 128, 2 if D <= 64 else 1, 8)
-            mod.get_fwd_config = mod.get_bwd_kv_config = mod.get_bwd_q_config = cfg
+            # The forward grid defines start_index and stays 128 x 128.  At head dim 128 Triton's sm_100 lowering
+            # of the backward kernels with 128 x 128 tiles needs more shared memory (two stages) and more tensor
+            # memory (576 of 512 columns) than the SM has, so they run on upstream's own H100 tile for the key side
+            # and a 128 x 64 tile for the query side; backward tiles only decide which nearly-empty tiles are
+            # skipped (each carries less than e^threshold of a row's mass).
+            mod.get_fwd_config = lambda B, H, M, N, D, causal: (128, 128, 2 if D <= 64 else 1, 8)
+            mod.get_bwd_kv_config = lambda B, H, M, N, D, causal: (128, 128, 2, 8) if D <= 64 else (64, 64, 2, 4)
+            mod.get_bwd_q_config = lambda B, H, M, N, D, causal: (128, 128, 2, 8) if D <= 64 else (128, 64, 2, 8)
             return mod
     return None

@@ -260,3 +260,39 @@ def test_generation_with_cache_matches_full_forward(with_mask):
     scale = yr.abs().max().item()
     assert (gen.float().cpu() - yr)[valid].abs().max().item() < 3e-2 * scale
     assert (gen.float().cpu() - full.float().cpu())[valid].abs().max().item() < 3e-2 * scale
+
+
+@pytest.mark.parametrize("inplace", [False, True])
+def test_cross_entropy_against_upstream_kernels_and_oracle(inplace):
+    """fox_cross_entropy_fwd / _bwd through the module mirror: every fixture case of upstream's own kernels
+    (fp32 and fp16 logits, 1003 classes: rows that do not start on 16 bytes are re-laid), then bf16 logits at a
+    vocabulary-sized class count against the oracle, in place and out of place."""
+    from conftest import load_ce_golden
+    for name, c in load_ce_golden().items():
+        ls, scale, zs = [float(x) for x in c["args"]]
+        x = c["logits"].cuda().requires_grad_()
+        losses, zl = fox.cross_entropy_loss(x, c["labels"].cuda(), ls, scale, zs, -100, False)
+        (losses * c["dloss"].cuda()).sum().backward()
+        # (with 16-bit logits upstream forms logit_scale * logits[label] and its (1 - smoothing) multiple in the
+        # logits' dtype, fused_cross_entropy.py:65-72: its loss carries that one rounding)
+        loss_tol = 2e-5 * max(1.0, c["losses"].abs().max().item()) if x.dtype == torch.float32 else 8e-3
+        assert _err(losses, c["losses"].cuda()) < loss_tol, name
+        assert _err(zl, c["z_losses"].cuda()) < 1e-6, name
+        tol = 1e-6 if x.dtype == torch.float32 else 2e-3 * c["dlogits"].float().abs().max().item()
+        assert _err(x.grad, c["dlogits"].cuda()) < tol, name
+    g = torch.Generator().manual_seed(9)
+    rows, cols = 300, 50304
+    logits = (torch.randn(rows, cols, generator=g) * 2).bfloat16()
+    labels = torch.randint(0, cols, (rows,), generator=g)
+    labels[::7] = -100
+    dloss = torch.rand(rows, generator=g)
+    rl, rz, rd = orc.cross_entropy_fwd_bwd(logits, labels, dloss, lse_square_scale=1e-4)
+    mod = fox.FusedCrossEntropyLoss(reduction="none", lse_square_scale=1e-4, inplace_backward=inplace, return_z_loss=True)
+    x = logits.cuda().requires_grad_()
+    xin = x.clone() if inplace else x          # (an in-place backward overwrites the tensor the function saved)
+    losses, zl = mod(xin, labels.cuda())
+    (losses * dloss.cuda()).sum().backward()
+    assert _err(losses.cpu(), rl) < 1e-4 and _err(zl.cpu(), rz) < 1e-6
+    assert _err(x.grad.cpu(), rd) < 4e-3 * rd.abs().max().item()     # one bf16 rounding of the gradient
+    mean = fox.FusedCrossEntropyLoss()(logits.cuda(), labels.cuda())
+    assert abs(mean.item() - (orc.cross_entropy(logits, labels)[0].sum() / (labels != -100).sum()).item()) < 1e-4

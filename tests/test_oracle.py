@@ -194,3 +194,25 @@ def test_glue_oracles_against_upstream_references():
     assert torch.equal(y, z["rn_y"]) and torch.equal(zs, z["rn_z"].to(zs.dtype))
     assert _err(dx, z["rn_dx"]) < 4e-3 and _err(dx, z["rn_dr"]) < 4e-3
     assert _err(dw, z["rn_dw"]) < 2e-3 * z["rn_dw"].abs().max()
+
+
+def test_cross_entropy_oracle_against_upstream_kernels():
+    """Losses, z-losses and the gradient of the logits against upstream's own fused cross-entropy kernels
+    (tests/golden/cross_entropy.npz): fp32 and fp16 logits, 1003 classes, ignore_index rows, label smoothing,
+    logit scale and z-loss."""
+    from conftest import load_ce_golden
+    cases = load_ce_golden()
+    assert len(cases) == 8
+    for name, c in cases.items():
+        ls, scale, zs = [float(x) for x in c["args"]]
+        losses, zl, dl = orc.cross_entropy_fwd_bwd(c["logits"], c["labels"], c["dloss"], label_smoothing=ls,
+                                                   logit_scale=scale, lse_square_scale=zs)
+        # (with 16-bit logits upstream forms logit_scale * logits[label] and its (1 - smoothing) multiple in the
+        # logits' dtype, lines 65-72: its loss carries that one rounding of a value of magnitude <= 16)
+        loss_tol = 2e-5 * max(1.0, c["losses"].abs().max().item()) if c["logits"].dtype == torch.float32 else 8e-3
+        assert _err(losses, c["losses"]) < loss_tol, name
+        assert _err(zl, c["z_losses"]) < 1e-6, name
+        # upstream returns the gradient in the logits' dtype
+        tol = 1e-6 if c["logits"].dtype == torch.float32 else 2e-3 * c["dlogits"].float().abs().max().item()
+        assert _err(dl, c["dlogits"]) < tol, name
+        assert torch.all(losses[c["labels"] == -100] == 0) and torch.all(dl[c["labels"] == -100] == 0)

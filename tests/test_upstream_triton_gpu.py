@@ -40,8 +40,8 @@ def _upstream_prefix(lf, seq):
     """The prefix sum upstream's forward forms and saves (forgetting_attention.py:111-127)."""
     lf = lf.float()
     if seq is not None:
-        lf = lf.clone()
-        lf[torch.arange(lf.shape[-1], device=lf.device)[None, None, :] < seq[:, None, None]] = 0.0
+        mask = torch.arange(lf.shape[-1], device=lf.device)[None, None, :] < seq[:, None, None]
+        lf = torch.where(mask, torch.zeros_like(lf), lf)
     return torch.cumsum(lf, dim=-1, dtype=lf.dtype).float()
 
 
