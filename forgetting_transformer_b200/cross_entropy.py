@@ -68,7 +68,9 @@ class CrossEntropyLossFunction(torch.autograd.Function):
         logits, lse, target = ctx.saved_tensors
         label_smoothing, logit_scale, lse_square_scale, ignore_index = ctx.args
         n_rows, n_cols = logits.shape
-        dlogits = logits if ctx.inplace_backward else torch.empty_like(logits)
+        # (same row stride as the saved logits: a re-laid class count keeps its 16-byte aligned rows)
+        dlogits = logits if ctx.inplace_backward else torch.empty_strided(logits.shape, logits.stride(),
+                                                                          dtype=logits.dtype, device=logits.device)
         grad_losses = grad_losses.float()
         lib = _lib.load()
         dev = logits.device

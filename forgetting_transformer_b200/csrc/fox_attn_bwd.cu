@@ -253,7 +253,7 @@ fox_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         for (int rr = 0; rr < kBwdBM / 32; ++rr) {
           const float Li = rawL[slot][rr];
           s_e[st][rr * 32 + lane] = (Li == -INFINITY) ? -INFINITY : ((rawLam[slot][rr] - lam_ref) - Li) * kLog2eB;
-          s_delta[st][rr * 32 + lane] = rawD[slot][rr];
+          s_delta[st][rr * 32 + lane] = -rawD[slot][rr];   // (phase B adds it)
         }
         __syncwarp();
         if (elect_one()) mbar_arrive(&bar_q_full[st]);
@@ -493,6 +493,7 @@ fox_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     const uint32_t tS = tbase + lane_base + kColS, tDP = tbase + lane_base + kColDP;
     float colsum = 0.f;
     bool ok = true;
+    const float2 scale2 = make_float2(p.qk_scale, p.qk_scale), negb2 = make_float2(-b_j, -b_j);
 
     for (int it = 0; it < n_tiles; ++it) {
       const int mb = mb_lo + it;
@@ -515,14 +516,18 @@ fox_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         tmem_ld32(tS + col0, sreg);
         tmem_ld_wait();
         const float4* e4 = reinterpret_cast<const float4*>(&s_e[it % STQ][col0]);
+        // packed two-wide fp32 arithmetic: x = s c + (e_i - b_j), one add and one fused multiply-add per column pair
 #pragma unroll
         for (int c4 = 0; c4 < 8; ++c4) {
           const float4 ev = e4[c4];
-          const float es[4] = {ev.x, ev.y, ev.z, ev.w};
+          const float2 x01 = __ffma2_rn(make_float2(__uint_as_float(sreg[c4 * 4]), __uint_as_float(sreg[c4 * 4 + 1])),
+                                        scale2, __fadd2_rn(make_float2(ev.x, ev.y), negb2));
+          const float2 x23 = __ffma2_rn(make_float2(__uint_as_float(sreg[c4 * 4 + 2]), __uint_as_float(sreg[c4 * 4 + 3])),
+                                        scale2, __fadd2_rn(make_float2(ev.z, ev.w), negb2));
+          const float xs[4] = {x01.x, x01.y, x23.x, x23.y};
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
-            const float x = fmaf(__uint_as_float(sreg[c4 * 4 + e]), p.qk_scale, es[e]) - b_j;
-            float pe = fast_exp2(x);
+            float pe = fast_exp2(xs[e]);
             if (diag) pe = (col0 + c4 * 4 + e >= c_min) ? pe : 0.f;
             pf[ch * 32 + c4 * 4 + e] = pe;
           }
@@ -555,12 +560,15 @@ fox_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         const float4* d4 = reinterpret_cast<const float4*>(&s_delta[it % STQ][col0]);
 #pragma unroll
         for (int c4 = 0; c4 < 8; ++c4) {
-          const float4 dv4 = d4[c4];
-          const float dl[4] = {dv4.x, dv4.y, dv4.z, dv4.w};
-          float dsv[4];
-#pragma unroll
-          for (int e = 0; e < 4; ++e)
-            dsv[e] = pf[ch * 32 + c4 * 4 + e] * (__uint_as_float(dpreg[c4 * 4 + e]) - dl[e]);
+          const float4 nd4 = d4[c4];   // -delta_i
+          const int c0 = ch * 32 + c4 * 4;
+          const float2 ds01 = __fmul2_rn(make_float2(pf[c0], pf[c0 + 1]),
+                                         __fadd2_rn(make_float2(__uint_as_float(dpreg[c4 * 4]), __uint_as_float(dpreg[c4 * 4 + 1])),
+                                                    make_float2(nd4.x, nd4.y)));
+          const float2 ds23 = __fmul2_rn(make_float2(pf[c0 + 2], pf[c0 + 3]),
+                                         __fadd2_rn(make_float2(__uint_as_float(dpreg[c4 * 4 + 2]), __uint_as_float(dpreg[c4 * 4 + 3])),
+                                                    make_float2(nd4.z, nd4.w)));
+          const float dsv[4] = {ds01.x, ds01.y, ds23.x, ds23.y};
           const uint32_t d01 = pack2<kBf16>(dsv[0], dsv[1]), d23 = pack2<kBf16>(dsv[2], dsv[3]);
           dsk[c4 * 2] = d01;
           dsk[c4 * 2 + 1] = d23;

@@ -9,8 +9,11 @@ one set of weights:
   * upstream's block after the name patch a maintainer would apply (the snippet in INTEGRATION.md), i.e.
     upstream's module code calling this package's operators.
 
-Outputs are compared element-wise with the bf16 bar (2e-2 + 1e-2 |ref|); input and weight gradients, which
-pass through a dozen 16-bit operators on each side, by their relative error in the Frobenius norm.
+A block is a dozen 16-bit operators on each side and its output a residual sum of their results (an output of
+0.2 can be the sum of a residual of -5.8 and an MLP output of 6.0 that was rounded to 16 bits at that magnitude),
+so outputs are compared with the bf16 bar taken at the magnitude of the largest activation,
+|a - b| <= 2e-2 + 1e-2 max|ref|, and together with the input and weight gradients by their relative error in the
+Frobenius norm.
 """
 import pytest
 import torch
@@ -61,7 +64,8 @@ def _compare(label, ref, got, valid):
     rels = {n: rel(gg[n], rg[n]) for n in rg}
     print(label, "out", round(_bars(go * v, ro * v), 3), "bars; relative errors: dx", round(rel(gdx * v, rdx * v), 4),
           "weights, worst", max(rels, key=rels.get), round(max(rels.values()), 4))
-    _close(go * v, ro * v, ATOL_BF16, RTOL_BF16, label + " out")
+    assert ((go - ro) * v).abs().max().item() <= ATOL_BF16 + RTOL_BF16 * (ro * v).abs().max().item(), label + " out"
+    assert rel(go * v, ro * v) < 1e-2, f"{label} out: relative error {rel(go * v, ro * v):.3e}"
     assert rel(gdx * v, rdx * v) < 2e-2, f"{label} dx: relative error {rel(gdx * v, rdx * v):.3e}"
     for n, r_ in rels.items():
         assert r_ < 3e-2, f"{label} grad of {n}: relative error {r_:.3e}"

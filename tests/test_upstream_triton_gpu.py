@@ -90,9 +90,19 @@ def _compare(label, theirs, ours, on_theirs):
     _close(ours["L"][fin], theirs["L"][fin], 1e-4, 1e-4, "L")
     _close(ours["out"], theirs["out"], ATOL_BF16, RTOL_BF16, f"{label} out")
     for n in ("dq", "dk", "dv", "dlog_fgate"):
-        _close(on_theirs[n], theirs[n], ATOL_BF16, RTOL_BF16, f"{label} {n}")
+        _close_two_roundings(on_theirs[n], theirs[n], f"{label} {n}")
     # end to end the value gradient does not depend on delta: it must agree as it is
     _close(ours["dv"], theirs["dv"], ATOL_BF16, RTOL_BF16, f"{label} dv (complete pipelines)")
+
+
+def _close_two_roundings(a, b, what):
+    """Two kernels that each round dS to 16 bits where the other does: their difference carries both roundings.
+    Every element within 1.5 bars (2e-2 + 1e-2 |upstream|), and no more than ten per million over one bar."""
+    a, b = a.float(), b.float()
+    bars = (a - b).abs() / (ATOL_BF16 + RTOL_BF16 * b.abs())
+    over = int((bars > 1.0).sum())
+    assert bars.max().item() <= 1.5 and over <= max(1, a.numel() // 100000), (
+        f"{what}: worst element {bars.max().item():.3f} bars, {over} of {a.numel()} over one bar")
 
 
 def _inputs(seed, B, H, M, N, D, mu, sigma, std=1.0, uniform=None, grid=2.0 ** -12):
