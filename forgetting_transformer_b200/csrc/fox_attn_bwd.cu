@@ -22,29 +22,21 @@
 // The tensor pipe and the compute warps overlap: while phase B(i) runs the pipe does
 // dV(i) and S(i+1); while phase A(i+1) runs it does dK(i), dP(i+1), dQ(i) (D = 128, where the dQ
 // accumulator has to share columns with S^T / dP^T: dK(i), dQ(i), drain, S(i+1), dP(i+1)).
-// The two halves of the log-gate gradient, colsum(dS) per key and rowsum(dS) per query (upstream lines 1122,
-// 1326), come out of the products themselves: a 16-column "ones" tile appended (through the descriptors'
-// leading offset) to K makes the dQ product also deliver rowsum(dS); at D=64 the same tile appended to Q
-// makes the dK product deliver colsum(dS).  Both halves are thus sums of the same 16-bit dS values and cancel
-// in the reverse prefix sum the way upstream's fp32 sums do; what remains is the rounding of dS, summed over
-// the (query, key) pairs that straddle a position.  With dS in bf16 (8 significant bits) that is 2-4e-2 on the
-// gate gradient.  So for bf16 inputs dS is written as fp16 (11 significant bits: 3-5e-3), scaled by 2^-6 so
-// that it cannot leave the fp16 range (the conversion saturates beyond |dS| = 4e6) -- A and B of a kind::f16
-// product may differ in format (fp16 dS against bf16 K / Q) -- and the products' results are scaled back by
-// 2^6, which is exact.  (FOX_BWD_DS_FP16=0: dS in the input dtype, as upstream rounds it.
-// FOX_BWD_FP32_SUMS=1: sums of the fp32 values instead -- the column sum is a running sum of the thread that
-// owns the KV row, the row sum of a tile a transposing reduction over the 32 lanes of a warp, 31 shuffles --
-// which reproduces upstream's gate gradient to 1e-4 and costs 17 % of the kernel at D=64, measured.)
+// The two halves of the log-gate gradient, colsum(dS) per key and rowsum(dS) per query, are sums of the fp32
+// dS values, as upstream's are (lines 1122, 1326): the column sum is a running sum of the thread that owns
+// the KV row; the row sum of a tile is formed across the 32 lanes of a warp by a transposing reduction
+// (31 shuffles leave lane l with the warp's sum of query column l) after dS has been handed to the tensor
+// pipe, i.e. under the dK / dQ products, and added to the fp32 workspace.  Both halves sum the same values,
+// so they cancel in the reverse prefix sum as upstream's do.  (FOX_BWD_FP32_SUMS=0 builds the earlier form:
+// a 16-column "ones" tile appended to K and Q through the descriptors' leading offset makes the dQ and dK
+// products deliver the sums of the 16-bit dS values, which is free but 2-4e-2 off upstream's gate gradient.)
 #include <type_traits>
 
 #include "fox_common.cuh"
 #include "fox_host.h"
 
 #ifndef FOX_BWD_FP32_SUMS
-#define FOX_BWD_FP32_SUMS 0
-#endif
-#ifndef FOX_BWD_DS_FP16
-#define FOX_BWD_DS_FP16 1
+#define FOX_BWD_FP32_SUMS 1
 #endif
 
 namespace fox {
@@ -93,10 +85,6 @@ fox_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   // drain, no reductions, and at D = 128 no sharing of TMEM columns
   constexpr bool kAliasDQ = (D == 128) && !kNoDQ;  // dQ accumulator shares columns with S^T / dP^T
   constexpr bool kFp32Sums = FOX_BWD_FP32_SUMS != 0;            // gate-gradient sums of the fp32 dS values
-  constexpr bool kDsFp16 = kBf16 && (FOX_BWD_DS_FP16 != 0);     // dS as scaled fp16 although the inputs are bf16
-  constexpr float kDsScale = kDsFp16 ? 0.015625f : 1.f;         // 2^-6 on dS, 2^6 on everything summed from it
-  constexpr float kDsUnscale = kDsFp16 ? 64.f : 1.f;
-  constexpr uint32_t kDsFmt = kDsFp16 ? 0u : kFmt;
   constexpr bool kColsumMMA = (D == 64) && !kNoDQ && !kFp32Sums;  // colsum(dS) from the dK product
   constexpr int STQ = 2;
   constexpr int STDO = (D == 64) ? 2 : 1;
@@ -265,7 +253,7 @@ fox_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         for (int rr = 0; rr < kBwdBM / 32; ++rr) {
           const float Li = rawL[slot][rr];
           s_e[st][rr * 32 + lane] = (Li == -INFINITY) ? -INFINITY : ((rawLam[slot][rr] - lam_ref) - Li) * kLog2eB;
-          s_delta[st][rr * 32 + lane] = -rawD[slot][rr] * kDsScale;   // (phase B: dS kDsScale = p (dP kDsScale - this))
+          s_delta[st][rr * 32 + lane] = -rawD[slot][rr];   // (phase B adds it)
         }
         __syncwarp();
         if (elect_one()) mbar_arrive(&bar_q_full[st]);
@@ -297,8 +285,8 @@ fox_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     if (n_tiles > 0) {
       constexpr uint32_t idS = umma_idesc(kFmt, 128, 128, 0, 0);
       constexpr uint32_t idDV = umma_idesc(kFmt, 128, D, 0, 1);
-      constexpr uint32_t idDK = umma_idesc_ab(kDsFmt, kFmt, 128, kNdk, 0, 1);   // A = dS^T (TMEM), B = [Q | 1]
-      constexpr uint32_t idDQ = umma_idesc_ab(kDsFmt, kFmt, 128, kNdq, 1, 1);   // A = dS (smem),   B = [K | 1]
+      constexpr uint32_t idDK = umma_idesc(kFmt, 128, kNdk, 0, 1);
+      constexpr uint32_t idDQ = umma_idesc(kFmt, 128, kNdq, 1, 1);
       // Operand descriptors are built once; inside the loops only the start-address field moves
       // (the issuing thread must stay far ahead of the tensor pipe, so its instruction count matters).
       const uint32_t q_base = smem_u32(sQ), do_base = smem_u32(sDO), ones0 = smem_u32(sOnes);
@@ -459,10 +447,6 @@ fox_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           tmem_ld32(tDQ + (round * kStageSub + sub) * 32, v);
           tmem_ld_wait();
           uint8_t* srow = sStage + sub * 16384 + r * 128;
-          if constexpr (kDsFp16) {
-#pragma unroll
-            for (int c = 0; c < 32; ++c) v[c] = __float_as_uint(__uint_as_float(v[c]) * kDsUnscale);
-          }
 #pragma unroll
           for (int q4 = 0; q4 < 8; ++q4)
             *reinterpret_cast<uint4*>(srow + ((q4 ^ (r & 7)) << 4)) =
@@ -491,7 +475,7 @@ fox_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       }
       if (!ok) break;
       if (warp == kDrainWarp0) stamp(1, 2, it);
-      if (!kFp32Sums && i < M) atomicAdd(p.dlam_row + bh * M + i, __uint_as_float(rs[0]) * kDsUnscale);
+      if (!kFp32Sums && i < M) atomicAdd(p.dlam_row + bh * M + i, __uint_as_float(rs[0]));
     }
     if (warp == kDrainWarp0) tma_store_wait_all<0>();
   } else {
@@ -510,7 +494,6 @@ fox_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     float colsum = 0.f;
     bool ok = true;
     const float2 scale2 = make_float2(p.qk_scale, p.qk_scale), negb2 = make_float2(-b_j, -b_j);
-    const float2 dscale2 = make_float2(kDsScale, kDsScale);
 
     for (int it = 0; it < n_tiles; ++it) {
       const int mb = mb_lo + it;
@@ -580,14 +563,13 @@ fox_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           const float4 nd4 = d4[c4];   // -delta_i
           const int c0 = ch * 32 + c4 * 4;
           const float2 ds01 = __fmul2_rn(make_float2(pf[c0], pf[c0 + 1]),
-                                         __ffma2_rn(make_float2(__uint_as_float(dpreg[c4 * 4]), __uint_as_float(dpreg[c4 * 4 + 1])),
-                                                    dscale2, make_float2(nd4.x, nd4.y)));
+                                         __fadd2_rn(make_float2(__uint_as_float(dpreg[c4 * 4]), __uint_as_float(dpreg[c4 * 4 + 1])),
+                                                    make_float2(nd4.x, nd4.y)));
           const float2 ds23 = __fmul2_rn(make_float2(pf[c0 + 2], pf[c0 + 3]),
-                                         __ffma2_rn(make_float2(__uint_as_float(dpreg[c4 * 4 + 2]), __uint_as_float(dpreg[c4 * 4 + 3])),
-                                                    dscale2, make_float2(nd4.z, nd4.w)));
+                                         __fadd2_rn(make_float2(__uint_as_float(dpreg[c4 * 4 + 2]), __uint_as_float(dpreg[c4 * 4 + 3])),
+                                                    make_float2(nd4.z, nd4.w)));
           const float dsv[4] = {ds01.x, ds01.y, ds23.x, ds23.y};
-          const uint32_t d01 = kDsFp16 ? pack2_f16_sat(dsv[0], dsv[1]) : pack2<kBf16>(dsv[0], dsv[1]);
-          const uint32_t d23 = kDsFp16 ? pack2_f16_sat(dsv[2], dsv[3]) : pack2<kBf16>(dsv[2], dsv[3]);
+          const uint32_t d01 = pack2<kBf16>(dsv[0], dsv[1]), d23 = pack2<kBf16>(dsv[2], dsv[3]);
           dsk[c4 * 2] = d01;
           dsk[c4 * 2 + 1] = d23;
           if constexpr (kNoDQ || kFp32Sums) {
@@ -599,7 +581,7 @@ fox_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
               for (int e = 0; e < 4; ++e) pf[ch * 32 + c4 * 4 + e] = dsv[e];   // p is no longer needed
             }
           } else if (!kColsumMMA) {
-            const float2 r01 = unpack2<kBf16 && !kDsFp16>(d01), r23 = unpack2<kBf16 && !kDsFp16>(d23);
+            const float2 r01 = unpack2<kBf16>(d01), r23 = unpack2<kBf16>(d23);
             colsum += (r01.x + r01.y) + (r23.x + r23.y);
           }
         }
@@ -634,7 +616,7 @@ fox_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             }
           }
           const int i = mb * kBwdBM + g * CW + ch * 32 + lane;
-          if (i < M) atomicAdd(p.dlam_row + bh * M + i, vsum[0] * kDsUnscale);
+          if (i < M) atomicAdd(p.dlam_row + bh * M + i, vsum[0]);
         }
       }
     }
@@ -667,7 +649,7 @@ fox_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       const int which = g / kPer, part_c = (g % kPer) * kCols;
       const bool keep = j_ok && n_tiles > 0;
       const uint32_t tcol = tbase + lane_base + (which == 0 ? kColDK : kColDV) + part_c;
-      const float sc = which == 0 ? p.sm_scale * kDsUnscale : 1.f;
+      const float sc = which == 0 ? p.sm_scale : 1.f;
       uint16_t* orow = (which == 0
           ? reinterpret_cast<uint16_t*>(p.dk) + b * p.dk_sb + h * p.dk_sh + static_cast<int64_t>(j) * p.dk_st
           : reinterpret_cast<uint16_t*>(p.dv) + b * p.dv_sb + h * p.dv_sh + static_cast<int64_t>(j) * p.dv_st) + part_c;
@@ -699,7 +681,7 @@ fox_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           tmem_ld_wait();
           colsum = __uint_as_float(cs[0]);
         }
-        if (j < N) p.dlam_col[bh * N + j] = keep ? -colsum * kDsUnscale : 0.f;
+        if (j < N) p.dlam_col[bh * N + j] = keep ? -colsum : 0.f;
       }
     }
   }

@@ -344,20 +344,7 @@ __host__ __device__ constexpr uint32_t umma_idesc(uint32_t fmt, uint32_t m, uint
          ((m >> 4) << 24);
 }
 
-// Same with separate operand formats: A and B of a kind::f16 product may each be fp16 or bf16.
-__host__ __device__ constexpr uint32_t umma_idesc_ab(uint32_t a_fmt, uint32_t b_fmt, uint32_t m, uint32_t n,
-                                                     uint32_t a_mn_major, uint32_t b_mn_major) {
-  return (1u << 4) | (a_fmt << 7) | (b_fmt << 10) | (a_mn_major << 15) | (b_mn_major << 16) | ((n >> 3) << 17) |
-         ((m >> 4) << 24);
-}
-
 // ------------------------------------------------------------------- helpers
-// two fp32 -> packed fp16 pair, round to nearest, values beyond the fp16 range clamped to the largest finite one
-__device__ __forceinline__ uint32_t pack2_f16_sat(float lo, float hi) {
-  uint32_t r;
-  asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
-  return r;
-}
 template <bool kBf16>
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
   if constexpr (kBf16) {
