@@ -27,9 +27,15 @@
 // the KV row; the row sum of a tile is formed across the 32 lanes of a warp by a transposing reduction
 // (31 shuffles leave lane l with the warp's sum of query column l) after dS has been handed to the tensor
 // pipe, i.e. under the dK / dQ products, and added to the fp32 workspace.  Both halves sum the same values,
-// so they cancel in the reverse prefix sum as upstream's do.  (FOX_BWD_FP32_SUMS=0 builds the earlier form:
-// a 16-column "ones" tile appended to K and Q through the descriptors' leading offset makes the dQ and dK
-// products deliver the sums of the 16-bit dS values, which is free but 2-4e-2 off upstream's gate gradient.)
+// so they cancel in the reverse prefix sum as upstream's do; against upstream's own backward kernels on the
+// same saved tensors the gate gradient then agrees to 1e-4.  The reduction sits on the elementwise warps' own
+// chain (phase A -> phase B -> reduction -> next tile) and costs 0.7 ms of 4.2 ms on B2 T16384 H24 D64.
+// (FOX_BWD_FP32_SUMS=0 builds the earlier form: a 16-column "ones" tile appended to K and Q through the
+// descriptors' leading offset makes the dQ and dK products deliver the sums of the 16-bit dS values -- free,
+// but the rounding of dS to 8 significant bits, summed over the (query, key) pairs that straddle a position,
+// leaves the gate gradient 2-4e-2 off upstream's, up to 1.8 times the tolerance.  Writing dS as fp16 for bf16
+// inputs, to keep the free sums at 11 significant bits, is not an option: a kind::f16 product whose A and B
+// operands differ in format raises an illegal-instruction error on sm_100a.)
 #include <type_traits>
 
 #include "fox_common.cuh"
