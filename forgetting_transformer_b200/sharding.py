@@ -18,9 +18,9 @@ Two schemes, neither present upstream (which only knows data-parallel training):
   ``seqlen_q <= seqlen_k`` contract (queries are the last rows), reading the staging buffer
   through strided views, no reordering copies.  Rows are complete on their owner, so no partial
   (max, sum, out) triples have to travel; the log-gate prefix is recomputed from the gathered
-  gates by the operator's own prefix-sum kernel.  Backward: the upper chunk's call first, the
-  reduce-scatter of the upper halves' key / value / gate gradients runs under the lower chunk's
-  backward, the lower halves follow.  Tiles are only ever read from this GPU's own memory.
+  gates by the operator's own prefix-sum kernel.  Backward: both calls, then one reduce-scatter
+  per tensor of the key / value / gate gradients arranged by owner.  Tiles are only ever read from
+  this GPU's own memory.
 """
 from __future__ import annotations
 
@@ -30,7 +30,7 @@ import torch
 import torch.distributed as dist
 
 __all__ = ["unit_slice", "shard_batch_heads", "zigzag_chunks", "ContextParallelAttention",
-           "context_parallel_attention", "context_parallel_threshold"]
+           "context_parallel_attention", "context_parallel_threshold", "context_parallel_group"]
 
 
 # ----------------------------------------------------------------------------- batch x head
@@ -82,6 +82,18 @@ def _wait(work):
         work.wait()
 
 
+# Optional stopwatch for the phases of a context-parallel step: when set to a list, (label, CUDA event) pairs are
+# appended at the phase boundaries on the current stream (benchmark / profiling scripts read them back).
+PHASE_TRACE = None
+
+
+def _mark(label: str) -> None:
+    if PHASE_TRACE is not None:
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record()
+        PHASE_TRACE.append((label, ev))
+
+
 def _seq_major(x: torch.Tensor) -> torch.Tensor:
     """(B, H, t, ...) -> contiguous (t, B, H, ...)."""
     return x.movedim(2, 0).contiguous()
@@ -92,6 +104,21 @@ def _head_first(x: torch.Tensor) -> torch.Tensor:
     return x.movedim(0, 2)
 
 
+def context_parallel_group(ranks: Optional[Sequence[int]] = None):
+    """A process group for :func:`context_parallel_attention` whose NCCL kernels run on a high-priority stream.
+
+    The second wave of gathers and the first reduce-scatter travel while an attention kernel occupies every SM;
+    on a stream of default priority the collective's few thread blocks queue behind thousands of attention
+    blocks and a 0.3 ms transfer takes 3 ms (measured on two B200s).  With a high-priority stream they take
+    the next SMs that become free.  Falls back to an ordinary group for other backends (gloo in the CPU tests).
+    Collective call: every rank of the default group must call it."""
+    if dist.get_backend() != "nccl":
+        return dist.new_group(ranks=ranks)
+    opts = dist.ProcessGroupNCCL.Options()
+    opts.is_high_priority_stream = True
+    return dist.new_group(ranks=ranks, backend="nccl", pg_options=opts)
+
+
 class _ContextParallel(torch.autograd.Function):
     """Forward and backward of the zig-zag context-parallel attention as one autograd node, so that the
     collectives, the two operator calls per direction and their overlap are scheduled by hand."""
@@ -99,6 +126,7 @@ class _ContextParallel(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, log_fgate, seq_start, sm_scale, threshold, group, attn_fn):
         world, rank = dist.get_world_size(group), dist.get_rank(group)
+        _mark("fwd begin")
         B, H, t2, D = q.shape
         tc = t2 // 2
         P = world
@@ -137,15 +165,19 @@ class _ContextParallel(torch.autograd.Function):
         Gf[P * tc:].view(P, tc, B, H).copy_(g_all[:, 1].flip(0))
         _wait(w_k1)
         _wait(w_v1)
+        _mark("lower halves gathered")
         n_lo, n_hi = (lo_c + 1) * tc, (hi_c + 1) * tc
         out_lo, leaves_lo = call(q[:, :, :tc], n_lo)              # runs while wave 2 travels
+        _mark("lower chunk forward")
         _wait(w_k2)
         _wait(w_v2)
         # (written through aliases with their own version counter: the lower call's saved views share the
         # allocation but cover only rows below P*tc, which stay as they are)
         Kf.data[P * tc:].view(P, tc, B, H, D).copy_(up_k.flip(0))
         Vf.data[P * tc:].view(P, tc, B, H, D).copy_(up_v.flip(0))
+        _mark("upper halves gathered")
         out_hi, leaves_hi = call(q[:, :, tc:], n_hi)
+        _mark("upper chunk forward")
         ctx.graph = (out_lo, leaves_lo, out_hi, leaves_hi)
         ctx.geom = (group, P, rank, B, H, D, tc)
         return torch.cat([out_lo.detach(), out_hi.detach()], dim=2)
@@ -163,31 +195,34 @@ class _ContextParallel(torch.autograd.Function):
             g = g.movedim(2, 0)
             return g if g.is_contiguous() else g.contiguous()
 
-        # upper chunk first: only it contributes to the upper halves, whose reduce-scatter then runs
-        # under the lower chunk's backward
         dq_hi, dk_hi, dv_hi, dg_hi = torch.autograd.grad(out_hi, leaves_hi, dout[:, :, tc:])
-        dk_hi, dv_hi, dg_hi = seq_major_mem(dk_hi), seq_major_mem(dv_hi), seq_major_mem(dg_hi)
-        mine, works = {}, []
-        for name, g_hi in (("k", dk_hi), ("v", dv_hi), ("g", dg_hi)):
-            # slab i of the input belongs to rank i, i.e. to chunk 2P-1-i; this rank saw chunks up to 2P-1-rank
-            tail = g_hi.shape[1:]
-            inp = torch.zeros((P, tc) + tail, dtype=g_hi.dtype, device=dev)
-            inp[rank:].copy_(g_hi[P * tc:].view((P - rank, tc) + tail).flip(0))
-            out = torch.empty((tc,) + tail, dtype=g_hi.dtype, device=dev)
-            works.append(_reduce_scatter(out, inp, group, True))
-            mine[name + "_hi"] = out
+        _mark("upper chunk backward")
         dq_lo, dk_lo, dv_lo, dg_lo = torch.autograd.grad(out_lo, leaves_lo, dout[:, :, :tc])
+        _mark("lower chunk backward")
+        # One reduce-scatter per tensor, after both calls: slab i of its input is what rank i owns, the pair
+        # (chunk i, chunk 2P-1-i).  (Queued earlier, under the second call, the collective would spin on its
+        # SMs until the slowest rank's first call has finished -- ranks finish it at very different times.)
+        mine, works = {}, []
         for name, g_hi, g_lo in (("k", dk_hi, dk_lo), ("v", dv_hi, dv_lo), ("g", dg_hi, dg_lo)):
-            g_hi[:n_lo] += seq_major_mem(g_lo)
-            out = torch.empty((tc,) + g_hi.shape[1:], dtype=g_hi.dtype, device=dev)
-            works.append(_reduce_scatter(out, g_hi[:P * tc], group, True))     # chunk j belongs to rank j
-            mine[name + "_lo"] = out
+            g_hi, g_lo = seq_major_mem(g_hi), seq_major_mem(g_lo)
+            tail = g_hi.shape[1:]
+            inp = torch.empty((P, 2, tc) + tail, dtype=g_hi.dtype, device=dev)
+            inp[:, 0].copy_(g_hi[:P * tc].view((P, tc) + tail))
+            inp[:rank + 1, 0] += g_lo.view((rank + 1, tc) + tail)        # the lower call saw chunks 0..rank
+            inp[:rank, 1].zero_()                                        # chunks above 2P-1-rank: never seen
+            inp[rank:, 1].copy_(g_hi[P * tc:].view((P - rank, tc) + tail).flip(0))
+            out = torch.empty((2, tc) + tail, dtype=g_hi.dtype, device=dev)
+            works.append(_reduce_scatter(out, inp, group, True))
+            mine[name] = out
+        _mark("reduce-scatter queued")
         for w in works:
             _wait(w)
-        dk = _head_first(torch.cat([mine["k_lo"], mine["k_hi"]], dim=0))
-        dv = _head_first(torch.cat([mine["v_lo"], mine["v_hi"]], dim=0))
-        dg = _head_first(torch.cat([mine["g_lo"], mine["g_hi"]], dim=0))
+        _mark("gradients reduce-scattered")
+        dk = _head_first(mine["k"].view((2 * tc,) + mine["k"].shape[2:]))
+        dv = _head_first(mine["v"].view((2 * tc,) + mine["v"].shape[2:]))
+        dg = _head_first(mine["g"].view((2 * tc,) + mine["g"].shape[2:]))
         dq = torch.cat([dq_lo, dq_hi], dim=2)
+        _mark("bwd end")
         return dq, dk, dv, dg, None, None, None, None, None
 
 
