@@ -281,9 +281,10 @@ def context_parallel_leg(world, rank, dev, steps=5, warmup=3):
             "ms_per_step": ms, "tflops": flops / (ms * 1e-3) / 1e12, "one_gpu_ms": one_gpu_ms,
             "one_gpu_tflops": flops / (one_gpu_ms * 1e-3) / 1e12, "speedup": one_gpu_ms / ms,
             "efficiency": one_gpu_ms / (world * ms), "steps": steps, "warmup": warmup,
-            "exchange": "two waves of NCCL all-gathers of K, V (sequence-major staging; the second under the first "
-                        "chunk's forward) and the log gates, one reduce-scatter per gradient tensor; NCCL kernels on "
-                        "a high-priority stream; no collective inside the kernels"}
+            "exchange": "batched NCCL point-to-point transfers of K, V and log-gate chunk slabs into sequence-major "
+                        "staging (two waves, the second under the first chunk's forward), partial gradients sent to "
+                        "each chunk's owner and summed in fp32; NCCL kernels on a high-priority stream; no "
+                        "collective inside the kernels"}
 
 
 # --------------------------------------------------------------------------- upstream's Triton operator
@@ -708,8 +709,8 @@ def run_ours(args, w, wname):
             "config": {"workload": wname, "description": DESCR[wname], "per_gpu_batch": w["B"],
                        "global_batch": w["B"] * (1 if cp else world), "seq_len": w["T"], "heads": w["H"],
                        "head_dim": w["D"],
-                       "sharding": ("context parallel: zig-zag sequence chunks, two waves of NCCL all-gathers of K, V "
-                                    "and log gates, reduce-scatter of their gradients") if cp else
+                       "sharding": ("context parallel: zig-zag sequence chunks, batched NCCL point-to-point transfers of "
+                                    "K, V and log-gate chunk slabs, partial gradients summed by the owner") if cp else
                                    "independent (batch, head) units per rank, no collective",
                        "l2": "inputs (>=400 MB per step) larger than the 126 MB L2; no explicit flush",
                        "algorithmic_flops_per_step_per_gpu": flops,

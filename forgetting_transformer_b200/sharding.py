@@ -9,18 +9,18 @@ Two schemes, neither present upstream (which only knows data-parallel training):
   contiguous slice of the flattened units and no collective touches the data path.
 
 * context parallel for long sequences -- the sequence is cut into 2P chunks and rank r owns
-  chunks r and 2P-1-r ("zig-zag": causal work is balanced).  Keys, values and log gates are
-  gathered into a sequence-major staging buffer (T, B, H, D) in two waves of asynchronous
-  collectives: the lower halves (chunks 0..P-1, one per rank, landing in natural order), after
-  which a rank's lower query chunk can already run, and the upper halves (chunks P..2P-1),
-  which travel while that first call computes.  Each query chunk is one call of the ordinary
+  chunks r and 2P-1-r ("zig-zag": causal work is balanced).  Keys, values and log gates travel
+  point to point (batched NCCL sends / receives) into a sequence-major staging buffer
+  (T', B, H, D) in two waves: the lower halves (chunks 0..P-1, one per rank), after which a
+  rank's lower query chunk can already run, and the upper halves a rank may attend to (chunks
+  P..2P-1-r), which travel while that first call computes.  Each query chunk is one call of the ordinary
   operator against the key prefix it may attend to -- exactly the operator's
   ``seqlen_q <= seqlen_k`` contract (queries are the last rows), reading the staging buffer
   through strided views, no reordering copies.  Rows are complete on their owner, so no partial
   (max, sum, out) triples have to travel; the log-gate prefix is recomputed from the gathered
-  gates by the operator's own prefix-sum kernel.  Backward: both calls, then one reduce-scatter
-  per tensor of the key / value / gate gradients arranged by owner.  Tiles are only ever read from
-  this GPU's own memory.
+  gates by the operator's own prefix-sum kernel.  Backward: both calls, then every chunk's partial
+  key / value / gate gradient is sent to the chunk's owner, who sums in fp32.  Tiles are only ever
+  read from this GPU's own memory.
 """
 from __future__ import annotations
 
@@ -68,15 +68,6 @@ def zigzag_chunks(world: int, rank: int) -> Tuple[int, int]:
     return rank, 2 * world - 1 - rank
 
 
-def _reduce_scatter(out: torch.Tensor, inp: torch.Tensor, group, async_op: bool):
-    """reduce_scatter_tensor; gloo (CPU tests) has none: all-reduce and keep this rank's slab."""
-    if dist.get_backend(group) == "gloo":
-        dist.all_reduce(inp, group=group)
-        out.copy_(inp.view(dist.get_world_size(group), -1)[dist.get_rank(group)].view_as(out))
-        return None
-    return dist.reduce_scatter_tensor(out, inp, op=dist.ReduceOp.SUM, group=group, async_op=async_op)
-
-
 def _wait(work):
     if work is not None:
         work.wait()
@@ -92,11 +83,6 @@ def _mark(label: str) -> None:
         ev = torch.cuda.Event(enable_timing=True)
         ev.record()
         PHASE_TRACE.append((label, ev))
-
-
-def _seq_major(x: torch.Tensor) -> torch.Tensor:
-    """(B, H, t, ...) -> contiguous (t, B, H, ...)."""
-    return x.movedim(2, 0).contiguous()
 
 
 def _head_first(x: torch.Tensor) -> torch.Tensor:
@@ -119,9 +105,28 @@ def context_parallel_group(ranks: Optional[Sequence[int]] = None):
     return dist.new_group(ranks=ranks, backend="nccl", pg_options=opts)
 
 
+def _owner(chunk: int, world: int) -> int:
+    """Rank that owns a chunk of the zig-zag split."""
+    return chunk if chunk < world else 2 * world - 1 - chunk
+
+
+def _exchange(ops_list):
+    """Post a list of (kind, tensor, peer global rank, group) point-to-point operations as one batch; returns
+    the requests to wait on.  Every tensor is a contiguous slab that is sent from / received into its final
+    place, so nothing is reordered or copied around the transfer."""
+    if not ops_list:
+        return []
+    return dist.batch_isend_irecv([dist.P2POp(dist.isend if kind == "send" else dist.irecv, t, peer, group)
+                                   for kind, t, peer, group in ops_list])
+
+
 class _ContextParallel(torch.autograd.Function):
     """Forward and backward of the zig-zag context-parallel attention as one autograd node, so that the
-    collectives, the two operator calls per direction and their overlap are scheduled by hand."""
+    transfers, the two operator calls per direction and their overlap are scheduled by hand.
+
+    Data movement is point to point (one batched group of NCCL sends / receives per wave): chunk slabs travel
+    between the sequence-major staging buffers of their owner and of the ranks that attend to them, straight
+    into place; causality halves the upper half's traffic (rank r only ever sees chunks up to 2P-1-r)."""
 
     @staticmethod
     def forward(ctx, q, k, v, log_fgate, seq_start, sm_scale, threshold, group, attn_fn):
@@ -132,23 +137,35 @@ class _ContextParallel(torch.autograd.Function):
         P = world
         T = 2 * P * tc
         lo_c, hi_c = zigzag_chunks(P, rank)
+        n_lo, n_hi = (lo_c + 1) * tc, (hi_c + 1) * tc
         dev, dt = k.device, k.dtype
-        # sequence-major staging: chunk j is the contiguous slab [j*tc, (j+1)*tc)
-        Kf = torch.empty((T, B, H, D), dtype=dt, device=dev)
-        Vf = torch.empty((T, B, H, D), dtype=dt, device=dev)
-        Gf = torch.empty((T, B, H), dtype=log_fgate.dtype, device=dev)
-        up_k = torch.empty((P, tc, B, H, D), dtype=dt, device=dev)
-        up_v = torch.empty((P, tc, B, H, D), dtype=dt, device=dev)
-        g_all = torch.empty((P, 2, tc, B, H), dtype=log_fgate.dtype, device=dev)
-        k_sm, v_sm = _seq_major(k), _seq_major(v)                 # (2tc, B, H, D): lower chunk, upper chunk
-        g_sm = _seq_major(log_fgate).view(2, tc, B, H)
-        # wave 1: gates and the lower halves (rank r owns chunk r: they land in natural order);
-        # wave 2: the upper halves (rank r owns chunk 2P-1-r: reversed afterwards)
-        w_g = dist.all_gather_into_tensor(g_all.view(P * 2, tc, B, H), g_sm, group=group, async_op=True)
-        w_k1 = dist.all_gather_into_tensor(Kf[:P * tc], k_sm[:tc], group=group, async_op=True)
-        w_v1 = dist.all_gather_into_tensor(Vf[:P * tc], v_sm[:tc], group=group, async_op=True)
-        w_k2 = dist.all_gather_into_tensor(up_k.view(P * tc, B, H, D), k_sm[tc:], group=group, async_op=True)
-        w_v2 = dist.all_gather_into_tensor(up_v.view(P * tc, B, H, D), v_sm[tc:], group=group, async_op=True)
+        peer = [dist.get_global_rank(group, j) for j in range(P)]
+        # sequence-major staging of the keys this rank attends to: chunk j is the contiguous slab
+        # [j*tc, (j+1)*tc); own chunks are copied in, the others received in place
+        Kf = torch.empty((n_hi, B, H, D), dtype=dt, device=dev)
+        Vf = torch.empty((n_hi, B, H, D), dtype=dt, device=dev)
+        Gf = torch.empty((n_hi, B, H), dtype=log_fgate.dtype, device=dev)
+        slab = lambda buf, c: buf.data[c * tc:(c + 1) * tc]     # (alias with its own version counter, see below)
+        for buf, src in ((Kf, k), (Vf, v), (Gf, log_fgate)):
+            slab(buf, lo_c).copy_(src[:, :, :tc].movedim(2, 0))
+            slab(buf, hi_c).copy_(src[:, :, tc:].movedim(2, 0))
+        # wave 1: the lower halves (chunk j < P lives on rank j; every rank attends to all of them) and all gates;
+        # wave 2: the upper halves this rank may attend to (chunks P .. hi_c, owned by the ranks above this one)
+        wave1, wave2 = [], []
+        for j in range(P):
+            if j == rank:
+                continue
+            for buf in (Kf, Vf, Gf):
+                wave1.append(("send", slab(buf, lo_c), peer[j], group))
+                wave1.append(("recv", slab(buf, j), peer[j], group))
+            if j < rank:        # rank j attends to chunks up to 2P-1-j, which include this rank's upper chunk
+                for buf in (Kf, Vf, Gf):
+                    wave2.append(("send", slab(buf, hi_c), peer[j], group))
+            else:               # and this rank to the upper chunk of every rank above it
+                for buf in (Kf, Vf, Gf):
+                    wave2.append(("recv", slab(buf, 2 * P - 1 - j), peer[j], group))
+        reqs1 = _exchange(wave1)
+        reqs2 = _exchange(wave2)
 
         def call(q_c, n):
             """The operator on one query chunk against keys [0, n), on views of the staging buffers."""
@@ -160,21 +177,15 @@ class _ContextParallel(torch.autograd.Function):
                               adaptive_threshold=threshold)
             return out, leaves
 
-        _wait(w_g)
-        Gf[:P * tc].view(P, tc, B, H).copy_(g_all[:, 0])
-        Gf[P * tc:].view(P, tc, B, H).copy_(g_all[:, 1].flip(0))
-        _wait(w_k1)
-        _wait(w_v1)
+        for r_ in reqs1:
+            r_.wait()
         _mark("lower halves gathered")
-        n_lo, n_hi = (lo_c + 1) * tc, (hi_c + 1) * tc
         out_lo, leaves_lo = call(q[:, :, :tc], n_lo)              # runs while wave 2 travels
         _mark("lower chunk forward")
-        _wait(w_k2)
-        _wait(w_v2)
-        # (written through aliases with their own version counter: the lower call's saved views share the
-        # allocation but cover only rows below P*tc, which stay as they are)
-        Kf.data[P * tc:].view(P, tc, B, H, D).copy_(up_k.flip(0))
-        Vf.data[P * tc:].view(P, tc, B, H, D).copy_(up_v.flip(0))
+        # (wave 2 lands in rows at and above P*tc of the same allocations, through aliases with their own version
+        # counter: the lower call's saved views cover only rows below that, which stay as they are)
+        for r_ in reqs2:
+            r_.wait()
         _mark("upper halves gathered")
         out_hi, leaves_hi = call(q[:, :, tc:], n_hi)
         _mark("upper chunk forward")
@@ -187,40 +198,58 @@ class _ContextParallel(torch.autograd.Function):
         out_lo, leaves_lo, out_hi, leaves_hi = ctx.graph
         group, P, rank, B, H, D, tc = ctx.geom
         ctx.graph = None
-        n_lo, n_hi = leaves_lo[1].shape[2], leaves_hi[1].shape[2]
+        lo_c, hi_c = zigzag_chunks(P, rank)
+        n_lo = (lo_c + 1) * tc
         dev = dout.device
+        peer = [dist.get_global_rank(group, j) for j in range(P)]
 
         def seq_major_mem(g):
             """Gradient of a (B, H, n, ...) view of sequence-major memory, as (n, B, H, ...) contiguous."""
             g = g.movedim(2, 0)
             return g if g.is_contiguous() else g.contiguous()
 
+        _mark("bwd begin")
         dq_hi, dk_hi, dv_hi, dg_hi = torch.autograd.grad(out_hi, leaves_hi, dout[:, :, tc:])
         _mark("upper chunk backward")
         dq_lo, dk_lo, dv_lo, dg_lo = torch.autograd.grad(out_lo, leaves_lo, dout[:, :, :tc])
         _mark("lower chunk backward")
-        # One reduce-scatter per tensor, after both calls: slab i of its input is what rank i owns, the pair
-        # (chunk i, chunk 2P-1-i).  (Queued earlier, under the second call, the collective would spin on its
-        # SMs until the slowest rank's first call has finished -- ranks finish it at very different times.)
-        mine, works = {}, []
+        # Every chunk's partial gradient goes to the chunk's owner, straight from its slab; the owner sums what
+        # arrives in fp32.  Posted after both calls: ranks finish their first call at very different times, and a
+        # transfer posted under the second call would spin on its SMs until the slowest rank arrives.
+        ops_list, recv, mine = [], {}, {}
         for name, g_hi, g_lo in (("k", dk_hi, dk_lo), ("v", dv_hi, dv_lo), ("g", dg_hi, dg_lo)):
             g_hi, g_lo = seq_major_mem(g_hi), seq_major_mem(g_lo)
+            g_hi[:n_lo] += g_lo                                   # chunks both calls attended to
+            mine[name] = g_hi
             tail = g_hi.shape[1:]
-            inp = torch.empty((P, 2, tc) + tail, dtype=g_hi.dtype, device=dev)
-            inp[:, 0].copy_(g_hi[:P * tc].view((P, tc) + tail))
-            inp[:rank + 1, 0] += g_lo.view((rank + 1, tc) + tail)        # the lower call saw chunks 0..rank
-            inp[:rank, 1].zero_()                                        # chunks above 2P-1-rank: never seen
-            inp[rank:, 1].copy_(g_hi[P * tc:].view((P - rank, tc) + tail).flip(0))
-            out = torch.empty((2, tc) + tail, dtype=g_hi.dtype, device=dev)
-            works.append(_reduce_scatter(out, inp, group, True))
-            mine[name] = out
-        _mark("reduce-scatter queued")
-        for w in works:
-            _wait(w)
-        _mark("gradients reduce-scattered")
-        dk = _head_first(mine["k"].view((2 * tc,) + mine["k"].shape[2:]))
-        dv = _head_first(mine["v"].view((2 * tc,) + mine["v"].shape[2:]))
-        dg = _head_first(mine["g"].view((2 * tc,) + mine["g"].shape[2:]))
+            # senders of this rank's lower chunk: everyone; of its upper chunk: the ranks below it
+            recv[name] = (torch.empty((P - 1, tc) + tail, dtype=g_hi.dtype, device=dev),
+                          torch.empty((rank, tc) + tail, dtype=g_hi.dtype, device=dev))
+        for j in range(P):
+            if j == rank:
+                continue
+            for name in ("k", "v", "g"):
+                g_hi = mine[name]
+                ops_list.append(("send", g_hi[j * tc:(j + 1) * tc], peer[j], group))            # chunk j (lower half)
+                ops_list.append(("recv", recv[name][0][j if j < rank else j - 1], peer[j], group))
+                if j > rank:     # chunk 2P-1-j is below this rank's horizon 2P-1-rank: it has a partial for it
+                    c = 2 * P - 1 - j
+                    ops_list.append(("send", g_hi[c * tc:(c + 1) * tc], peer[j], group))
+                else:            # and the ranks below this one have partials for this rank's upper chunk
+                    ops_list.append(("recv", recv[name][1][j], peer[j], group))
+        reqs = _exchange(ops_list)
+        _mark("gradient exchange posted")
+        for r_ in reqs:
+            r_.wait()
+        _mark("gradients exchanged")
+        grads = []
+        for name in ("k", "v", "g"):
+            g_hi = mine[name]
+            own_lo, own_hi = g_hi[lo_c * tc:(lo_c + 1) * tc], g_hi[hi_c * tc:(hi_c + 1) * tc]
+            lo = (own_lo.float() + recv[name][0].sum(0, dtype=torch.float32)) if P > 1 else own_lo.float()
+            hi = (own_hi.float() + recv[name][1].sum(0, dtype=torch.float32)) if rank > 0 else own_hi.float()
+            grads.append(_head_first(torch.cat([lo.to(g_hi.dtype), hi.to(g_hi.dtype)], dim=0)))
+        dk, dv, dg = grads
         dq = torch.cat([dq_lo, dq_hi], dim=2)
         _mark("bwd end")
         return dq, dk, dv, dg, None, None, None, None, None

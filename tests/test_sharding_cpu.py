@@ -101,9 +101,9 @@ def _cp_worker(rank, world, port, ret):
         dist.destroy_process_group()
 
 
-@pytest.mark.timeout(120)
-def test_context_parallel_matches_unsharded_world2():
-    world = 2
+@pytest.mark.timeout(240)
+@pytest.mark.parametrize("world", [2, 4])
+def test_context_parallel_matches_unsharded(world):
     mgr = mp.Manager()
     ret = mgr.dict()
     mp.spawn(_cp_worker, args=(world, _free_port(), ret), nprocs=world, join=True)
