@@ -124,9 +124,10 @@ class _ContextParallel(torch.autograd.Function):
     """Forward and backward of the zig-zag context-parallel attention as one autograd node, so that the
     transfers, the two operator calls per direction and their overlap are scheduled by hand.
 
-    Data movement is point to point (one batched group of NCCL sends / receives per wave): chunk slabs travel
-    between the sequence-major staging buffers of their owner and of the ranks that attend to them, straight
-    into place; causality halves the upper half's traffic (rank r only ever sees chunks up to 2P-1-r)."""
+    The lower halves (chunk j on rank j, needed by everyone) move by all-gather / reduce-scatter, which land
+    them in natural order as they lie; the upper halves move point to point (one batched group of NCCL sends /
+    receives), each slab straight between the staging buffer of its owner and of the ranks that attend to it --
+    causality halves their traffic (rank r only ever sees chunks up to 2P-1-r)."""
 
     @staticmethod
     def forward(ctx, q, k, v, log_fgate, seq_start, sm_scale, threshold, group, attn_fn):
@@ -146,25 +147,26 @@ class _ContextParallel(torch.autograd.Function):
         Vf = torch.empty((n_hi, B, H, D), dtype=dt, device=dev)
         Gf = torch.empty((n_hi, B, H), dtype=log_fgate.dtype, device=dev)
         slab = lambda buf, c: buf.data[c * tc:(c + 1) * tc]     # (alias with its own version counter, see below)
-        for buf, src in ((Kf, k), (Vf, v), (Gf, log_fgate)):
-            slab(buf, lo_c).copy_(src[:, :, :tc].movedim(2, 0))
+        for buf, src in ((Kf, k), (Vf, v)):
             slab(buf, hi_c).copy_(src[:, :, tc:].movedim(2, 0))
-        # wave 1: the lower halves (chunk j < P lives on rank j; every rank attends to all of them) and all gates;
-        # wave 2: the upper halves this rank may attend to (chunks P .. hi_c, owned by the ranks above this one)
-        wave1, wave2 = [], []
+        # wave 1: the lower halves -- chunk j < P lives on rank j and every rank attends to all of them, so an
+        # all-gather lands them in natural order -- and the (small) gates of both halves;
+        # wave 2: the upper halves this rank may attend to (chunks P .. hi_c, owned by the ranks above this one),
+        # point to point
+        k_lo, v_lo = k[:, :, :tc].movedim(2, 0).contiguous(), v[:, :, :tc].movedim(2, 0).contiguous()
+        g_both = log_fgate.movedim(2, 0).contiguous().view(2, tc, B, H)
+        g_all = torch.empty((P, 2, tc, B, H), dtype=log_fgate.dtype, device=dev)
+        w1 = [dist.all_gather_into_tensor(g_all.view(P * 2, tc, B, H), g_both, group=group, async_op=True),
+              dist.all_gather_into_tensor(Kf.data[:P * tc], k_lo, group=group, async_op=True),
+              dist.all_gather_into_tensor(Vf.data[:P * tc], v_lo, group=group, async_op=True)]
+        wave2 = []
         for j in range(P):
-            if j == rank:
-                continue
-            for buf in (Kf, Vf, Gf):
-                wave1.append(("send", slab(buf, lo_c), peer[j], group))
-                wave1.append(("recv", slab(buf, j), peer[j], group))
             if j < rank:        # rank j attends to chunks up to 2P-1-j, which include this rank's upper chunk
-                for buf in (Kf, Vf, Gf):
+                for buf in (Kf, Vf):
                     wave2.append(("send", slab(buf, hi_c), peer[j], group))
-            else:               # and this rank to the upper chunk of every rank above it
-                for buf in (Kf, Vf, Gf):
+            elif j > rank:      # and this rank to the upper chunk of every rank above it
+                for buf in (Kf, Vf):
                     wave2.append(("recv", slab(buf, 2 * P - 1 - j), peer[j], group))
-        reqs1 = _exchange(wave1)
         reqs2 = _exchange(wave2)
 
         def call(q_c, n):
@@ -177,8 +179,12 @@ class _ContextParallel(torch.autograd.Function):
                               adaptive_threshold=threshold)
             return out, leaves
 
-        for r_ in reqs1:
-            r_.wait()
+        _wait(w1[0])
+        Gf.data[:P * tc].view(P, tc, B, H).copy_(g_all[:, 0])
+        n_up = hi_c + 1 - P                                       # upper chunks P .. hi_c = ranks P-1 .. rank
+        Gf.data[P * tc:].view(n_up, tc, B, H).copy_(g_all[rank:, 1].flip(0))
+        _wait(w1[1])
+        _wait(w1[2])
         _mark("lower halves gathered")
         out_lo, leaves_lo = call(q[:, :, :tc], n_lo)              # runs while wave 2 travels
         _mark("lower chunk forward")
@@ -213,42 +219,46 @@ class _ContextParallel(torch.autograd.Function):
         _mark("upper chunk backward")
         dq_lo, dk_lo, dv_lo, dg_lo = torch.autograd.grad(out_lo, leaves_lo, dout[:, :, :tc])
         _mark("lower chunk backward")
-        # Every chunk's partial gradient goes to the chunk's owner, straight from its slab; the owner sums what
-        # arrives in fp32.  Posted after both calls: ranks finish their first call at very different times, and a
-        # transfer posted under the second call would spin on its SMs until the slowest rank arrives.
-        ops_list, recv, mine = [], {}, {}
+        # Lower halves: chunk j belongs to rank j and every rank holds a partial for it: one reduce-scatter per
+        # tensor over the first P slabs, as they lie.  Upper halves: rank r holds partials for chunks P .. 2P-1-r
+        # only; each goes point to point from its slab to the chunk's owner, who sums what arrives in fp32.
+        # Posted after both calls: ranks finish their first call at very different times, and a transfer posted
+        # under the second call would spin on its SMs until the slowest rank arrives.
+        works, ops_list, mine, recv, out_lo_hi = [], [], {}, {}, {}
         for name, g_hi, g_lo in (("k", dk_hi, dk_lo), ("v", dv_hi, dv_lo), ("g", dg_hi, dg_lo)):
             g_hi, g_lo = seq_major_mem(g_hi), seq_major_mem(g_lo)
             g_hi[:n_lo] += g_lo                                   # chunks both calls attended to
-            mine[name] = g_hi
             tail = g_hi.shape[1:]
-            # senders of this rank's lower chunk: everyone; of its upper chunk: the ranks below it
-            recv[name] = (torch.empty((P - 1, tc) + tail, dtype=g_hi.dtype, device=dev),
-                          torch.empty((rank, tc) + tail, dtype=g_hi.dtype, device=dev))
+            final = torch.empty((2 * tc,) + tail, dtype=g_hi.dtype, device=dev)
+            if dist.get_backend(group) == "gloo":                 # (no reduce-scatter in gloo: all-reduce, keep a slab)
+                red = g_hi[:P * tc].clone()
+                dist.all_reduce(red, group=group)
+                final[:tc].copy_(red[rank * tc:(rank + 1) * tc])
+            else:
+                works.append(dist.reduce_scatter_tensor(final[:tc], g_hi[:P * tc], op=dist.ReduceOp.SUM, group=group,
+                                                        async_op=True))
+            # partials of this rank's upper chunk: its own (slot 0) and one from every rank below it
+            recv[name] = torch.empty((rank + 1, tc) + tail, dtype=g_hi.dtype, device=dev)
+            recv[name][0].copy_(g_hi[hi_c * tc:(hi_c + 1) * tc])
+            mine[name], out_lo_hi[name] = g_hi, final
         for j in range(P):
-            if j == rank:
-                continue
             for name in ("k", "v", "g"):
-                g_hi = mine[name]
-                ops_list.append(("send", g_hi[j * tc:(j + 1) * tc], peer[j], group))            # chunk j (lower half)
-                ops_list.append(("recv", recv[name][0][j if j < rank else j - 1], peer[j], group))
                 if j > rank:     # chunk 2P-1-j is below this rank's horizon 2P-1-rank: it has a partial for it
                     c = 2 * P - 1 - j
-                    ops_list.append(("send", g_hi[c * tc:(c + 1) * tc], peer[j], group))
-                else:            # and the ranks below this one have partials for this rank's upper chunk
-                    ops_list.append(("recv", recv[name][1][j], peer[j], group))
+                    ops_list.append(("send", mine[name][c * tc:(c + 1) * tc], peer[j], group))
+                elif j < rank:   # and the ranks below this one have partials for this rank's upper chunk
+                    ops_list.append(("recv", recv[name][1 + j], peer[j], group))
         reqs = _exchange(ops_list)
         _mark("gradient exchange posted")
+        for w in works:
+            _wait(w)
         for r_ in reqs:
             r_.wait()
         _mark("gradients exchanged")
         grads = []
         for name in ("k", "v", "g"):
-            g_hi = mine[name]
-            own_lo, own_hi = g_hi[lo_c * tc:(lo_c + 1) * tc], g_hi[hi_c * tc:(hi_c + 1) * tc]
-            lo = (own_lo.float() + recv[name][0].sum(0, dtype=torch.float32)) if P > 1 else own_lo.float()
-            hi = (own_hi.float() + recv[name][1].sum(0, dtype=torch.float32)) if rank > 0 else own_hi.float()
-            grads.append(_head_first(torch.cat([lo.to(g_hi.dtype), hi.to(g_hi.dtype)], dim=0)))
+            torch.sum(recv[name], dim=0, out=out_lo_hi[name][tc:])     # (16-bit sums accumulate in fp32)
+            grads.append(_head_first(out_lo_hi[name]))
         dk, dv, dg = grads
         dq = torch.cat([dq_lo, dq_hi], dim=2)
         _mark("bwd end")
