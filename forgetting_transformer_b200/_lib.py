@@ -39,6 +39,9 @@ _F = c_void_p  # device pointers are passed as integers
 _SIGNATURES = {
     "fox_version": (c_char_p, []),
     "fox_cumsum_fwd": (c_int, [c_int, c_void_p, c_int64, c_int64, c_int64, _F, c_int64, c_int64, c_int64, _F, _F, _F, _F]),
+    "fox_gate_prefix_fwd": (c_int, [c_int, c_void_p, c_int, c_int64, c_int64, c_int64, _F, c_int64, c_int64, c_int64, _F, _F, _F]),
+    "fox_gate_prefix_bwd": (c_int, [c_int, c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, _F, _F, _F, c_int64, c_int64,
+                                    c_int64, _F]),
     "fox_revcumsum": (c_int, [c_int, c_void_p, c_int64, c_int64, c_int64, c_int64, _F, _F, _F, _F, _F]),
     "fox_find_index": (c_int, [c_int, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, _F, _F, c_int64, c_int64, _F, _F]),
     "fox_max_row_norm": (c_int, [c_int, c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, _T4P, _F]),

@@ -20,7 +20,8 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from .norm_gate import FusedGroupNormGated, GroupNorm, RMSNorm
-from .ops import acp_threshold_from_qk_norm, forgetting_attention, seq_start_from_attention_mask
+from .ops import (acp_threshold_from_qk_norm, forgetting_attention, forgetting_attention_from_gate_logits,
+                  seq_start_from_attention_mask)
 from .glu import swiglu_linear_packed
 from .token_shift import token_shift
 
@@ -120,12 +121,13 @@ class FoxProAttentionLayer(nn.Module):
         if self.qk_norm:
             q = self.q_norm(q).to(q.dtype)
             k = self.k_norm(k).to(k.dtype)
-        fgate_logit = self.fgate_proj(hidden_states).transpose(1, 2)               # (B, H, T)
-        log_fgate = F.logsigmoid(fgate_logit.float())
+        fgate_logit = self.fgate_proj(hidden_states).transpose(1, 2)               # (B, H, T) view
         q, k, v = [t.view(B, T, H, D).transpose(1, 2) for t in (q, k, v)]          # head-first views
-        if past_key_values is not None:
+        log_fgate = None
+        if past_key_values is not None:     # the cache holds log gates: form them here
+            log_fgate = F.logsigmoid(fgate_logit.float())
             k, v, log_fgate = past_key_values.update(k, v, log_fgate, layer_idx)
-        N = log_fgate.shape[-1]
+        N = k.shape[2]
         thr = None
         if self.log_pruning_tolerance is not None:
             assert self.qk_norm, "the closed-form threshold needs QK-norm"
@@ -135,8 +137,12 @@ class FoxProAttentionLayer(nn.Module):
         if attention_mask is not None:
             assert attention_mask.shape == (B, N), ((B, N), tuple(attention_mask.shape))
             seq_start = seq_start_from_attention_mask(attention_mask)
-        o = forgetting_attention(q, k, v, log_fgate, head_first=True, seq_start=seq_start,
-                                 sm_scale=1 / math.sqrt(D), adaptive_threshold=thr)
+        if log_fgate is None:               # training path: log sigmoid folded into the operator's prefix sums
+            o = forgetting_attention_from_gate_logits(q, k, v, fgate_logit, head_first=True, seq_start=seq_start,
+                                                      sm_scale=1 / math.sqrt(D), adaptive_threshold=thr)
+        else:
+            o = forgetting_attention(q, k, v, log_fgate, head_first=True, seq_start=seq_start,
+                                     sm_scale=1 / math.sqrt(D), adaptive_threshold=thr)
         o = o.transpose(1, 2).reshape(B, T, self.hidden_size)
         o = self.output_norm(o, self.ogate_proj(hidden_states))
         return self.o_proj(o)

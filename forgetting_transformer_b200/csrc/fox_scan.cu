@@ -47,15 +47,32 @@ __device__ __forceinline__ float block_inclusive_scan(float v, float* red, float
   return v + prefix;
 }
 
+// One gate value: kIn = 3 reads an fp32 log gate; kIn = 0 / 1 / 2 reads an fp16 / bf16 / fp32 gate LOGIT and
+// returns log sigmoid(x) = min(x, 0) - log1p(exp(-|x|)) in fp32 (the F.logsigmoid(fgate_logit.float()) of
+// upstream's layer, modeling_forgetting_transformer.py:343-346).
+template <int kIn>
+__device__ __forceinline__ float load_gate(const void* base, int64_t idx) {
+  if constexpr (kIn == 3) {
+    return reinterpret_cast<const float*>(base)[idx];
+  } else {
+    float x;
+    if constexpr (kIn == 2) x = reinterpret_cast<const float*>(base)[idx];
+    else x = unpack2<kIn == 1>(static_cast<uint32_t>(reinterpret_cast<const uint16_t*>(base)[idx])).x;
+    return fminf(x, 0.f) - log1pf(expf(-fabsf(x)));
+  }
+}
+
 // log_lambda[b,h,t] = carry_in[b,h] + sum_{u<=t, u>=seq_start[b]} log_fgate[b,h,u]
-// One CTA per (b,h); chunks of 4096 elements with a carried running total.
+// One CTA per (b,h); chunks of 4096 elements with a carried running total.  With gate logits as input
+// (kIn < 3) the log gates themselves are formed on the fly and, if lf_out is given, written out (unmasked).
+template <int kIn>
 __global__ void __launch_bounds__(kScanThreads)
-fox_cumsum_kernel(const float* __restrict__ lf, int64_t sb, int64_t sh, int64_t sn,
+fox_cumsum_kernel(const void* __restrict__ lf, int64_t sb, int64_t sh, int64_t sn,
                   const int64_t* __restrict__ seq_start, const float* __restrict__ carry_in,
-                  float* __restrict__ out, float* __restrict__ total_out, int H, int N) {
+                  float* __restrict__ out, float* __restrict__ total_out, float* __restrict__ lf_out, int H, int N) {
   __shared__ float red[32];
   const int bh = blockIdx.x, b = bh / H, h = bh % H;
-  const float* src = lf + b * sb + h * sh;
+  const int64_t src0 = b * sb + h * sh;
   float* dst = out + static_cast<int64_t>(bh) * N;
   const int s0 = seq_start ? static_cast<int>(seq_start[b]) : 0;
   float carry = carry_in ? carry_in[bh] : 0.f;
@@ -65,7 +82,10 @@ fox_cumsum_kernel(const float* __restrict__ lf, int64_t sb, int64_t sh, int64_t 
 #pragma unroll
     for (int j = 0; j < kScanPerThread; ++j) {
       const int t = t0 + j;
-      x[j] = (t < N && t >= s0) ? src[static_cast<int64_t>(t) * sn] : 0.f;
+      float g = 0.f;
+      if (t < N && (t >= s0 || (kIn < 3 && lf_out))) g = load_gate<kIn>(lf, src0 + static_cast<int64_t>(t) * sn);
+      if (kIn < 3 && lf_out && t < N) lf_out[static_cast<int64_t>(bh) * N + t] = g;
+      x[j] = (t < N && t >= s0) ? g : 0.f;
     }
 #pragma unroll
     for (int j = 1; j < kScanPerThread; ++j) x[j] += x[j - 1];
@@ -83,11 +103,14 @@ fox_cumsum_kernel(const float* __restrict__ lf, int64_t sb, int64_t sh, int64_t 
 }
 
 // dlog_fgate[t] = carry_in + sum_{u >= t} (dcol[u] + drow[u - P] if u >= P)
-// Reverse inclusive scan, one CTA per (b,h).
+// Reverse inclusive scan, one CTA per (b,h).  kIn < 3: the chain rule through log sigmoid is applied on the way
+// out, dlogit[t] = dlog_fgate[t] * sigmoid(-logit[t]), written in the logits' dtype with the logits' strides.
+template <int kIn>
 __global__ void __launch_bounds__(kScanThreads)
 fox_revcumsum_kernel(const float* __restrict__ dcol, const float* __restrict__ drow,
                      const float* __restrict__ carry_in, float* __restrict__ out,
-                     float* __restrict__ total_out, int M, int N) {
+                     float* __restrict__ total_out, int M, int N, const void* __restrict__ logit,
+                     void* __restrict__ dlogit, int64_t sb, int64_t sh, int64_t sn, int H) {
   __shared__ float red[32];
   const int bh = blockIdx.x;
   const float* c = dcol + static_cast<int64_t>(bh) * N;
@@ -117,7 +140,20 @@ fox_revcumsum_kernel(const float* __restrict__ dcol, const float* __restrict__ d
 #pragma unroll
     for (int j = 0; j < kScanPerThread; ++j) {
       const int t = N - 1 - (i0 + j);
-      if (t >= 0) dst[t] = x[j] + excl;
+      if (t >= 0) {
+        const float gsum = x[j] + excl;
+        if constexpr (kIn == 3) {
+          dst[t] = gsum;
+        } else {
+          const int64_t idx = static_cast<int64_t>(bh / H) * sb + static_cast<int64_t>(bh % H) * sh + static_cast<int64_t>(t) * sn;
+          float xl;
+          if constexpr (kIn == 2) xl = reinterpret_cast<const float*>(logit)[idx];
+          else xl = unpack2<kIn == 1>(static_cast<uint32_t>(reinterpret_cast<const uint16_t*>(logit)[idx])).x;
+          const float dl = gsum / (1.f + expf(xl));     // d/dx log sigmoid(x) = sigmoid(-x)
+          if constexpr (kIn == 2) reinterpret_cast<float*>(dlogit)[idx] = dl;
+          else reinterpret_cast<uint16_t*>(dlogit)[idx] = static_cast<uint16_t>(pack2<kIn == 1>(dl, 0.f) & 0xffffu);
+        }
+      }
     }
     carry += total;
   }
@@ -288,8 +324,25 @@ extern "C" int fox_cumsum_fwd(int device, void* stream, int64_t B, int64_t H, in
                               const float* carry_in, float* log_lambda, float* total_out) {
   if (!log_fgate || !log_lambda || B <= 0 || H <= 0 || N <= 0) return FOX_ERR_BAD_ARG;
   if (cudaSetDevice(device) != cudaSuccess) return FOX_ERR_DEVICE;
-  fox_cumsum_kernel<<<(unsigned)(B * H), kScanThreads, 0, (cudaStream_t)stream>>>(
-      log_fgate, sb, sh, sn, seq_start, carry_in, log_lambda, total_out, (int)H, (int)N);
+  fox_cumsum_kernel<3><<<(unsigned)(B * H), kScanThreads, 0, (cudaStream_t)stream>>>(
+      log_fgate, sb, sh, sn, seq_start, carry_in, log_lambda, total_out, nullptr, (int)H, (int)N);
+  return launch_rc();
+}
+
+extern "C" int fox_gate_prefix_fwd(int device, void* stream, int dtype, int64_t B, int64_t H, int64_t N,
+                                   const void* fgate_logit, int64_t sb, int64_t sh, int64_t sn,
+                                   const int64_t* seq_start, float* log_fgate_out, float* log_lambda) {
+  if (!fgate_logit || !log_lambda || B <= 0 || H <= 0 || N <= 0) return FOX_ERR_BAD_ARG;
+  if (dtype != FOX_DTYPE_FP16 && dtype != FOX_DTYPE_BF16 && dtype != FOX_DTYPE_FP32) return FOX_ERR_BAD_ARG;
+  if (cudaSetDevice(device) != cudaSuccess) return FOX_ERR_DEVICE;
+  const unsigned grid = (unsigned)(B * H);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (dtype == FOX_DTYPE_FP16)
+    fox_cumsum_kernel<0><<<grid, kScanThreads, 0, st>>>(fgate_logit, sb, sh, sn, seq_start, nullptr, log_lambda, nullptr, log_fgate_out, (int)H, (int)N);
+  else if (dtype == FOX_DTYPE_BF16)
+    fox_cumsum_kernel<1><<<grid, kScanThreads, 0, st>>>(fgate_logit, sb, sh, sn, seq_start, nullptr, log_lambda, nullptr, log_fgate_out, (int)H, (int)N);
+  else
+    fox_cumsum_kernel<2><<<grid, kScanThreads, 0, st>>>(fgate_logit, sb, sh, sn, seq_start, nullptr, log_lambda, nullptr, log_fgate_out, (int)H, (int)N);
   return launch_rc();
 }
 
@@ -298,8 +351,24 @@ extern "C" int fox_revcumsum(int device, void* stream, int64_t B, int64_t H, int
                              float* dlog_fgate, float* total_out) {
   if (!dlam_col || !dlog_fgate || B <= 0 || H <= 0 || N <= 0 || M <= 0 || M > N) return FOX_ERR_BAD_ARG;
   if (cudaSetDevice(device) != cudaSuccess) return FOX_ERR_DEVICE;
-  fox_revcumsum_kernel<<<(unsigned)(B * H), kScanThreads, 0, (cudaStream_t)stream>>>(
-      dlam_col, dlam_row, carry_in, dlog_fgate, total_out, (int)M, (int)N);
+  fox_revcumsum_kernel<3><<<(unsigned)(B * H), kScanThreads, 0, (cudaStream_t)stream>>>(
+      dlam_col, dlam_row, carry_in, dlog_fgate, total_out, (int)M, (int)N, nullptr, nullptr, 0, 0, 0, (int)H);
+  return launch_rc();
+}
+
+extern "C" int fox_gate_prefix_bwd(int device, void* stream, int dtype, int64_t B, int64_t H, int64_t M, int64_t N,
+                                   const float* dlam_col, const float* dlam_row, const void* fgate_logit,
+                                   int64_t sb, int64_t sh, int64_t sn, void* dfgate_logit) {
+  if (!dlam_col || !fgate_logit || !dfgate_logit || B <= 0 || H <= 0 || N <= 0 || M <= 0 || M > N) return FOX_ERR_BAD_ARG;
+  if (dtype != FOX_DTYPE_FP16 && dtype != FOX_DTYPE_BF16 && dtype != FOX_DTYPE_FP32) return FOX_ERR_BAD_ARG;
+  if (cudaSetDevice(device) != cudaSuccess) return FOX_ERR_DEVICE;
+  const unsigned grid = (unsigned)(B * H);
+  cudaStream_t st = (cudaStream_t)stream;
+#define FOX_GPB(K) fox_revcumsum_kernel<K><<<grid, kScanThreads, 0, st>>>(dlam_col, dlam_row, nullptr, nullptr, nullptr, (int)M, (int)N, fgate_logit, dfgate_logit, sb, sh, sn, (int)H)
+  if (dtype == FOX_DTYPE_FP16) FOX_GPB(0);
+  else if (dtype == FOX_DTYPE_BF16) FOX_GPB(1);
+  else FOX_GPB(2);
+#undef FOX_GPB
   return launch_rc();
 }
 

@@ -17,7 +17,8 @@ import torch
 
 from . import _lib
 
-__all__ = ["forgetting_attention", "ForgettingAttention", "FWD_BLOCK", "BWD_BLOCK"]
+__all__ = ["forgetting_attention", "forgetting_attention_from_gate_logits", "ForgettingAttention", "FWD_BLOCK",
+           "BWD_BLOCK"]
 
 # (BLOCK_M, BLOCK_N) of the kernels; pruning indices are defined on this grid.
 _PADDED_HEAD_DIM = 64   # head dims 16 and 32 are zero-padded to this
@@ -110,6 +111,23 @@ def log_lambda_cumsum(log_fgate: torch.Tensor, seq_start: Optional[torch.Tensor]
     return (out, total) if return_total else out
 
 
+_GATE_DTYPES = {torch.float16: _lib.FOX_DTYPE_FP16, torch.bfloat16: _lib.FOX_DTYPE_BF16, torch.float32: _lib.FOX_DTYPE_FP32}
+
+
+def gate_prefix_from_logits(fgate_logit: torch.Tensor, seq_start: Optional[torch.Tensor]) -> torch.Tensor:
+    """fp32 prefix sum of log sigmoid(fgate_logit.float()) over the last axis of a (B,H,N) tensor of any strides
+    and dtype fp16 / bf16 / fp32, gates left of ``seq_start`` treated as zero: upstream's
+    ``F.logsigmoid(fgate_logit.float())`` (modeling_forgetting_transformer.py:343-346) and masked cumsum
+    (forgetting_attention.py:117-127) in one kernel."""
+    lib = _lib.load()
+    B, H, N = fgate_logit.shape
+    out = torch.empty((B, H, N), dtype=torch.float32, device=fgate_logit.device)
+    _call("fox_gate_prefix_fwd", lib.fox_gate_prefix_fwd, fgate_logit.device.index, _stream(),
+          _GATE_DTYPES[fgate_logit.dtype], B, H, N, fgate_logit.data_ptr(), fgate_logit.stride(0),
+          fgate_logit.stride(1), fgate_logit.stride(2), _lib.ptr(seq_start), None, out.data_ptr())
+    return out
+
+
 def find_index(log_lambda: torch.Tensor, threshold: torch.Tensor, M: int, block_m: int, block_n: int,
                want_start: bool = True, want_end: bool = False):
     """Block-pruning index arrays (upstream lines 695-795) on a (block_m, block_n) grid."""
@@ -131,7 +149,9 @@ class ForgettingAttention(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, log_fgate, seq_start, causal, sm_scale, adaptive_threshold,
                 return_log_normalizer=False, return_start_index=False, record_time_key=None,
-                record_attention_time=False, record_find_index_time=False):
+                record_attention_time=False, record_find_index_time=False, gate_is_logit=False):
+        """``gate_is_logit`` (not part of upstream's signature): ``log_fgate`` holds the gate LOGITS (fp16 / bf16 /
+        fp32); log sigmoid and its derivative are folded into the prefix-sum kernels."""
         assert causal, "Only causal attention is supported"
         Dq, Dk, Dv = q.shape[-1], k.shape[-1], v.shape[-1]
         assert Dq == Dk == Dv, "feature size of q, k, v should be equal"
@@ -140,7 +160,10 @@ class ForgettingAttention(torch.autograd.Function):
         B, H, M, D = q.shape
         N = k.shape[2]
         assert log_fgate.shape == (B, H, N)
-        assert log_fgate.dtype == torch.float32, "log_fgate must be in torch.float32. It is best to do this cast before logsigmoid, e.g., torch.nn.functional.logsigmoid(fgate_logit.float())."
+        if gate_is_logit:
+            assert log_fgate.dtype in _GATE_DTYPES, f"gate logits must be fp16, bf16 or fp32, but got {log_fgate.dtype}"
+        else:
+            assert log_fgate.dtype == torch.float32, "log_fgate must be in torch.float32. It is best to do this cast before logsigmoid, e.g., torch.nn.functional.logsigmoid(fgate_logit.float())."
         if sm_scale is None:
             sm_scale = 1. / math.sqrt(D)
         Hk, Hv = k.shape[1], v.shape[1]
@@ -194,7 +217,8 @@ class ForgettingAttention(torch.autograd.Function):
             else:
                 has_seq_start = False
 
-            log_lambda = log_lambda_cumsum(log_fgate, seq_start)
+            log_lambda = (gate_prefix_from_logits(log_fgate, seq_start) if gate_is_logit
+                          else log_lambda_cumsum(log_fgate, seq_start))
 
             start_index = None
             if adaptive_threshold is not None:
@@ -225,6 +249,7 @@ class ForgettingAttention(torch.autograd.Function):
                 _lib.check_status(dev)
 
         ctx.save_for_backward(q, k, v, o, L, log_lambda, seq_start, adaptive_threshold)
+        ctx.gate_logit = log_fgate if gate_is_logit else None    # (an input of the function: kept as it is)
         ctx.sm_scale = sm_scale
         ctx.has_seq_start = has_seq_start
         # the query-side backward kernel prunes by the same array when the two block grids agree (not an input or
@@ -286,15 +311,13 @@ class ForgettingAttention(torch.autograd.Function):
                       _lib.t4(k), _lib.t4(v), _lib.t4(do), log_lambda.data_ptr(), L.data_ptr(), delta.data_ptr(),
                       _lib.ptr(seq_start), _lib.ptr(start_index), float(sm_scale), _lib.t4(dq), dlam_row.data_ptr(),
                       status.data_ptr())
-                dlog_fgate = torch.empty((B, H, N), dtype=torch.float32, device=dev)
-                _call("fox_revcumsum", lib.fox_revcumsum, dev.index, _stream(), B, H, M, N, dlam_col.data_ptr(),
-                      dlam_row.data_ptr(), None, dlog_fgate.data_ptr(), None)
+                dlog_fgate = _gate_gradient(ctx, lib, dev, B, H, M, N, dlam_col, dlam_row)
                 _lib.queue_status_readback(dev)
                 if _DEBUG_SYNC:
                     _lib.check_status(dev)
                 if ctx.head_dim != D:
                     dq, dk, dv = [t[..., :ctx.head_dim].contiguous() for t in (dq, dk, dv)]
-                return dq, dk, dv, dlog_fgate, None, None, None, None, None, None, None, None, None
+                return dq, dk, dv, dlog_fgate, None, None, None, None, None, None, None, None, None, None
             # scratch: fp32 dQ accumulator and the query-side log-gate gradient (both reduced into)
             scratch = torch.zeros(B * H * M * (D + 1), dtype=torch.float32, device=dev)
             dq_accum = scratch[: B * H * M * D]
@@ -305,15 +328,49 @@ class ForgettingAttention(torch.autograd.Function):
                   dlam_row.data_ptr(), dlam_col.data_ptr(), _lib.t4(dk), _lib.t4(dv), status.data_ptr())
             _call("fox_dq_convert", lib.fox_dq_convert, dev.index, _stream(), code, B, H, M, D,
                   dq_accum.data_ptr(), float(sm_scale), _lib.t4(dq))
-            dlog_fgate = torch.empty((B, H, N), dtype=torch.float32, device=dev)
-            _call("fox_revcumsum", lib.fox_revcumsum, dev.index, _stream(), B, H, M, N, dlam_col.data_ptr(),
-                  dlam_row.data_ptr(), None, dlog_fgate.data_ptr(), None)
+            dlog_fgate = _gate_gradient(ctx, lib, dev, B, H, M, N, dlam_col, dlam_row)
             _lib.queue_status_readback(dev)
             if _DEBUG_SYNC:
                 _lib.check_status(dev)
         if ctx.head_dim != D:
             dq, dk, dv = [t[..., :ctx.head_dim].contiguous() for t in (dq, dk, dv)]
-        return dq, dk, dv, dlog_fgate, None, None, None, None, None, None, None, None, None
+        return dq, dk, dv, dlog_fgate, None, None, None, None, None, None, None, None, None, None
+
+
+def _gate_gradient(ctx, lib, dev, B, H, M, N, dlam_col, dlam_row):
+    """Reverse prefix sum of the two halves of dlog_lambda (upstream lines 390-392); for gate logits also the
+    chain rule through log sigmoid, in the logits' dtype and layout."""
+    logit = getattr(ctx, "gate_logit", None)
+    if logit is None:
+        dlog_fgate = torch.empty((B, H, N), dtype=torch.float32, device=dev)
+        _call("fox_revcumsum", lib.fox_revcumsum, dev.index, _stream(), B, H, M, N, dlam_col.data_ptr(),
+              dlam_row.data_ptr(), None, dlog_fgate.data_ptr(), None)
+        return dlog_fgate
+    dlogit = torch.empty_strided(logit.shape, logit.stride(), dtype=logit.dtype, device=dev)
+    _call("fox_gate_prefix_bwd", lib.fox_gate_prefix_bwd, dev.index, _stream(), _GATE_DTYPES[logit.dtype], B, H, M, N,
+          dlam_col.data_ptr(), dlam_row.data_ptr(), logit.data_ptr(), logit.stride(0), logit.stride(1),
+          logit.stride(2), dlogit.data_ptr())
+    return dlogit
+
+
+def forgetting_attention_from_gate_logits(q, k, v, fgate_logit, *, head_first: bool = False,
+                                          seq_start: Optional[torch.Tensor] = None, sm_scale: Optional[float] = None,
+                                          adaptive_threshold=None):
+    """``forgetting_attention(q, k, v, F.logsigmoid(fgate_logit.float()), ...)`` with the log sigmoid folded into
+    the operator's prefix-sum kernel and its derivative into the reverse prefix sum of the backward: the layer's
+    gate projection output (fp16 / bf16 / fp32, (B, T, H) or (B, H, T) with ``head_first``, any strides) goes in as
+    it is and receives its gradient in its own dtype (upstream forms the log gates with two elementwise kernels in
+    front of the operator, modeling_forgetting_transformer.py:343-346).  Everything else as ``forgetting_attention``."""
+    for name, entry in dict(q=q, k=k, v=v).items():
+        assert entry.dtype in [torch.float16, torch.bfloat16], f"Only torch.float16 or torch.bfloat16 are supported for q/k/v, but got {entry.dtype} for {name}."
+    if not head_first:
+        q, k, v = [item.permute(0, 2, 1, 3) for item in (q, k, v)]
+        fgate_logit = fgate_logit.permute(0, 2, 1)
+    out = ForgettingAttention.apply(q, k, v, fgate_logit, seq_start, True, sm_scale, adaptive_threshold,
+                                    False, False, None, False, False, True)
+    if not head_first:
+        out = out.permute(0, 2, 1, 3)
+    return out
 
 
 def forgetting_attention(

@@ -76,6 +76,22 @@ int fox_cumsum_fwd(int device, void* stream, int64_t B, int64_t H, int64_t N, co
                    int64_t sb, int64_t sh, int64_t sn, const int64_t* seq_start, const float* carry_in,
                    float* log_lambda, float* total_out);
 
+/* The same prefix sum straight from the gate LOGITS: log_fgate = log sigmoid(float(fgate_logit)) is formed on the
+ * load, i.e. the F.logsigmoid(fgate_logit.float()) of upstream's layer (modeling_forgetting_transformer.py:343-346)
+ * and the masked cumsum (forgetting_attention.py:117-127) in one pass.  fgate_logit: fp16 / bf16 / fp32 (dtype) with
+ * element strides (sb, sh, sn), e.g. the (B,H,N) view of the (B,N,H) output of fgate_proj.  log_fgate_out (B,H,N)
+ * fp32 or NULL receives the (unmasked) log gates. */
+int fox_gate_prefix_fwd(int device, void* stream, int dtype, int64_t B, int64_t H, int64_t N, const void* fgate_logit,
+                        int64_t sb, int64_t sh, int64_t sn, const int64_t* seq_start, float* log_fgate_out,
+                        float* log_lambda);
+
+/* Its backward: fox_revcumsum with the chain rule through log sigmoid applied on the way out,
+ * dfgate_logit[b,h,t] = sigmoid(-fgate_logit[b,h,t]) * sum_{u >= t} (dlam_col[b,h,u] + dlam_row[b,h,u-(N-M)]),
+ * written in the logits' dtype with the logits' strides (sb, sh, sn). */
+int fox_gate_prefix_bwd(int device, void* stream, int dtype, int64_t B, int64_t H, int64_t M, int64_t N,
+                        const float* dlam_col, const float* dlam_row, const void* fgate_logit, int64_t sb,
+                        int64_t sh, int64_t sn, void* dfgate_logit);
+
 /* dlog_fgate[b,h,t] = carry_in[b,h] + sum_{u >= t} (dlam_col[b,h,u] + dlam_row[b,h,u-(N-M)]),
  * the reverse prefix sum of forgetting_attention.py:390-392 fused with the addition of the
  * key-side and query-side halves of dlog_lambda (lines 1122, 1326-1344).  dlam_row may be NULL. */

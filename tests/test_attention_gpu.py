@@ -332,6 +332,36 @@ def test_threshold_validation():
         fox.forgetting_attention(q, k, v, lf, head_first=True, adaptive_threshold=torch.zeros(3, device="cuda"))
 
 
+@pytest.mark.parametrize("D,dtype", [(64, torch.bfloat16), (128, torch.float32)])
+def test_gate_logits_path_matches_the_log_gate_path(D, dtype):
+    """``forgetting_attention_from_gate_logits`` (log sigmoid folded into the prefix-sum kernels) against
+    ``forgetting_attention`` on ``F.logsigmoid(logit.float())`` with autograd through the log sigmoid, as upstream's
+    layer does it (modeling_forgetting_transformer.py:343-346): the gate projection's (B, T, H) output as it is."""
+    B, T, H = 2, 700, 3
+    g = torch.Generator().manual_seed(31 + D)
+    q, k, v, do = [torch.randn(B, T, H, D, generator=g).bfloat16().cuda() for _ in range(4)]
+    logit = (torch.randn(B, T, H, generator=g) * 1.5 + 2).to(dtype).cuda()
+    seq = torch.tensor([0, 129]).cuda()
+    lam = ops.gate_prefix_from_logits(logit.permute(0, 2, 1), seq)
+    ref_lam = orc.log_lambda(torch.nn.functional.logsigmoid(logit.float().cpu().double()).permute(0, 2, 1), seq.cpu())
+    assert (lam.cpu().double() - ref_lam).abs().max().item() <= 1e-5 * ref_lam.abs().max().item() + 1e-5
+    res = []
+    for fused in (False, True):
+        qq, kk, vv, ll = [t.detach().clone().requires_grad_() for t in (q, k, v, logit)]
+        if fused:
+            out = fox.forgetting_attention_from_gate_logits(qq, kk, vv, ll, seq_start=seq, adaptive_threshold=-15.0)
+        else:
+            out = fox.forgetting_attention(qq, kk, vv, torch.nn.functional.logsigmoid(ll.float()), seq_start=seq,
+                                           adaptive_threshold=-15.0)
+        out.backward(do)
+        res.append((out.detach(), qq.grad, kk.grad, vv.grad, ll.grad))
+    torch.cuda.synchronize()
+    _lib.check_status()
+    assert res[1][4].dtype == dtype and res[1][4].shape == logit.shape
+    for name, a, b in zip(("out", "dq", "dk", "dv", "dlogit"), res[1], res[0]):
+        _close(a, b, 1e-2, 1e-2, name)     # same kernels; the prefix sums differ in the last bits of log sigmoid
+
+
 def test_expired_wait_is_reported_at_the_next_call():
     """A kernel that gives up on a bounded wait leaves a record in the device's status words; the operator copies
     them to pinned host memory after every backward and raises at the next call, without any synchronisation of
