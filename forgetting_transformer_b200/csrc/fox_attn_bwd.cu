@@ -104,12 +104,16 @@ fox_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   constexpr int kNdq = kFp32Sums ? D : D + 16;
   constexpr uint32_t kColS = 0, kColDP = 128, kColDK = 256, kColDV = 256 + kNdk;
   constexpr uint32_t kColDQ = kAliasDQ ? 0 : kColDV + D;
-  static_assert(kAliasDQ || kNoDQ || kColDQ + kNdq <= 512, "TMEM budget");
+  // With the sums off the tensor pipe (no "ones" columns) a second dQ accumulator fits at D = 64: the dQ product
+  // of the next tile then runs while this tile's accumulator is still being drained and add-reduced into L2.
+  constexpr int kDqBufs = (D == 64 && kFp32Sums && !kNoDQ) ? 2 : 1;
+  static_assert(kAliasDQ || kNoDQ || kColDQ + kDqBufs * kNdq <= 512, "TMEM budget");
 
   // 1024-byte aligned by declaration: at D=128 the tiles use all but 3 KiB of the 227 KiB a CTA may
   // have, so there is no room for a manual alignment slack.
   extern __shared__ __align__(1024) uint8_t smem_raw[];
-  __shared__ uint64_t bar_kv, bar_s_full, bar_dp_full, bar_p_done, bar_ds_done, bar_dq_full, bar_dq_free, bar_done,
+  __shared__ uint64_t bar_dq_full[kDqBufs], bar_dq_free[kDqBufs];
+  __shared__ uint64_t bar_kv, bar_s_full, bar_dp_full, bar_p_done, bar_ds_done, bar_done,
       bar_colsum;
   __shared__ uint64_t bar_q_full[STQ], bar_q_empty[STQ], bar_do_full[STDO], bar_do_empty[STDO],
       bar_staged, bar_stage_free;
@@ -155,8 +159,7 @@ fox_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     mbar_init(&bar_dp_full, 1);
     mbar_init(&bar_p_done, 128 * kCWG);
     mbar_init(&bar_ds_done, 128 * kCWG);
-    mbar_init(&bar_dq_full, 1);
-    mbar_init(&bar_dq_free, 128);
+    for (int s = 0; s < kDqBufs; ++s) { mbar_init(&bar_dq_full[s], 1); mbar_init(&bar_dq_free[s], 128); }
     mbar_init(&bar_done, 1);
     mbar_init(&bar_colsum, 128 * (kCWG - 1));
     // q_full: the TMA transaction plus one arrival of the producer warp for the per-row vectors
@@ -390,23 +393,26 @@ fox_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         }
         // ---- dQ_tile = dS [K | 1] ----
         if (!kNoDQ && it > 0) {
-          ok = mbar_wait_warp(&bar_dq_free, (it - 1) & 1, abortp, p.status, kBSiteDqFree, it);
+          // (accumulator it % kDqBufs was last used by tile it - kDqBufs)
+          if (it >= kDqBufs)
+            ok = mbar_wait_warp(&bar_dq_free[it % kDqBufs], ((it - kDqBufs) / kDqBufs) & 1, abortp, p.status,
+                                kBSiteDqFree, it);
           if (!ok) break;
           tc_fence_after();
         }
         if (!kNoDQ && elect_one()) {
 #pragma unroll
           for (int kk = 0; kk < 8; ++kk)
-            mma_ss_raw(tbase + kColDQ, umma_desc_advance(ads_mn, kk * 2048), umma_desc_advance(dK_mn, kk * 2048),
+            mma_ss_raw(tbase + kColDQ + (it % kDqBufs) * kNdq, umma_desc_advance(ads_mn, kk * 2048), umma_desc_advance(dK_mn, kk * 2048),
                        idDQ, kk > 0);
-          tc_commit_raw(&bar_dq_full);
+          tc_commit_raw(&bar_dq_full[it % kDqBufs]);
         }
         __syncwarp();
         stamp(0, 4, it);
         if (it + 1 < n_tiles) {
           if (kAliasDQ) {
             // the dQ tile sits on the S^T / dP^T columns: wait until it has been drained
-            ok = mbar_wait_warp(&bar_dq_free, it & 1, abortp, p.status, kBSiteDqFree, it);
+            ok = mbar_wait_warp(&bar_dq_free[0], it & 1, abortp, p.status, kBSiteDqFree, it);
             if (!ok) break;
             tc_fence_after();
             ok = issue_S(it + 1);
@@ -426,11 +432,12 @@ fox_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     // ===================== dQ drain + per-row vectors =====================
     const int quarter = warp & 3;
     const int r = quarter * 32 + lane;  // query row inside the tile == TMEM lane
-    const uint32_t tDQ = tbase + (static_cast<uint32_t>(quarter * 32) << 16) + kColDQ;
+    const uint32_t tDQ0 = tbase + (static_cast<uint32_t>(quarter * 32) << 16) + kColDQ;
     bool ok = true;
     for (int it = 0; it < (kNoDQ ? 0 : n_tiles); ++it) {
       if (warp == kDrainWarp0) stamp(1, 0, it);
-      ok = mbar_wait_warp(&bar_dq_full, it & 1, abortp, p.status, kBSiteDq, it);
+      const uint32_t tDQ = tDQ0 + (it % kDqBufs) * kNdq;
+      ok = mbar_wait_warp(&bar_dq_full[it % kDqBufs], (it / kDqBufs) & 1, abortp, p.status, kBSiteDq, it);
       if (!ok) break;
       if (warp == kDrainWarp0) stamp(1, 1, it);
       tc_fence_after();
@@ -460,7 +467,7 @@ fox_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         }
         if (round == D / (32 * kStageSub) - 1) {
           tc_fence_before();
-          mbar_arrive(&bar_dq_free);
+          mbar_arrive(&bar_dq_free[it % kDqBufs]);
         }
         fence_proxy_async_smem();
         mbar_arrive(&bar_staged);

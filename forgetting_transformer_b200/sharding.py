@@ -105,6 +105,14 @@ def context_parallel_group(ranks: Optional[Sequence[int]] = None):
     return dist.new_group(ranks=ranks, backend="nccl", pg_options=opts)
 
 
+def _upper_half_mode(group) -> str:
+    """How the upper halves travel: "p2p" (point to point, the causal subset only, straight into place) or
+    "collective" (all-gather / reduce-scatter of all of them plus reordering copies).  FOX_B200_CP_UPPER selects;
+    default p2p."""
+    import os
+    return os.environ.get("FOX_B200_CP_UPPER", "p2p")
+
+
 def _owner(chunk: int, world: int) -> int:
     """Rank that owns a chunk of the zig-zag split."""
     return chunk if chunk < world else 2 * world - 1 - chunk
@@ -159,14 +167,23 @@ class _ContextParallel(torch.autograd.Function):
         w1 = [dist.all_gather_into_tensor(g_all.view(P * 2, tc, B, H), g_both, group=group, async_op=True),
               dist.all_gather_into_tensor(Kf.data[:P * tc], k_lo, group=group, async_op=True),
               dist.all_gather_into_tensor(Vf.data[:P * tc], v_lo, group=group, async_op=True)]
-        wave2 = []
-        for j in range(P):
-            if j < rank:        # rank j attends to chunks up to 2P-1-j, which include this rank's upper chunk
-                for buf in (Kf, Vf):
-                    wave2.append(("send", slab(buf, hi_c), peer[j], group))
-            elif j > rank:      # and this rank to the upper chunk of every rank above it
-                for buf in (Kf, Vf):
-                    wave2.append(("recv", slab(buf, 2 * P - 1 - j), peer[j], group))
+        collective = _upper_half_mode(group) == "collective"
+        wave2, w2, up = [], [], []
+        if collective:
+            # the upper halves by all-gather as well (every rank receives all of them, in rank order = reversed
+            # chunk order); the slabs this rank attends to are copied into place afterwards
+            for buf in (Kf, Vf):
+                tmp = torch.empty((P * tc, B, H, D), dtype=dt, device=dev)
+                w2.append(dist.all_gather_into_tensor(tmp, slab(buf, hi_c).clone(), group=group, async_op=True))
+                up.append(tmp)
+        else:
+            for j in range(P):
+                if j < rank:        # rank j attends to chunks up to 2P-1-j, which include this rank's upper chunk
+                    for buf in (Kf, Vf):
+                        wave2.append(("send", slab(buf, hi_c), peer[j], group))
+                elif j > rank:      # and this rank to the upper chunk of every rank above it
+                    for buf in (Kf, Vf):
+                        wave2.append(("recv", slab(buf, 2 * P - 1 - j), peer[j], group))
         reqs2 = _exchange(wave2)
 
         def call(q_c, n):
@@ -192,6 +209,9 @@ class _ContextParallel(torch.autograd.Function):
         # counter: the lower call's saved views cover only rows below that, which stay as they are)
         for r_ in reqs2:
             r_.wait()
+        for w, tmp, buf in zip(w2, up, (Kf, Vf)):
+            _wait(w)
+            buf.data[P * tc:].view(P - rank, tc, B, H, D).copy_(tmp.view(P, tc, B, H, D)[rank:].flip(0))
         _mark("upper halves gathered")
         out_hi, leaves_hi = call(q[:, :, tc:], n_hi)
         _mark("upper chunk forward")
@@ -207,6 +227,7 @@ class _ContextParallel(torch.autograd.Function):
         lo_c, hi_c = zigzag_chunks(P, rank)
         n_lo = (lo_c + 1) * tc
         dev = dout.device
+        collective = _upper_half_mode(group) == "collective"
         peer = [dist.get_global_rank(group, j) for j in range(P)]
 
         def seq_major_mem(g):
@@ -237,12 +258,26 @@ class _ContextParallel(torch.autograd.Function):
             else:
                 works.append(dist.reduce_scatter_tensor(final[:tc], g_hi[:P * tc], op=dist.ReduceOp.SUM, group=group,
                                                         async_op=True))
-            # partials of this rank's upper chunk: its own (slot 0) and one from every rank below it
-            recv[name] = torch.empty((rank + 1, tc) + tail, dtype=g_hi.dtype, device=dev)
-            recv[name][0].copy_(g_hi[hi_c * tc:(hi_c + 1) * tc])
+            if collective:
+                # upper halves by reduce-scatter too: slab i of the input belongs to rank i, i.e. is chunk 2P-1-i;
+                # this rank has partials for i >= rank only
+                inp = torch.zeros((P, tc) + tail, dtype=g_hi.dtype, device=dev)
+                inp[rank:].copy_(g_hi[P * tc:].view((P - rank, tc) + tail).flip(0))
+                if dist.get_backend(group) == "gloo":
+                    dist.all_reduce(inp, group=group)
+                    final[tc:].copy_(inp[rank])
+                else:
+                    works.append(dist.reduce_scatter_tensor(final[tc:], inp, op=dist.ReduceOp.SUM, group=group,
+                                                            async_op=True))
+            else:
+                # partials of this rank's upper chunk: its own (slot 0) and one from every rank below it
+                recv[name] = torch.empty((rank + 1, tc) + tail, dtype=g_hi.dtype, device=dev)
+                recv[name][0].copy_(g_hi[hi_c * tc:(hi_c + 1) * tc])
             mine[name], out_lo_hi[name] = g_hi, final
         for j in range(P):
             for name in ("k", "v", "g"):
+                if collective:
+                    break
                 if j > rank:     # chunk 2P-1-j is below this rank's horizon 2P-1-rank: it has a partial for it
                     c = 2 * P - 1 - j
                     ops_list.append(("send", mine[name][c * tc:(c + 1) * tc], peer[j], group))
@@ -257,7 +292,8 @@ class _ContextParallel(torch.autograd.Function):
         _mark("gradients exchanged")
         grads = []
         for name in ("k", "v", "g"):
-            torch.sum(recv[name], dim=0, out=out_lo_hi[name][tc:])     # (16-bit sums accumulate in fp32)
+            if not collective:
+                torch.sum(recv[name], dim=0, out=out_lo_hi[name][tc:])     # (16-bit sums accumulate in fp32)
             grads.append(_head_first(out_lo_hi[name]))
         dk, dv, dg = grads
         dq = torch.cat([dq_lo, dq_hi], dim=2)
