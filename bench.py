@@ -264,13 +264,28 @@ def context_parallel_leg(world, rank, dev, steps=5, warmup=3):
            for n in ("q", "k", "v", "log_fgate", "dout")}
     q, k, v, lf = [loc[n].requires_grad_() for n in ("q", "k", "v", "log_fgate")]
 
-    group = sharding.context_parallel_group()     # NCCL kernels on a high-priority stream
+    # How the upper halves travel and the priority of the NCCL stream are tuned here, in the run itself: every
+    # candidate is timed for a few steps and the fastest one measured (all of them are reported).
+    candidates = [("p2p", True), ("collective", True), ("collective", False)]
+    groups = {True: sharding.context_parallel_group(high_priority=True),
+              False: sharding.context_parallel_group(high_priority=False)}
+    state = {"group": None}
 
     def cp_step():
         q.grad = k.grad = v.grad = lf.grad = None
-        sharding.context_parallel_attention(q, k, v, lf, group=group).backward(loc["dout"])
+        sharding.context_parallel_attention(q, k, v, lf, group=state["group"]).backward(loc["dout"])
 
+    trial = {}
+    for mode, hp in candidates:
+        sharding.UPPER_EXCHANGE, state["group"] = mode, groups[hp]
+        t_ = torch.tensor([timed(cp_step, 2, 3)], dtype=torch.float64, device=dev)
+        dist.all_reduce(t_, op=dist.ReduceOp.MAX)
+        trial[f"{mode}, {'high' if hp else 'default'}-priority stream"] = float(t_.item())
+    best = min(trial, key=trial.get)              # (the same on every rank: the times were max-reduced)
+    mode, hp = candidates[list(trial).index(best)]
+    sharding.UPPER_EXCHANGE, state["group"] = mode, groups[hp]
     ms = timed(cp_step, warmup, steps)
+    sharding.UPPER_EXCHANGE = None
     _lib.check_status()
     t = torch.tensor([ms], dtype=torch.float64, device=dev)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -281,10 +296,11 @@ def context_parallel_leg(world, rank, dev, steps=5, warmup=3):
             "ms_per_step": ms, "tflops": flops / (ms * 1e-3) / 1e12, "one_gpu_ms": one_gpu_ms,
             "one_gpu_tflops": flops / (one_gpu_ms * 1e-3) / 1e12, "speedup": one_gpu_ms / ms,
             "efficiency": one_gpu_ms / (world * ms), "steps": steps, "warmup": warmup,
-            "exchange": "batched NCCL point-to-point transfers of K, V and log-gate chunk slabs into sequence-major "
-                        "staging (two waves, the second under the first chunk's forward), partial gradients sent to "
-                        "each chunk's owner and summed in fp32; NCCL kernels on a high-priority stream; no "
-                        "collective inside the kernels"}
+            "upper_half_exchange": best, "ms_per_step_by_exchange_3_steps": trial,
+            "exchange": "lower halves of K, V (chunk j on rank j) by NCCL all-gather into sequence-major staging, "
+                        "their gradients by reduce-scatter; upper halves point to point (causal subset, slabs "
+                        "straight into place, under the first chunk's forward) or by collectives, whichever "
+                        "measured faster in this run; no collective inside the kernels"}
 
 
 # --------------------------------------------------------------------------- upstream's Triton operator
@@ -667,23 +683,25 @@ def run_ours(args, w, wname):
             qry_tf = (6.0 / 14.0) * flops / (dq_ms * max(dq_n // args.steps, 1) * 1e-3) / 1e12
             pair_tf = (10.0 / 14.0) * flops / ((bwd_ms + dq_ms) * per * 1e-3) / 1e12
             two = {"key_side": {"kernel": "fox_attn_bwd_kv_kernel", "ms_per_launch": bwd_ms, "executed_tflops": key_tf,
-                                "frac": key_tf / peaks["bf16_sustained"]},
+                                "frac": key_tf / peaks["bf16"], "frac_of_sustained_peak": key_tf / peaks["bf16_sustained"]},
                    "query_side": {"kernel": "fox_attn_bwd_dq2_kernel", "ms_per_launch": dq_ms, "executed_tflops": qry_tf,
-                                  "frac": qry_tf / peaks["bf16_sustained"]},
+                                  "frac": qry_tf / peaks["bf16"], "frac_of_sustained_peak": qry_tf / peaks["bf16_sustained"]},
                    "algorithmic_tflops_of_the_pair": pair_tf,
-                   "algorithmic_frac_of_the_pair": pair_tf / peaks["bf16_sustained"]}
+                   "algorithmic_frac_of_the_pair": pair_tf / peaks["bf16"]}
             if dq_ms > bwd_ms:
                 bwd_kernel_name, bwd_tf, bwd_ms, bwd_n = "fox_attn_bwd_dq2_kernel", qry_tf, dq_ms, dq_n
             else:
                 bwd_kernel_name, bwd_tf = "fox_attn_bwd_kv_kernel", key_tf
         roof = {
             "kernel": bwd_kernel_name, "bound": "tensor", "achieved": bwd_tf,
-            "peak": peaks["bf16_sustained"], "unit": "TFLOP/s", "frac": bwd_tf / peaks["bf16_sustained"],
-            "peak_kind": f"bf16_tflops_sustained of {peaks['source']} (kernel timed inside the stepping loop)",
-            "frac_of_burst_peak": bwd_tf / peaks["bf16"],
+            "peak": peaks["bf16"], "unit": "TFLOP/s", "frac": bwd_tf / peaks["bf16"],
+            "peak_kind": (f"bf16_tflops (burst) of {peaks['source']}: the timed region lasts a fraction of a second at "
+                          "full clocks; the sustained figure is beside it"),
+            "frac_of_sustained_peak": bwd_tf / peaks["bf16_sustained"],
             "traffic": TRAFFIC_BYTES_PER_LAUNCH.get((wname, bwd_kernel_name), TRAFFIC_BYTES_PER_LAUNCH.get(wname)),
             "ms_per_launch": bwd_ms, "launches": bwd_n,
-            "fwd_kernel": {"achieved": fwd_tf, "frac": fwd_tf / peaks["bf16_sustained"], "ms_per_launch": fwd_ms},
+            "fwd_kernel": {"achieved": fwd_tf, "frac": fwd_tf / peaks["bf16"],
+                           "frac_of_sustained_peak": fwd_tf / peaks["bf16_sustained"], "ms_per_launch": fwd_ms},
             "all_kernels_ms": {k_: round(v_[1], 4) for k_, v_ in kern.items()},
         }
         if two_kernel:

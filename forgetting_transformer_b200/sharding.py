@@ -90,7 +90,7 @@ def _head_first(x: torch.Tensor) -> torch.Tensor:
     return x.movedim(0, 2)
 
 
-def context_parallel_group(ranks: Optional[Sequence[int]] = None):
+def context_parallel_group(ranks: Optional[Sequence[int]] = None, high_priority: bool = True):
     """A process group for :func:`context_parallel_attention` whose NCCL kernels run on a high-priority stream.
 
     The second wave of gathers and the first reduce-scatter travel while an attention kernel occupies every SM;
@@ -101,16 +101,19 @@ def context_parallel_group(ranks: Optional[Sequence[int]] = None):
     if dist.get_backend() != "nccl":
         return dist.new_group(ranks=ranks)
     opts = dist.ProcessGroupNCCL.Options()
-    opts.is_high_priority_stream = True
+    opts.is_high_priority_stream = bool(high_priority)
     return dist.new_group(ranks=ranks, backend="nccl", pg_options=opts)
+
+
+UPPER_EXCHANGE = None   # "p2p" | "collective"; None: $FOX_B200_CP_UPPER, else "p2p"
 
 
 def _upper_half_mode(group) -> str:
     """How the upper halves travel: "p2p" (point to point, the causal subset only, straight into place) or
-    "collective" (all-gather / reduce-scatter of all of them plus reordering copies).  FOX_B200_CP_UPPER selects;
-    default p2p."""
+    "collective" (all-gather / reduce-scatter of all of them plus reordering copies).  Set
+    ``sharding.UPPER_EXCHANGE`` (every rank alike) or FOX_B200_CP_UPPER; default p2p."""
     import os
-    return os.environ.get("FOX_B200_CP_UPPER", "p2p")
+    return UPPER_EXCHANGE or os.environ.get("FOX_B200_CP_UPPER", "p2p")
 
 
 def _owner(chunk: int, world: int) -> int:
