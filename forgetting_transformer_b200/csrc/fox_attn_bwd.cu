@@ -44,6 +44,11 @@
 #ifndef FOX_BWD_FP32_SUMS
 #define FOX_BWD_FP32_SUMS 1
 #endif
+// of every 8 column groups of 4 in phase A, how many take one of their two column pairs through the FMA-pipe
+// exponential instead of the ex2 unit (0: none)
+#ifndef FOX_BWD_POLY
+#define FOX_BWD_POLY 0
+#endif
 
 namespace fox {
 
@@ -538,9 +543,13 @@ fox_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           const float2 x23 = __ffma2_rn(make_float2(__uint_as_float(sreg[c4 * 4 + 2]), __uint_as_float(sreg[c4 * 4 + 3])),
                                         scale2, __fadd2_rn(make_float2(ev.z, ev.w), negb2));
           const float xs[4] = {x01.x, x01.y, x23.x, x23.y};
+          float2 poly23 = make_float2(0.f, 0.f);
+          const bool use_poly = (c4 < FOX_BWD_POLY);
+          if (use_poly) poly23 = poly_exp2_x2(make_float2(fminf(x23.x, 0.f), fminf(x23.y, 0.f)));   // (p <= 1)
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
-            float pe = fast_exp2(xs[e]);
+            float pe = (use_poly && e >= 2) ? (e == 2 ? poly23.x : poly23.y) : fast_exp2(xs[e]);
+            if (use_poly && e >= 2 && !(xs[e] > -120.f)) pe = 0.f;   // (the polynomial bottoms out at 2^-125; also -inf / NaN)
             if (diag) pe = (col0 + c4 * 4 + e >= c_min) ? pe : 0.f;
             pf[ch * 32 + c4 * 4 + e] = pe;
           }
