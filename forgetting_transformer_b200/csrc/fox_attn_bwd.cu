@@ -7,9 +7,10 @@
 //
 // One CTA = one (batch, head, 128-row KV tile); it keeps K and V resident and
 // streams the query tiles from the causal diagonal downwards.  704 threads:
-//   warps 0-15 : compute.  Thread (g = warp/4, r = tid%128) owns KV row r (TMEM lane r
-//                of S^T / dP^T) and the 32 query columns [32g, 32g+32) of the tile; four
-//                warps per scheduler are what it takes to keep the ex2 unit busy.
+//   warps 0-15 : compute.  Warp (g = warp/4, quarter = warp%4) owns KV rows [32 quarter, +32) (TMEM lanes of
+//                S^T / dP^T) x query columns [32g, 32g+32) of the tile and reads them as matrix fragments
+//                (tcgen05.ld 16x256b): a thread holds 4 KV rows x 4 column pairs.  Four warps per scheduler
+//                are what it takes to keep the ex2 unit busy.
 //   warp  16   : TMA producer (also stages the per-row vectors)    warp 17 : tcgen05.mma issuer
 //   warps 18-21: dQ drain.  Thread owns one query row of the dQ tile accumulator: TMEM ->
 //                swizzled shared memory -> TMA add-reduction into the fp32 workspace.
@@ -23,19 +24,21 @@
 // dV(i) and S(i+1); while phase A(i+1) runs it does dK(i), dP(i+1), dQ(i) (D = 128, where the dQ
 // accumulator has to share columns with S^T / dP^T: dK(i), dQ(i), drain, S(i+1), dP(i+1)).
 // The two halves of the log-gate gradient, colsum(dS) per key and rowsum(dS) per query, are sums of the fp32
-// dS values, as upstream's are (lines 1122, 1326): the column sum is a running sum of the thread that owns
-// the KV row; the row sum of a tile is formed across the 32 lanes of a warp by a transposing reduction
-// (31 shuffles leave lane l with the warp's sum of query column l) after dS has been handed to the tensor
-// pipe, i.e. under the dK / dQ products, and added to the fp32 workspace.  Both halves sum the same values,
-// so they cancel in the reverse prefix sum as upstream's do; against upstream's own backward kernels on the
-// same saved tensors the gate gradient then agrees to 1e-4.  The reduction sits on the elementwise warps' own
-// chain (phase A -> phase B -> reduction -> next tile) and costs 0.7 ms of 4.2 ms on B2 T16384 H24 D64.
-// (FOX_BWD_FP32_SUMS=0 builds the earlier form: a 16-column "ones" tile appended to K and Q through the
-// descriptors' leading offset makes the dQ and dK products deliver the sums of the 16-bit dS values -- free,
-// but the rounding of dS to 8 significant bits, summed over the (query, key) pairs that straddle a position,
-// leaves the gate gradient 2-4e-2 off upstream's, up to 1.8 times the tolerance.  Writing dS as fp16 for bf16
-// inputs, to keep the free sums at 11 significant bits, is not an option: a kind::f16 product whose A and B
-// operands differ in format raises an illegal-instruction error on sm_100a.)
+// dS values, as upstream's are (lines 1122, 1326).  With the fragment layout a thread's column sums (over the
+// query index) are running sums of its four KV rows, joined across the four threads of a row once per launch;
+// the row sum of a tile (over the KV index) is a sum over the thread's four rows followed by a transposing
+// reduction across the eight threads that share a column pair (7 shuffles leave each thread with one query
+// column's sum), done after dS has been handed to the tensor pipe and added to the fp32 workspace.  Both halves
+// sum the same values, so they cancel in the reverse prefix sum as upstream's do; against upstream's own backward
+// kernels on the same saved tensors the gate gradient then agrees to 1e-4.
+// Measured on B2 T16384 H24 D64: 4.18 ms.  With one KV row per thread (tcgen05.ld 32x32b: 32 columns of one
+// lane) the same sums took a 31-shuffle, 62-select reduction per warp and tile and the kernel 4.96 ms; that
+// layout with the sums taken from 16 "ones" columns appended to K and Q (the dQ and dK products then deliver
+// sums of the 16-bit dS values for free: FOX_BWD_FP32_SUMS=0) took 4.23 ms but left the gate gradient 2-4e-2
+// off upstream's, up to 1.8 times the tolerance: the rounding of dS to 8 significant bits, summed over the
+// (query, key) pairs that straddle a position.  Writing dS as fp16 for bf16 inputs, to keep the free sums at
+// 11 significant bits, is not an option: a kind::f16 product whose A and B operands differ in format raises an
+// illegal-instruction error on sm_100a.
 #include <type_traits>
 
 #include "fox_common.cuh"
@@ -44,12 +47,6 @@
 #ifndef FOX_BWD_FP32_SUMS
 #define FOX_BWD_FP32_SUMS 1
 #endif
-// of every 8 column groups of 4 in phase A, how many take one of their two column pairs through the FMA-pipe
-// exponential instead of the ex2 unit (0: none)
-#ifndef FOX_BWD_POLY
-#define FOX_BWD_POLY 0
-#endif
-
 namespace fox {
 
 constexpr int kBwdBM = FOX_BWD_BLOCK_M;
@@ -166,7 +163,7 @@ fox_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     mbar_init(&bar_ds_done, 128 * kCWG);
     for (int s = 0; s < kDqBufs; ++s) { mbar_init(&bar_dq_full[s], 1); mbar_init(&bar_dq_free[s], 128); }
     mbar_init(&bar_done, 1);
-    mbar_init(&bar_colsum, 128 * (kCWG - 1));
+    mbar_init(&bar_colsum, 128 * kCWG);
     // q_full: the TMA transaction plus one arrival of the producer warp for the per-row vectors
     for (int s = 0; s < STQ; ++s) { mbar_init(&bar_q_full[s], 2); mbar_init(&bar_q_empty[s], 1); }
     for (int s = 0; s < STDO; ++s) { mbar_init(&bar_do_full[s], 1); mbar_init(&bar_do_empty[s], 1); }
@@ -498,65 +495,90 @@ fox_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     if (warp == kDrainWarp0) tma_store_wait_all<0>();
   } else {
     // ===================== compute warps =====================
-    const int g = warp >> 2;              // which CW-column slice of the query tile
-    const int r = tid & 127;              // KV row inside the tile == TMEM lane
+    // A warp reads its 32 KV rows x 32 query columns of S^T / dP^T as matrix fragments (two 16-lane loads):
+    // a thread holds four KV rows (r0 + 8 m) x eight query columns (pairs 8 k + q2, + 1).  Row sums of dS over the
+    // KV index then need three shuffle steps over 8 values instead of five over 32, the column sums stay in
+    // registers for the whole launch, and the per-query vectors are read as four 8-byte pairs.
+    static_assert(CW == 32, "the fragment mapping below is written for four compute warpgroups");
+    const int g = warp >> 2;               // which 32-column slice of the query tile
+    const int quarter = warp & 3;          // which 32 KV rows (TMEM lanes) of the tile
+    const int q2 = (lane & 3) * 2;         // this thread's column pair inside every 8-column group
+    const int r0 = quarter * 32 + (lane >> 2);
+    const int r = tid & 127;               // epilogue: KV row inside the tile == TMEM lane
     const int j = nb * kBwdBN + r;
     const bool j_ok = (j < N) && (j >= seq0);
     const float* lam = p.lam + bh * N;
-    // an invalid KV row gets b_j = +inf, i.e. probability 0 everywhere
     // Lambda_i - Lambda_j is formed from prefixes relative to the tile's first key: scaling a prefix of -1e4
-    // by log2(e) first would cost an absolute 2e-3 per logit
-    const float b_j = j_ok ? (lam[j] - lam[min(nb * kBwdBN, N - 1)]) * kLog2eB : INFINITY;
-    const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
-    const uint32_t tS = tbase + lane_base + kColS, tDP = tbase + lane_base + kColDP;
-    float colsum = 0.f;
+    // by log2(e) first would cost an absolute 2e-3 per logit.  An invalid KV row gets b_j = +inf, i.e.
+    // probability 0 everywhere.
+    const float lam_ref = lam[min(nb * kBwdBN, N - 1)];
+    float2 negb2[4];
+    int jp[4];                             // KV index minus the causal offset, relative to this thread's first column
+#pragma unroll
+    for (int m = 0; m < 4; ++m) {
+      const int jm = nb * kBwdBN + r0 + 8 * m;
+      const bool okm = (jm < N) && (jm >= seq0);
+      const float nb_j = okm ? -(lam[min(jm, N - 1)] - lam_ref) * kLog2eB : -INFINITY;
+      negb2[m] = make_float2(nb_j, nb_j);
+      jp[m] = jm - P - g * 32 - q2;
+    }
+    const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
+    const uint32_t tS = tbase + lane_base + kColS + g * 32, tDP = tbase + lane_base + kColDP + g * 32;
+    // stmatrix: this thread addresses row (lane & 7) of the 8x8 block of column group (lane >> 3)
+    const uint32_t ds_addr0 = smem_u32(sdS) + ((g * 32) >> 6) * 16384 + (quarter * 32 + (lane & 7)) * 128 +
+                              ((((((g * 32) & 63) >> 3) + (lane >> 3)) ^ (lane & 7)) << 4);
+    float2 colacc[4];
+#pragma unroll
+    for (int m = 0; m < 4; ++m) colacc[m] = make_float2(0.f, 0.f);
     bool ok = true;
-    const float2 scale2 = make_float2(p.qk_scale, p.qk_scale), negb2 = make_float2(-b_j, -b_j);
+    const float2 scale2 = make_float2(p.qk_scale, p.qk_scale);
 
-    for (int it = 0; it < n_tiles; ++it) {
+    auto tile = [&](auto diag_tag, int it) -> bool {
+      constexpr bool kDiag = decltype(diag_tag)::value;
       const int mb = mb_lo + it;
+      const int st = it % STQ;
       if (warp < 8) stamp(6 + warp, 4, it);
-      ok = mbar_wait(&bar_s_full, it & 1, abortp, p.status, kBSiteSFull, it);
+      bool good = mbar_wait(&bar_s_full, it & 1, abortp, p.status, kBSiteSFull, it);
       if (warp < 8) stamp(6 + warp, 6, it);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
+      good = __all_sync(0xffffffffu, good);
+      if (!good) return false;
       tc_fence_after();
       if (warp < 8) stamp(6 + warp, 0, it);
-      // first query column of this tile this KV row may be attended from (causal)
-      const int c_min = j - P - mb * kBwdBM;
-      const bool diag = (nb * kBwdBN + kBwdBN - 1 - P - mb * kBwdBM) > 0;
-      float pf[CW];
+      float2 pf[2][4][2];   // [16-lane half][column group][row + 8]
       // ---------------- phase A: probabilities ----------------
+      {
+        const float2* e2 = reinterpret_cast<const float2*>(&s_e[st][g * 32 + q2]);
+        float2 ev[4];
 #pragma unroll
-      for (int ch = 0; ch < CW / 32; ++ch) {
-        const int col0 = g * CW + ch * 32;
-        uint32_t sreg[32], pk[16];
-        tmem_ld32(tS + col0, sreg);
-        tmem_ld_wait();
-        const float4* e4 = reinterpret_cast<const float4*>(&s_e[it % STQ][col0]);
-        // packed two-wide fp32 arithmetic: x = s c + (e_i - b_j), one add and one fused multiply-add per column pair
+        for (int k = 0; k < 4; ++k) ev[k] = e2[4 * k];
 #pragma unroll
-        for (int c4 = 0; c4 < 8; ++c4) {
-          const float4 ev = e4[c4];
-          const float2 x01 = __ffma2_rn(make_float2(__uint_as_float(sreg[c4 * 4]), __uint_as_float(sreg[c4 * 4 + 1])),
-                                        scale2, __fadd2_rn(make_float2(ev.x, ev.y), negb2));
-          const float2 x23 = __ffma2_rn(make_float2(__uint_as_float(sreg[c4 * 4 + 2]), __uint_as_float(sreg[c4 * 4 + 3])),
-                                        scale2, __fadd2_rn(make_float2(ev.z, ev.w), negb2));
-          const float xs[4] = {x01.x, x01.y, x23.x, x23.y};
-          float2 poly23 = make_float2(0.f, 0.f);
-          const bool use_poly = (c4 < FOX_BWD_POLY);
-          if (use_poly) poly23 = poly_exp2_x2(make_float2(fminf(x23.x, 0.f), fminf(x23.y, 0.f)));   // (p <= 1)
+        for (int half = 0; half < 2; ++half) {
+          uint32_t sreg[16], pk[8];
+          tmem_ld_16x256b_x4(tS + (static_cast<uint32_t>(half * 16) << 16), sreg);
+          tmem_ld_wait();
 #pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            float pe = (use_poly && e >= 2) ? (e == 2 ? poly23.x : poly23.y) : fast_exp2(xs[e]);
-            if (use_poly && e >= 2 && !(xs[e] > -120.f)) pe = 0.f;   // (the polynomial bottoms out at 2^-125; also -inf / NaN)
-            if (diag) pe = (col0 + c4 * 4 + e >= c_min) ? pe : 0.f;
-            pf[ch * 32 + c4 * 4 + e] = pe;
+          for (int k = 0; k < 4; ++k) {
+#pragma unroll
+            for (int h8 = 0; h8 < 2; ++h8) {
+              const int m = half * 2 + h8;
+              // packed two-wide fp32 arithmetic: x = s c + (e_i - b_j)
+              const float2 x = __ffma2_rn(make_float2(__uint_as_float(sreg[4 * k + 2 * h8]),
+                                                      __uint_as_float(sreg[4 * k + 2 * h8 + 1])),
+                                          scale2, __fadd2_rn(ev[k], negb2[m]));
+              float2 pe = make_float2(fast_exp2(x.x), fast_exp2(x.y));
+              if constexpr (kDiag) {
+                // query column (8 k + e past this thread's first) below the first one this KV row is attended from
+                const int c_min = jp[m] - mb * kBwdBM;
+                pe.x = (8 * k >= c_min) ? pe.x : 0.f;
+                pe.y = (8 * k + 1 >= c_min) ? pe.y : 0.f;
+              }
+              pf[half][k][h8] = pe;
+              pk[2 * k + h8] = pack2<kBf16>(pe.x, pe.y);
+            }
           }
-          pk[c4 * 2] = pack2<kBf16>(pf[ch * 32 + c4 * 4], pf[ch * 32 + c4 * 4 + 1]);
-          pk[c4 * 2 + 1] = pack2<kBf16>(pf[ch * 32 + c4 * 4 + 2], pf[ch * 32 + c4 * 4 + 3]);
+          // inside this warpgroup's own (already loaded) S columns
+          tmem_st_16x128b_x4(tS + (static_cast<uint32_t>(half * 16) << 16), pk);
         }
-        tmem_st16(tS + g * CW + ch * 16, pk);  // inside this warpgroup's own (already loaded) S columns
       }
       tmem_st_wait();
       tc_fence_before();
@@ -565,54 +587,52 @@ fox_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 
       // ---------------- phase B: dS ----------------
       if (warp < 8) stamp(6 + warp, 7, it);
-      ok = mbar_wait(&bar_dp_full, it & 1, abortp, p.status, kBSiteDpFull, it);
+      good = mbar_wait(&bar_dp_full, it & 1, abortp, p.status, kBSiteDpFull, it);
       // dP(it) was issued behind dQ(it - kDsBufs) and a commit covers everything issued before it, so the
       // dS buffer about to be overwritten is no longer being read.
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
+      good = __all_sync(0xffffffffu, good);
+      if (!good) return false;
       tc_fence_after();
       if (warp < 8) stamp(6 + warp, 2, it);
-      uint8_t* dbuf = sdS + (it % kDsBufs) * 32768 + r * 128;
+      const uint32_t ds_addr = ds_addr0 + (it % kDsBufs) * 32768;
+      float2 rs[4];         // sums over this thread's four KV rows, per query-column pair
+      {
+        const float2* d2 = reinterpret_cast<const float2*>(&s_delta[st][g * 32 + q2]);
+        float2 nd[4];       // -delta_i
 #pragma unroll
-      for (int ch = 0; ch < CW / 32; ++ch) {
-        const int col0 = g * CW + ch * 32;
-        uint32_t dpreg[32], dsk[16];
-        tmem_ld32(tDP + col0, dpreg);
-        tmem_ld_wait();
-        const float4* d4 = reinterpret_cast<const float4*>(&s_delta[it % STQ][col0]);
+        for (int k = 0; k < 4; ++k) nd[k] = d2[4 * k];
 #pragma unroll
-        for (int c4 = 0; c4 < 8; ++c4) {
-          const float4 nd4 = d4[c4];   // -delta_i
-          const int c0 = ch * 32 + c4 * 4;
-          const float2 ds01 = __fmul2_rn(make_float2(pf[c0], pf[c0 + 1]),
-                                         __fadd2_rn(make_float2(__uint_as_float(dpreg[c4 * 4]), __uint_as_float(dpreg[c4 * 4 + 1])),
-                                                    make_float2(nd4.x, nd4.y)));
-          const float2 ds23 = __fmul2_rn(make_float2(pf[c0 + 2], pf[c0 + 3]),
-                                         __fadd2_rn(make_float2(__uint_as_float(dpreg[c4 * 4 + 2]), __uint_as_float(dpreg[c4 * 4 + 3])),
-                                                    make_float2(nd4.z, nd4.w)));
-          const float dsv[4] = {ds01.x, ds01.y, ds23.x, ds23.y};
-          const uint32_t d01 = pack2<kBf16>(dsv[0], dsv[1]), d23 = pack2<kBf16>(dsv[2], dsv[3]);
-          dsk[c4 * 2] = d01;
-          dsk[c4 * 2 + 1] = d23;
-          if constexpr (kNoDQ || kFp32Sums) {
-            // fp32 values on both sides (with kNoDQ the row sums come from another kernel's recomputed dS, which
-            // agrees to fp32 rounding; the two kernels' 16-bit roundings differ on a few percent of the elements)
-            colsum += (dsv[0] + dsv[1]) + (dsv[2] + dsv[3]);
-            if constexpr (kFp32Sums && !kNoDQ) {
+        for (int half = 0; half < 2; ++half) {
+          uint32_t dpreg[16], dsk[8];
+          tmem_ld_16x256b_x4(tDP + (static_cast<uint32_t>(half * 16) << 16), dpreg);
+          tmem_ld_wait();
 #pragma unroll
-              for (int e = 0; e < 4; ++e) pf[ch * 32 + c4 * 4 + e] = dsv[e];   // p is no longer needed
+          for (int k = 0; k < 4; ++k) {
+#pragma unroll
+            for (int h8 = 0; h8 < 2; ++h8) {
+              const int m = half * 2 + h8;
+              const float2 ds = __fmul2_rn(pf[half][k][h8],
+                                           __fadd2_rn(make_float2(__uint_as_float(dpreg[4 * k + 2 * h8]),
+                                                                  __uint_as_float(dpreg[4 * k + 2 * h8 + 1])),
+                                                      nd[k]));
+              const uint32_t d16 = pack2<kBf16>(ds.x, ds.y);
+              dsk[2 * k + h8] = d16;
+              if constexpr (kNoDQ || kFp32Sums) {
+                // fp32 values on both sides (with kNoDQ the row sums come from another kernel's recomputed dS, which
+                // agrees to fp32 rounding; the two kernels' 16-bit roundings differ on a few percent of the elements)
+                colacc[m] = __fadd2_rn(colacc[m], ds);
+                if constexpr (kFp32Sums && !kNoDQ) rs[k] = (m == 0) ? ds : __fadd2_rn(rs[k], ds);
+              } else if (!kColsumMMA) {
+                colacc[m] = __fadd2_rn(colacc[m], unpack2<kBf16>(d16));
+              }
             }
-          } else if (!kColsumMMA) {
-            const float2 r01 = unpack2<kBf16>(d01), r23 = unpack2<kBf16>(d23);
-            colsum += (r01.x + r01.y) + (r23.x + r23.y);
           }
-        }
-        tmem_st16(tDP + g * CW + ch * 16, dsk);
+          tmem_st_16x128b_x4(tDP + (static_cast<uint32_t>(half * 16) << 16), dsk);
+          if constexpr (!kNoDQ) {   // (dS in shared memory only feeds the dQ product)
 #pragma unroll
-        for (int q4 = 0; q4 < (kNoDQ ? 0 : 4); ++q4) {  // (dS in shared memory only feeds the dQ product)
-          const int cj = ((col0 & 63) >> 3) + q4;
-          *reinterpret_cast<uint4*>(dbuf + (col0 >> 6) * 16384 + ((cj ^ (r & 7)) << 4)) =
-              make_uint4(dsk[q4 * 4], dsk[q4 * 4 + 1], dsk[q4 * 4 + 2], dsk[q4 * 4 + 3]);
+            for (int h8 = 0; h8 < 2; ++h8)
+              stmatrix_x4(ds_addr + (half * 2 + h8) * 1024, dsk[h8], dsk[2 + h8], dsk[4 + h8], dsk[6 + h8]);
+          }
         }
       }
       tmem_st_wait();
@@ -621,26 +641,34 @@ fox_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       mbar_arrive(&bar_ds_done);
       if (warp < 8) stamp(6 + warp, 3, it);
       if constexpr (kFp32Sums && !kNoDQ) {
-        // rowsum(dS) of this warp's 32 KV rows, under the products that now read dS: at the step with lane
-        // distance `off` a lane keeps the half of its columns whose index has that bit as its own lane number
-        // does and receives the partner's sums of them, so lane l ends with the sum of column l
+        // rowsum(dS) over this warp's 32 KV rows, under the products that now read dS: the eight threads that
+        // share a column pair differ in lane bits 2..4; at the step with lane distance `off` a thread keeps the
+        // half of its values whose index has that bit as its own lane number does and receives the partner's
+        // sums of them, so it ends with the sum of one column
+        float v[8] = {rs[0].x, rs[0].y, rs[1].x, rs[1].y, rs[2].x, rs[2].y, rs[3].x, rs[3].y};
 #pragma unroll
-        for (int ch = 0; ch < CW / 32; ++ch) {
-          float* vsum = &pf[ch * 32];
+        for (int step = 0; step < 3; ++step) {
+          const int off = 16 >> step, n = 4 >> step;
+          const bool upper = (lane & off) != 0;
 #pragma unroll
-          for (int off = 16; off >= 1; off >>= 1) {
-            const bool upper = (lane & off) != 0;
-#pragma unroll
-            for (int c = 0; c < off; ++c) {
-              const float send = upper ? vsum[c] : vsum[c + off];
-              const float keep = upper ? vsum[c + off] : vsum[c];
-              vsum[c] = keep + __shfl_xor_sync(0xffffffffu, send, off);
-            }
+          for (int c = 0; c < n; ++c) {
+            const float send = upper ? v[c] : v[c + n];
+            const float keep = upper ? v[c + n] : v[c];
+            v[c] = keep + __shfl_xor_sync(0xffffffffu, send, off);
           }
-          const int i = mb * kBwdBM + g * CW + ch * 32 + lane;
-          if (i < M) atomicAdd(p.dlam_row + bh * M + i, vsum[0]);
         }
+        const int c8 = ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1);
+        const int i = mb * kBwdBM + g * 32 + 8 * (c8 >> 1) + q2 + (c8 & 1);
+        if (i < M) atomicAdd(p.dlam_row + bh * M + i, v[0]);
       }
+      return true;
+    };
+
+    for (int it = 0; it < n_tiles; ++it) {
+      // (only the tiles on the diagonal mask by position)
+      const bool diag = (nb * kBwdBN + kBwdBN - 1 - P - (mb_lo + it) * kBwdBM) > 0;
+      ok = diag ? tile(std::true_type{}, it) : tile(std::false_type{}, it);
+      if (!ok) break;
     }
 
     // ---- epilogue: warpgroup 0 writes dK (and the key-side gate gradient), warpgroup 1 writes dV ----
@@ -648,19 +676,23 @@ fox_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       ok = mbar_wait(&bar_done, 0, abortp, p.status, kBSiteDone);
       ok = __all_sync(0xffffffffu, ok);
     }
+    float colsum = 0.f;
     if (!kColsumMMA && ok) {
-      // per-thread partial column sums of the kCWG slices -> slice 0 (the per-row vector buffers are dead by now)
-      float* part = (g - 1) < 2 ? &s_e[(g - 1) & 1][0] : &s_delta[0][0];
-      if (g > 0) {
-        part[r] = colsum;
-        mbar_arrive(&bar_colsum);
-      } else {
+      // per-thread partial column sums -> the four threads of a row -> one array per query-column slice (the
+      // per-row vector buffers are dead by now) -> warpgroup 0, whose thread r owns KV row r from here on
+      float* part = g < 2 ? &s_e[g][0] : &s_delta[g - 2][0];
+#pragma unroll
+      for (int m = 0; m < 4; ++m) {
+        float c = colacc[m].x + colacc[m].y;
+        c += __shfl_xor_sync(0xffffffffu, c, 1);
+        c += __shfl_xor_sync(0xffffffffu, c, 2);
+        if ((lane & 3) == m) part[r0 + 8 * m] = c;
+      }
+      mbar_arrive(&bar_colsum);
+      if (g == 0) {
         ok = mbar_wait(&bar_colsum, 0, abortp, p.status, kBSiteColsum);
         ok = __all_sync(0xffffffffu, ok);
-        if (ok) {
-          colsum += s_e[0][r];
-          if (kCWG > 2) colsum += s_e[1][r] + s_delta[0][r];
-        }
+        if (ok) colsum = (s_e[0][r] + s_e[1][r]) + (s_delta[0][r] + s_delta[1][r]);
       }
     }
     if (ok) {

@@ -294,6 +294,37 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* r) {
       : "memory");
 }
 
+// Matrix-fragment shapes: the warp touches 16 lanes (base lane of taddr: the warp's own quarter, +0 or +16).
+// 16 lanes x 256 bit, four times (32 columns): thread t gets, for each 8-column group k,
+//   r[4k + 0], r[4k + 1] = lane (t / 4),     columns 8k + 2 (t % 4), + 1
+//   r[4k + 2], r[4k + 3] = lane (t / 4) + 8, the same two columns
+// (the accumulator fragment of an m16n8 product).
+__device__ __forceinline__ void tmem_ld_16x256b_x4(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.16x256b.x4.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+// 16 lanes x 128 bit, four times (16 columns): r[2k + 0] = lane (t / 4), column 4k + (t % 4);
+// r[2k + 1] = lane (t / 4) + 8, the same column -- the fragment above with each column pair packed into 32 bits.
+__device__ __forceinline__ void tmem_st_16x128b_x4(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.16x128b.x4.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+      : "memory");
+}
+// Four 8x8 matrices of 16-bit elements to shared memory: matrix m's row (t % 8) is written at the address
+// given by thread 8 m + (t % 8) (16 contiguous bytes); register m of thread t holds that matrix's row t / 4,
+// columns 2 (t % 4), + 1.
+__device__ __forceinline__ void stmatrix_x4(uint32_t smem_addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("stmatrix.sync.aligned.m8n8.x4.shared.b16 [%0], {%1, %2, %3, %4};" ::"r"(smem_addr), "r"(a),
+               "r"(b), "r"(c), "r"(d)
+               : "memory");
+}
+
 // ------------------------------------------------------------ UMMA descriptors
 // Shared-memory tiles are [rows][64 x 16-bit] = 128-byte rows, 8-row groups of
 // 1024 bytes, 128-byte swizzle (16-byte chunk index XOR (row & 7)); tile bases
