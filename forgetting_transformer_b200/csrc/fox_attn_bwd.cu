@@ -47,6 +47,12 @@
 #ifndef FOX_BWD_FP32_SUMS
 #define FOX_BWD_FP32_SUMS 1
 #endif
+// how the two 16-lane halves of a fragment load are scheduled: 0 one after the other, 1 the second in flight
+// under the first half's arithmetic, 2 both before one wait
+#ifndef FOX_BWD_PIPE
+#define FOX_BWD_PIPE 1
+#endif
+
 namespace fox {
 
 constexpr int kBwdBM = FOX_BWD_BLOCK_M;
@@ -551,11 +557,17 @@ fox_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         float2 ev[4];
 #pragma unroll
         for (int k = 0; k < 4; ++k) ev[k] = e2[4 * k];
+        uint32_t sregs[2][16];
+        tmem_ld_16x256b_x4(tS, sregs[0]);
+        if (FOX_BWD_PIPE == 2) tmem_ld_16x256b_x4(tS + (16u << 16), sregs[1]);
+        tmem_ld_wait();
+        if (FOX_BWD_PIPE == 1) tmem_ld_16x256b_x4(tS + (16u << 16), sregs[1]);   // in flight under the first half
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
-          uint32_t sreg[16], pk[8];
-          tmem_ld_16x256b_x4(tS + (static_cast<uint32_t>(half * 16) << 16), sreg);
-          tmem_ld_wait();
+          uint32_t pk[8];
+          if (half == 1 && FOX_BWD_PIPE == 0) tmem_ld_16x256b_x4(tS + (16u << 16), sregs[1]);
+          if (half == 1 && FOX_BWD_PIPE != 2) tmem_ld_wait();
+          const uint32_t* sreg = sregs[half];
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
 #pragma unroll
@@ -601,11 +613,17 @@ fox_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         float2 nd[4];       // -delta_i
 #pragma unroll
         for (int k = 0; k < 4; ++k) nd[k] = d2[4 * k];
+        uint32_t dpregs[2][16];
+        tmem_ld_16x256b_x4(tDP, dpregs[0]);
+        if (FOX_BWD_PIPE == 2) tmem_ld_16x256b_x4(tDP + (16u << 16), dpregs[1]);
+        tmem_ld_wait();
+        if (FOX_BWD_PIPE == 1) tmem_ld_16x256b_x4(tDP + (16u << 16), dpregs[1]);
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
-          uint32_t dpreg[16], dsk[8];
-          tmem_ld_16x256b_x4(tDP + (static_cast<uint32_t>(half * 16) << 16), dpreg);
-          tmem_ld_wait();
+          uint32_t dsk[8];
+          if (half == 1 && FOX_BWD_PIPE == 0) tmem_ld_16x256b_x4(tDP + (16u << 16), dpregs[1]);
+          if (half == 1 && FOX_BWD_PIPE != 2) tmem_ld_wait();
+          const uint32_t* dpreg = dpregs[half];
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
 #pragma unroll
