@@ -774,10 +774,10 @@ def run_ours(args, w, wname):
 # DRAM bytes (read + write) of one backward-kernel launch from an ncu capture of the profiler-sized cases,
 # per workload (None = not captured).
 TRAFFIC_BYTES_PER_LAUNCH = {
-    # backward kernel: 265.6 MB measured on prof_d64; the traffic is per-row (inputs once, outputs once, dQ
+    # backward kernel: 264.4 MB measured on prof_d64; the traffic is per-row (inputs once, outputs once, dQ
     # workspace once), cfg3 has 3x the rows
-    "cfg3": 3 * 265.6e6,
-    "prof_d64": 265.6e6,
+    "cfg3": 3 * 264.4e6,
+    "prof_d64": 264.4e6,
     # head dim 128, one-pass kernel (FOX_B200_ONE_PASS_BWD=1)
     "prof_d128": 632.8e6,
     "cfg4": 4 * 632.8e6,
