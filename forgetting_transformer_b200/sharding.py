@@ -9,18 +9,20 @@ Two schemes, neither present upstream (which only knows data-parallel training):
   contiguous slice of the flattened units and no collective touches the data path.
 
 * context parallel for long sequences -- the sequence is cut into 2P chunks and rank r owns
-  chunks r and 2P-1-r ("zig-zag": causal work is balanced).  Keys, values and log gates travel
-  point to point (batched NCCL sends / receives) into a sequence-major staging buffer
-  (T', B, H, D) in two waves: the lower halves (chunks 0..P-1, one per rank), after which a
-  rank's lower query chunk can already run, and the upper halves a rank may attend to (chunks
-  P..2P-1-r), which travel while that first call computes.  Each query chunk is one call of the ordinary
-  operator against the key prefix it may attend to -- exactly the operator's
-  ``seqlen_q <= seqlen_k`` contract (queries are the last rows), reading the staging buffer
-  through strided views, no reordering copies.  Rows are complete on their owner, so no partial
-  (max, sum, out) triples have to travel; the log-gate prefix is recomputed from the gathered
-  gates by the operator's own prefix-sum kernel.  Backward: both calls, then every chunk's partial
-  key / value / gate gradient is sent to the chunk's owner, who sums in fp32.  Tiles are only ever
-  read from this GPU's own memory.
+  chunks r and 2P-1-r ("zig-zag": causal work is balanced).  Keys, values and log gates land in a
+  sequence-major staging buffer (T', B, H, D) in two waves: the lower halves (chunks 0..P-1, one per rank,
+  already in sequence order) by one all-gather per tensor, after which a rank's lower query chunk can already
+  run, and the upper halves a rank may attend to (chunks P..2P-1-r), which travel while that first call
+  computes -- point to point (batched NCCL sends / receives; causality halves this traffic) or as a second
+  all-gather (``UPPER_EXCHANGE``).  Each query chunk is one call of the ordinary operator against the key prefix
+  it may attend to -- exactly the operator's ``seqlen_q <= seqlen_k`` contract (queries are the last rows),
+  reading the staging buffer through strided views, no reordering copies.  Rows are complete on their owner, so
+  no partial (max, sum, out) triples have to travel; the log-gate prefix is recomputed from the gathered gates by
+  the operator's own prefix-sum kernel.  Backward: both calls, then the partial key / value / gate gradients of
+  the lower halves are reduce-scattered as they lie and those of the upper halves are sent to the chunk's owner,
+  who sums in fp32.  The collectives run on a high-priority NCCL stream (``context_parallel_group``) so that they
+  are not queued behind the attention kernels' thousands of CTAs.  Tiles are only ever read from this GPU's own
+  memory.
 """
 from __future__ import annotations
 
