@@ -8,7 +8,7 @@ from .glu import swiglu, swiglu_linear, swiglu_linear_packed  # noqa: F401
 from .token_shift import TokenShift, token_shift  # noqa: F401
 from .block import FoxMLP, FoxProAttentionLayer, FoxProBlock, ShiftLinear  # noqa: F401
 from .cache import FgateCache  # noqa: F401
-from .graphs import make_graphed  # noqa: F401
+from .ops import make_graphed  # noqa: F401
 from ._lib import FoxError, check_status  # noqa: F401
 from .cross_entropy import CrossEntropyLossFunction, FusedCrossEntropyLoss, cross_entropy_loss  # noqa: F401
 

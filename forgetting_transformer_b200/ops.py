@@ -17,7 +17,7 @@ import torch
 
 from . import _lib
 
-__all__ = ["forgetting_attention", "forgetting_attention_from_gate_logits", "ForgettingAttention", "FWD_BLOCK",
+__all__ = ["forgetting_attention", "forgetting_attention_from_gate_logits", "ForgettingAttention", "make_graphed", "FWD_BLOCK",
            "BWD_BLOCK"]
 
 # (BLOCK_M, BLOCK_N) of the kernels; pruning indices are defined on this grid.
@@ -443,3 +443,24 @@ def acp_threshold_from_data(q: torch.Tensor, k: torch.Tensor, log_pruning_tolera
         D, T = q.shape[-1], k.shape[2]
         bound = max_row_norm(q) * max_row_norm(k) / math.sqrt(D)
         return -(2 * bound + math.log(T)) + log_pruning_tolerance
+
+
+def make_graphed(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, log_fgate: torch.Tensor, *,
+                 head_first: bool = False, seq_start: Optional[torch.Tensor] = None,
+                 sm_scale: Optional[float] = None,
+                 adaptive_threshold=None, num_warmup_iters: int = 3):
+    """CUDA-graph replay of a step for launch-bound shapes (B4 T512 H12 D64: 7 launches whose device time is a
+    fraction of their launch cost).  Returns ``f(q, k, v, log_fgate) -> out`` with the same autograd contract as
+    ``forgetting_attention`` for tensors of exactly the sample arguments' shapes, dtypes and ``requires_grad``
+    flags.  Every entry point of the library launches on the caller's current stream, allocates nothing and never
+    synchronises, and the cached TMA descriptors are keyed by (pointer, shape, strides), so
+    ``torch.cuda.make_graphed_callables`` can capture the forward and the backward once.  ``seq_start`` and a
+    tensor ``adaptive_threshold`` are captured by reference: update them in place between calls.  The sample
+    tensors are only used for warm-up and capture."""
+    assert q.is_cuda, "CUDA graphs need CUDA tensors"
+
+    def op(q_, k_, v_, lf_):
+        return forgetting_attention(q_, k_, v_, lf_, head_first=head_first, seq_start=seq_start, sm_scale=sm_scale,
+                                    adaptive_threshold=adaptive_threshold)
+
+    return torch.cuda.make_graphed_callables(op, (q, k, v, log_fgate), num_warmup_iters=num_warmup_iters)
