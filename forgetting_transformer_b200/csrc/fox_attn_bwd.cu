@@ -47,10 +47,14 @@
 #ifndef FOX_BWD_FP32_SUMS
 #define FOX_BWD_FP32_SUMS 1
 #endif
-// how the two 16-lane halves of a fragment load are scheduled: 0 one after the other, 1 the second in flight
-// under the first half's arithmetic, 2 both before one wait
-#ifndef FOX_BWD_PIPE
-#define FOX_BWD_PIPE 1
+// 1: the probabilities of a fragment's second half and dS of its first half are computed in one stretch of code
+#ifndef FOX_BWD_FUSE
+#define FOX_BWD_FUSE 0
+#endif
+// of a thread's 16 column pairs per tile, how many take the FMA-pipe exponential instead of the ex2 unit
+// (only on tiles off the diagonal whose KV rows are all valid)
+#ifndef FOX_BWD_POLY
+#define FOX_BWD_POLY 0
 #endif
 
 namespace fox {
@@ -539,8 +543,9 @@ fox_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     bool ok = true;
     const float2 scale2 = make_float2(p.qk_scale, p.qk_scale);
 
-    auto tile = [&](auto diag_tag, int it) -> bool {
+    auto tile = [&](auto diag_tag, auto poly_tag, int it) -> bool {
       constexpr bool kDiag = decltype(diag_tag)::value;
+      constexpr bool kPoly = decltype(poly_tag)::value;
       const int mb = mb_lo + it;
       const int st = it % STQ;
       if (warp < 8) stamp(6 + warp, 4, it);
@@ -551,46 +556,113 @@ fox_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       tc_fence_after();
       if (warp < 8) stamp(6 + warp, 0, it);
       float2 pf[2][4][2];   // [16-lane half][column group][row + 8]
-      // ---------------- phase A: probabilities ----------------
+      const uint32_t ds_addr = ds_addr0 + (it % kDsBufs) * 32768;
+      float2 rs[4];         // sums over this thread's four KV rows, per query-column pair
+      float2 ev[4], nd[4];  // e_i and -delta_i of this thread's four column pairs
       {
         const float2* e2 = reinterpret_cast<const float2*>(&s_e[st][g * 32 + q2]);
-        float2 ev[4];
+        const float2* d2 = reinterpret_cast<const float2*>(&s_delta[st][g * 32 + q2]);
 #pragma unroll
-        for (int k = 0; k < 4; ++k) ev[k] = e2[4 * k];
-        uint32_t sregs[2][16];
-        tmem_ld_16x256b_x4(tS, sregs[0]);
-        if (FOX_BWD_PIPE == 2) tmem_ld_16x256b_x4(tS + (16u << 16), sregs[1]);
-        tmem_ld_wait();
-        if (FOX_BWD_PIPE == 1) tmem_ld_16x256b_x4(tS + (16u << 16), sregs[1]);   // in flight under the first half
+        for (int k = 0; k < 4; ++k) { ev[k] = e2[4 * k]; nd[k] = d2[4 * k]; }
+      }
+      // phase A, one column group of one 16-lane half: probabilities (fp32 kept in pf, 16-bit pairs into pk)
+      auto a_k = [&](int half, int k, const uint32_t* sreg, uint32_t* pk) {
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          uint32_t pk[8];
-          if (half == 1 && FOX_BWD_PIPE == 0) tmem_ld_16x256b_x4(tS + (16u << 16), sregs[1]);
-          if (half == 1 && FOX_BWD_PIPE != 2) tmem_ld_wait();
-          const uint32_t* sreg = sregs[half];
-#pragma unroll
-          for (int k = 0; k < 4; ++k) {
-#pragma unroll
-            for (int h8 = 0; h8 < 2; ++h8) {
-              const int m = half * 2 + h8;
-              // packed two-wide fp32 arithmetic: x = s c + (e_i - b_j)
-              const float2 x = __ffma2_rn(make_float2(__uint_as_float(sreg[4 * k + 2 * h8]),
-                                                      __uint_as_float(sreg[4 * k + 2 * h8 + 1])),
-                                          scale2, __fadd2_rn(ev[k], negb2[m]));
-              float2 pe = make_float2(fast_exp2(x.x), fast_exp2(x.y));
-              if constexpr (kDiag) {
-                // query column (8 k + e past this thread's first) below the first one this KV row is attended from
-                const int c_min = jp[m] - mb * kBwdBM;
-                pe.x = (8 * k >= c_min) ? pe.x : 0.f;
-                pe.y = (8 * k + 1 >= c_min) ? pe.y : 0.f;
-              }
-              pf[half][k][h8] = pe;
-              pk[2 * k + h8] = pack2<kBf16>(pe.x, pe.y);
-            }
+        for (int h8 = 0; h8 < 2; ++h8) {
+          const int m = half * 2 + h8;
+          // packed two-wide fp32 arithmetic: x = s c + (e_i - b_j)
+          const float2 x = __ffma2_rn(make_float2(__uint_as_float(sreg[4 * k + 2 * h8]),
+                                                  __uint_as_float(sreg[4 * k + 2 * h8 + 1])),
+                                      scale2, __fadd2_rn(ev[k], negb2[m]));
+          float2 pe;
+          if (kPoly && (((half * 8 + 2 * k + h8) * FOX_BWD_POLY) % 16) < FOX_BWD_POLY) pe = poly_exp2_x2(x);
+          else pe = make_float2(fast_exp2(x.x), fast_exp2(x.y));
+          if constexpr (kDiag) {
+            // query column (8 k + e past this thread's first) below the first one this KV row is attended from
+            const int c_min = jp[m] - mb * kBwdBM;
+            pe.x = (8 * k >= c_min) ? pe.x : 0.f;
+            pe.y = (8 * k + 1 >= c_min) ? pe.y : 0.f;
           }
-          // inside this warpgroup's own (already loaded) S columns
-          tmem_st_16x128b_x4(tS + (static_cast<uint32_t>(half * 16) << 16), pk);
+          pf[half][k][h8] = pe;
+          pk[2 * k + h8] = pack2<kBf16>(pe.x, pe.y);
         }
+      };
+      // phase B, the same unit: dS (16-bit pairs into dsk) and the two sums
+      auto b_k = [&](int half, int k, const uint32_t* dpreg, uint32_t* dsk) {
+#pragma unroll
+        for (int h8 = 0; h8 < 2; ++h8) {
+          const int m = half * 2 + h8;
+          const float2 ds = __fmul2_rn(pf[half][k][h8],
+                                       __fadd2_rn(make_float2(__uint_as_float(dpreg[4 * k + 2 * h8]),
+                                                              __uint_as_float(dpreg[4 * k + 2 * h8 + 1])),
+                                                  nd[k]));
+          const uint32_t d16 = pack2<kBf16>(ds.x, ds.y);
+          dsk[2 * k + h8] = d16;
+          if constexpr (kNoDQ || kFp32Sums) {
+            // fp32 values on both sides (with kNoDQ the row sums come from another kernel's recomputed dS, which
+            // agrees to fp32 rounding; the two kernels' 16-bit roundings differ on a few percent of the elements)
+            colacc[m] = __fadd2_rn(colacc[m], ds);
+            if constexpr (kFp32Sums && !kNoDQ) rs[k] = (m == 0) ? ds : __fadd2_rn(rs[k], ds);
+          } else if (!kColsumMMA) {
+            colacc[m] = __fadd2_rn(colacc[m], unpack2<kBf16>(d16));
+          }
+        }
+      };
+      auto store_ds = [&](int half, const uint32_t* dsk) {
+        tmem_st_16x128b_x4(tDP + (static_cast<uint32_t>(half * 16) << 16), dsk);
+        if constexpr (!kNoDQ) {   // (dS in shared memory only feeds the dQ product)
+#pragma unroll
+          for (int h8 = 0; h8 < 2; ++h8)
+            stmatrix_x4(ds_addr + (half * 2 + h8) * 1024, dsk[h8], dsk[2 + h8], dsk[4 + h8], dsk[6 + h8]);
+        }
+      };
+      uint32_t sregs[2][16], dpregs[2][16], pk[8], dsk[8];
+#if FOX_BWD_FUSE
+      // Probabilities of the second half and dS of the first half in one stretch of code: the ex2 unit works on
+      // the one while the FMA pipe works on the other (all four warps of a scheduler reach a phase together, so
+      // a phase of exponentials alone is bound by the ex2 unit and a phase without any leaves it idle).
+      tmem_ld_16x256b_x4(tS, sregs[0]);
+      tmem_ld_wait();
+      tmem_ld_16x256b_x4(tS + (16u << 16), sregs[1]);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) a_k(0, k, sregs[0], pk);
+      tmem_st_16x128b_x4(tS, pk);
+      good = mbar_wait(&bar_dp_full, it & 1, abortp, p.status, kBSiteDpFull, it);
+      // dP(it) was issued behind dQ(it - kDsBufs) and a commit covers everything issued before it, so the
+      // dS buffer about to be overwritten is no longer being read.
+      good = __all_sync(0xffffffffu, good);
+      if (!good) return false;
+      tc_fence_after();
+      tmem_ld_16x256b_x4(tDP, dpregs[0]);
+      tmem_ld_wait();
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        a_k(1, k, sregs[1], pk);
+        b_k(0, k, dpregs[0], dsk);
+      }
+      tmem_st_16x128b_x4(tS + (16u << 16), pk);
+      tmem_ld_16x256b_x4(tDP + (16u << 16), dpregs[1]);
+      store_ds(0, dsk);
+      tmem_st_wait();
+      tc_fence_before();
+      mbar_arrive(&bar_p_done);
+      if (warp < 8) stamp(6 + warp, 1, it);
+      tmem_ld_wait();
+#pragma unroll
+      for (int k = 0; k < 4; ++k) b_k(1, k, dpregs[1], dsk);
+      store_ds(1, dsk);
+#else
+      // ---------------- phase A: probabilities ----------------
+      tmem_ld_16x256b_x4(tS, sregs[0]);
+      tmem_ld_wait();
+      tmem_ld_16x256b_x4(tS + (16u << 16), sregs[1]);   // in flight under the first half's arithmetic
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        if (half == 1) tmem_ld_wait();
+#pragma unroll
+        for (int k = 0; k < 4; ++k) a_k(half, k, sregs[half], pk);
+        // inside this warpgroup's own (already loaded) S columns
+        tmem_st_16x128b_x4(tS + (static_cast<uint32_t>(half * 16) << 16), pk);
       }
       tmem_st_wait();
       tc_fence_before();
@@ -606,53 +678,17 @@ fox_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       if (!good) return false;
       tc_fence_after();
       if (warp < 8) stamp(6 + warp, 2, it);
-      const uint32_t ds_addr = ds_addr0 + (it % kDsBufs) * 32768;
-      float2 rs[4];         // sums over this thread's four KV rows, per query-column pair
-      {
-        const float2* d2 = reinterpret_cast<const float2*>(&s_delta[st][g * 32 + q2]);
-        float2 nd[4];       // -delta_i
+      tmem_ld_16x256b_x4(tDP, dpregs[0]);
+      tmem_ld_wait();
+      tmem_ld_16x256b_x4(tDP + (16u << 16), dpregs[1]);
 #pragma unroll
-        for (int k = 0; k < 4; ++k) nd[k] = d2[4 * k];
-        uint32_t dpregs[2][16];
-        tmem_ld_16x256b_x4(tDP, dpregs[0]);
-        if (FOX_BWD_PIPE == 2) tmem_ld_16x256b_x4(tDP + (16u << 16), dpregs[1]);
-        tmem_ld_wait();
-        if (FOX_BWD_PIPE == 1) tmem_ld_16x256b_x4(tDP + (16u << 16), dpregs[1]);
+      for (int half = 0; half < 2; ++half) {
+        if (half == 1) tmem_ld_wait();
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          uint32_t dsk[8];
-          if (half == 1 && FOX_BWD_PIPE == 0) tmem_ld_16x256b_x4(tDP + (16u << 16), dpregs[1]);
-          if (half == 1 && FOX_BWD_PIPE != 2) tmem_ld_wait();
-          const uint32_t* dpreg = dpregs[half];
-#pragma unroll
-          for (int k = 0; k < 4; ++k) {
-#pragma unroll
-            for (int h8 = 0; h8 < 2; ++h8) {
-              const int m = half * 2 + h8;
-              const float2 ds = __fmul2_rn(pf[half][k][h8],
-                                           __fadd2_rn(make_float2(__uint_as_float(dpreg[4 * k + 2 * h8]),
-                                                                  __uint_as_float(dpreg[4 * k + 2 * h8 + 1])),
-                                                      nd[k]));
-              const uint32_t d16 = pack2<kBf16>(ds.x, ds.y);
-              dsk[2 * k + h8] = d16;
-              if constexpr (kNoDQ || kFp32Sums) {
-                // fp32 values on both sides (with kNoDQ the row sums come from another kernel's recomputed dS, which
-                // agrees to fp32 rounding; the two kernels' 16-bit roundings differ on a few percent of the elements)
-                colacc[m] = __fadd2_rn(colacc[m], ds);
-                if constexpr (kFp32Sums && !kNoDQ) rs[k] = (m == 0) ? ds : __fadd2_rn(rs[k], ds);
-              } else if (!kColsumMMA) {
-                colacc[m] = __fadd2_rn(colacc[m], unpack2<kBf16>(d16));
-              }
-            }
-          }
-          tmem_st_16x128b_x4(tDP + (static_cast<uint32_t>(half * 16) << 16), dsk);
-          if constexpr (!kNoDQ) {   // (dS in shared memory only feeds the dQ product)
-#pragma unroll
-            for (int h8 = 0; h8 < 2; ++h8)
-              stmatrix_x4(ds_addr + (half * 2 + h8) * 1024, dsk[h8], dsk[2 + h8], dsk[4 + h8], dsk[6 + h8]);
-          }
-        }
+        for (int k = 0; k < 4; ++k) b_k(half, k, dpregs[half], dsk);
+        store_ds(half, dsk);
       }
+#endif
       tmem_st_wait();
       if (!kNoDQ) fence_proxy_async_smem();
       tc_fence_before();
@@ -682,10 +718,14 @@ fox_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       return true;
     };
 
+    // the polynomial bottoms out at 2^-125 instead of 0: only where every KV row of the tile is a valid one
+    const bool poly_ok = (nb * kBwdBN >= seq0) && (nb * kBwdBN + kBwdBN <= N);
     for (int it = 0; it < n_tiles; ++it) {
       // (only the tiles on the diagonal mask by position)
       const bool diag = (nb * kBwdBN + kBwdBN - 1 - P - (mb_lo + it) * kBwdBM) > 0;
-      ok = diag ? tile(std::true_type{}, it) : tile(std::false_type{}, it);
+      ok = diag ? tile(std::true_type{}, std::false_type{}, it)
+                : (poly_ok ? tile(std::false_type{}, std::integral_constant<bool, (FOX_BWD_POLY > 0)>{}, it)
+                           : tile(std::false_type{}, std::false_type{}, it));
       if (!ok) break;
     }
 

@@ -46,8 +46,19 @@ struct KvParams {
 __device__ long long g_kv_trace[24 * 8 * 16];
 #define KVSTAMP(role, ev, it) do { if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0 && (it) >= 32 && (it) < 48) g_kv_trace[((role) * 8 + (ev)) * 16 + (it) - 32] = clock64(); } while (0)
 extern "C" int fox_debug_read_kv_trace(long long* host) { return cudaMemcpyFromSymbol(host, g_kv_trace, sizeof(g_kv_trace)); }
+// CTA timeline: nanosecond stamps of up to 8192 CTAs (entry, after set-up, first S^T, last tile, products done,
+// stores done, exit) and the SM they ran on
+__device__ unsigned long long g_kv_cta[8192 * 8];
+__device__ __forceinline__ unsigned long long kv_now_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+#define KVCTA(ev) do { const unsigned cta_ = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z); if (cta_ < 8192) g_kv_cta[cta_ * 8 + (ev)] = kv_now_ns(); } while (0)
+extern "C" int fox_debug_read_kv_cta(unsigned long long* host) { return cudaMemcpyFromSymbol(host, g_kv_cta, sizeof(g_kv_cta)); }
 #else
 #define KVSTAMP(role, ev, it)
+#define KVCTA(ev)
 #endif
 
 enum KvWaitSite { kKvSiteQ = 71, kKvSiteDO = 72, kKvSiteQE = 73, kKvSiteDOE = 74, kKvSiteS = 75, kKvSiteDP = 76,
@@ -85,6 +96,14 @@ fox_attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
   uint8_t* sV = sK + kTileBytes;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (tid == 0) {
+    KVCTA(0);
+#ifdef FOX_KV_TRACE
+    unsigned smid_;
+    asm volatile("mov.u32 %0, %%smid;" : "=r"(smid_));
+    { const unsigned cta_ = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z); if (cta_ < 8192) g_kv_cta[cta_ * 8 + 7] = smid_; }
+#endif
+  }
   const int nb = static_cast<int>(blockIdx.x);   // (KV tile 0 sees every query row: heavy tiles first)
   const int h = blockIdx.y, b = blockIdx.z;
   const int M = p.M, N = p.N, P = N - M;
@@ -132,6 +151,7 @@ fox_attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
   tc_fence_after();
   const uint32_t tbase = tmem_slot;
   volatile int* abortp = &abort_flag;
+  if (tid == 0) KVCTA(1);
 
   if (warp == kTmaWarp) {
     // ===================== TMA producer =====================
@@ -335,6 +355,7 @@ fox_attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       KVSTAMP(warp, 1, it);
+      if (tid == 0 && it == 0) KVCTA(2);
       tc_fence_after();
       uint32_t sreg[32], pk[16];
       float2 pf[16];
@@ -392,6 +413,7 @@ fox_attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       KVSTAMP(warp, 4, it);
     }
     // ---- epilogue: dK * sm_scale, dV -> 16-bit -> global; -colsum(dS) ----
+    if (tid == 0) KVCTA(3);
     float colsum = colsum2.x + colsum2.y;
     if (g > 0) {
       s_part[g - 1][r] = colsum;
@@ -405,6 +427,7 @@ fox_attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       ok = mbar_wait(&bar_done, 0, abortp, p.status, kKvSiteDone);
       ok = __all_sync(0xffffffffu, ok);
     }
+    if (tid == 0) KVCTA(4);
     if (ok) {
       tc_fence_after();
       // warpgroups 0, 1 write the halves of dK, 2 and 3 those of dV
@@ -439,11 +462,13 @@ fox_attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       }
       if (g == 0 && j < N) p.dlam_col[bh * N + j] = keep ? -colsum : 0.f;
     }
+    if (tid == 0) KVCTA(5);
   }
 
   tc_fence_before();
   __syncthreads();
   if (warp == kTmaWarp) tmem_dealloc(tbase, kTmemCols);
+  if (tid == 0) KVCTA(6);
 }
 
 template <int D, bool kBf16>
