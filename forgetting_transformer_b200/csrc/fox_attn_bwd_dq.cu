@@ -376,13 +376,13 @@ fox_attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
 // A 128-column S / dP product re-reads Q / dO from shared memory once per 128 columns instead of once per 64.
 constexpr int kDq2BN = 128;
 enum Dq2WaitSite { kDq2SiteQ = 51, kDq2SiteK = 52, kDq2SiteV = 53, kDq2SiteKE = 54, kDq2SiteVE = 55, kDq2SiteS = 56,
-                   kDq2SiteDP = 57, kDq2SiteDS = 58, kDq2SiteDone = 59, kDq2SiteNegB = 60, kDq2SiteRow = 61 };
+                   kDq2SiteDP = 57, kDq2SiteDS = 58, kDq2SiteDone = 59, kDq2SiteNegB = 60, kDq2SiteRow = 61, kDq2SiteEpi = 62 };
 
 template <int D, bool kBf16>
 __global__ void __launch_bounds__(576, 1)
 fox_attn_bwd_dq2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                         const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
-                        const DqParams p) {
+                        const __grid_constant__ CUtensorMap tmDQ, const DqParams p) {
   static_assert(D == 64 || D == 128, "head dim");
   constexpr int BN = kDq2BN;
   constexpr int kWG = 4, CW = BN / kWG;          // 32 columns of every tile per warpgroup
@@ -398,7 +398,7 @@ fox_attn_bwd_dq2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
 
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   __shared__ uint64_t bar_q_full, bar_k_full[kKS], bar_k_empty[kKS], bar_v_full, bar_v_empty, bar_s_full[2], bar_dp_full,
-      bar_ds_full, bar_done, bar_rowsum;
+      bar_ds_full, bar_done, bar_rowsum, bar_epi;
   __shared__ uint64_t bar_negb[3];
   __shared__ __align__(16) float s_negb[3][BN];
   __shared__ float s_rowsum[kWG - 1][128];
@@ -442,6 +442,7 @@ fox_attn_bwd_dq2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
     mbar_init(&bar_ds_full, 128 * kWG);
     mbar_init(&bar_done, 1);
     mbar_init(&bar_rowsum, 128 * (kWG - 1));
+    mbar_init(&bar_epi, 128 * kWG);
     for (int i = 0; i < 3; ++i) mbar_init(&bar_negb[i], 1);
     mbar_fence_init();
   }
@@ -704,25 +705,44 @@ fox_attn_bwd_dq2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
     }
     if (ok) {
       tc_fence_after();
+      // With pruning on, a CTA lives for a few tiles and this epilogue weighs: the 16-bit tile then goes through
+      // shared memory (Q is idle: every product has retired) and leaves as TMA stores, which write whole lines
+      // and clip the rows past M.  Without pruning the direct stores measured 2 % faster for the whole kernel.
       constexpr int kCols = D / kWG;   // 32 or 16
+      const bool via_tma = p.start_index != nullptr;
       uint16_t* orow = reinterpret_cast<uint16_t*>(p.dq) + b * p.dq_sb + h * p.dq_sh + static_cast<int64_t>(row) * p.dq_st + g * kCols;
       uint32_t t0[kCols];
       if (n_tiles > 0) {
         if constexpr (kCols == 32) tmem_ld32(tDQ + g * kCols, t0); else tmem_ld16(tDQ + g * kCols, t0);
         tmem_ld_wait();
       }
-      if (row_ok) {
 #pragma unroll
-        for (int j = 0; j < kCols; j += 8) {
-          uint4 w = make_uint4(0, 0, 0, 0);
-          if (n_tiles > 0) {
-            w.x = pack2<kBf16>(__uint_as_float(t0[j + 0]) * p.sm_scale, __uint_as_float(t0[j + 1]) * p.sm_scale);
-            w.y = pack2<kBf16>(__uint_as_float(t0[j + 2]) * p.sm_scale, __uint_as_float(t0[j + 3]) * p.sm_scale);
-            w.z = pack2<kBf16>(__uint_as_float(t0[j + 4]) * p.sm_scale, __uint_as_float(t0[j + 5]) * p.sm_scale);
-            w.w = pack2<kBf16>(__uint_as_float(t0[j + 6]) * p.sm_scale, __uint_as_float(t0[j + 7]) * p.sm_scale);
-          }
-          *reinterpret_cast<uint4*>(orow + j) = w;
+      for (int j = 0; j < kCols; j += 8) {
+        uint4 w = make_uint4(0, 0, 0, 0);
+        if (n_tiles > 0) {
+          w.x = pack2<kBf16>(__uint_as_float(t0[j + 0]) * p.sm_scale, __uint_as_float(t0[j + 1]) * p.sm_scale);
+          w.y = pack2<kBf16>(__uint_as_float(t0[j + 2]) * p.sm_scale, __uint_as_float(t0[j + 3]) * p.sm_scale);
+          w.z = pack2<kBf16>(__uint_as_float(t0[j + 4]) * p.sm_scale, __uint_as_float(t0[j + 5]) * p.sm_scale);
+          w.w = pack2<kBf16>(__uint_as_float(t0[j + 6]) * p.sm_scale, __uint_as_float(t0[j + 7]) * p.sm_scale);
         }
+        const int col = g * kCols + j;
+        if (via_tma) *reinterpret_cast<uint4*>(sQ + (col >> 6) * 16384 + r * 128 + ((((col & 63) >> 3) ^ (r & 7)) << 4)) = w;
+        else if (row_ok) *reinterpret_cast<uint4*>(orow + j) = w;
+      }
+      if (via_tma) {
+        fence_proxy_async_smem();
+        mbar_arrive(&bar_epi);
+      }
+      if (via_tma && warp == 0) {
+        // (a bounded wait like every other one: a warp that gave up elsewhere never arrives)
+        if (mbar_wait_warp(&bar_epi, 0, abortp, p.status, kDq2SiteEpi) && elect_one()) {
+#pragma unroll
+          for (int sub = 0; sub < D / 64; ++sub)
+            tma_store_4d(&tmDQ, sQ + sub * 16384, sub * 64, mb * kDqBM, h, b);
+          tma_store_commit();
+          tma_store_wait_read<0>();   // the tile must stay in shared memory until it has been read
+        }
+        __syncwarp();
       }
       if (g == 0 && row_ok)
         p.dlam_row[bh * M + row] = (rowsum2.x + rowsum2.y) + (s_rowsum[0][r] + s_rowsum[1][r]) + s_rowsum[2][r];
@@ -782,6 +802,10 @@ static int launch_dq2(int device, cudaStream_t stream, int64_t B, int64_t H, int
   if ((rc = cached_tmap_4d(&tmDO, tdo, 2, false, kBf16, 64, 128, true))) return rc;
   if ((rc = cached_tmap_4d(&tmK, tk, 2, false, kBf16, 64, kDq2BN, true))) return rc;
   if ((rc = cached_tmap_4d(&tmV, tv, 2, false, kBf16, 64, kDq2BN, true))) return rc;
+  CUtensorMap tmDQ;
+  Tensor4 tdq{prm.dq, B, H, M, D, prm.dq_sb, prm.dq_sh, prm.dq_st};
+  if (!tma_compatible(tdq, 2)) return FOX_ERR_ALIGNMENT;
+  if ((rc = cached_tmap_4d(&tmDQ, tdq, 2, false, kBf16, 64, 128, true))) return rc;
   constexpr int smem = 2 * 128 * D * 2 + 4 * kDq2BN * D * 2 + 1024;
   auto kern = fox_attn_bwd_dq2_kernel<D, kBf16>;
   static bool configured[64] = {};
@@ -791,7 +815,7 @@ static int launch_dq2(int device, cudaStream_t stream, int64_t B, int64_t H, int
     configured[device] = true;
   }
   dim3 grid((unsigned)((M + kDqBM - 1) / kDqBM), (unsigned)H, (unsigned)B);
-  kern<<<grid, 576, smem, stream>>>(tmQ, tmK, tmV, tmDO, prm);
+  kern<<<grid, 576, smem, stream>>>(tmQ, tmK, tmV, tmDO, tmDQ, prm);
   return cudaGetLastError() == cudaSuccess ? FOX_OK : FOX_ERR_LAUNCH;
 }
 

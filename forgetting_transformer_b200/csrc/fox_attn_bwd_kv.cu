@@ -62,12 +62,13 @@ extern "C" int fox_debug_read_kv_cta(unsigned long long* host) { return cudaMemc
 #endif
 
 enum KvWaitSite { kKvSiteQ = 71, kKvSiteDO = 72, kKvSiteQE = 73, kKvSiteDOE = 74, kKvSiteS = 75, kKvSiteDP = 76,
-                  kKvSiteP = 77, kKvSiteDS = 78, kKvSiteDone = 79, kKvSiteVec = 80, kKvSiteCol = 81, kKvSiteKV = 82 };
+                  kKvSiteP = 77, kKvSiteDS = 78, kKvSiteDone = 79, kKvSiteVec = 80, kKvSiteCol = 81, kKvSiteKV = 82, kKvSiteEpi = 83 };
 
 template <int D, bool kBf16>
 __global__ void __launch_bounds__(576, 1)
 fox_attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                       const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO, const KvParams p) {
+                       const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
+                       const __grid_constant__ CUtensorMap tmDK, const __grid_constant__ CUtensorMap tmDV, const KvParams p) {
   static_assert(D == 64 || D == 128, "head dim");
   constexpr int BM = kKvBM;                      // query rows per tile
   constexpr int kWG = 4, CW = BM / kWG;          // 32 query columns of every tile per warpgroup
@@ -83,7 +84,7 @@ fox_attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
 
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   __shared__ uint64_t bar_q_full[kSt], bar_q_empty[kSt], bar_do_full[kSt], bar_do_empty[kSt], bar_vec[kVec], bar_s_full,
-      bar_dp_full, bar_s_read, bar_ds_full, bar_done, bar_kv, bar_colsum;
+      bar_dp_full, bar_s_read, bar_ds_full, bar_done, bar_kv, bar_colsum, bar_epi[2];
   __shared__ __align__(16) float s_e[kVec][BM];
   __shared__ __align__(16) float s_delta[kVec][BM];
   __shared__ float s_part[kWG - 1][128];
@@ -140,6 +141,8 @@ fox_attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     mbar_init(&bar_done, 1);
     mbar_init(&bar_kv, 1);
     mbar_init(&bar_colsum, 128 * (kWG - 1));
+    mbar_init(&bar_epi[0], 256);
+    mbar_init(&bar_epi[1], 256);
     mbar_fence_init();
   }
   if (warp == kTmaWarp) {
@@ -430,15 +433,15 @@ fox_attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     if (tid == 0) KVCTA(4);
     if (ok) {
       tc_fence_after();
-      // warpgroups 0, 1 write the halves of dK, 2 and 3 those of dV
+      // warpgroups 0, 1 hold the halves of dK, 2 and 3 those of dV.  The 16-bit tiles go through shared memory
+      // (the Q stages are idle: every product has retired) and leave as TMA stores, which write whole lines and
+      // clip the rows past N; a thread storing its own row 16 bytes at a time kept the CTA ~7 us in this epilogue.
       constexpr int kHalf = D / 2;   // columns of dK or dV per warpgroup
       const int which = g >> 1, part_c = (g & 1) * kHalf;
       const bool keep = j_ok && n_tiles > 0;
       const uint32_t tcol = tbase + lane_base + (which == 0 ? kColDK : kColDV) + part_c;
       const float sc = which == 0 ? p.sm_scale : 1.f;
-      uint16_t* orow = (which == 0
-          ? reinterpret_cast<uint16_t*>(p.dk) + b * p.dk_sb + h * p.dk_sh + static_cast<int64_t>(j) * p.dk_st
-          : reinterpret_cast<uint16_t*>(p.dv) + b * p.dv_sb + h * p.dv_sh + static_cast<int64_t>(j) * p.dv_st) + part_c;
+      uint8_t* stile = sQ + which * kTileBytes;
 #pragma unroll
       for (int c = 0; c < kHalf; c += 32) {
         uint32_t t0[32];
@@ -446,19 +449,32 @@ fox_attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
           tmem_ld32(tcol + c, t0);
           tmem_ld_wait();
         }
-        if (j < N) {
+        const int col = part_c + c;
+        uint8_t* srow = stile + (col >> 6) * kSubBytes + r * 128;
 #pragma unroll
-          for (int q8 = 0; q8 < 32; q8 += 8) {
-            uint4 w = make_uint4(0, 0, 0, 0);
-            if (keep) {
-              w.x = pack2<kBf16>(__uint_as_float(t0[q8 + 0]) * sc, __uint_as_float(t0[q8 + 1]) * sc);
-              w.y = pack2<kBf16>(__uint_as_float(t0[q8 + 2]) * sc, __uint_as_float(t0[q8 + 3]) * sc);
-              w.z = pack2<kBf16>(__uint_as_float(t0[q8 + 4]) * sc, __uint_as_float(t0[q8 + 5]) * sc);
-              w.w = pack2<kBf16>(__uint_as_float(t0[q8 + 6]) * sc, __uint_as_float(t0[q8 + 7]) * sc);
-            }
-            *reinterpret_cast<uint4*>(orow + c + q8) = w;
+        for (int q8 = 0; q8 < 32; q8 += 8) {
+          uint4 w = make_uint4(0, 0, 0, 0);
+          if (keep) {
+            w.x = pack2<kBf16>(__uint_as_float(t0[q8 + 0]) * sc, __uint_as_float(t0[q8 + 1]) * sc);
+            w.y = pack2<kBf16>(__uint_as_float(t0[q8 + 2]) * sc, __uint_as_float(t0[q8 + 3]) * sc);
+            w.z = pack2<kBf16>(__uint_as_float(t0[q8 + 4]) * sc, __uint_as_float(t0[q8 + 5]) * sc);
+            w.w = pack2<kBf16>(__uint_as_float(t0[q8 + 6]) * sc, __uint_as_float(t0[q8 + 7]) * sc);
           }
+          *reinterpret_cast<uint4*>(srow + (((((col & 63) + q8) >> 3) ^ (r & 7)) << 4)) = w;
         }
+      }
+      fence_proxy_async_smem();
+      mbar_arrive(&bar_epi[which]);
+      if ((g & 1) == 0 && (warp & 3) == 0) {
+        // (a bounded wait like every other one: a warp that gave up elsewhere never arrives)
+        if (mbar_wait_warp(&bar_epi[which], 0, abortp, p.status, kKvSiteEpi) && elect_one()) {
+#pragma unroll
+          for (int sub = 0; sub < kSub; ++sub)
+            tma_store_4d(which == 0 ? &tmDK : &tmDV, stile + sub * kSubBytes, sub * 64, j0, h, b);
+          tma_store_commit();
+          tma_store_wait_read<0>();   // the tile must stay in shared memory until it has been read
+        }
+        __syncwarp();
       }
       if (g == 0 && j < N) p.dlam_col[bh * N + j] = keep ? -colsum : 0.f;
     }
@@ -486,6 +502,12 @@ static int launch_kv(int device, cudaStream_t stream, int64_t B, int64_t H, int6
   if ((rc = cached_tmap_4d(&tmDO, tdo, 2, false, kBf16, 64, kKvBM, true))) return rc;
   if ((rc = cached_tmap_4d(&tmK, tk, 2, false, kBf16, 64, kKvBN, true))) return rc;
   if ((rc = cached_tmap_4d(&tmV, tv, 2, false, kBf16, 64, kKvBN, true))) return rc;
+  CUtensorMap tmDK, tmDV;
+  Tensor4 tdk{prm.dk, B, H, N, D, prm.dk_sb, prm.dk_sh, prm.dk_st};
+  Tensor4 tdv{prm.dv, B, H, N, D, prm.dv_sb, prm.dv_sh, prm.dv_st};
+  if (!tma_compatible(tdk, 2) || !tma_compatible(tdv, 2)) return FOX_ERR_ALIGNMENT;
+  if ((rc = cached_tmap_4d(&tmDK, tdk, 2, false, kBf16, 64, kKvBN, true))) return rc;
+  if ((rc = cached_tmap_4d(&tmDV, tdv, 2, false, kBf16, 64, kKvBN, true))) return rc;
   constexpr int smem = (2 * 2 + 2) * 128 * D * 2 + 1024;   // Q, dO in two stages each, K, V
   auto kern = fox_attn_bwd_kv_kernel<D, kBf16>;
   static bool configured[64] = {};
@@ -495,7 +517,7 @@ static int launch_kv(int device, cudaStream_t stream, int64_t B, int64_t H, int6
     configured[device] = true;
   }
   dim3 grid((unsigned)((N + kKvBN - 1) / kKvBN), (unsigned)H, (unsigned)B);
-  kern<<<grid, 576, smem, stream>>>(tmQ, tmK, tmV, tmDO, prm);
+  kern<<<grid, 576, smem, stream>>>(tmQ, tmK, tmV, tmDO, tmDK, tmDV, prm);
   return cudaGetLastError() == cudaSuccess ? FOX_OK : FOX_ERR_LAUNCH;
 }
 

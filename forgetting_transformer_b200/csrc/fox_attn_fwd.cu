@@ -67,13 +67,14 @@ __device__ long long g_fwd_trace[16 * 8 * 16];
 
 enum FwdWaitSite {
   kSiteQFull = 11, kSiteKFull = 12, kSiteVFull = 13, kSiteKEmpty = 14, kSiteVEmpty = 15,
-  kSiteSFull = 16, kSitePFull = 17, kSiteODone = 18, kSiteDrain = 19, kSiteNegB = 20, kSiteMerge = 21
+  kSiteSFull = 16, kSitePFull = 17, kSiteODone = 18, kSiteDrain = 19, kSiteNegB = 20, kSiteMerge = 21, kSiteEpi = 22
 };
 
 template <int D, bool kBf16, int BN, int STAGES, int CTAS, int NWG, bool PREF>
 __global__ void __launch_bounds__(128 * NWG + 64, CTAS)
 fox_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                    const __grid_constant__ CUtensorMap tmV, const FwdParams p) {
+                    const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO,
+                    const FwdParams p) {
   // KV tiles of BN rows (64 or 128; the pruning grid stays 128 wide, BN = 64 just walks it in halves).
   // NWG softmax warpgroups per CTA, each owning a BN / NWG wide column slice of every tile with its own
   // running maximum, row sum and O accumulator (independent online-softmax streams, merged in the
@@ -92,7 +93,7 @@ fox_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   constexpr int kTmaWarp = 4 * kWG, kMmaWarp = 4 * kWG + 1;
 
   extern __shared__ uint8_t smem_raw[];
-  __shared__ uint64_t bar_q_full, bar_o_done, bar_merge;
+  __shared__ uint64_t bar_q_full, bar_o_done, bar_merge, bar_epi;
   __shared__ uint64_t bar_s_full[NWG], bar_p_full[NWG];  // per warpgroup
   __shared__ uint64_t bar_k_full[STAGES], bar_k_empty[STAGES], bar_v_full[STAGES], bar_v_empty[STAGES];
   // -b_j = -Lambda_j log2(e) of a tile's columns and the maximum over each warpgroup's slice, staged by the
@@ -138,6 +139,7 @@ fox_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     for (int i = 0; i < 3; ++i) mbar_init(&bar_negb[i], 1);
     mbar_init(&bar_o_done, 1);
     mbar_init(&bar_merge, 128 * NWG);
+    mbar_init(&bar_epi, 128 * NWG);
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&bar_k_full[s], 1);
       mbar_init(&bar_k_empty[s], 1);
@@ -515,7 +517,8 @@ fox_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       const float inv_l = empty ? 0.f : 1.f / l_sum;
 #pragma unroll
       for (int q = 0; q < NWG; ++q) w[q] *= inv_l;
-      uint16_t* orow = reinterpret_cast<uint16_t*>(p.o) + b * p.o_sb + h * p.o_sh + static_cast<int64_t>(row) * p.o_st;
+      // The 16-bit tile goes through shared memory (Q is idle: every product has retired) and leaves as TMA
+      // stores, which write whole lines and clip the rows past M.
       const uint32_t tO0 = tbase + lane_base + kColO;
 #pragma unroll
       for (int c = 0; c < D; c += 32) {
@@ -531,19 +534,29 @@ fox_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             for (int j = 0; j < 32; ++j) o[j] = q == 0 ? __uint_as_float(t0[j]) * w[0] : fmaf(__uint_as_float(t0[j]), w[q], o[j]);
           }
         }
-        if (row_ok) {
 #pragma unroll
-          for (int j = 0; j < 32; j += 8) {
-            uint4 wv = make_uint4(0, 0, 0, 0);
-            if (!empty) {
-              wv.x = pack2<kBf16>(o[j + 0], o[j + 1]);
-              wv.y = pack2<kBf16>(o[j + 2], o[j + 3]);
-              wv.z = pack2<kBf16>(o[j + 4], o[j + 5]);
-              wv.w = pack2<kBf16>(o[j + 6], o[j + 7]);
-            }
-            *reinterpret_cast<uint4*>(orow + c + j) = wv;
+        for (int j = 0; j < 32; j += 8) {
+          uint4 wv = make_uint4(0, 0, 0, 0);
+          if (!empty) {
+            wv.x = pack2<kBf16>(o[j + 0], o[j + 1]);
+            wv.y = pack2<kBf16>(o[j + 2], o[j + 3]);
+            wv.z = pack2<kBf16>(o[j + 4], o[j + 5]);
+            wv.w = pack2<kBf16>(o[j + 6], o[j + 7]);
           }
+          *reinterpret_cast<uint4*>(sQ + (c >> 6) * 16384 + r * 128 + (((((c & 63) + j) >> 3) ^ (r & 7)) << 4)) = wv;
         }
+      }
+      fence_proxy_async_smem();
+      mbar_arrive(&bar_epi);
+      if (warp == 0) {
+        // (a bounded wait like every other one: a warp that gave up elsewhere never arrives)
+        if (mbar_wait_warp(&bar_epi, 0, abortp, p.status, kSiteEpi) && elect_one()) {
+#pragma unroll
+          for (int sub = 0; sub < kSub; ++sub) tma_store_4d(&tmO, sQ + sub * 16384, sub * 64, mb * kFwdBM, h, b);
+          tma_store_commit();
+          tma_store_wait_read<0>();   // the tile must stay in shared memory until it has been read
+        }
+        __syncwarp();
       }
       if (row_ok && g == 0) p.L[bh * M + row] = empty ? -INFINITY : m_ref * kLn2 + __logf(l_sum);
     }
@@ -579,6 +592,10 @@ static int launch_fwd_t(int device, cudaStream_t stream, int64_t B, int64_t H, i
   if ((rc = cached_tmap_4d(&tmQ, tq, 2, false, kBf16, 64, 128, true))) return rc;
   if ((rc = cached_tmap_4d(&tmK, tk, 2, false, kBf16, 64, BN, true))) return rc;
   if ((rc = cached_tmap_4d(&tmV, tv, 2, false, kBf16, 64, BN, true))) return rc;
+  CUtensorMap tmO;
+  Tensor4 to{prm.o, B, H, M, D, prm.o_sb, prm.o_sh, prm.o_st};
+  if (!tma_compatible(to, 2)) return FOX_ERR_ALIGNMENT;
+  if ((rc = cached_tmap_4d(&tmO, to, 2, false, kBf16, 64, 128, true))) return rc;
   constexpr int smem = 128 * D * 2 + 2 * STAGES * BN * D * 2 + 1024;
   auto kern = fox_attn_fwd_kernel<D, kBf16, BN, STAGES, CTAS, NWG, PREF>;
   static bool configured[64] = {};  // per template instance and device
@@ -588,7 +605,7 @@ static int launch_fwd_t(int device, cudaStream_t stream, int64_t B, int64_t H, i
     configured[device] = true;
   }
   dim3 grid((unsigned)((M + kFwdBM - 1) / kFwdBM), (unsigned)H, (unsigned)B);
-  kern<<<grid, 128 * NWG + 64, smem, stream>>>(tmQ, tmK, tmV, prm);
+  kern<<<grid, 128 * NWG + 64, smem, stream>>>(tmQ, tmK, tmV, tmO, prm);
   return cudaGetLastError() == cudaSuccess ? FOX_OK : FOX_ERR_LAUNCH;
 }
 
