@@ -718,6 +718,7 @@ fox_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         const int i = mb * kBwdBM + g * 32 + 8 * (c8 >> 1) + q2 + (c8 & 1);
         if (i < M) atomicAdd(p.dlam_row + bh * M + i, v[0]);
       }
+      if (warp < 8) stamp(6 + warp, 5, it);
       return true;
     };
 
