@@ -70,6 +70,10 @@ _SIGNATURES = {
                                       c_float, c_int64, _F, _F, _F]),
     "fox_cross_entropy_bwd": (c_int, [c_int, c_void_p, c_int, c_int64, c_int64, _F, c_int64, _F, _F, _F, c_int64,
                                       c_float, c_float, c_float, c_int64, _F, c_int64]),
+    "fox_cross_entropy_fwd_split": (c_int, [c_int, c_void_p, c_int, c_int64, c_int64, _F, c_int64, _F, c_float, c_float,
+                                            c_int64, c_int64, c_int64, _F, _F]),
+    "fox_cross_entropy_bwd_split": (c_int, [c_int, c_void_p, c_int, c_int64, c_int64, _F, c_int64, _F, _F, _F, c_int64,
+                                            c_float, c_float, c_float, c_int64, c_int64, c_int64, _F, c_int64]),
     "fox_token_shift_fwd": (c_int, [c_int, c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, _F, c_int64, c_int64,
                                     c_int64, _F, _F, c_int64, c_int64, c_int64, _F]),
     "fox_token_shift_bwd": (c_int, [c_int, c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, _F, c_int64, c_int64,

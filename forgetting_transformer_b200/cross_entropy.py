@@ -3,14 +3,17 @@
 Host-side mirror of upstream's ``CrossEntropyLossFunction`` / ``cross_entropy_loss`` / ``FusedCrossEntropyLoss``
 (src/forgetting_transformer/model/forgetting_transformer/fused_cross_entropy.py:137-401): same arguments,
 defaults and returned (losses, z_losses), label smoothing, logit scale, z-loss, ``ignore_index`` and the
-in-place backward the model's loss uses (modeling_forgetting_transformer.py:877-884).  Tensor parallelism over
-the classes (``process_group``) is not built.  No CPU path.
+in-place backward the model's loss uses (modeling_forgetting_transformer.py:877-884).  With ``process_group`` the
+classes are split over the group's ranks (upstream lines 150-151, 196-226): every rank passes its own (rows,
+classes / world) slice of the logits and the full targets; the ranks' log-sum-exps are all-gathered and joined, the
+loss parts all-reduced.  No CPU path.
 """
 from __future__ import annotations
 
 from typing import Any, Tuple
 
 import torch
+import torch.distributed as dist
 import torch.nn as nn
 
 from . import _lib
@@ -24,19 +27,79 @@ def _stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 
 
+def _local_forward(logits, target, label_smoothing, logit_scale, lse_square_scale, ignore_index, total_classes,
+                   class_start, split):
+    """One rank's kernel launch: (losses or loss parts, z_losses or None, lse of this rank's classes)."""
+    n_rows, n_cols = logits.shape
+    lib = _lib.load()
+    dev = logits.device
+    with torch.cuda.device(dev):
+        losses = torch.empty(n_rows, dtype=torch.float32, device=dev)
+        lse = torch.empty(n_rows, dtype=torch.float32, device=dev)
+        if split:
+            _lib.check(lib.fox_cross_entropy_fwd_split(dev.index, _stream(), _DTYPES[logits.dtype], n_rows, n_cols,
+                                                       logits.data_ptr(), logits.stride(0), target.data_ptr(),
+                                                       float(label_smoothing), float(logit_scale), int(ignore_index),
+                                                       int(total_classes), int(class_start), losses.data_ptr(),
+                                                       lse.data_ptr()), "fox_cross_entropy_fwd_split")
+            return losses, None, lse
+        z_losses = torch.empty(n_rows, dtype=torch.float32, device=dev)
+        _lib.check(lib.fox_cross_entropy_fwd(dev.index, _stream(), _DTYPES[logits.dtype], n_rows, n_cols,
+                                             logits.data_ptr(), logits.stride(0), target.data_ptr(),
+                                             float(label_smoothing), float(logit_scale), float(lse_square_scale),
+                                             int(ignore_index), losses.data_ptr(), z_losses.data_ptr(),
+                                             lse.data_ptr()), "fox_cross_entropy_fwd")
+    return losses, z_losses, lse
+
+
+def _local_backward(logits, target, lse, grad_losses, label_smoothing, logit_scale, lse_square_scale, ignore_index,
+                    total_classes, class_start, dlogits):
+    n_rows, n_cols = logits.shape
+    lib = _lib.load()
+    dev = logits.device
+    with torch.cuda.device(dev):
+        _lib.check(lib.fox_cross_entropy_bwd_split(dev.index, _stream(), _DTYPES[logits.dtype], n_rows, n_cols,
+                                                   logits.data_ptr(), logits.stride(0), target.data_ptr(),
+                                                   lse.data_ptr(), grad_losses.data_ptr(), grad_losses.stride(0),
+                                                   label_smoothing, logit_scale, lse_square_scale, ignore_index,
+                                                   int(total_classes), int(class_start), dlogits.data_ptr(),
+                                                   dlogits.stride(0)), "fox_cross_entropy_bwd_split")
+    return dlogits
+
+
+def join_class_shards(loss_parts, lse_local, target, lse_square_scale, ignore_index, process_group):
+    """Global (losses, z_losses, lse) from every rank's loss parts and local log-sum-exp (upstream lines 206-226)."""
+    world = dist.get_world_size(process_group)
+    gathered = torch.empty((world,) + tuple(lse_local.shape), dtype=lse_local.dtype, device=lse_local.device)
+    dist.all_gather_into_tensor(gathered.view(-1), lse_local.contiguous(), group=process_group)
+    handle = dist.all_reduce(loss_parts, op=dist.ReduceOp.SUM, group=process_group, async_op=True)
+    lse = torch.logsumexp(gathered, dim=0)
+    handle.wait()
+    losses = loss_parts + lse
+    if lse_square_scale != 0.0:
+        z_losses = lse_square_scale * lse.square()
+        z_losses.masked_fill_(target == ignore_index, 0.0)
+        losses = losses + z_losses
+    else:
+        z_losses = torch.zeros_like(losses)
+    losses.masked_fill_(target == ignore_index, 0.0)
+    return losses, z_losses, lse
+
+
 class CrossEntropyLossFunction(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, logits, target, label_smoothing=0.0, logit_scale=1.0, lse_square_scale=0.0, ignore_index=-100,
                 inplace_backward=False, process_group=None):
-        if process_group is not None:
-            raise NotImplementedError("the class dimension is not split over ranks here (process_group must be None)")
         if not logits.is_cuda:
             raise _lib.FoxError("cross_entropy_loss needs CUDA tensors on an sm_100 device; there is no CPU path")
         n_rows, n_cols = logits.shape
         assert target.shape == (n_rows,)
         if logits.dtype not in _DTYPES:
             raise _lib.FoxError(f"unsupported logits dtype {logits.dtype}")
+        world = 1 if process_group is None else dist.get_world_size(process_group)
+        rank = 0 if process_group is None else dist.get_rank(process_group)
+        total_classes, class_start = world * n_cols, rank * n_cols
         es = logits.element_size()
         if logits.stride(-1) != 1 or (logits.stride(0) * es) % 16 or logits.data_ptr() % 16:
             logits = logits.contiguous()
@@ -45,20 +108,15 @@ class CrossEntropyLossFunction(torch.autograd.Function):
                 pad[:, :n_cols] = logits
                 logits = pad[:, :n_cols]
         target = target.to(torch.long).contiguous()
-        lib = _lib.load()
-        dev = logits.device
-        with torch.cuda.device(dev):
-            losses = torch.empty(n_rows, dtype=torch.float32, device=dev)
-            z_losses = torch.empty(n_rows, dtype=torch.float32, device=dev)
-            lse = torch.empty(n_rows, dtype=torch.float32, device=dev)
-            _lib.check(lib.fox_cross_entropy_fwd(dev.index, _stream(), _DTYPES[logits.dtype], n_rows, n_cols,
-                                                 logits.data_ptr(), logits.stride(0), target.data_ptr(),
-                                                 float(label_smoothing), float(logit_scale), float(lse_square_scale),
-                                                 int(ignore_index), losses.data_ptr(), z_losses.data_ptr(),
-                                                 lse.data_ptr()), "fox_cross_entropy_fwd")
+        losses, z_losses, lse = _local_forward(logits, target, label_smoothing, logit_scale, lse_square_scale,
+                                               ignore_index, total_classes, class_start, world > 1)
+        if world > 1:
+            losses, z_losses, lse = join_class_shards(losses, lse, target, float(lse_square_scale), int(ignore_index),
+                                                      process_group)
         ctx.save_for_backward(logits, lse, target)
         ctx.mark_non_differentiable(z_losses)
         ctx.args = (float(label_smoothing), float(logit_scale), float(lse_square_scale), int(ignore_index))
+        ctx.classes = (total_classes, class_start)
         ctx.inplace_backward = inplace_backward
         return losses, z_losses
 
@@ -67,19 +125,11 @@ class CrossEntropyLossFunction(torch.autograd.Function):
         del grad_z_losses  # z_losses are for logging only, as upstream
         logits, lse, target = ctx.saved_tensors
         label_smoothing, logit_scale, lse_square_scale, ignore_index = ctx.args
-        n_rows, n_cols = logits.shape
         # (same row stride as the saved logits: a re-laid class count keeps its 16-byte aligned rows)
         dlogits = logits if ctx.inplace_backward else torch.empty_strided(logits.shape, logits.stride(),
                                                                           dtype=logits.dtype, device=logits.device)
-        grad_losses = grad_losses.float()
-        lib = _lib.load()
-        dev = logits.device
-        with torch.cuda.device(dev):
-            _lib.check(lib.fox_cross_entropy_bwd(dev.index, _stream(), _DTYPES[logits.dtype], n_rows, n_cols,
-                                                 logits.data_ptr(), logits.stride(0), target.data_ptr(),
-                                                 lse.data_ptr(), grad_losses.data_ptr(), grad_losses.stride(0),
-                                                 label_smoothing, logit_scale, lse_square_scale, ignore_index,
-                                                 dlogits.data_ptr(), dlogits.stride(0)), "fox_cross_entropy_bwd")
+        _local_backward(logits, target, lse, grad_losses.float(), label_smoothing, logit_scale, lse_square_scale,
+                        ignore_index, ctx.classes[0], ctx.classes[1], dlogits)
         return dlogits, None, None, None, None, None, None, None
 
 

@@ -248,6 +248,23 @@ int fox_cross_entropy_bwd(int device, void* stream, int dtype, int64_t n_rows, i
                           int64_t dloss_stride, float label_smoothing, float logit_scale, float lse_square_scale,
                           int64_t ignore_index, void* dlogits, int64_t dlogits_row_stride);
 
+/* The same loss with the classes split over ranks (tensor parallelism over the vocabulary; replaces the
+ * `process_group` path of fused_cross_entropy.py:150-151, 196-226 and :229-273).  This rank holds n_cols of
+ * total_classes classes, starting at class_start.  The forward writes the rank's own log-sum-exp (lse_local) and
+ * the part of the loss that needs no global one: -(1 - label_smoothing) z_label [label on this rank]
+ * - label_smoothing sum_c z_c / total_classes (0 where label == ignore_index).  The host all-gathers lse_local,
+ * takes their log-sum-exp, sums loss_parts over the ranks and adds the global lse (and the z-loss).  The backward
+ * takes the global lse. */
+int fox_cross_entropy_fwd_split(int device, void* stream, int dtype, int64_t n_rows, int64_t n_cols,
+                                const void* logits, int64_t row_stride, const int64_t* labels, float label_smoothing,
+                                float logit_scale, int64_t ignore_index, int64_t total_classes, int64_t class_start,
+                                float* loss_parts, float* lse_local);
+int fox_cross_entropy_bwd_split(int device, void* stream, int dtype, int64_t n_rows, int64_t n_cols,
+                                const void* logits, int64_t row_stride, const int64_t* labels, const float* lse_global,
+                                const float* dloss, int64_t dloss_stride, float label_smoothing, float logit_scale,
+                                float lse_square_scale, int64_t ignore_index, int64_t total_classes,
+                                int64_t class_start, void* dlogits, int64_t dlogits_row_stride);
+
 /* Data-dependent token shift, forward: out[b,t,h,:] = x[b,t,h,:] * curr[b,t,h] + x[b,t-1,h,:] *
  * prev[b,t,h] with x[b,-1] = 0, products in fp32, rounded once.  Replaces shift_fwd_kernel
  * (token_shift.py:21-80; TokenShift.forward 164-195), which ShiftLinear calls as

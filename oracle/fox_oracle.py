@@ -541,6 +541,22 @@ def cross_entropy(logits: torch.Tensor, target: torch.Tensor, label_smoothing: f
     return torch.where(keep, loss + zl, zero), torch.where(keep, zl, zero)
 
 
+def cross_entropy_class_shard(logits_shard: torch.Tensor, target: torch.Tensor, class_start: int, total_classes: int,
+                              label_smoothing: float = 0.0, logit_scale: float = 1.0, ignore_index: int = -100):
+    """What one rank contributes when the classes are split over ranks (fused_cross_entropy.py:84-92, 196-205):
+    (loss_parts, lse_local) with loss_parts = -(1 - eps) z[label] [label on this rank] - eps sum(z) / total_classes,
+    0 where the label is ``ignore_index``; the global loss is sum over ranks of loss_parts + logsumexp of the ranks'
+    lse_local (+ the z-loss of that global lse)."""
+    z = logits_shard.float() * logit_scale
+    lse = torch.logsumexp(z, dim=-1)
+    local = target - class_start
+    mine = (target != ignore_index) & (local >= 0) & (local < z.shape[1])
+    safe = torch.where(mine, local, torch.zeros_like(local))
+    zlab = torch.where(mine, z.gather(1, safe[:, None])[:, 0], torch.zeros_like(lse))
+    parts = -(1.0 - label_smoothing) * zlab - label_smoothing * z.sum(dim=-1) / total_classes
+    return torch.where(target != ignore_index, parts, torch.zeros_like(parts)), lse
+
+
 def cross_entropy_fwd_bwd(logits, target, dloss, **kw):
     """losses, z_losses and d(sum(losses * dloss)) / dlogits in fp32."""
     x = logits.detach().float().requires_grad_()

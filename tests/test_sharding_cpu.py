@@ -110,3 +110,39 @@ def test_context_parallel_matches_unsharded(world):
     assert len(ret) == world
     assert max(w for w, _ in ret.values()) < 1e-5  # the dense formulation does its softmax in fp32
     assert all(same for _, same in ret.values())
+
+
+def _ce_worker(rank, world, port, ret):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from forgetting_transformer_b200 import cross_entropy as ce
+        g = torch.Generator().manual_seed(5)
+        rows, classes = 37, 64 * world
+        logits = torch.randn(rows, classes, generator=g) * 3
+        target = torch.randint(0, classes, (rows,), generator=g)
+        target[::7] = -100
+        worst = 0.0
+        for eps, scale, zsq in ((0.0, 1.0, 0.0), (0.1, 0.5, 1e-4)):
+            n = classes // world
+            parts, lse_local = orc.cross_entropy_class_shard(logits[:, rank * n:(rank + 1) * n], target, rank * n,
+                                                                classes, label_smoothing=eps, logit_scale=scale)
+            losses, z_losses, lse = ce.join_class_shards(parts, lse_local, target, zsq, -100, None)
+            ref_l, ref_z = orc.cross_entropy(logits, target, label_smoothing=eps, logit_scale=scale,
+                                                lse_square_scale=zsq)
+            ref_lse = torch.logsumexp(logits.float() * scale, dim=-1)
+            worst = max(worst, float((losses - ref_l).abs().max()), float((z_losses - ref_z).abs().max()),
+                        float((lse - ref_lse).abs().max()))
+        ret[rank] = worst
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_cross_entropy_class_shards_join_to_the_unsplit_loss(world):
+    """Every rank's (loss part, local log-sum-exp) of its slice of the classes, joined over gloo by the host code the
+    CUDA path uses, equals the loss over all classes (label smoothing, logit scale, z-loss, ignored rows)."""
+    ret = mp.Manager().dict()
+    mp.spawn(_ce_worker, args=(world, _free_port(), ret), nprocs=world, join=True)
+    assert len(ret) == world and max(ret.values()) < 1e-5, dict(ret)

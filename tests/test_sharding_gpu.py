@@ -103,3 +103,51 @@ def test_context_parallel_over_nccl_matches_single_gpu():
             # k/v/gate gradients are sums of bf16 partial gradients from two calls and two ranks: more roundings
             # than the single call makes
             assert errs[0] < 2e-2 and errs[1] < 3e-2 and errs[2] < 6e-2 and errs[3] < 6e-2 and errs[4] < 3e-2, (name, errs)
+
+
+def _ce_worker(rank, world, port, ret):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        g = torch.Generator().manual_seed(11)
+        rows, classes = 300, 4096 * world
+        logits = (torch.randn(rows, classes, generator=g) * 3).bfloat16().cuda()
+        target = torch.randint(0, classes, (rows,), generator=g)
+        target[::9] = -100
+        target = target.cuda()
+        dloss = torch.randn(rows, generator=g).cuda()
+        n = classes // world
+        worst = {}
+        for eps, scale, zsq in ((0.0, 1.0, 0.0), (0.1, 0.5, 1e-4)):
+            full = logits.clone().requires_grad_()
+            l_full, z_full = fox.cross_entropy_loss(full, target, label_smoothing=eps, logit_scale=scale,
+                                                    lse_square_scale=zsq)
+            (l_full * dloss).sum().backward()
+            mine = logits[:, rank * n:(rank + 1) * n].contiguous().requires_grad_()
+            l_tp, z_tp = fox.cross_entropy_loss(mine, target, label_smoothing=eps, logit_scale=scale,
+                                                lse_square_scale=zsq, process_group=dist.group.WORLD)
+            (l_tp * dloss).sum().backward()
+            torch.cuda.synchronize()
+            worst[(eps, scale, zsq)] = [
+                (l_tp - l_full).abs().max().item(), (z_tp - z_full).abs().max().item(),
+                (mine.grad.float() - full.grad[:, rank * n:(rank + 1) * n].float()).abs().max().item()]
+        ret[rank] = worst
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_cross_entropy_with_classes_split_over_two_gpus():
+    """The fused loss with the classes split over two ranks (process_group) against the same kernels on all classes:
+    losses, z-losses and this rank's slice of the logit gradient."""
+    world = 2
+    ret = mp.Manager().dict()
+    mp.spawn(_ce_worker, args=(world, _free_port(), ret), nprocs=world, join=True)
+    assert len(ret) == world
+    for worst in ret.values():
+        for key, (dl, dz, dg) in worst.items():
+            # fp32 losses from the same bf16 logits; gradients are rounded to bf16 on both sides
+            assert dl < 2e-4 and dz < 1e-5 and dg < 4e-3, (key, dl, dz, dg)
