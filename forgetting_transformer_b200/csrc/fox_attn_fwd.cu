@@ -56,6 +56,15 @@ struct FwdParams {
 #define FOX_POLYQ128 2
 #endif
 
+// 1: at D = 64 a warpgroup's 64-column slice of S is computed, consumed and multiplied with V in two halves with
+// their own barriers, so that the S product of a half for the next tile is under way while the warpgroup works on
+// the other half (0: one S product and one P V product per slice and tile).  Measured on B2 T16384 H24 D64:
+// results identical, 2.02 ms against 1.93 ms -- eight more product instructions and two more barrier round trips
+// per tile cost more than the wait they hide; off.
+#ifndef FOX_FWD_SUBSTREAMS
+#define FOX_FWD_SUBSTREAMS 0
+#endif
+
 // Debug builds with -DFOX_FWD_TRACE record clock64 stamps of CTA (0,0,0), tiles 32..47:
 // trace[(role * 8 + event) * 16 + tile - 32], role = softmax warp index or 8 for the MMA issuer.
 #ifdef FOX_FWD_TRACE
@@ -91,10 +100,13 @@ fox_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   constexpr uint32_t kTmemCols = (kColO + kWG * D <= 128) ? 128 : ((kColO + kWG * D <= 256) ? 256 : 512);
   static_assert(kColO + kWG * D <= 512, "TMEM budget");
   constexpr int kTmaWarp = 4 * kWG, kMmaWarp = 4 * kWG + 1;
+  // halves of a warpgroup's slice with their own S -> P -> P V chain (32 columns each)
+  constexpr int kSubs = (FOX_FWD_SUBSTREAMS && CW == 64 && !PREF) ? 2 : 1;
+  constexpr int SW = CW / kSubs;
 
   extern __shared__ uint8_t smem_raw[];
   __shared__ uint64_t bar_q_full, bar_o_done, bar_merge, bar_epi;
-  __shared__ uint64_t bar_s_full[NWG], bar_p_full[NWG];  // per warpgroup
+  __shared__ uint64_t bar_s_full[NWG][kSubs], bar_p_full[NWG][kSubs];  // per warpgroup and half
   __shared__ uint64_t bar_k_full[STAGES], bar_k_empty[STAGES], bar_v_full[STAGES], bar_v_empty[STAGES];
   // -b_j = -Lambda_j log2(e) of a tile's columns and the maximum over each warpgroup's slice, staged by the
   // producer warp one tile ahead in a ring of three (slot of tile t is reused for t+3, which the producer
@@ -133,8 +145,10 @@ fox_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     abort_flag = 0;
     mbar_init(&bar_q_full, 1);
     for (int g = 0; g < NWG; ++g) {
-      mbar_init(&bar_s_full[g], 1);
-      mbar_init(&bar_p_full[g], 128);
+      for (int u = 0; u < kSubs; ++u) {
+        mbar_init(&bar_s_full[g][u], 1);
+        mbar_init(&bar_p_full[g][u], 128);
+      }
     }
     for (int i = 0; i < 3; ++i) mbar_init(&bar_negb[i], 1);
     mbar_init(&bar_o_done, 1);
@@ -259,21 +273,24 @@ fox_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         // Every softmax warpgroup g has its own chain S_g -> P_g -> O_g += P_g V_g -> S_g(next tile): the S
         // product is issued per column slice right behind the P V product that frees the slice, so a
         // warpgroup never waits for the other one.
-        constexpr uint32_t idQK = umma_idesc(kFmt, 128, CW, 0, 0);
-        auto issue_s = [&](int g, int st) {  // S[:, g CW : (g+1) CW] = Q K[g CW : (g+1) CW, :]^T
-          const uint64_t dK = umma_desc_advance(dK0, st * kTileBytes + g * CW * 128);
+        constexpr uint32_t idQK = umma_idesc(kFmt, 128, SW, 0, 0);
+        // S[:, g CW + u SW : +SW] = Q K[g CW + u SW : +SW, :]^T
+        auto issue_s = [&](int g, int u, int st) {
+          const uint64_t dK = umma_desc_advance(dK0, st * kTileBytes + (g * CW + u * SW) * 128);
 #pragma unroll
           for (int kk = 0; kk < D / 16; ++kk)
-            mma_ss_raw(tbase + g * CW, umma_desc_advance(dQ, (kk >> 2) * 16384 + (kk & 3) * 32),
+            mma_ss_raw(tbase + g * CW + u * SW, umma_desc_advance(dQ, (kk >> 2) * 16384 + (kk & 3) * 32),
                        umma_desc_advance(dK, (kk >> 2) * kSubBytes + (kk & 3) * 32), idQK, kk > 0);
-          tc_commit_raw(&bar_s_full[g]);
+          tc_commit_raw(&bar_s_full[g][u]);
         };
         ok = ok && mbar_wait_warp(&bar_k_full[0], 0, abortp, p.status, kSiteKFull, 0);
         if (ok) {
           tc_fence_after();
           if (elect_one()) {
 #pragma unroll
-            for (int g = 0; g < kWG; ++g) issue_s(g, 0);
+            for (int u = 0; u < kSubs; ++u)
+#pragma unroll
+              for (int g = 0; g < kWG; ++g) issue_s(g, u, 0);
             tc_commit_raw(&bar_k_empty[0]);
           }
           __syncwarp();
@@ -291,26 +308,31 @@ fox_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           }
           const uint64_t dV = umma_desc_advance(dV0, st * kTileBytes);
 #pragma unroll
-          for (int g = 0; g < kWG; ++g) {
-            STAMP(8, (g & 1) * 3 + 0, it);
-            ok = mbar_wait_warp(&bar_p_full[g], it & 1, abortp, p.status, kSitePFull, it);
-            if (!ok) break;
-            STAMP(8, (g & 1) * 3 + 1, it);
-            tc_fence_after();
-            if (elect_one()) {
-              // O_g += P[:, g CW : (g+1) CW] V[g CW : (g+1) CW, :]; the 16-bit P sits at S columns g CW ...
+          for (int u = 0; u < kSubs; ++u) {
 #pragma unroll
-              for (int kk = 0; kk < CW / 16; ++kk)
-                mma_ts_raw(tbase + kColO + g * D, tbase + g * CW + kk * 8,
-                           umma_desc_advance(dV, (g * (CW / 16) + kk) * 2048), idPV, (it > 0 || kk > 0) ? 1u : 0u);
-              if (more) issue_s(g, st1);
-              if (g == kWG - 1) {
-                tc_commit_raw(&bar_v_empty[st]);
-                if (more) tc_commit_raw(&bar_k_empty[st1]);
+            for (int g = 0; g < kWG; ++g) {
+              STAMP(8, (g & 1) * 3 + 0, it);
+              ok = mbar_wait_warp(&bar_p_full[g][u], it & 1, abortp, p.status, kSitePFull, it);
+              if (!ok) break;
+              STAMP(8, (g & 1) * 3 + 1, it);
+              tc_fence_after();
+              if (elect_one()) {
+                // O_g += P[:, slice] V[slice, :]; the 16-bit P sits at the slice's own first S columns
+#pragma unroll
+                for (int kk = 0; kk < SW / 16; ++kk)
+                  mma_ts_raw(tbase + kColO + g * D, tbase + g * CW + u * SW + kk * 8,
+                             umma_desc_advance(dV, ((g * CW + u * SW) / 16 + kk) * 2048), idPV,
+                             (it > 0 || u > 0 || kk > 0) ? 1u : 0u);
+                if (more) issue_s(g, u, st1);
+                if (g == kWG - 1 && u == kSubs - 1) {
+                  tc_commit_raw(&bar_v_empty[st]);
+                  if (more) tc_commit_raw(&bar_k_empty[st1]);
+                }
               }
+              __syncwarp();
+              STAMP(8, (g & 1) * 3 + 2, it);
             }
-            __syncwarp();
-            STAMP(8, (g & 1) * 3 + 2, it);
+            if (!ok) break;
           }
           if (!ok) break;
         }
@@ -362,11 +384,12 @@ fox_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       const int col0 = nb * BN + g * CW;  // first column of this thread's slice
       STAMP(warp & 7, 0, it);
       ok = mbar_wait(&bar_negb[it % 3], (it / 3) & 1, abortp, p.status, kSiteNegB, it);
-      ok = mbar_wait(&bar_s_full[g], it & 1, abortp, p.status, kSiteSFull, it) && ok;
+      // (with two halves per slice each half's S is waited for where it is first read)
+      if (kSubs == 1) ok = mbar_wait(&bar_s_full[g][0], it & 1, abortp, p.status, kSiteSFull, it) && ok;
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       STAMP(warp & 7, 1, it);
-      tc_fence_after();
+      if (kSubs == 1) tc_fence_after();
       // Two passes over this thread's slice of S, 32 columns at a time, in packed two-wide fp32 arithmetic.
       // Both read S from TMEM (a TMEM load costs ~50 cycles; holding a 64/128-column slice in registers
       // costs spills):
@@ -410,6 +433,16 @@ fox_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       // (NaN or -inf reference -> false -> the maximum pass runs)
       const bool skip1 = __all_sync(0xffffffffu, dead || (qbound + nbmax <= m_ref + kSkipShift));
       if (!skip1) {
+        if (kSubs > 1) {
+          // the maximum pass reads the whole slice and may rescale O: both halves' S products must have landed
+          // (the commit of the second one also covers P V of the previous tile's second half, which adds to O)
+#pragma unroll
+          for (int u_ = 0; u_ < kSubs; ++u_)
+            ok = mbar_wait(&bar_s_full[g][u_], it & 1, abortp, p.status, kSiteSFull, it) && ok;
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          tc_fence_after();
+        }
         float umax = -INFINITY;
 #pragma unroll
         for (int ch = 0; ch < CW / 32; ++ch) {
@@ -450,6 +483,12 @@ fox_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       float2 psum = make_float2(0.f, 0.f);
 #pragma unroll
       for (int ch = 0; ch < CW / 32; ++ch) {
+        if (kSubs > 1 && skip1) {
+          ok = mbar_wait(&bar_s_full[g][ch], it & 1, abortp, p.status, kSiteSFull, it);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          tc_fence_after();
+        }
         float2 u[16];
         load_u(ch, u, true, off2);
         uint32_t pk[16];
@@ -469,13 +508,23 @@ fox_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             pk[j] = pack2<kBf16>(pp.x, pp.y);
           }
         }
-        tmem_st16(tS + ch * 16, pk);  // columns already consumed by this thread
+        // columns already consumed by this thread (a half keeps its P inside its own columns: the other half's
+        // next S product may already be writing)
+        tmem_st16(tS + ch * (kSubs > 1 ? SW : 16), pk);
+        if (kSubs > 1) {
+          tmem_st_wait();
+          tc_fence_before();
+          mbar_arrive(&bar_p_full[g][ch]);
+        }
       }
+      if (!ok) break;
       l_sum += psum.x + psum.y;
       STAMP(warp & 7, 4, it);
-      tmem_st_wait();
-      tc_fence_before();
-      mbar_arrive(&bar_p_full[g]);
+      if (kSubs == 1) {
+        tmem_st_wait();
+        tc_fence_before();
+        mbar_arrive(&bar_p_full[g][0]);
+      }
       STAMP(warp & 7, 5, it);
     }
 
