@@ -264,26 +264,28 @@ def context_parallel_leg(world, rank, dev, steps=5, warmup=3):
            for n in ("q", "k", "v", "log_fgate", "dout")}
     q, k, v, lf = [loc[n].requires_grad_() for n in ("q", "k", "v", "log_fgate")]
 
-    # How the upper halves travel and the priority of the NCCL stream are tuned here, in the run itself: every
-    # candidate is timed for a few steps and the fastest one measured (all of them are reported).
-    candidates = [("p2p", True), ("collective", True), ("collective", False)]
+    # How the upper halves travel, the priority of the NCCL stream and the number of head groups (each a complete
+    # step on its own CUDA stream, so that one group's exposed collectives run under the other's kernels) are tuned
+    # here, in the run itself: every candidate is timed for a few steps and the fastest one measured (all reported).
+    candidates = [("p2p", True, 2), ("p2p", True, 1), ("collective", True, 2), ("collective", False, 1)]
     groups = {True: sharding.context_parallel_group(high_priority=True),
               False: sharding.context_parallel_group(high_priority=False)}
-    state = {"group": None}
+    state = {"group": None, "head_groups": 1}
 
     def cp_step():
         q.grad = k.grad = v.grad = lf.grad = None
-        sharding.context_parallel_attention(q, k, v, lf, group=state["group"]).backward(loc["dout"])
+        sharding.context_parallel_attention(q, k, v, lf, group=state["group"],
+                                            head_groups=state["head_groups"]).backward(loc["dout"])
 
     trial = {}
-    for mode, hp in candidates:
-        sharding.UPPER_EXCHANGE, state["group"] = mode, groups[hp]
+    for mode, hp, hg in candidates:
+        sharding.UPPER_EXCHANGE, state["group"], state["head_groups"] = mode, groups[hp], hg
         t_ = torch.tensor([timed(cp_step, 2, 3)], dtype=torch.float64, device=dev)
         dist.all_reduce(t_, op=dist.ReduceOp.MAX)
-        trial[f"{mode}, {'high' if hp else 'default'}-priority stream"] = float(t_.item())
+        trial[f"{mode}, {'high' if hp else 'default'}-priority stream, {hg} head group{'s' if hg > 1 else ''}"] = float(t_.item())
     best = min(trial, key=trial.get)              # (the same on every rank: the times were max-reduced)
-    mode, hp = candidates[list(trial).index(best)]
-    sharding.UPPER_EXCHANGE, state["group"] = mode, groups[hp]
+    mode, hp, hg = candidates[list(trial).index(best)]
+    sharding.UPPER_EXCHANGE, state["group"], state["head_groups"] = mode, groups[hp], hg
     ms = timed(cp_step, warmup, steps)
     sharding.UPPER_EXCHANGE = None
     _lib.check_status()

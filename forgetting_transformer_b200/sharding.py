@@ -320,9 +320,25 @@ def context_parallel_threshold(q, k, sm_scale: float, seq_len: int, group, max_r
     return (-(2 * bound + math.log(seq_len)) + tolerance).float()
 
 
+# side streams of the head-group pipeline, one per (device, group index)
+_SIDE_STREAMS = {}
+# how many head groups a context-parallel call is cut into (None: the environment's FOX_B200_CP_HEAD_GROUPS, else 1)
+HEAD_GROUPS = None
+
+
+def _head_groups(n_heads: int, is_cuda: bool) -> int:
+    import os
+    n = HEAD_GROUPS if HEAD_GROUPS is not None else int(os.environ.get("FOX_B200_CP_HEAD_GROUPS", "1"))
+    n = max(1, min(n, n_heads))
+    while n_heads % n:
+        n -= 1
+    return n
+
+
 def context_parallel_attention(q, k, v, log_fgate, *, group=None, seq_start: Optional[torch.Tensor] = None,
                                sm_scale: Optional[float] = None, adaptive_threshold=None,
-                               attn_fn: Optional[Callable] = None, max_row_norm: Optional[Callable] = None):
+                               attn_fn: Optional[Callable] = None, max_row_norm: Optional[Callable] = None,
+                               head_groups: Optional[int] = None):
     """Head-first forgetting attention over a sequence sharded in zig-zag chunks.
 
     Every rank passes its local shard: q, k, v (B, H, 2*Tc, D) and log_fgate (B, H, 2*Tc), the
@@ -338,6 +354,12 @@ def context_parallel_attention(q, k, v, log_fgate, *, group=None, seq_start: Opt
     ``attn_fn(q, k, v, log_fgate, head_first=True, seq_start=..., sm_scale=..., adaptive_threshold=...)``
     defaults to the CUDA operator and ``max_row_norm(x) -> (B, H)`` to its row-norm kernel; the CPU
     tests inject the oracle.
+
+    ``head_groups`` (default 1): heads are independent, so the call can be cut into that many groups of heads,
+    each a complete context-parallel step on its own CUDA stream.  The first all-gather of a group and its final
+    gradient exchange, which nothing of the same group can hide, then run under the other groups' kernels.
+    Measured on B1 T65536 H24 D64 with two groups: 30.4 against 29.9 ms on 2 GPUs, 16.8 against 15.7 ms on 4 --
+    the kernels of two streams share the SMs worse than the exposed collectives cost, so it is off by default.
     """
     if attn_fn is None:
         from .ops import forgetting_attention as attn_fn
@@ -353,7 +375,44 @@ def context_parallel_attention(q, k, v, log_fgate, *, group=None, seq_start: Opt
             from .ops import max_row_norm
         with torch.no_grad():
             adaptive_threshold = context_parallel_threshold(q, k, sm_scale, 2 * world * tc, group, max_row_norm)
-    return _ContextParallel.apply(q, k, v, log_fgate, seq_start, sm_scale, adaptive_threshold, group, attn_fn)
+    B, H = q.shape[0], q.shape[1]
+    n_groups = _head_groups(H, q.is_cuda) if head_groups is None else _head_groups_checked(head_groups, H)
+    if n_groups == 1:
+        return _ContextParallel.apply(q, k, v, log_fgate, seq_start, sm_scale, adaptive_threshold, group, attn_fn)
+    hg = H // n_groups
+    thr = adaptive_threshold
+    if isinstance(thr, torch.Tensor) and thr.dim() > 0:
+        thr = torch.broadcast_to(thr, (B, H))
+    outs = []
+    main = torch.cuda.current_stream() if q.is_cuda else None
+    if main is not None:
+        ready = torch.cuda.Event()     # the inputs are ready where the caller's stream stands now
+        ready.record(main)
+    for gi in range(n_groups):
+        sl = slice(gi * hg, (gi + 1) * hg)
+        thr_g = thr[:, sl] if (isinstance(thr, torch.Tensor) and thr.dim() > 0) else thr
+        args = (q[:, sl], k[:, sl], v[:, sl], log_fgate[:, sl], seq_start, sm_scale, thr_g, group, attn_fn)
+        if main is None or gi == 0:
+            outs.append(_ContextParallel.apply(*args))      # (the first group stays on the caller's stream)
+            continue
+        key = (q.device.index, gi)
+        side = _SIDE_STREAMS.get(key)
+        if side is None:
+            side = _SIDE_STREAMS[key] = torch.cuda.Stream(device=q.device)
+        side.wait_event(ready)
+        with torch.cuda.stream(side):
+            o = _ContextParallel.apply(*args)
+        o.record_stream(main)
+        outs.append(o)
+    if main is not None:
+        for gi in range(1, n_groups):
+            main.wait_stream(_SIDE_STREAMS[(q.device.index, gi)])
+    return torch.cat(outs, dim=1)
+
+
+def _head_groups_checked(n: int, n_heads: int) -> int:
+    assert n >= 1 and n_heads % n == 0, f"head_groups={n} must divide the head count {n_heads}"
+    return n
 
 
 class ContextParallelAttention(torch.nn.Module):

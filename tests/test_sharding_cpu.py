@@ -72,10 +72,12 @@ def _cp_worker(rank, world, port, ret):
         idx = torch.cat([torch.arange(a * tc, (a + 1) * tc), torch.arange(b * tc, (b + 1) * tc)])
         worst = 0.0
         # no padding; left padding inside the first chunk and beyond it (whole lower chunks of rank 0 are empty)
-        for seq in (None, torch.tensor([3, tc + 5])):
+        # (and the same cut into two head groups, which on CUDA run on their own streams)
+        for seq, hg in ((None, 1), (torch.tensor([3, tc + 5]), 1), (torch.tensor([3, tc + 5]), 2)):
             ro, rdq, rdk, rdv, rdl = orc.dense_fwd_bwd(q, k, v, lf, do, seq, mask_gates=True)
             ql, kl, vl, ll = [t.index_select(2, idx).clone().requires_grad_() for t in (q, k, v, lf)]
-            out = sharding.context_parallel_attention(ql, kl, vl, ll, seq_start=seq, attn_fn=_oracle_attn)
+            out = sharding.context_parallel_attention(ql, kl, vl, ll, seq_start=seq, attn_fn=_oracle_attn,
+                                                      head_groups=hg)
             out.backward(do.index_select(2, idx))
             errs = [
                 (out - ro.index_select(2, idx)).abs().max().item(),
@@ -93,7 +95,7 @@ def _cp_worker(rank, world, port, ret):
         row_norm_max = lambda x: torch.linalg.vector_norm(x, dim=-1).max(dim=-1).values
         qb, kb, vb = [t.detach().bfloat16() for t in (ql, kl, vl)]   # the norms are taken in the input dtype
         sharding.context_parallel_attention(qb, kb, vb, ll.detach().float(), adaptive_threshold="auto",
-                                            attn_fn=_oracle_attn, max_row_norm=row_norm_max)
+                                            attn_fn=_oracle_attn, max_row_norm=row_norm_max, head_groups=1)
         ref_thr = orc.auto_threshold(q.bfloat16(), k.bfloat16(), D ** -0.5)
         same = all(torch.equal(t.double(), ref_thr.double()) for t in _oracle_attn.thresholds)
         ret[rank] = (worst, same and len(_oracle_attn.thresholds) == 2)
