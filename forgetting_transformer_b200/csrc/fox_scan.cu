@@ -415,8 +415,11 @@ extern "C" int fox_max_row_norm(int device, void* stream, int dtype, int64_t B, 
   if (!aligned16(x)) return FOX_ERR_ALIGNMENT;
   if (cudaSetDevice(device) != cudaSuccess) return FOX_ERR_DEVICE;
   const int rows_per_block = 256 / (int)(D / 8);
+  // one wave of resident blocks (8 of 256 threads per SM on 148 SMs) shared among the (b, h) rows of the grid:
+  // more blocks than that run as a second, partly filled wave
   int64_t gx = (T + rows_per_block - 1) / rows_per_block;
-  if (gx > 64) gx = 64;
+  const int64_t per_unit = (148 * 8) / (B * H) > 0 ? (148 * 8) / (B * H) : 1;
+  if (gx > per_unit) gx = per_unit;
   dim3 grid((unsigned)gx, (unsigned)(B * H));
   if (dtype == FOX_DTYPE_BF16)
     fox_max_row_norm_kernel<true><<<grid, 256, 0, (cudaStream_t)stream>>>((const uint16_t*)x->ptr, x->sb, x->sh, x->st, (int)H, (int)T, (int)D, out_zeroed);
