@@ -324,6 +324,32 @@ def test_layout_b_t_h_d_views_and_output_strides():
     assert ll.grad.shape == lf.shape
 
 
+@pytest.mark.parametrize("D", [64, 128])
+def test_pruned_call_on_b_t_h_d_views_equals_the_head_first_call(D):
+    """With a threshold every output tile of the backward leaves through shared memory and TMA stores; on the
+    permuted (B, T, H, D) views and a ragged length they must land where the head-first call puts them."""
+    B, T, H = 2, 333, 3
+    g = torch.Generator().manual_seed(17)
+    q, k, v, do = [torch.randn(B, T, H, D, generator=g).bfloat16() for _ in range(4)]
+    lf = torch.nn.functional.logsigmoid(torch.randn(B, T, H, generator=g))
+    seq = torch.tensor([0, 70])
+    outs = []
+    for head_first in (False, True):
+        args = [t.transpose(1, 2).contiguous() if head_first else t for t in (q, k, v, lf)]
+        qq, kk, vv, ll = [t.cuda().requires_grad_() for t in args]
+        out = fox.forgetting_attention(qq, kk, vv, ll, head_first=head_first, seq_start=seq.cuda(),
+                                       adaptive_threshold=-8.0)
+        out.backward((do.transpose(1, 2).contiguous() if head_first else do).cuda())
+        _lib.check_status()
+        res = [out.detach(), qq.grad, kk.grad, vv.grad, ll.grad]
+        outs.append([t.transpose(1, 2) if not head_first else t for t in res])
+    for name, a, b in zip(("out", "dq", "dk", "dv", "dlog_fgate"), *outs):
+        if name in ("out", "dk", "dv") or D == 128:   # (the one-pass backward adds dq and the gate sums atomically)
+            assert torch.equal(a, b), name
+        else:
+            _close(a, b, 1e-2, 1e-2, name)
+
+
 def test_threshold_validation():
     q, k, v, lf, do = [t.cuda() for t in _inputs(14, 2, 2, 128, 128, 64, torch.bfloat16)]
     with pytest.raises(AssertionError, match="adaptive_threshold must be either"):
