@@ -47,10 +47,6 @@
 #ifndef FOX_BWD_FP32_SUMS
 #define FOX_BWD_FP32_SUMS 1
 #endif
-// 1: the probabilities of a fragment's second half and dS of its first half are computed in one stretch of code
-#ifndef FOX_BWD_FUSE
-#define FOX_BWD_FUSE 0
-#endif
 // of a thread's 16 column pairs per tile, how many take the FMA-pipe exponential instead of the ex2 unit
 // (only on tiles off the diagonal whose KV rows are all valid)
 #ifndef FOX_BWD_POLY
@@ -620,41 +616,6 @@ fox_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         }
       };
       uint32_t sregs[2][16], dpregs[2][16], pk[8], dsk[8];
-#if FOX_BWD_FUSE
-      // Probabilities of the second half and dS of the first half in one stretch of code: the ex2 unit works on
-      // the one while the FMA pipe works on the other (all four warps of a scheduler reach a phase together, so
-      // a phase of exponentials alone is bound by the ex2 unit and a phase without any leaves it idle).
-      tmem_ld_16x256b_x4(tS, sregs[0]);
-      tmem_ld_wait();
-      tmem_ld_16x256b_x4(tS + (16u << 16), sregs[1]);
-#pragma unroll
-      for (int k = 0; k < 4; ++k) a_k(0, k, sregs[0], pk);
-      tmem_st_16x128b_x4(tS, pk);
-      good = mbar_wait(&bar_dp_full, it & 1, abortp, p.status, kBSiteDpFull, it);
-      // dP(it) was issued behind dQ(it - kDsBufs) and a commit covers everything issued before it, so the
-      // dS buffer about to be overwritten is no longer being read.
-      good = __all_sync(0xffffffffu, good);
-      if (!good) return false;
-      tc_fence_after();
-      tmem_ld_16x256b_x4(tDP, dpregs[0]);
-      tmem_ld_wait();
-#pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        a_k(1, k, sregs[1], pk);
-        b_k(0, k, dpregs[0], dsk);
-      }
-      tmem_st_16x128b_x4(tS + (16u << 16), pk);
-      tmem_ld_16x256b_x4(tDP + (16u << 16), dpregs[1]);
-      store_ds(0, dsk);
-      tmem_st_wait();
-      tc_fence_before();
-      mbar_arrive(&bar_p_done);
-      if (warp < 8) stamp(6 + warp, 1, it);
-      tmem_ld_wait();
-#pragma unroll
-      for (int k = 0; k < 4; ++k) b_k(1, k, dpregs[1], dsk);
-      store_ds(1, dsk);
-#else
       // ---------------- phase A: probabilities ----------------
       tmem_ld_16x256b_x4(tS, sregs[0]);
       tmem_ld_wait();
@@ -691,7 +652,6 @@ fox_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         for (int k = 0; k < 4; ++k) b_k(half, k, dpregs[half], dsk);
         store_ds(half, dsk);
       }
-#endif
       tmem_st_wait();
       if (!kNoDQ) fence_proxy_async_smem();
       tc_fence_before();

@@ -56,23 +56,6 @@ struct FwdParams {
 #define FOX_POLYQ128 2
 #endif
 
-// 1: at D = 64 a warpgroup's 64-column slice of S is computed, consumed and multiplied with V in two halves with
-// their own barriers, so that the S product of a half for the next tile is under way while the warpgroup works on
-// the other half (0: one S product and one P V product per slice and tile).  Measured on B2 T16384 H24 D64:
-// results identical, 2.02 ms against 1.93 ms -- eight more product instructions and two more barrier round trips
-// per tile cost more than the wait they hide; off.
-#ifndef FOX_FWD_SUBSTREAMS
-#define FOX_FWD_SUBSTREAMS 0
-#endif
-
-// 1: head dim 128 runs two softmax warpgroups per CTA on one shared O accumulator (two CTAs per SM, four softmax
-// warps per scheduler); 2: the same with one CTA per SM and K / V double-buffered; 0: one warpgroup per CTA, two
-// CTAs per SM.  Measured on B4 T16384 H16 D128 (results within the tests' bars in all three): 4.60 / 6.2 / 4.61 ms
-// -- twice the softmax warps buy nothing, so the exponentials are not what bounds this shape; 0 is kept.
-#ifndef FOX_FWD_SHARED128
-#define FOX_FWD_SHARED128 0
-#endif
-
 // Debug builds with -DFOX_FWD_TRACE record clock64 stamps of CTA (0,0,0), tiles 32..47:
 // trace[(role * 8 + event) * 16 + tile - 32], role = softmax warp index or 8 for the MMA issuer.
 #ifdef FOX_FWD_TRACE
@@ -84,11 +67,10 @@ __device__ long long g_fwd_trace[16 * 8 * 16];
 
 enum FwdWaitSite {
   kSiteQFull = 11, kSiteKFull = 12, kSiteVFull = 13, kSiteKEmpty = 14, kSiteVEmpty = 15,
-  kSiteSFull = 16, kSitePFull = 17, kSiteODone = 18, kSiteDrain = 19, kSiteNegB = 20, kSiteMerge = 21, kSiteEpi = 22,
-  kSiteXchg = 23
+  kSiteSFull = 16, kSitePFull = 17, kSiteODone = 18, kSiteDrain = 19, kSiteNegB = 20, kSiteMerge = 21, kSiteEpi = 22
 };
 
-template <int D, bool kBf16, int BN, int STAGES, int CTAS, int NWG, bool PREF, bool SHARED>
+template <int D, bool kBf16, int BN, int STAGES, int CTAS, int NWG, bool PREF>
 __global__ void __launch_bounds__(128 * NWG + 64, CTAS)
 fox_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                     const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO,
@@ -106,23 +88,13 @@ fox_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   constexpr int kSub = D / 64;
   constexpr uint32_t kFmt = kBf16 ? 1u : 0u;
   constexpr uint32_t kColO = BN;            // S (fp32) in columns [0, BN), O_g in [BN + g D, BN + (g+1) D)
-  // SHARED: the warpgroups' streams share one reference maximum and one O accumulator (D = 128: two accumulators
-  // would need 384 columns, i.e. one CTA per SM, and a single warpgroup leaves two softmax warps per scheduler).
-  // The rare change of the reference is agreed between the two warps that own the same rows and applied to O by
-  // warpgroup 0 alone; the issuer takes warpgroup 0's P first, so no P V product meets a half-rescaled O.
-  constexpr bool kShared = SHARED;
-  static_assert(!kShared || NWG == 2, "the shared accumulator is written for two warpgroups");
-  constexpr int kAccs = kShared ? 1 : kWG;  // O accumulators
-  constexpr uint32_t kTmemCols = (kColO + kAccs * D <= 128) ? 128 : ((kColO + kAccs * D <= 256) ? 256 : 512);
-  static_assert(kColO + kAccs * D <= 512, "TMEM budget");
+  constexpr uint32_t kTmemCols = (kColO + kWG * D <= 128) ? 128 : ((kColO + kWG * D <= 256) ? 256 : 512);
+  static_assert(kColO + kWG * D <= 512, "TMEM budget");
   constexpr int kTmaWarp = 4 * kWG, kMmaWarp = 4 * kWG + 1;
-  // halves of a warpgroup's slice with their own S -> P -> P V chain (32 columns each)
-  constexpr int kSubs = (FOX_FWD_SUBSTREAMS && CW == 64 && !PREF) ? 2 : 1;
-  constexpr int SW = CW / kSubs;
 
   extern __shared__ uint8_t smem_raw[];
   __shared__ uint64_t bar_q_full, bar_o_done, bar_merge, bar_epi;
-  __shared__ uint64_t bar_s_full[NWG][kSubs], bar_p_full[NWG][kSubs];  // per warpgroup and half
+  __shared__ uint64_t bar_s_full[NWG], bar_p_full[NWG];  // per warpgroup
   __shared__ uint64_t bar_k_full[STAGES], bar_k_empty[STAGES], bar_v_full[STAGES], bar_v_empty[STAGES];
   // -b_j = -Lambda_j log2(e) of a tile's columns and the maximum over each warpgroup's slice, staged by the
   // producer warp one tile ahead in a ring of three (slot of tile t is reused for t+3, which the producer
@@ -131,8 +103,6 @@ fox_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   __shared__ __align__(16) float s_negb[3][BN];  // read as float4
   __shared__ float s_nbmax[3][NWG];
   __shared__ float s_mg[NWG][128], s_lg[NWG][128];  // every stream's (m, l) for the merge
-  __shared__ float s_xmax[2][kShared ? 2 : 1][kShared ? 128 : 1];  // slice maxima of a tile, by exchange parity
-  __shared__ uint64_t bar_x[4];                  // one per pair of warps that own the same 32 rows
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
 
@@ -163,16 +133,13 @@ fox_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     abort_flag = 0;
     mbar_init(&bar_q_full, 1);
     for (int g = 0; g < NWG; ++g) {
-      for (int u = 0; u < kSubs; ++u) {
-        mbar_init(&bar_s_full[g][u], 1);
-        mbar_init(&bar_p_full[g][u], 128);
-      }
+      mbar_init(&bar_s_full[g], 1);
+      mbar_init(&bar_p_full[g], 128);
     }
     for (int i = 0; i < 3; ++i) mbar_init(&bar_negb[i], 1);
     mbar_init(&bar_o_done, 1);
     mbar_init(&bar_merge, 128 * NWG);
     mbar_init(&bar_epi, 128 * NWG);
-    for (int i = 0; i < 4; ++i) mbar_init(&bar_x[i], 64);
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&bar_k_full[s], 1);
       mbar_init(&bar_k_empty[s], 1);
@@ -292,24 +259,21 @@ fox_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         // Every softmax warpgroup g has its own chain S_g -> P_g -> O_g += P_g V_g -> S_g(next tile): the S
         // product is issued per column slice right behind the P V product that frees the slice, so a
         // warpgroup never waits for the other one.
-        constexpr uint32_t idQK = umma_idesc(kFmt, 128, SW, 0, 0);
-        // S[:, g CW + u SW : +SW] = Q K[g CW + u SW : +SW, :]^T
-        auto issue_s = [&](int g, int u, int st) {
-          const uint64_t dK = umma_desc_advance(dK0, st * kTileBytes + (g * CW + u * SW) * 128);
+        constexpr uint32_t idQK = umma_idesc(kFmt, 128, CW, 0, 0);
+        auto issue_s = [&](int g, int st) {  // S[:, g CW : (g+1) CW] = Q K[g CW : (g+1) CW, :]^T
+          const uint64_t dK = umma_desc_advance(dK0, st * kTileBytes + g * CW * 128);
 #pragma unroll
           for (int kk = 0; kk < D / 16; ++kk)
-            mma_ss_raw(tbase + g * CW + u * SW, umma_desc_advance(dQ, (kk >> 2) * 16384 + (kk & 3) * 32),
+            mma_ss_raw(tbase + g * CW, umma_desc_advance(dQ, (kk >> 2) * 16384 + (kk & 3) * 32),
                        umma_desc_advance(dK, (kk >> 2) * kSubBytes + (kk & 3) * 32), idQK, kk > 0);
-          tc_commit_raw(&bar_s_full[g][u]);
+          tc_commit_raw(&bar_s_full[g]);
         };
         ok = ok && mbar_wait_warp(&bar_k_full[0], 0, abortp, p.status, kSiteKFull, 0);
         if (ok) {
           tc_fence_after();
           if (elect_one()) {
 #pragma unroll
-            for (int u = 0; u < kSubs; ++u)
-#pragma unroll
-              for (int g = 0; g < kWG; ++g) issue_s(g, u, 0);
+            for (int g = 0; g < kWG; ++g) issue_s(g, 0);
             tc_commit_raw(&bar_k_empty[0]);
           }
           __syncwarp();
@@ -327,31 +291,26 @@ fox_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           }
           const uint64_t dV = umma_desc_advance(dV0, st * kTileBytes);
 #pragma unroll
-          for (int u = 0; u < kSubs; ++u) {
-#pragma unroll
-            for (int g = 0; g < kWG; ++g) {
-              STAMP(8, (g & 1) * 3 + 0, it);
-              ok = mbar_wait_warp(&bar_p_full[g][u], it & 1, abortp, p.status, kSitePFull, it);
-              if (!ok) break;
-              STAMP(8, (g & 1) * 3 + 1, it);
-              tc_fence_after();
-              if (elect_one()) {
-                // O_g += P[:, slice] V[slice, :]; the 16-bit P sits at the slice's own first S columns
-#pragma unroll
-                for (int kk = 0; kk < SW / 16; ++kk)
-                  mma_ts_raw(tbase + kColO + (kShared ? 0 : g * D), tbase + g * CW + u * SW + kk * 8,
-                             umma_desc_advance(dV, ((g * CW + u * SW) / 16 + kk) * 2048), idPV,
-                             (it > 0 || u > 0 || kk > 0 || (kShared && g > 0)) ? 1u : 0u);
-                if (more) issue_s(g, u, st1);
-                if (g == kWG - 1 && u == kSubs - 1) {
-                  tc_commit_raw(&bar_v_empty[st]);
-                  if (more) tc_commit_raw(&bar_k_empty[st1]);
-                }
-              }
-              __syncwarp();
-              STAMP(8, (g & 1) * 3 + 2, it);
-            }
+          for (int g = 0; g < kWG; ++g) {
+            STAMP(8, (g & 1) * 3 + 0, it);
+            ok = mbar_wait_warp(&bar_p_full[g], it & 1, abortp, p.status, kSitePFull, it);
             if (!ok) break;
+            STAMP(8, (g & 1) * 3 + 1, it);
+            tc_fence_after();
+            if (elect_one()) {
+              // O_g += P[:, g CW : (g+1) CW] V[g CW : (g+1) CW, :]; the 16-bit P sits at S columns g CW ...
+#pragma unroll
+              for (int kk = 0; kk < CW / 16; ++kk)
+                mma_ts_raw(tbase + kColO + g * D, tbase + g * CW + kk * 8,
+                           umma_desc_advance(dV, (g * (CW / 16) + kk) * 2048), idPV, (it > 0 || kk > 0) ? 1u : 0u);
+              if (more) issue_s(g, st1);
+              if (g == kWG - 1) {
+                tc_commit_raw(&bar_v_empty[st]);
+                if (more) tc_commit_raw(&bar_k_empty[st1]);
+              }
+            }
+            __syncwarp();
+            STAMP(8, (g & 1) * 3 + 2, it);
           }
           if (!ok) break;
         }
@@ -369,10 +328,9 @@ fox_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     const float a_i = row_ok ? (lam[P + row] - lam[min(P + mb * kFwdBM, N - 1)]) * kLog2e : 0.f;  // (see the producer)
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const uint32_t tS = tbase + lane_base + g * CW;
-    const uint32_t tO = tbase + lane_base + kColO + (kShared ? 0 : g * D);
+    const uint32_t tO = tbase + lane_base + kColO + g * D;
 
     float m_ref = -INFINITY, l_sum = 0.f;
-    int n_exchanges = 0;   // (shared reference) exchanges of slice maxima so far: the same in both warps of a pair
     bool ok = true;
     // Upper bound of this row's scaled logits q_i.k_j*c <= ||q_i|| max_j||k_j|| c (Cauchy-Schwarz): with the
     // largest -b_j of a tile it tells, before S is even read, that no logit of the tile can exceed the
@@ -404,12 +362,11 @@ fox_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       const int col0 = nb * BN + g * CW;  // first column of this thread's slice
       STAMP(warp & 7, 0, it);
       ok = mbar_wait(&bar_negb[it % 3], (it / 3) & 1, abortp, p.status, kSiteNegB, it);
-      // (with two halves per slice each half's S is waited for where it is first read)
-      if (kSubs == 1) ok = mbar_wait(&bar_s_full[g][0], it & 1, abortp, p.status, kSiteSFull, it) && ok;
+      ok = mbar_wait(&bar_s_full[g], it & 1, abortp, p.status, kSiteSFull, it) && ok;
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       STAMP(warp & 7, 1, it);
-      if (kSubs == 1) tc_fence_after();
+      tc_fence_after();
       // Two passes over this thread's slice of S, 32 columns at a time, in packed two-wide fp32 arithmetic.
       // Both read S from TMEM (a TMEM load costs ~50 cycles; holding a 64/128-column slice in registers
       // costs spills):
@@ -449,29 +406,10 @@ fox_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           }
         }
       };
-      // (with a shared reference both warpgroups must take the same decision: the tile's maximum)
-      const float nbmax = kShared ? fmaxf(s_nbmax[it % 3][0], s_nbmax[it % 3][NWG - 1]) : s_nbmax[it % 3][g];
+      const float nbmax = s_nbmax[it % 3][g];
       // (NaN or -inf reference -> false -> the maximum pass runs)
       const bool skip1 = __all_sync(0xffffffffu, dead || (qbound + nbmax <= m_ref + kSkipShift));
       if (!skip1) {
-        if (kSubs > 1) {
-          // the maximum pass reads the whole slice and may rescale O: both halves' S products must have landed
-          // (the commit of the second one also covers P V of the previous tile's second half, which adds to O)
-#pragma unroll
-          for (int u_ = 0; u_ < kSubs; ++u_)
-            ok = mbar_wait(&bar_s_full[g][u_], it & 1, abortp, p.status, kSiteSFull, it) && ok;
-          ok = __all_sync(0xffffffffu, ok);
-          if (!ok) break;
-          tc_fence_after();
-        }
-        if (kShared) {
-          // O may be rescaled below: the other warpgroup's P V of the previous tile, which adds to the same
-          // accumulator, is covered by the commit of ITS S product of this tile
-          ok = mbar_wait(&bar_s_full[g ^ (NWG - 1)][0], it & 1, abortp, p.status, kSiteSFull, it);
-          ok = __all_sync(0xffffffffu, ok);
-          if (!ok) break;
-          tc_fence_after();
-        }
         float umax = -INFINITY;
 #pragma unroll
         for (int ch = 0; ch < CW / 32; ++ch) {
@@ -480,17 +418,6 @@ fox_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 #pragma unroll
           for (int c = 0; c < 16; ++c) umax = fmax3(umax, u[c].x, u[c].y);
         }
-        if (kShared) {
-          // the maximum over the whole tile: exchanged with the warp of the other warpgroup that owns the same
-          // rows (it takes the same branches: same rows, same bound, same reference)
-          s_xmax[n_exchanges & 1][g][r] = umax;
-          mbar_arrive(&bar_x[warp & 3]);
-          ok = mbar_wait(&bar_x[warp & 3], n_exchanges & 1, abortp, p.status, kSiteXchg, it);
-          ok = __all_sync(0xffffffffu, ok);
-          if (!ok) break;
-          umax = fmaxf(umax, s_xmax[n_exchanges & 1][g ^ 1][r]);
-          ++n_exchanges;
-        }
         STAMP(warp & 7, 2, it);
         // ---- running maximum with lazy rescaling ----
         const float m_new = fmaxf(m_ref, a_i + umax);
@@ -498,7 +425,7 @@ fox_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         if (__any_sync(0xffffffffu, need)) {
           const float alpha = (m_new == -INFINITY) ? 1.f : fast_exp2(m_ref - m_new);
           l_sum *= alpha;
-          if (it > 0 && (!kShared || g == 0)) {
+          if (it > 0) {
             const float2 alpha2 = make_float2(alpha, alpha);
 #pragma unroll
             for (int c = 0; c < D; c += 32) {
@@ -523,12 +450,6 @@ fox_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       float2 psum = make_float2(0.f, 0.f);
 #pragma unroll
       for (int ch = 0; ch < CW / 32; ++ch) {
-        if (kSubs > 1 && skip1) {
-          ok = mbar_wait(&bar_s_full[g][ch], it & 1, abortp, p.status, kSiteSFull, it);
-          ok = __all_sync(0xffffffffu, ok);
-          if (!ok) break;
-          tc_fence_after();
-        }
         float2 u[16];
         load_u(ch, u, true, off2);
         uint32_t pk[16];
@@ -548,23 +469,13 @@ fox_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             pk[j] = pack2<kBf16>(pp.x, pp.y);
           }
         }
-        // columns already consumed by this thread (a half keeps its P inside its own columns: the other half's
-        // next S product may already be writing)
-        tmem_st16(tS + ch * (kSubs > 1 ? SW : 16), pk);
-        if (kSubs > 1) {
-          tmem_st_wait();
-          tc_fence_before();
-          mbar_arrive(&bar_p_full[g][ch]);
-        }
+        tmem_st16(tS + ch * 16, pk);  // columns already consumed by this thread
       }
-      if (!ok) break;
       l_sum += psum.x + psum.y;
       STAMP(warp & 7, 4, it);
-      if (kSubs == 1) {
-        tmem_st_wait();
-        tc_fence_before();
-        mbar_arrive(&bar_p_full[g][0]);
-      }
+      tmem_st_wait();
+      tc_fence_before();
+      mbar_arrive(&bar_p_full[g]);
       STAMP(warp & 7, 5, it);
     }
 
@@ -615,7 +526,7 @@ fox_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         float o[32];
         if (n_tiles > 0) {
 #pragma unroll
-          for (int q = 0; q < kAccs; ++q) {   // (a shared accumulator: both streams' weights are 1 / l)
+          for (int q = 0; q < NWG; ++q) {
             uint32_t t0[32];
             tmem_ld32(tO0 + q * D + c, t0);
             tmem_ld_wait();
@@ -669,7 +580,7 @@ extern "C" int fox_debug_read_fwd_trace(long long* host) {
 }
 #endif
 
-template <bool kBf16, int D, int BN, int STAGES, int CTAS, int NWG, bool PREF, bool SHARED = false>
+template <bool kBf16, int D, int BN, int STAGES, int CTAS, int NWG, bool PREF>
 static int launch_fwd_t(int device, cudaStream_t stream, int64_t B, int64_t H, int64_t M, int64_t N, const fox_tensor4* q,
                       const fox_tensor4* k, const fox_tensor4* v, const FwdParams& prm) {
   CUtensorMap tmQ, tmK, tmV;
@@ -686,7 +597,7 @@ static int launch_fwd_t(int device, cudaStream_t stream, int64_t B, int64_t H, i
   if (!tma_compatible(to, 2)) return FOX_ERR_ALIGNMENT;
   if ((rc = cached_tmap_4d(&tmO, to, 2, false, kBf16, 64, 128, true))) return rc;
   constexpr int smem = 128 * D * 2 + 2 * STAGES * BN * D * 2 + 1024;
-  auto kern = fox_attn_fwd_kernel<D, kBf16, BN, STAGES, CTAS, NWG, PREF, SHARED>;
+  auto kern = fox_attn_fwd_kernel<D, kBf16, BN, STAGES, CTAS, NWG, PREF>;
   static bool configured[64] = {};  // per template instance and device
   if (device < 0 || device >= 64) return FOX_ERR_DEVICE;
   if (!configured[device]) {
@@ -753,12 +664,6 @@ extern "C" int fox_attn_fwd(int device, void* stream, int dtype, int64_t B, int6
   if (D == 128 && variant == 2) return FOX_FWD_LAUNCH(128, 64, 2, 2, 1, false);
 #endif
   if (D == 64) return FOX_FWD_LAUNCH(64, 128, 2, 2, 2, false);
-#if FOX_FWD_SHARED128 == 2
-  return FOX_FWD_LAUNCH(128, 128, 2, 1, 2, false, true);   // one CTA per SM, K / V double-buffered
-#elif FOX_FWD_SHARED128
-  return FOX_FWD_LAUNCH(128, 128, 1, 2, 2, false, true);
-#else
   return FOX_FWD_LAUNCH(128, 128, 1, 2, 1, true);
-#endif
 #undef FOX_FWD_LAUNCH
 }
