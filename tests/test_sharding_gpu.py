@@ -69,13 +69,15 @@ def _cp_worker(rank, world, port, ret):
         idx = torch.cat([torch.arange(a * tc, (a + 1) * tc), torch.arange(b * tc, (b + 1) * tc)]).cuda()
         results = {}
         # plain; left padding inside and beyond the first chunk; pruning with the "auto" threshold
+        # (and the plain case cut into two head groups, each a complete step on its own CUDA stream)
         for name, seq, thr in (("plain", None, None), ("seq_start", torch.tensor([40, tc + 77]).cuda(), None),
-                               ("auto", None, "auto")):
+                               ("auto", None, "auto"), ("head_groups", None, None)):
             qq, kk, vv, ll = [t.detach().clone().requires_grad_() for t in (q, k, v, lf)]
             full = fox.forgetting_attention(qq, kk, vv, ll, head_first=True, seq_start=seq, adaptive_threshold=thr)
             full.backward(do)
             ql, kl, vl, l_l = [t.index_select(2, idx).contiguous().requires_grad_() for t in (q, k, v, lf)]
-            out = sharding.context_parallel_attention(ql, kl, vl, l_l, seq_start=seq, adaptive_threshold=thr)
+            out = sharding.context_parallel_attention(ql, kl, vl, l_l, seq_start=seq, adaptive_threshold=thr,
+                                                      head_groups=2 if name == "head_groups" else 1)
             out.backward(do.index_select(2, idx).contiguous())
             torch.cuda.synchronize()
             _lib.check_status()
