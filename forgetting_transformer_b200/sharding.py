@@ -358,7 +358,8 @@ def context_parallel_attention(q, k, v, log_fgate, *, group=None, seq_start: Opt
     ``head_groups`` (default 1): heads are independent, so the call can be cut into that many groups of heads,
     each a complete context-parallel step on its own CUDA stream.  The first all-gather of a group and its final
     gradient exchange, which nothing of the same group can hide, then run under the other groups' kernels.
-    Measured on B1 T65536 H24 D64 with two groups: 30.4 against 29.9 ms on 2 GPUs, 16.8 against 15.7 ms on 4 --
+    Measured on B1 T65536 H24 D64 with two groups: 30.4 against 29.9 ms on 2 GPUs, 16.8 against 15.7 ms on 4, 10.8
+    against 9.6 ms on 8 --
     the kernels of two streams share the SMs worse than the exposed collectives cost, so it is off by default.
     """
     if attn_fn is None:
